@@ -1,0 +1,1112 @@
+// Lowers one scheduled kernel (SINK → END → STORE(INDEX(PARAM0, ranges), body)) to CUDA C
+// for sm_100a.  What the reference does in codegen/lower.go + codegen/wgsl.go for WGSL, redone
+// for a machine with 32-wide warps, shared memory and 128-bit global accesses:
+//
+//  * index arithmetic is canonicalised first.  The scheduler emits reshape/permute/pad as
+//    unsimplified i32 div/mod chains (schedule/index.go:231-293); here every integer node is
+//    folded into an affine form over the loop variables using their bounds, so that
+//    ((r0*I + r1) / I) % B becomes r0.  Strides recovered this way drive the choice between
+//    vector and scalar accesses and the thread layout of reductions;
+//  * a kernel without REDUCE becomes one thread per V consecutive outputs with 128-bit loads and
+//    stores when alignment is provable, scalar otherwise;
+//  * REDUCE nodes (several per kernel are allowed, codegen/lower.go:654-719) are evaluated by
+//    groups of L threads: lanes stride the flattened reduce space, partial accumulators are
+//    combined by warp shuffles and, across warps, shared memory.  L = 1 reproduces the reference's
+//    serial ascending loop exactly;
+//  * a single long REDUCE feeding few outputs is split over many blocks: a partials kernel writes
+//    f32 partials to scratch memory, a finish kernel combines them in ascending order and applies
+//    the epilogue, so results do not depend on scheduling;
+//  * loads whose index cannot be proven inside the buffer (the guarded load of a PAD,
+//    schedule/index.go:101-134) are clamped: WGSL defines out-of-range reads, CUDA does not.
+//
+// Arithmetic follows codegen/wgsl.go:240-447: f16 values use native half add/sub/mul outside
+// reductions and are widened to f32 inside an f16 reduction with a single narrowing at the end
+// (codegen/lower.go:158-171, 698-716); bf16 lives in 32-bit slots and is truncated at the store;
+// reduce identities are 0, 1 and -FLT_MAX; infinite literals clamp to +-FLT_MAX.
+#include "codegen.hpp"
+
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstring>
+#include <functional>
+#include <map>
+#include <set>
+#include <sstream>
+
+namespace anl {
+
+uint64_t structure_hash(const Item& item) {
+    uint64_t h = 1469598103934665603ull;
+    for (const Node& n : item.nodes) {
+        int64_t rec[5] = {n.op, n.dtype, n.flags, (int64_t)n.aux, n.arg};
+        h = fnv1a(rec, sizeof rec, h);
+        for (int s : n.src) h = fnv1a(&s, sizeof s, h);
+    }
+    for (const BufDesc& b : item.bufs) {
+        int64_t rec[2] = {b.dtype, (int64_t)b.shape.size()};
+        h = fnv1a(rec, sizeof rec, h);
+        for (int64_t s : b.shape) h = fnv1a(&s, sizeof s, h);
+    }
+    for (const std::string& s : item.sym_vars) h = fnv1a(s.data(), s.size(), h);
+    return h;
+}
+
+namespace {
+
+enum Cls { CF32, CF16, CINT, CUINT, CBOOL };
+
+Cls dtype_cls(int dt) {
+    switch (dt) {
+        case DT_F16: return CF16;
+        case DT_BOOL: return CBOOL;
+        case DT_F32: case DT_BF16: case DT_F64: case DT_VOID: return CF32;
+        case DT_U8: case DT_U16: case DT_U32: case DT_U64: return CUINT;
+        default: return CINT;
+    }
+}
+const char* cls_ctype(Cls c) {
+    switch (c) { case CF32: return "float"; case CF16: return "__half"; case CINT: return "int"; case CUINT: return "unsigned"; default: return "bool"; }
+}
+const char* buf_ctype(int dt) {
+    switch (dtype_cls(dt)) { case CF16: return "__half"; case CF32: return "float"; case CINT: return "int"; default: return "unsigned"; }
+}
+
+// ── affine forms over loop variables ────────────────────────────────────────────────────────────
+struct Lin {
+    int64_t c = 0;
+    std::vector<std::pair<int, int64_t>> t;   // (atom, coefficient), sorted by atom
+    bool is_const() const { return t.empty(); }
+};
+
+struct Atom {
+    enum Kind { RANGE, DIV, MOD, OPAQUE } kind = RANGE;
+    int node = -1;        // RANGE / OPAQUE: node index
+    Lin inner;            // DIV / MOD
+    int64_t d = 1;
+    int64_t lo = 0, hi = 0;
+};
+
+const int64_t UNBOUNDED = (int64_t)1 << 40;
+
+struct Gen {
+    const Item& it;
+    const CodegenOpts& opts;
+    std::string err;
+
+    int n;                                 // nodes
+    int sink, end, store, body, dst;
+    std::vector<int> loop_ranges;          // node indices, END order, loop axis
+    std::vector<int> all_ranges;           // every RANGE node
+    std::vector<int> range_slot;           // node → slot or -1
+    std::vector<std::vector<bool>> dep;    // node × range slot
+    std::vector<bool> widen;
+    std::vector<int> reduces;              // REDUCE nodes in node order
+    bool has_sym = false;
+
+    std::vector<Atom> atoms;
+    std::map<std::string, int> atom_key;
+    std::vector<int> range_atom;           // node → atom
+    std::map<int, Lin> lin_memo;
+
+    explicit Gen(const Item& i, const CodegenOpts& o) : it(i), opts(o) {}
+
+    const Node& N(int i) const { return it.nodes[i]; }
+    Cls cls(int i) const { Cls c = dtype_cls(N(i).dtype); return (c == CF16 && widen[i]) ? CF32 : c; }
+
+    bool fail(const std::string& m) { if (err.empty()) err = m; return false; }
+
+    // ── structure ──────────────────────────────────────────────────────────────────────────────
+    bool analyse() {
+        n = (int)it.nodes.size();
+        if (n == 0) return fail("codegen: item has no AST");
+        sink = n - 1;
+        if (N(sink).op != OP_SINK || N(sink).src.empty()) return fail("codegen: last node is not a SINK");
+        end = N(sink).src[0];
+        if (N(end).op != OP_END || N(end).src.empty()) return fail("codegen: SINK source is not END");
+        store = N(end).src[0];
+        if (N(store).op != OP_STORE || N(store).src.size() != 2) return fail("codegen: END source is not STORE");
+        dst = N(store).src[0];
+        body = N(store).src[1];
+        range_slot.assign(n, -1);
+        for (int i = 0; i < n; i++)
+            if (N(i).op == OP_RANGE) { range_slot[i] = (int)all_ranges.size(); all_ranges.push_back(i); if (N(i).symbolic()) has_sym = true; }
+        for (size_t s = 1; s < N(end).src.size(); s++) {
+            int r = N(end).src[s];
+            if (N(r).op == OP_RANGE && N(r).axis() != 1) loop_ranges.push_back(r);
+        }
+        int nr = (int)all_ranges.size();
+        dep.assign(n, std::vector<bool>(nr, false));
+        widen.assign(n, false);
+        for (int i = 0; i < n; i++) {
+            const Node& nd = N(i);
+            if (nd.op == OP_RANGE) dep[i][range_slot[i]] = true;
+            for (int s : nd.src) for (int r = 0; r < nr; r++) if (dep[s][r]) dep[i][r] = true;
+            if (nd.op == OP_REDUCE) {
+                reduces.push_back(i);
+                for (size_t s = 1; s < nd.src.size(); s++) if (N(nd.src[s]).op == OP_RANGE) dep[i][range_slot[nd.src[s]]] = false;
+            }
+        }
+        // only nodes reachable from the body matter
+        std::vector<bool> live(n, false);
+        std::function<void(int)> mark = [&](int i) { if (live[i]) return; live[i] = true; for (int s : N(i).src) mark(s); };
+        mark(body);
+        std::vector<int> lr;
+        for (int r : reduces) if (live[r]) lr.push_back(r);
+        reduces = lr;
+        std::function<void(int)> mw = [&](int i) {
+            if (widen[i]) return;
+            widen[i] = true;
+            if (N(i).op == OP_INDEX) return;
+            for (int s : N(i).src) mw(s);
+        };
+        for (int r : reduces) if (N(r).dtype == DT_F16) mw(N(r).src[0]);
+        // atoms for ranges
+        range_atom.assign(n, -1);
+        for (int r : all_ranges) {
+            Atom a; a.kind = Atom::RANGE; a.node = r; a.lo = 0;
+            a.hi = N(r).symbolic() ? UNBOUNDED : std::max<int64_t>(N(r).arg - 1, 0);
+            range_atom[r] = (int)atoms.size();
+            atoms.push_back(a);
+        }
+        return true;
+    }
+
+    bool depends_on_reduce(int node, int red) const {
+        const Node& r = N(red);
+        for (size_t s = 1; s < r.src.size(); s++) {
+            int rn = r.src[s];
+            if (N(rn).op == OP_RANGE && dep[node][range_slot[rn]]) return true;
+        }
+        return false;
+    }
+
+    // ── Lin algebra ────────────────────────────────────────────────────────────────────────────
+    static Lin lconst(int64_t c) { Lin l; l.c = c; return l; }
+    Lin latom(int a) const { Lin l; l.t.push_back({a, 1}); return l; }
+    static Lin ladd(const Lin& a, const Lin& b, int64_t sb = 1) {
+        Lin r; r.c = a.c + sb * b.c;
+        size_t i = 0, j = 0;
+        while (i < a.t.size() || j < b.t.size()) {
+            if (j == b.t.size() || (i < a.t.size() && a.t[i].first < b.t[j].first)) r.t.push_back(a.t[i++]);
+            else if (i == a.t.size() || b.t[j].first < a.t[i].first) { r.t.push_back({b.t[j].first, sb * b.t[j].second}); j++; }
+            else { int64_t c = a.t[i].second + sb * b.t[j].second; if (c) r.t.push_back({a.t[i].first, c}); i++; j++; }
+        }
+        return r;
+    }
+    static Lin lscale(const Lin& a, int64_t k) {
+        Lin r; if (k == 0) return r;
+        r.c = a.c * k; for (auto& p : a.t) r.t.push_back({p.first, p.second * k});
+        return r;
+    }
+    int64_t llo(const Lin& l) const {
+        int64_t v = l.c;
+        for (auto& p : l.t) { int64_t b = p.second > 0 ? atoms[p.first].lo : atoms[p.first].hi; if (std::llabs(b) >= UNBOUNDED) return p.second > 0 ? (b < 0 ? -UNBOUNDED : v) : -UNBOUNDED; v += p.second * b; }
+        return v;
+    }
+    int64_t lhi(const Lin& l) const {
+        int64_t v = l.c;
+        for (auto& p : l.t) { int64_t b = p.second > 0 ? atoms[p.first].hi : atoms[p.first].lo; if (std::llabs(b) >= UNBOUNDED) return UNBOUNDED; v += p.second * b; }
+        return v;
+    }
+    std::string lkey(const Lin& l) const {
+        std::ostringstream o; o << l.c;
+        for (auto& p : l.t) o << "+" << p.second << "*a" << p.first;
+        return o.str();
+    }
+    int make_atom(Atom::Kind k, const Lin& inner, int64_t d, int64_t lo, int64_t hi, int node = -1) {
+        std::ostringstream key;
+        key << (int)k << ":" << node << ":" << d << ":" << lkey(inner);
+        auto f = atom_key.find(key.str());
+        if (f != atom_key.end()) return f->second;
+        Atom a; a.kind = k; a.inner = inner; a.d = d; a.lo = lo; a.hi = hi; a.node = node;
+        atoms.push_back(a);
+        atom_key[key.str()] = (int)atoms.size() - 1;
+        return (int)atoms.size() - 1;
+    }
+    // split e = d*q + r with every coefficient of q*d a multiple of d and 0 <= const(r) < d
+    void split(const Lin& e, int64_t d, Lin& q, Lin& r) const {
+        q = Lin(); r = Lin();
+        int64_t cq = e.c / d, cr = e.c % d;
+        if (cr < 0) { cr += d; cq -= 1; }
+        q.c = cq; r.c = cr;
+        for (auto& p : e.t) {
+            if (p.second % d == 0) q.t.push_back({p.first, p.second / d});
+            else r.t.push_back(p);
+        }
+    }
+    Lin ldiv(const Lin& e, int64_t d) {
+        if (d == 1) return e;
+        if (e.is_const()) return lconst(e.c / d);
+        int64_t lo = llo(e), hi = lhi(e);
+        if (d <= 0 || lo < 0) return latom(make_atom(Atom::DIV, e, d, -UNBOUNDED, UNBOUNDED));
+        Lin q, r; split(e, d, q, r);
+        if (r.is_const()) return q;                       // r.c in [0,d)
+        int64_t rlo = llo(r), rhi = lhi(r);
+        if (rlo >= 0 && rhi < d) return q;
+        if (rlo >= 0) return ladd(q, latom(make_atom(Atom::DIV, r, d, rlo / d, rhi >= UNBOUNDED ? UNBOUNDED : rhi / d)));
+        return latom(make_atom(Atom::DIV, e, d, lo / d, hi >= UNBOUNDED ? UNBOUNDED : hi / d));
+    }
+    Lin lmod(const Lin& e, int64_t m) {
+        if (m == 1) return lconst(0);
+        if (e.is_const() && m > 0) return lconst(e.c % m);
+        int64_t lo = llo(e), hi = lhi(e);
+        if (m <= 0 || lo < 0) return latom(make_atom(Atom::MOD, e, m, -UNBOUNDED, UNBOUNDED));
+        if (hi < m) return e;
+        Lin q, r; split(e, m, q, r);
+        if (r.is_const()) return lconst(r.c);
+        int64_t rlo = llo(r), rhi = lhi(r);
+        if (rlo >= 0 && rhi < m) return r;
+        if (rlo >= 0) return latom(make_atom(Atom::MOD, r, m, 0, std::min(m - 1, rhi)));
+        return latom(make_atom(Atom::MOD, e, m, 0, m - 1));
+    }
+
+    bool is_intlike(int i) const { Cls c = dtype_cls(N(i).dtype); return c == CINT || c == CUINT; }
+
+    Lin lin(int i) {
+        auto f = lin_memo.find(i);
+        if (f != lin_memo.end()) return f->second;
+        const Node& nd = N(i);
+        Lin r;
+        switch (nd.op) {
+            case OP_CONST: r = lconst(nd.arg); break;
+            case OP_RANGE: r = latom(range_atom[i]); break;
+            case OP_ADD: r = ladd(lin(nd.src[0]), lin(nd.src[1])); break;
+            case OP_SUB: r = ladd(lin(nd.src[0]), lin(nd.src[1]), -1); break;
+            case OP_NEG: r = lscale(lin(nd.src[0]), -1); break;
+            case OP_MUL: {
+                Lin a = lin(nd.src[0]), b = lin(nd.src[1]);
+                if (b.is_const()) r = lscale(a, b.c);
+                else if (a.is_const()) r = lscale(b, a.c);
+                else r = latom(make_atom(Atom::OPAQUE, Lin(), 1, -UNBOUNDED, UNBOUNDED, i));
+                break;
+            }
+            case OP_IDIV: {
+                Lin b = lin(nd.src[1]);
+                if (b.is_const() && b.c > 0) r = ldiv(lin(nd.src[0]), b.c);
+                else r = latom(make_atom(Atom::OPAQUE, Lin(), 1, -UNBOUNDED, UNBOUNDED, i));
+                break;
+            }
+            case OP_MOD: {
+                Lin b = lin(nd.src[1]);
+                if (b.is_const() && b.c > 0) r = lmod(lin(nd.src[0]), b.c);
+                else r = latom(make_atom(Atom::OPAQUE, Lin(), 1, -UNBOUNDED, UNBOUNDED, i));
+                break;
+            }
+            default: r = latom(make_atom(Atom::OPAQUE, Lin(), 1, -UNBOUNDED, UNBOUNDED, i)); break;
+        }
+        lin_memo[i] = r;
+        return r;
+    }
+
+    // does the affine form read loop variable `range_node`, directly or through an atom?
+    bool lin_reads(const Lin& l, int range_node) const {
+        for (auto& p : l.t) {
+            const Atom& a = atoms[p.first];
+            if (a.kind == Atom::RANGE) { if (a.node == range_node) return true; }
+            else if (a.kind == Atom::OPAQUE) { if (dep[a.node][range_slot[range_node]]) return true; }
+            else if (lin_reads(a.inner, range_node)) return true;
+        }
+        return false;
+    }
+    // coefficient of a loop variable when it appears only as a direct term; ok=false otherwise
+    int64_t lin_coef(const Lin& l, int range_node, bool& ok) const {
+        int64_t c = 0; ok = true;
+        for (auto& p : l.t) {
+            const Atom& a = atoms[p.first];
+            if (a.kind == Atom::RANGE && a.node == range_node) c = p.second;
+            else if (a.kind != Atom::RANGE) {
+                Lin one; one.t.push_back({p.first, 1});
+                if (lin_reads(one, range_node)) ok = false;
+            }
+        }
+        return c;
+    }
+
+    // ── flat load index ────────────────────────────────────────────────────────────────────────
+    Lin flat_index(int index_node) {
+        const Node& nd = N(index_node);
+        int p = (int)N(nd.src[0]).arg;
+        int ndim = (int)nd.src.size() - 1;
+        if (ndim == 0) return lconst(0);
+        if (ndim == 1) return lin(nd.src[1]);
+        const std::vector<int64_t>& sh = it.bufs[p].shape;
+        std::vector<int64_t> st(ndim, 1);
+        for (int d = ndim - 2; d >= 0; d--) st[d] = (d + 1 < (int)sh.size()) ? st[d + 1] * (sh[d + 1] ? sh[d + 1] : 1) : 1;
+        Lin r;
+        for (int d = 0; d < ndim; d++) r = ladd(r, lscale(lin(nd.src[1 + d]), st[d]));
+        return r;
+    }
+    bool in_bounds(const Lin& f, int param) const {
+        const BufDesc& b = it.bufs[param];
+        int64_t lo = llo(f), hi = lhi(f);
+        if (!b.symbolic()) return lo >= 0 && hi < b.elems(0);
+        // symbolic outermost dim: need coef(sym range) == trailing and the rest inside one row
+        int64_t tr = b.trailing();
+        Lin rest; rest.c = f.c; bool found = false;
+        for (auto& p : f.t) {
+            const Atom& a = atoms[p.first];
+            if (a.kind == Atom::RANGE && N(a.node).symbolic()) { if (p.second != tr) return false; found = true; }
+            else rest.t.push_back(p);
+        }
+        return found && llo(rest) >= 0 && lhi(rest) < tr;
+    }
+
+    // ── emission ───────────────────────────────────────────────────────────────────────────────
+    struct Block { std::string code; int indent = 1; };
+    Block top;                              // statements outside reduce loops
+    std::map<int, Block> loop;              // REDUCE node → statements inside its loop
+    std::map<std::pair<int, int>, std::string> memo;   // (node, ctx) → expression
+    int vec_range = -1;                     // loop variable unrolled by the vector path, or -1
+    std::map<int, std::string> vec_load;    // INDEX node → array name holding V preloaded values
+    int finish_reduce = -1;                 // finish kernel: this REDUCE reads partials instead
+    std::string reduce_combine_mode;        // set by the kernel builder
+    int lanes = 1, touts = 1, threads = 256; bool rc_layout = true;
+
+    Block prelude;                          // vector path: statements that must precede the unrolled loop
+    Block* cur_top = nullptr;
+    std::map<int, std::vector<bool>> atom_dep_memo;
+
+    void stmt(int ctx, const std::string& s) {
+        Block& b = ctx < 0 ? (cur_top ? *cur_top : top) : loop[ctx];
+        b.code += std::string((ctx < 0 ? 1 : 2) * 2, ' ') + s + "\n";
+    }
+
+    // loop variables an atom reads, as a bitset over range slots
+    const std::vector<bool>& atom_dep(int ai) {
+        auto f = atom_dep_memo.find(ai);
+        if (f != atom_dep_memo.end()) return f->second;
+        std::vector<bool> d(all_ranges.size(), false);
+        const Atom& a = atoms[ai];
+        if (a.kind == Atom::RANGE) d[range_slot[a.node]] = true;
+        else if (a.kind == Atom::OPAQUE) d = dep[a.node];
+        else for (auto& p : a.inner.t) { const std::vector<bool>& s = atom_dep(p.first); for (size_t r = 0; r < d.size(); r++) if (s[r]) d[r] = true; }
+        return atom_dep_memo[ai] = d;
+    }
+    bool atom_in_reduce(int ai, int red) {
+        const std::vector<bool>& d = atom_dep(ai);
+        const Node& r = N(red);
+        for (size_t s = 1; s < r.src.size(); s++) if (N(r.src[s]).op == OP_RANGE && d[range_slot[r.src[s]]]) return true;
+        return false;
+    }
+    // DIV / MOD atoms get a named temporary in the outermost context that can hold them
+    std::string atom_name(int ai, int ctx) {
+        if (ctx >= 0 && !atom_in_reduce(ai, ctx)) ctx = -1;
+        auto key = std::make_pair(-(ai + 1), ctx);
+        auto f = memo.find(key);
+        if (f != memo.end()) return f->second;
+        const Atom& a = atoms[ai];
+        std::string name = "a" + std::to_string(ai);
+        stmt(ctx, "const int " + name + " = " + render(a.inner, ctx) + (a.kind == Atom::DIV ? " / " : " % ") + std::to_string(a.d) + ";");
+        memo[key] = name;
+        return name;
+    }
+
+    std::string range_name(int r) const {
+        std::string s = "r" + std::to_string(N(r).aux);
+        return r == vec_range ? "(" + s + " + u)" : s;
+    }
+
+    std::string render(const Lin& l, int ctx) {
+        if (l.is_const()) return l.c < 0 ? "(" + std::to_string(l.c) + ")" : std::to_string(l.c);
+        std::string s = "(";
+        bool first = true;
+        for (auto& p : l.t) {
+            const Atom& a = atoms[p.first];
+            std::string v;
+            switch (a.kind) {
+                case Atom::RANGE: v = range_name(a.node); break;
+                case Atom::DIV: case Atom::MOD: v = atom_name(p.first, ctx); break;
+                case Atom::OPAQUE: v = opaque_int(a.node, ctx); break;
+            }
+            int64_t c = p.second;
+            if (!first) s += c < 0 ? " - " : " + ";
+            else if (c < 0) s += "-";
+            int64_t ac = std::llabs(c);
+            s += ac == 1 ? v : v + " * " + std::to_string(ac);
+            first = false;
+        }
+        if (l.c > 0) s += " + " + std::to_string(l.c);
+        else if (l.c < 0) s += " - " + std::to_string(-l.c);
+        return s + ")";
+    }
+
+    static std::string flit(double d) {
+        float f = (float)d;
+        if (std::isnan(f)) return "__int_as_float(0x7fc00000)";
+        if (std::isinf(f)) return f < 0 ? "__int_as_float(0xff7fffff)" : "__int_as_float(0x7f7fffff)";
+        char b[64]; std::snprintf(b, sizeof b, "%af", (double)f);
+        return std::string(b);
+    }
+    std::string const_lit(int i) {
+        const Node& nd = N(i);
+        if (dt_is_float(nd.dtype)) {
+            double d; std::memcpy(&d, &nd.arg, 8);
+            bool f16 = nd.dtype == DT_F16;
+            if (f16 && std::isinf(d)) d = d < 0 ? -65504.0 : 65504.0;
+            std::string f = flit(d);
+            return (f16 && !widen[i]) ? "__float2half_rn(" + f + ")" : f;
+        }
+        if (nd.dtype == DT_BOOL) return nd.arg ? "true" : "false";
+        if (nd.arg == INT32_MIN) return "(-2147483647 - 1)";
+        return nd.arg < 0 ? "(" + std::to_string(nd.arg) + ")" : std::to_string(nd.arg);
+    }
+
+    // integer node that the affine engine could not absorb: plain C on its operands
+    std::string opaque_int(int i, int ctx) {
+        if (ctx >= 0 && !depends_on_reduce(i, ctx)) ctx = -1;
+        auto key = std::make_pair(i, ctx);
+        auto f = memo.find(key);
+        if (f != memo.end()) return f->second;
+        const Node& nd = N(i);
+        std::string e;
+        auto a = [&](int k) { return val(nd.src[k], ctx); };
+        switch (nd.op) {
+            case OP_MUL: e = "(" + a(0) + " * " + a(1) + ")"; break;
+            case OP_IDIV: e = "idiv_(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_MOD: e = "imod_(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_MAX: e = "max(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_SHL: e = "(" + a(0) + " << (" + a(1) + " & 31))"; break;
+            case OP_SHR: e = "(" + a(0) + " >> (" + a(1) + " & 31))"; break;
+            case OP_AND: e = "(" + a(0) + " & " + a(1) + ")"; break;
+            case OP_OR: e = "(" + a(0) + " | " + a(1) + ")"; break;
+            case OP_XOR: e = "(" + a(0) + " ^ " + a(1) + ")"; break;
+            case OP_WHERE: e = "(" + a(0) + " ? " + a(1) + " : " + a(2) + ")"; break;
+            case OP_MULACC: e = "(" + a(0) + " + (" + a(1) + " * " + a(2) + "))"; break;
+            case OP_CAST: case OP_BITCAST: e = cast_expr(i, ctx); break;
+            case OP_INDEX: e = load_expr(i, ctx); break;
+            case OP_REDUCE: e = reduce_expr(i); break;
+            default: fail("codegen: unhandled integer op " + std::to_string(nd.op)); e = "0"; break;
+        }
+        std::string name = "t" + std::to_string(i);
+        stmt(ctx, std::string("const ") + cls_ctype(cls(i)) + " " + name + " = " + e + ";");
+        memo[key] = name;
+        return name;
+    }
+
+    std::string to_float(int src, const std::string& e) {
+        switch (cls(src)) { case CF32: return e; case CF16: return "__half2float(" + e + ")"; case CBOOL: return "(" + e + " ? 1.0f : 0.0f)"; default: return "(float)(" + e + ")"; }
+    }
+    std::string cast_expr(int i, int ctx) {
+        const Node& nd = N(i);
+        int s = nd.src[0];
+        std::string e = val(s, ctx);
+        Cls to = cls(i), from = cls(s);
+        if (nd.op == OP_BITCAST) {
+            if (to == from) return e;
+            if (to == CF32 && (from == CINT || from == CUINT)) return "__int_as_float((int)" + e + ")";
+            if ((to == CINT || to == CUINT) && from == CF32) return std::string("(") + cls_ctype(to) + ")__float_as_int(" + e + ")";
+            fail("codegen: unsupported bitcast"); return "0";
+        }
+        if (to == from) return e;
+        switch (to) {
+            case CF32: return to_float(s, e);
+            case CF16: return "__float2half_rn(" + to_float(s, e) + ")";
+            case CBOOL: return from == CF16 ? "(__half2float(" + e + ") != 0.0f)" : from == CF32 ? "(" + e + " != 0.0f)" : "(" + e + " != 0)";
+            case CINT: return from == CF16 ? "(int)__half2float(" + e + ")" : "(int)(" + e + ")";
+            default: return from == CF16 ? "(unsigned)__half2float(" + e + ")" : "(unsigned)(" + e + ")";
+        }
+    }
+
+    std::string load_expr(int i, int ctx) {
+        if (vec_load.count(i)) return vec_load[i] + "[u]";
+        const Node& nd = N(i);
+        if (N(nd.src[0]).op != OP_PARAM) { fail("codegen: INDEX of a non-parameter"); return "0"; }
+        int p = (int)N(nd.src[0]).arg;
+        if (p < 0 || p >= (int)it.bufs.size()) { fail("codegen: PARAM number out of range"); return "0"; }
+        Lin f = flat_index(i);
+        std::string idx = render(f, ctx);
+        if (opts.debug_bounds || !in_bounds(f, p)) {
+            const BufDesc& b = it.bufs[p];
+            std::string hi = b.symbolic() ? "(n0 * " + std::to_string(b.trailing()) + " - 1)" : std::to_string(std::max<int64_t>(b.elems(0) - 1, 0));
+            idx = "clampi_(" + idx + ", " + hi + ")";
+        }
+        std::string e = "data" + std::to_string(p) + "[" + idx + "]";
+        Cls bc = dtype_cls(it.bufs[p].dtype);
+        Cls want = cls(i);
+        if (dtype_cls(nd.dtype) == CBOOL) return "(" + e + " != 0u)";
+        if (bc == CF16 && want == CF32) return "__half2float(" + e + ")";
+        if (bc == CF32 && want == CF16) return "__float2half_rn(" + e + ")";
+        if (bc != want && (want == CINT || want == CUINT)) return std::string("(") + cls_ctype(want) + ")" + e;
+        if (bc != want && want == CF32) return "(float)" + e;
+        return e;
+    }
+
+    std::string identity(int rop, Cls c) {
+        if (c == CF32 || c == CF16) return rop == OP_MUL ? "1.0f" : rop == OP_MAX ? "__int_as_float(0xff7fffff)" : "0.0f";
+        if (c == CUINT) return rop == OP_MUL ? "1u" : "0u";
+        return rop == OP_MUL ? "1" : rop == OP_MAX ? "(-2147483647 - 1)" : "0";
+    }
+    std::string combine(int rop, Cls c, const std::string& a, const std::string& b) {
+        bool f = (c == CF32 || c == CF16);
+        switch (rop) {
+            case OP_MUL: return "(" + a + " * " + b + ")";
+            case OP_MAX: return f ? "fmaxf(" + a + ", " + b + ")" : "max(" + a + ", " + b + ")";
+            default: return "(" + a + " + " + b + ")";
+        }
+    }
+    const char* rop_tag(int rop) { return rop == OP_MUL ? "mul" : rop == OP_MAX ? "max" : "add"; }
+
+    // bound of a reduce range as a C expression
+    std::string range_bound(int r) { return N(r).symbolic() ? "n0" : std::to_string(N(r).arg); }
+
+    std::string reduce_expr(int i) {
+        const Node& nd = N(i);
+        int rop = (int)nd.aux;
+        Cls c = dtype_cls(nd.dtype);
+        bool isf = (c == CF32 || c == CF16);
+        Cls acc_c = isf ? CF32 : c;
+        const char* at = isf ? "float" : cls_ctype(acc_c);
+        std::string acc = "acc" + std::to_string(i);
+        std::vector<int> rr;
+        for (size_t s = 1; s < nd.src.size(); s++) if (N(nd.src[s]).op == OP_RANGE) rr.push_back(nd.src[s]);
+        stmt(-1, std::string(at) + " " + acc + " = " + identity(rop, acc_c) + ";");
+        if (i == finish_reduce) {
+            // finish kernel of a split reduce: partials in ascending part order
+            std::string pe = "scratch[(long long)g * SPLIT + p]";
+            if (!isf) pe = std::string("(") + at + ")__float_as_int(" + pe + ")";
+            stmt(-1, "for (int p = 0; p < SPLIT; p++) " + acc + " = " + combine(rop, acc_c, acc, pe) + ";");
+        } else {
+            std::string e = val(nd.src[0], i);
+            std::string ef = (isf && cls(nd.src[0]) == CF16) ? "__half2float(" + e + ")" : e;
+            // emit: loop header, hoisted code is already in `top`, then the loop body
+            std::string hdr;
+            if (rr.empty()) {
+                hdr = "if (lane == 0) {";
+            } else if (rr.size() == 1) {
+                std::string rn = "r" + std::to_string(N(rr[0]).aux);
+                hdr = "for (int " + rn + " = RED_BEGIN(" + range_bound(rr[0]) + "); " + rn + " < RED_END(" + range_bound(rr[0]) + "); " + rn + " += RED_STEP) {";
+            } else {
+                std::string tot = "(";
+                for (size_t k = 0; k < rr.size(); k++) tot += (k ? " * " : "") + range_bound(rr[k]);
+                tot += ")";
+                hdr = "for (int q = RED_BEGIN" + tot + "; q < RED_END" + tot + "; q += RED_STEP) {";
+            }
+            top.code += "  " + hdr + "\n";
+            if (rr.size() > 1) {
+                // decompose q, last range fastest
+                std::string stride = "1";
+                for (int k = (int)rr.size() - 1; k >= 0; k--) {
+                    std::string rn = "r" + std::to_string(N(rr[k]).aux);
+                    std::string b = range_bound(rr[k]);
+                    top.code += "    const int " + rn + " = " + (k == 0 ? "q / (" + stride + ")" : "(q / (" + stride + ")) % " + b) + ";\n";
+                    stride = stride + " * " + b;
+                }
+            }
+            top.code += loop[i].code;
+            top.code += "    " + acc + " = " + combine(rop, acc_c, acc, ef) + ";\n";
+            top.code += "  }\n";
+            if (reduce_combine_mode == "group")
+                stmt(-1, acc + " = group_" + rop_tag(rop) + "_" + (isf ? "f" : "i") + "(" + acc + ", lane, grp, red_smem);");
+            else if (reduce_combine_mode == "partial")
+                stmt(-1, acc + " = group_" + rop_tag(rop) + "_" + (isf ? "f" : "i") + "(" + acc + ", lane, grp, red_smem);");
+        }
+        if (nd.dtype == DT_F16) return "__float2half_rn(" + acc + ")";
+        return acc;
+    }
+
+    // value of node i as a C expression usable in context ctx (-1 = outside reduce loops)
+    std::string val(int i, int ctx) {
+        const Node& nd = N(i);
+        if (nd.op == OP_CONST) return const_lit(i);
+        if (nd.op == OP_RANGE) return range_name(i);
+        if (ctx >= 0 && !depends_on_reduce(i, ctx)) ctx = -1;
+        Cls c = cls(i);
+        if ((c == CINT || c == CUINT) && nd.op != OP_INDEX && nd.op != OP_REDUCE && nd.op != OP_CAST && nd.op != OP_BITCAST && nd.op != OP_WHERE)
+            return render(lin(i), ctx);
+        if (c == CINT || c == CUINT) return opaque_int(i, ctx);
+        auto key = std::make_pair(i, ctx);
+        auto f = memo.find(key);
+        if (f != memo.end()) return f->second;
+        std::string e;
+        auto a = [&](int k) { return val(nd.src[k], ctx); };
+        auto af = [&](int k) { return to_float(nd.src[k], val(nd.src[k], ctx)); };
+        bool h = (c == CF16);
+        auto wrap = [&](const std::string& fexpr) { return h ? "__float2half_rn(" + fexpr + ")" : fexpr; };
+        if (c == CBOOL) {
+            switch (nd.op) {
+                case OP_CMPLT: case OP_CMPNE: case OP_CMPEQ: {
+                    int s0 = nd.src[0], s1 = nd.src[1];
+                    const char* o = nd.op == OP_CMPLT ? " < " : nd.op == OP_CMPNE ? " != " : " == ";
+                    if (is_intlike(s0) && is_intlike(s1)) {
+                        Lin d = ladd(lin(s0), lin(s1), -1);     // s0 - s1
+                        int64_t lo = llo(d), hi = lhi(d);
+                        if (nd.op == OP_CMPLT) { if (hi < 0) return "true"; if (lo >= 0) return "false"; }
+                        if (nd.op == OP_CMPNE) { if (hi < 0 || lo > 0) return "true"; if (lo == 0 && hi == 0) return "false"; }
+                        if (nd.op == OP_CMPEQ) { if (hi < 0 || lo > 0) return "false"; if (lo == 0 && hi == 0) return "true"; }
+                        e = "(" + render(lin(s0), ctx) + o + render(lin(s1), ctx) + ")";
+                    } else if (cls(s0) == CF16 || cls(s1) == CF16) e = "(" + af(0) + o + af(1) + ")";
+                    else e = "(" + a(0) + o + a(1) + ")";
+                    break;
+                }
+                case OP_AND: { std::string x = a(0), y = a(1); if (x == "false" || y == "false") return "false"; if (x == "true") return y; if (y == "true") return x; e = "(" + x + " && " + y + ")"; break; }
+                case OP_OR: { std::string x = a(0), y = a(1); if (x == "true" || y == "true") return "true"; if (x == "false") return y; if (y == "false") return x; e = "(" + x + " || " + y + ")"; break; }
+                case OP_XOR: e = "(" + a(0) + " != " + a(1) + ")"; break;
+                case OP_WHERE: e = "(" + a(0) + " ? " + a(1) + " : " + a(2) + ")"; break;
+                case OP_CAST: case OP_BITCAST: e = cast_expr(i, ctx); break;
+                case OP_INDEX: e = load_expr(i, ctx); break;
+                default: fail("codegen: unhandled bool op " + std::to_string(nd.op)); return "false";
+            }
+        } else {
+            switch (nd.op) {
+                case OP_INDEX: e = load_expr(i, ctx); break;
+                case OP_REDUCE: if (ctx >= 0) { fail("codegen: nested REDUCE"); return "0.0f"; } e = reduce_expr(i); break;
+                case OP_CAST: case OP_BITCAST: e = cast_expr(i, ctx); break;
+                case OP_WHERE: { std::string cnd = a(0); if (cnd == "true") return a(1); if (cnd == "false") return a(2); e = "(" + cnd + " ? " + a(1) + " : " + a(2) + ")"; break; }
+                case OP_EXP2: e = wrap("exp2f(" + af(0) + ")"); break;
+                case OP_LOG2: e = wrap("log2f(" + af(0) + ")"); break;
+                case OP_SIN: e = wrap("sinf(" + af(0) + ")"); break;
+                case OP_SQRT: e = wrap("sqrtf(" + af(0) + ")"); break;
+                case OP_RECIP: e = wrap("(1.0f / " + af(0) + ")"); break;
+                case OP_TRUNC: e = wrap("truncf(" + af(0) + ")"); break;
+                case OP_NEG: e = h ? "__hneg(" + a(0) + ")" : "(-" + a(0) + ")"; break;
+                case OP_ADD: e = h ? "__hadd(" + a(0) + ", " + a(1) + ")" : "(" + a(0) + " + " + a(1) + ")"; break;
+                case OP_SUB: e = h ? "__hsub(" + a(0) + ", " + a(1) + ")" : "(" + a(0) + " - " + a(1) + ")"; break;
+                case OP_MUL: e = h ? "__hmul(" + a(0) + ", " + a(1) + ")" : "(" + a(0) + " * " + a(1) + ")"; break;
+                case OP_FDIV: e = wrap("(" + af(0) + " / " + af(1) + ")"); break;
+                case OP_MAX: e = h ? "__hmax(" + a(0) + ", " + a(1) + ")" : "fmaxf(" + a(0) + ", " + a(1) + ")"; break;
+                case OP_POW: e = wrap("powf(" + af(0) + ", " + af(1) + ")"); break;
+                case OP_MOD: e = wrap("fmodf(" + af(0) + ", " + af(1) + ")"); break;
+                case OP_MULACC: e = h ? "__hadd(" + a(0) + ", __hmul(" + a(1) + ", " + a(2) + "))" : "(" + a(0) + " + (" + a(1) + " * " + a(2) + "))"; break;
+                default: fail("codegen: unhandled op " + std::to_string(nd.op)); return "0.0f";
+            }
+        }
+        std::string name = "t" + std::to_string(i);
+        stmt(ctx, std::string("const ") + cls_ctype(c) + " " + name + " = " + e + ";");
+        memo[key] = name;
+        return name;
+    }
+
+    std::string store_value(const std::string& v, int node) {
+        int odt = it.bufs[0].dtype;
+        Cls vc = cls(node);
+        switch (dtype_cls(odt)) {
+            case CF16: return vc == CF16 ? v : "__float2half_rn(" + to_float(node, v) + ")";
+            case CF32: {
+                std::string f = to_float(node, v);
+                return odt == DT_BF16 ? "__int_as_float(__float_as_int(" + f + ") & 0xFFFF0000)" : f;
+            }
+            case CINT: return vc == CBOOL ? "(" + v + " ? 1 : 0)" : "(int)(" + v + ")";
+            default: return vc == CBOOL ? "(" + v + " ? 1u : 0u)" : "(unsigned)(" + v + ")";
+        }
+    }
+
+    // ── kernel assembly ────────────────────────────────────────────────────────────────────────
+    static const char* preamble() {
+        return
+            "#include <cuda_fp16.h>\n"
+            "__device__ __forceinline__ int clampi_(int i, int hi) { return i < 0 ? 0 : (i > hi ? hi : i); }\n"
+            "__device__ __forceinline__ int idiv_(int a, int b) { return b == 0 ? 0 : a / b; }\n"
+            "__device__ __forceinline__ int imod_(int a, int b) { return b == 0 ? 0 : a % b; }\n"
+            "template <int BYTES> struct vec_t_;\n"
+            "template <> struct vec_t_<16> { typedef uint4 type; };\n"
+            "template <> struct vec_t_<8> { typedef uint2 type; };\n"
+            "template <> struct vec_t_<4> { typedef unsigned type; };\n"
+            "template <> struct vec_t_<2> { typedef unsigned short type; };\n"
+            "template <class T, int V> __device__ __forceinline__ void ldv_(const T* p, T* out) {\n"
+            "  typedef typename vec_t_<sizeof(T) * V>::type W;\n"
+            "  W w = __ldg(reinterpret_cast<const W*>(p));\n"
+            "  *reinterpret_cast<W*>(out) = w;\n"
+            "}\n"
+            "template <class T, int V> __device__ __forceinline__ void stv_(T* p, const T* in) {\n"
+            "  typedef typename vec_t_<sizeof(T) * V>::type W;\n"
+            "  *reinterpret_cast<W*>(p) = *reinterpret_cast<const W*>(in);\n"
+            "}\n"
+            "__device__ __forceinline__ float op_add_f(float a, float b) { return a + b; }\n"
+            "__device__ __forceinline__ float op_mul_f(float a, float b) { return a * b; }\n"
+            "__device__ __forceinline__ float op_max_f(float a, float b) { return fmaxf(a, b); }\n"
+            "__device__ __forceinline__ int op_add_i(int a, int b) { return a + b; }\n"
+            "__device__ __forceinline__ int op_mul_i(int a, int b) { return a * b; }\n"
+            "__device__ __forceinline__ int op_max_i(int a, int b) { return a > b ? a : b; }\n"
+            // Combine the partial accumulators of the LANES threads that share one output.  RC layout:
+            // the lanes of a group are consecutive threads; OC layout: they are TOUTS threads apart.
+            // The combine order is fixed, so a kernel gives the same bits on every run.
+            "#define DEF_GROUP_(NAME, T, OP) \\\n"
+            "__device__ __forceinline__ T NAME(T v, int lane, int grp, float* sm) { \\\n"
+            "  if (LANES == 1) return v; \\\n"
+            "  if (RC_LAYOUT) { \\\n"
+            "    _Pragma(\"unroll\") for (int o = (LANES < 32 ? LANES : 32) / 2; o > 0; o >>= 1) v = OP(v, __shfl_xor_sync(0xffffffffu, v, o)); \\\n"
+            "    if (LANES > 32) { \\\n"
+            "      T* s = reinterpret_cast<T*>(sm); \\\n"
+            "      __syncthreads(); \\\n"
+            "      if ((threadIdx.x & 31) == 0) s[threadIdx.x >> 5] = v; \\\n"
+            "      __syncthreads(); \\\n"
+            "      const int w0 = grp * (LANES / 32); \\\n"
+            "      v = s[w0]; \\\n"
+            "      for (int w = 1; w < LANES / 32; w++) v = OP(v, s[w0 + w]); \\\n"
+            "    } \\\n"
+            "    return v; \\\n"
+            "  } else { \\\n"
+            "    T* s = reinterpret_cast<T*>(sm); \\\n"
+            "    __syncthreads(); \\\n"
+            "    s[lane * TOUTS + grp] = v; \\\n"
+            "    __syncthreads(); \\\n"
+            "    v = s[grp]; \\\n"
+            "    for (int l = 1; l < LANES; l++) v = OP(v, s[l * TOUTS + grp]); \\\n"
+            "    return v; \\\n"
+            "  } \\\n"
+            "}\n"
+            "DEF_GROUP_(group_add_f, float, op_add_f)\n"
+            "DEF_GROUP_(group_mul_f, float, op_mul_f)\n"
+            "DEF_GROUP_(group_max_f, float, op_max_f)\n"
+            "DEF_GROUP_(group_add_i, int, op_add_i)\n"
+            "DEF_GROUP_(group_mul_i, int, op_mul_i)\n"
+            "DEF_GROUP_(group_max_i, int, op_max_i)\n";
+    }
+
+    std::string signature(const std::string& name, bool with_scratch, int nthreads) {
+        std::string s = "extern \"C\" __global__ void __launch_bounds__(" + std::to_string(nthreads) + ") " + name + "(";
+        for (size_t b = 0; b < it.bufs.size(); b++) {
+            s += (b ? ", " : "");
+            s += (b ? "const " : "");
+            s += buf_ctype(it.bufs[b].dtype);
+            s += "* __restrict__ data" + std::to_string(b);
+        }
+        if (with_scratch) s += ", float* __restrict__ scratch";
+        if (has_sym) s += ", const int n0";
+        return s + ")";
+    }
+
+    int64_t static_total() const {
+        int64_t t = 1;
+        for (int r : loop_ranges) if (!N(r).symbolic()) t *= N(r).arg;
+        return t;
+    }
+    bool sym_output() const { for (int r : loop_ranges) if (N(r).symbolic()) return true; return false; }
+    std::string total_expr() const {
+        return sym_output() ? "((long long)n0 * " + std::to_string(static_total()) + ")" : std::to_string(static_total()) + "LL";
+    }
+
+    // r_i = (g / stride_i) % size_i for every loop range, innermost last
+    std::string decompose(const std::string& g) {
+        std::string s;
+        int64_t stride = 1;
+        for (int k = (int)loop_ranges.size() - 1; k >= 0; k--) {
+            int r = loop_ranges[k];
+            std::string rn = "r" + std::to_string(N(r).aux);
+            std::string e = stride == 1 ? g : "(" + g + " / " + std::to_string(stride) + ")";
+            if (k == 0 || N(r).symbolic()) s += "  const int " + rn + " = (int)" + e + ";\n";
+            else s += "  const int " + rn + " = (int)(" + e + " % " + std::to_string(N(r).arg) + ");\n";
+            if (!N(r).symbolic()) stride *= N(r).arg;
+        }
+        return s;
+    }
+
+    void reset_emit() { top = Block(); prelude = Block(); cur_top = nullptr; loop.clear(); memo.clear(); vec_load.clear(); vec_range = -1; finish_reduce = -1; }
+
+    // vector width the elementwise path may use, and the loads it can preload as vectors
+    int pick_vector(std::vector<int>& vloads) {
+        if (opts.vector_width == 1 || loop_ranges.empty() || opts.debug_bounds) return 1;
+        int rv = loop_ranges.back();
+        if (N(rv).symbolic()) return 1;
+        bool all16 = dt_storage_bytes(it.bufs[0].dtype) == 2;
+        std::vector<int> idx_nodes;
+        for (int i = 0; i < n; i++) if (N(i).op == OP_INDEX && i != dst && is_live(i)) idx_nodes.push_back(i);
+        for (int i : idx_nodes) if (dt_storage_bytes(it.bufs[(int)N(N(i).src[0]).arg].dtype) != 2) { all16 = false; }
+        int V = opts.vector_width > 1 ? opts.vector_width : (all16 ? 8 : 4);
+        if (N(rv).arg % V != 0) return 1;
+        vloads.clear();
+        for (int i : idx_nodes) {
+            int p = (int)N(N(i).src[0]).arg;
+            Lin f = flat_index(i);
+            bool ok; int64_t c = lin_coef(f, rv, ok);
+            if (!ok) return 1;                 // the unrolled variable is buried in a div/mod
+            if (c == 0) continue;              // broadcast along the vector
+            if (c != 1) return 1;
+            if (!in_bounds(f, p)) return 1;
+            if (f.c % V != 0) return 1;
+            for (auto& t : f.t) {
+                const Atom& a = atoms[t.first];
+                if (a.kind == Atom::RANGE && a.node == rv) continue;
+                if (t.second % V != 0) return 1;
+            }
+            vloads.push_back(i);
+        }
+        return V;
+    }
+    std::vector<bool> live_;
+    bool is_live(int i) {
+        if (live_.empty()) {
+            live_.assign(n, false);
+            std::function<void(int)> mark = [&](int k) { if (live_[k]) return; live_[k] = true; for (int s : N(k).src) mark(s); };
+            mark(body);
+        }
+        return live_[i];
+    }
+
+    bool build_elementwise(Rendered& out) {
+        std::vector<int> vloads;
+        int V = pick_vector(vloads);
+        int T = opts.block_threads > 0 ? opts.block_threads : 256;
+        reset_emit();
+        std::ostringstream k;
+        k << "#define LANES 1\n#define TOUTS 1\n#define RC_LAYOUT 1\n";
+        k << preamble();
+        std::string name = "ew_fused";
+        k << signature(name, false, T) << " {\n";
+        k << "  const long long g = (long long)blockIdx.x * " << T << " + threadIdx.x;\n";
+        if (V == 1) {
+            k << "  if (g >= " << total_expr() << ") return;\n";
+            k << decompose("g");
+            std::string v = val(body, -1);
+            if (!err.empty()) return false;
+            k << top.code;
+            k << "  data0[g] = " << store_value(v, body) << ";\n";
+        } else {
+            int rv = loop_ranges.back();
+            k << "  const long long base = g * " << V << ";\n";
+            k << "  if (base >= " << total_expr() << ") return;\n";
+            k << decompose("base");
+            // preload the unit-stride operands with one wide access each
+            vec_range = -1;
+            int vi = 0;
+            cur_top = &prelude;
+            for (int i : vloads) {
+                int p = (int)N(N(i).src[0]).arg;
+                Lin f = flat_index(i);
+                std::string arr = "v" + std::to_string(vi++);
+                std::string bt = buf_ctype(it.bufs[p].dtype), VS = std::to_string(V);
+                std::string idx = render(f, -1);
+                stmt(-1, bt + " " + arr + "_raw[" + VS + "];");
+                stmt(-1, "ldv_<" + bt + ", " + VS + ">(data" + std::to_string(p) + " + " + idx + ", " + arr + "_raw);");
+                // convert to the compute class of the INDEX node
+                Cls bc = dtype_cls(it.bufs[p].dtype), want = cls(i);
+                if (dtype_cls(N(i).dtype) == CBOOL) {
+                    stmt(-1, "bool " + arr + "[" + VS + "];");
+                    stmt(-1, "_Pragma(\"unroll\") for (int u = 0; u < " + VS + "; u++) " + arr + "[u] = " + arr + "_raw[u] != 0u;");
+                    vec_load[i] = arr;
+                } else if (bc == CF16 && want == CF32) {
+                    stmt(-1, "float " + arr + "[" + VS + "];");
+                    stmt(-1, "_Pragma(\"unroll\") for (int u = 0; u < " + VS + "; u++) " + arr + "[u] = __half2float(" + arr + "_raw[u]);");
+                    vec_load[i] = arr;
+                } else {
+                    vec_load[i] = arr + "_raw";
+                }
+            }
+            cur_top = nullptr;
+            vec_range = rv;
+            std::string v = val(body, -1);
+            if (!err.empty()) return false;
+            k << prelude.code;
+            k << "  " << buf_ctype(it.bufs[0].dtype) << " outv[" << V << "];\n";
+            k << "  _Pragma(\"unroll\") for (int u = 0; u < " << V << "; u++) {\n";
+            k << top.code;
+            k << "    outv[u] = " << store_value(v, body) << ";\n";
+            k << "  }\n";
+            k << "  stv_<" << buf_ctype(it.bufs[0].dtype) << ", " << V << ">(data0 + base, outv);\n";
+        }
+        k << "}\n";
+        out.klass = KC_ELEMENTWISE;
+        out.source = k.str();
+        out.vector_width = V;
+        out.main.entry = name;
+        out.main.block = T;
+        out.main.outputs_per_block = (int64_t)T * V;
+        out.main.static_outputs = static_total();
+        out.main.sym_trailing = sym_output() ? static_total() : 0;
+        out.uses_sym = has_sym;
+        out.note = "elementwise V=" + std::to_string(V);
+        return true;
+    }
+
+    // flattened size of a REDUCE's ranges; 0 if symbolic
+    int64_t reduce_total(int r) const {
+        int64_t t = 1;
+        for (size_t s = 1; s < N(r).src.size(); s++) {
+            int rn = N(r).src[s];
+            if (N(rn).op != OP_RANGE) continue;
+            if (N(rn).symbolic()) return 0;
+            t *= N(rn).arg;
+        }
+        return t;
+    }
+
+    void choose_layout(int64_t total, int64_t rtot_max) {
+        // votes: bytes of loads that are unit-stride along the innermost reduce range (RC) against
+        // loads unit-stride along the innermost output range (OC)
+        int64_t rc = 0, oc = 0;
+        int out_inner = loop_ranges.empty() ? -1 : loop_ranges.back();
+        for (int r : reduces) {
+            int red_inner = -1;
+            for (size_t s = 1; s < N(r).src.size(); s++) if (N(N(r).src[s]).op == OP_RANGE) red_inner = N(r).src[s];
+            if (red_inner < 0) continue;
+            for (int i = 0; i < n; i++) {
+                if (N(i).op != OP_INDEX || i == dst || !is_live(i) || !dep[i][range_slot[red_inner]]) continue;
+                Lin f = flat_index(i);
+                bool ok1, ok2 = false;
+                int64_t c1 = lin_coef(f, red_inner, ok1);
+                int64_t c2 = out_inner >= 0 ? lin_coef(f, out_inner, ok2) : 0;
+                int bytes = dt_storage_bytes(it.bufs[(int)N(N(i).src[0]).arg].dtype);
+                if (ok1 && std::llabs(c1) == 1) rc += bytes;
+                else if (ok2 && std::llabs(c2) == 1) oc += bytes;
+            }
+        }
+        threads = opts.block_threads > 0 ? opts.block_threads : 256;
+        const int64_t want_threads = 148LL * 1024;     // enough to fill the machine
+        if (oc > 0) {
+            rc_layout = false;
+            int L = 1;
+            if (opts.reduce_lanes > 0) L = opts.reduce_lanes;
+            else while (L < 32 && total * L < want_threads && rtot_max / (L * 2) >= 16) L *= 2;
+            lanes = L;
+        } else {
+            rc_layout = true;
+            int L;
+            if (opts.reduce_lanes > 0) L = opts.reduce_lanes;
+            else if (rtot_max == 0) L = 32;          // symbolic bound
+            else if (rtot_max <= 16) L = 1;
+            else if (rtot_max < 1024) { L = 32; while (L > rtot_max) L /= 2; }
+            else L = threads;
+            if (opts.reduce_lanes == 0 && L < threads && total * L < want_threads / 4 && rtot_max >= 64) {
+                while (L < threads && total * L < want_threads / 4 && rtot_max / (L * 2) >= 4) L *= 2;
+            }
+            lanes = L;
+        }
+        if (lanes > threads) lanes = threads;
+        touts = threads / lanes;
+    }
+
+    std::string reduce_macros(bool partial) {
+        std::ostringstream m;
+        m << "#define LANES " << lanes << "\n#define TOUTS " << touts << "\n#define RC_LAYOUT " << (rc_layout ? 1 : 0) << "\n";
+        if (partial) {
+            // each block owns a contiguous chunk of the flattened reduce space
+            m << "#define RED_BEGIN(n) (part_begin((n)) + lane)\n#define RED_END(n) part_end((n))\n#define RED_STEP LANES\n";
+        } else {
+            m << "#define RED_BEGIN(n) lane\n#define RED_END(n) (n)\n#define RED_STEP LANES\n";
+        }
+        return m.str();
+    }
+
+    bool build_reduce(Rendered& out) {
+        int64_t total = static_total();
+        int64_t rmax = 0; bool rsym = false;
+        for (int r : reduces) { int64_t t = reduce_total(r); if (t == 0) rsym = true; rmax = std::max(rmax, t); }
+        if (rsym) rmax = 0;
+        int64_t est_total = sym_output() ? total * 1024 : total;
+        choose_layout(est_total, rmax);
+
+        // split one long reduction over several blocks?
+        int split = 1;
+        if (reduces.size() == 1 && !rsym && !sym_output() && opts.split != 1) {
+            if (opts.split > 1) split = opts.split;
+            else if (total <= 64 && rmax >= (1 << 16)) {
+                int64_t s = std::max<int64_t>(2, (148 * 4) / std::max<int64_t>(total, 1));
+                s = std::min<int64_t>(s, rmax / 4096);
+                split = (int)std::max<int64_t>(1, std::min<int64_t>(s, 1024));
+            }
+        }
+        if (split > 1) return build_split(out, split, total, rmax);
+
+        reset_emit();
+        reduce_combine_mode = "group";
+        std::ostringstream k;
+        k << reduce_macros(false) << preamble();
+        std::string name = "reduce_fused";
+        k << signature(name, false, threads) << " {\n";
+        k << "  __shared__ float red_smem[" << (rc_layout ? std::max(threads / 32, 1) : threads) << "];\n";
+        if (rc_layout) k << "  const int lane = threadIdx.x % LANES, grp = threadIdx.x / LANES;\n";
+        else k << "  const int grp = threadIdx.x % TOUTS, lane = threadIdx.x / TOUTS;\n";
+        k << "  long long g = (long long)blockIdx.x * TOUTS + grp;\n";
+        k << "  const bool valid = g < " << total_expr() << ";\n";
+        k << "  if (!valid) g = " << total_expr() << " - 1;\n";
+        k << decompose("g");
+        std::string v = val(body, -1);
+        if (!err.empty()) return false;
+        k << top.code;
+        k << "  if (valid && lane == 0) data0[g] = " << store_value(v, body) << ";\n";
+        k << "}\n";
+        out.klass = KC_REDUCE;
+        out.source = k.str();
+        out.main.entry = name;
+        out.main.block = threads;
+        out.main.outputs_per_block = touts;
+        out.main.static_outputs = total;
+        out.main.sym_trailing = sym_output() ? total : 0;
+        out.uses_sym = has_sym;
+        out.note = std::string("reduce ") + (rc_layout ? "RC" : "OC") + " lanes=" + std::to_string(lanes) + " touts=" + std::to_string(touts);
+        return true;
+    }
+
+    bool build_split(Rendered& out, int split, int64_t total, int64_t rtot) {
+        // partials kernel: block b reduces chunk (b % SPLIT) of output (b / SPLIT)
+        threads = opts.block_threads > 0 ? opts.block_threads : 256;
+        lanes = threads; touts = 1; rc_layout = true;
+        int red = reduces[0];
+        Cls rc = dtype_cls(N(red).dtype);
+        bool isf = (rc == CF32 || rc == CF16);
+        reset_emit();
+        reduce_combine_mode = "partial";
+        std::ostringstream k;
+        k << "#define SPLIT " << split << "\n";
+        k << reduce_macros(true) << preamble();
+        k << "__device__ __forceinline__ int part_begin(int n);\n__device__ __forceinline__ int part_end(int n);\n";
+        std::string pname = "reduce_partials", fname = "reduce_finish";
+        k << signature(pname, true, threads) << " {\n";
+        k << "  __shared__ float red_smem[" << std::max(threads / 32, 1) << "];\n";
+        k << "  const int lane = threadIdx.x, grp = 0;\n";
+        k << "  const long long g = blockIdx.x / SPLIT;\n";
+        k << decompose("g");
+        // evaluate only the REDUCE; its hoisted operands land in `top`
+        std::string accv = val(red, -1);
+        (void)accv;
+        if (!err.empty()) return false;
+        k << top.code;
+        std::string acc = "acc" + std::to_string(red);
+        k << "  if (lane == 0) scratch[blockIdx.x] = " << (isf ? acc : "__int_as_float((int)" + acc + ")") << ";\n";
+        k << "}\n";
+        int64_t chunk = (rtot + split - 1) / split;
+        k << "__device__ __forceinline__ int part_begin(int n) { return (int)((blockIdx.x % SPLIT) * " << chunk << "LL); }\n";
+        k << "__device__ __forceinline__ int part_end(int n) { long long e = ((blockIdx.x % SPLIT) + 1) * " << chunk << "LL; return (int)(e < n ? e : n); }\n";
+        // finish kernel
+        reset_emit();
+        finish_reduce = red;
+        reduce_combine_mode = "";
+        k << "#undef RED_BEGIN\n#undef RED_END\n#undef RED_STEP\n";
+        k << "#define RED_BEGIN(n) 0\n#define RED_END(n) (n)\n#define RED_STEP 1\n";
+        k << signature(fname, true, 128) << " {\n";
+        k << "  const int lane = 0;\n  (void)lane;\n";
+        k << "  const long long g = (long long)blockIdx.x * 128 + threadIdx.x;\n";
+        k << "  if (g >= " << total_expr() << ") return;\n";
+        k << decompose("g");
+        std::string v = val(body, -1);
+        if (!err.empty()) return false;
+        k << top.code;
+        k << "  data0[g] = " << store_value(v, body) << ";\n";
+        k << "}\n";
+        out.klass = KC_REDUCE_SPLIT;
+        out.source = k.str();
+        out.split = split;
+        out.scratch_elems = total * split;
+        out.main.entry = pname;
+        out.main.block = threads;
+        out.main.outputs_per_block = 1;
+        out.main.static_outputs = total * split;
+        out.finish.entry = fname;
+        out.finish.block = 128;
+        out.finish.outputs_per_block = 128;
+        out.finish.static_outputs = total;
+        out.uses_sym = has_sym;
+        out.note = "split reduce parts=" + std::to_string(split);
+        return true;
+    }
+
+    bool run(Rendered& out) {
+        if (!analyse()) return false;
+        if (it.bufs.empty()) return fail("codegen: kernel has no output buffer");
+        if (static_total() >= ((int64_t)1 << 31)) return fail("codegen: more than 2^31 outputs");
+        bool ok = reduces.empty() ? build_elementwise(out) : build_reduce(out);
+        return ok && err.empty();
+    }
+};
+
+}  // namespace
+
+bool render_cuda(const Item& item, const CodegenOpts& opts, Rendered& out, std::string& err) {
+    Gen g(item, opts);
+    bool ok = g.run(out);
+    if (!ok) err = g.err.empty() ? "codegen: failed" : g.err;
+    return ok;
+}
+
+}  // namespace anl

@@ -1,0 +1,94 @@
+// Data-parallel gradient exchange: NCCL all-reduce over NVLink, one process per GPU.
+// The reference has no multi-device support at all (README.md:109-111; uop/ops.go:129 lists
+// OpAllReduce without any lowering), so this is new surface.  NCCL is bound at run time with
+// dlopen so that the library loads on machines without it and shares the copy a host process
+// (for example PyTorch) may already have loaded.
+#include <dlfcn.h>
+
+#include <cstring>
+#include <string>
+
+#include "runtime.hpp"
+
+namespace {
+typedef struct { char internal[128]; } nccl_uid;
+struct Nccl {
+    void* h = nullptr;
+    int (*GetUniqueId)(nccl_uid*) = nullptr;
+    int (*CommInitRank)(void**, int, nccl_uid, int) = nullptr;
+    int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*CommDestroy)(void*) = nullptr;
+    int (*CommAbort)(void*) = nullptr;
+    const char* (*GetErrorString)(int) = nullptr;
+    bool ok = false;
+};
+Nccl& nccl() {
+    static Nccl n;
+    if (n.h) return n;
+    const char* names[] = {"libnccl.so.2", "libnccl.so"};
+    for (const char* nm : names) { n.h = dlopen(nm, RTLD_NOW | RTLD_GLOBAL); if (n.h) break; }
+    if (!n.h) return n;
+    n.GetUniqueId = (int (*)(nccl_uid*))dlsym(n.h, "ncclGetUniqueId");
+    n.CommInitRank = (int (*)(void**, int, nccl_uid, int))dlsym(n.h, "ncclCommInitRank");
+    n.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(n.h, "ncclAllReduce");
+    n.CommDestroy = (int (*)(void*))dlsym(n.h, "ncclCommDestroy");
+    n.CommAbort = (int (*)(void*))dlsym(n.h, "ncclCommAbort");
+    n.GetErrorString = (const char* (*)(int))dlsym(n.h, "ncclGetErrorString");
+    n.ok = n.GetUniqueId && n.CommInitRank && n.AllReduce && n.CommDestroy;
+    return n;
+}
+// ncclDataType_t / ncclRedOp_t values from nccl.h
+enum { NCCL_FLOAT16 = 6, NCCL_FLOAT32 = 7, NCCL_SUM = 0 };
+}  // namespace
+
+extern "C" {
+
+int anl_comm_unique_id(uint8_t id[128]) {
+    Nccl& n = nccl();
+    if (!n.ok) return ANL_ERR_COMM;
+    nccl_uid u;
+    if (n.GetUniqueId(&u) != 0) return ANL_ERR_COMM;
+    std::memcpy(id, u.internal, 128);
+    return ANL_OK;
+}
+
+int anl_comm_init(anl_device* dev, int rank, int nranks, const uint8_t id[128]) {
+    if (!dev || rank < 0 || rank >= nranks) return ANL_ERR_INVALID;
+    Nccl& n = nccl();
+    if (!n.ok) return dev->fail(ANL_ERR_COMM, "nccl: library not found");
+    cudaSetDevice(dev->ordinal);
+    nccl_uid u;
+    std::memcpy(u.internal, id, 128);
+    int r = n.CommInitRank(&dev->nccl_comm, nranks, u, rank);
+    if (r != 0) return dev->fail(ANL_ERR_COMM, std::string("nccl: ncclCommInitRank: ") + (n.GetErrorString ? n.GetErrorString(r) : "?"));
+    dev->rank = rank; dev->nranks = nranks;
+    return ANL_OK;
+}
+
+// Sum `buf` over all ranks in place.  The collective runs on the device's communication stream,
+// ordered after everything queued so far on the compute stream; the compute stream then waits for
+// it, so later kernels see the reduced values while kernels queued before the call overlap with it.
+int anl_allreduce_sum(anl_device* dev, anl_buffer* buf) {
+    if (!dev || !buf) return ANL_ERR_INVALID;
+    if (dev->nranks == 1 || !dev->nccl_comm) return ANL_OK;
+    Nccl& n = nccl();
+    int dt = buf->dtype == ANL_F16 ? NCCL_FLOAT16 : NCCL_FLOAT32;
+    cudaSetDevice(dev->ordinal);
+    cudaEventRecord(dev->comm_event, dev->stream);
+    cudaStreamWaitEvent(dev->comm_stream, dev->comm_event, 0);
+    int r = n.AllReduce(buf->ptr, buf->ptr, (size_t)buf->elems, dt, NCCL_SUM, dev->nccl_comm, dev->comm_stream);
+    if (r != 0) return dev->fail(ANL_ERR_COMM, std::string("nccl: ncclAllReduce: ") + (n.GetErrorString ? n.GetErrorString(r) : "?"));
+    cudaEventRecord(dev->comm_done, dev->comm_stream);
+    cudaStreamWaitEvent(dev->stream, dev->comm_done, 0);
+    return ANL_OK;
+}
+
+int anl_comm_destroy(anl_device* dev) {
+    if (!dev || !dev->nccl_comm) return ANL_OK;
+    Nccl& n = nccl();
+    if (n.ok) n.CommDestroy(dev->nccl_comm);
+    dev->nccl_comm = nullptr; dev->nranks = 1; dev->rank = 0;
+    return ANL_OK;
+}
+
+}  // extern "C"

@@ -1,0 +1,713 @@
+// Device runtime: everything backend/webgpu/executor.go does per Run call (allocate, upload with
+// dtype conversion, compile, dispatch, read back, release) redone for CUDA so that the per-call
+// costs the reference pays every time are paid once: rendered sources and compiled modules are
+// cached by content, device blocks come from a size-keyed pool, conversion runs on the GPU.
+#include "runtime.hpp"
+
+#include <cuda_fp16.h>
+#include <nvrtc.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <cstring>
+#include <set>
+
+using namespace anl;
+
+#define CK(dev, call)                                                                            \
+    do {                                                                                         \
+        cudaError_t e_ = (call);                                                                 \
+        if (e_ != cudaSuccess)                                                                   \
+            return (dev)->fail(ANL_ERR_CUDA, std::string("cuda: ") + #call + ": " + cudaGetErrorString(e_)); \
+    } while (0)
+
+// ── boundary conversions ─────────────────────────────────────────────────────────────────────
+// f32 → f16 is round-to-nearest-even, f32 → bf16 clears the low 16 bits and keeps a 32-bit slot
+// (uop/dtype.go:392-487, backend/webgpu/executor.go:480-519).
+__global__ void cvt_f32_to_f16(const float* __restrict__ in, __half* __restrict__ out, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = __float2half_rn(in[i]);
+}
+__global__ void cvt_f32_to_bf16slot(const float* __restrict__ in, float* __restrict__ out, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = __int_as_float(__float_as_int(in[i]) & 0xFFFF0000);
+}
+__global__ void cvt_f16_to_f32(const __half* __restrict__ in, float* __restrict__ out, long long n) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) out[i] = __half2float(in[i]);
+}
+
+// Parameter.SGDStep (tensor/nn/nn.go:69-76) with the re-quantisation of Parameter.Load
+// (tensor/nn/nn.go:56-61) fused: one pass over master, grad and param.
+template <class G, class P>
+__global__ void sgd_kernel(float* __restrict__ master, P* __restrict__ param, const G* __restrict__ grad,
+                           float lr, float scale, long long n, int bf16) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < n; i += stride) {
+        float g = (float)grad[i] * scale;
+        float m = master[i] - lr * g;
+        master[i] = m;
+        if (bf16) m = __int_as_float(__float_as_int(m) & 0xFFFF0000);
+        if ((void*)param != (void*)master) param[i] = (P)m;
+    }
+}
+
+static unsigned grid_for(long long n, int block, int sms) {
+    long long g = (n + block - 1) / block;
+    long long cap = (long long)sms * 16;
+    return (unsigned)std::max<long long>(1, std::min(g, cap));
+}
+
+// ── device memory pool ───────────────────────────────────────────────────────────────────────
+int anl_device::alloc(size_t bytes, void** out) {
+    if (bytes == 0) bytes = 4;
+    bytes = (bytes + 255) & ~(size_t)255;
+    auto it = pool.find(bytes);
+    if (it != pool.end()) {
+        *out = it->second;
+        pool.erase(it);
+    } else {
+        cudaError_t e = cudaMalloc(out, bytes);
+        if (e != cudaSuccess) {
+            trim();
+            e = cudaMalloc(out, bytes);
+        }
+        if (e != cudaSuccess) return fail(ANL_ERR_CUDA, std::string("cuda: cudaMalloc(") + std::to_string(bytes) + "): " + cudaGetErrorString(e));
+        stats.device_allocs++;
+    }
+    live[*out] = bytes;
+    return ANL_OK;
+}
+void anl_device::release(void* p) {
+    if (!p) return;
+    auto it = live.find(p);
+    if (it == live.end()) return;
+    pool.insert({it->second, p});
+    live.erase(it);
+}
+void anl_device::trim() {
+    for (auto& kv : pool) cudaFree(kv.second);
+    pool.clear();
+}
+
+namespace anl {
+
+int ensure_driver(anl_device* dev) {
+    if (dev->drv.loaded) return ANL_OK;
+    auto get = [&](const char* name, void** fn) -> bool {
+        cudaDriverEntryPointQueryResult q;
+        cudaError_t e = cudaGetDriverEntryPointByVersion(name, fn, 12000, cudaEnableDefault, &q);
+        return e == cudaSuccess && q == cudaDriverEntryPointSuccess && *fn;
+    };
+    bool ok = get("cuModuleLoadData", (void**)&dev->drv.ModuleLoadData) && get("cuModuleUnload", (void**)&dev->drv.ModuleUnload) &&
+              get("cuModuleGetFunction", (void**)&dev->drv.ModuleGetFunction) && get("cuLaunchKernel", (void**)&dev->drv.LaunchKernel) &&
+              get("cuGetErrorString", (void**)&dev->drv.GetErrorString) && get("cuTensorMapEncodeTiled", (void**)&dev->drv.TensorMapEncodeTiled);
+    if (!ok) return dev->fail(ANL_ERR_CUDA, "cuda: driver entry points unavailable");
+    dev->drv.loaded = true;
+    return ANL_OK;
+}
+
+static std::string cuda_include_dir() {
+    const char* h = std::getenv("CUDA_HOME");
+    if (!h) h = std::getenv("CUDA_PATH");
+    return std::string("-I") + (h ? h : "/usr/local/cuda") + "/include";
+}
+
+// NVRTC → cubin for sm_100a.  No fast-math and no fused multiply-add contraction: generated
+// kernels keep the rounding of the expression tree they were given.
+static int nvrtc_compile(const std::string& src, std::vector<char>& cubin, std::string& log) {
+    nvrtcProgram prog;
+    if (nvrtcCreateProgram(&prog, src.c_str(), "anneal_kernel.cu", 0, nullptr, nullptr) != NVRTC_SUCCESS) { log = "nvrtcCreateProgram failed"; return ANL_ERR_COMPILE; }
+    std::string inc = cuda_include_dir();
+    const char* opts[] = {"--gpu-architecture=sm_100a", "--std=c++17", "--fmad=false", inc.c_str(), "-default-device"};
+    nvrtcResult r = nvrtcCompileProgram(prog, 5, opts);
+    size_t ls = 0;
+    nvrtcGetProgramLogSize(prog, &ls);
+    if (ls > 1) { log.resize(ls); nvrtcGetProgramLog(prog, &log[0]); }
+    if (r != NVRTC_SUCCESS) { nvrtcDestroyProgram(&prog); if (log.empty()) log = nvrtcGetErrorString(r); return ANL_ERR_COMPILE; }
+    size_t cs = 0;
+    nvrtcGetCUBINSize(prog, &cs);
+    cubin.resize(cs);
+    nvrtcGetCUBIN(prog, cubin.data());
+    nvrtcDestroyProgram(&prog);
+    return ANL_OK;
+}
+
+int compile_source(anl_device* dev, const std::string& src, std::shared_ptr<Module>& out) {
+    uint64_t h = fnv1a(src.data(), src.size());
+    auto it = dev->modules.find(h);
+    if (it != dev->modules.end()) { dev->stats.nvrtc_cache_hits++; out = it->second; return ANL_OK; }
+    if (int rc = ensure_driver(dev)) return rc;
+    std::vector<char> cubin; std::string log;
+    if (int rc = nvrtc_compile(src, cubin, log)) return dev->fail(rc, "cuda: compile failed: " + log + "\n--- source ---\n" + src);
+    dev->stats.nvrtc_compiles++;
+    auto m = std::make_shared<Module>();
+    CUresult cr = dev->drv.ModuleLoadData(&m->mod, cubin.data());
+    if (cr != CUDA_SUCCESS) { const char* s = nullptr; dev->drv.GetErrorString(cr, &s); return dev->fail(ANL_ERR_CUDA, std::string("cuda: cuModuleLoadData: ") + (s ? s : "?")); }
+    dev->modules[h] = m;
+    out = m;
+    return ANL_OK;
+}
+
+static int get_function(anl_device* dev, Module& m, const std::string& name, CUfunction* fn) {
+    auto it = m.fn.find(name);
+    if (it != m.fn.end()) { *fn = it->second; return ANL_OK; }
+    CUresult cr = dev->drv.ModuleGetFunction(fn, m.mod, name.c_str());
+    if (cr != CUDA_SUCCESS) return dev->fail(ANL_ERR_CUDA, "cuda: entry point " + name + " not found in compiled module");
+    m.fn[name] = *fn;
+    return ANL_OK;
+}
+
+static bool opts_default(const CodegenOpts& o) { return !o.block_threads && !o.reduce_lanes && !o.vector_width && !o.split; }
+
+int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::shared_ptr<Plan>& out) {
+    int64_t ok[5] = {opts.block_threads, opts.reduce_lanes, opts.vector_width, opts.split, opts.debug_bounds};
+    uint64_t key = fnv1a(ok, sizeof ok, structure_hash(item));
+    if (!item.source.empty()) key = fnv1a(item.source.data(), item.source.size(), key);
+    auto it = dev->plans.find(key);
+    if (it != dev->plans.end()) { dev->stats.lower_cache_hits++; out = it->second; return ANL_OK; }
+    auto p = std::make_shared<Plan>();
+    if (!item.source.empty()) {
+        // pre-rendered source with its launch shape (the reference's ExecItem.WGSL route,
+        // schedule/cache.go:80-88, backend/webgpu/executor.go:53-64): entry point "main_kernel"
+        p->r.klass = KC_RAW;
+        p->r.source = item.source;
+        p->r.main.entry = "main_kernel";
+        p->r.main.block = item.local[0] * item.local[1] * item.local[2];
+        p->r.main.static_outputs = (int64_t)item.grid[0];
+        p->r.main.outputs_per_block = 1;
+    } else {
+        bool routed = false;
+        if (opts_default(opts) && !(dev->flags & ANL_OPEN_NO_GEMM)) routed = plan_gemm(dev, item, *p) == ANL_OK;
+        if (!routed) {
+            std::string err;
+            if (!render_cuda(item, opts, p->r, err)) return dev->fail(ANL_ERR_UNSUPPORTED, err);
+        }
+    }
+    if (p->r.klass != KC_GEMM) {
+        std::shared_ptr<Module> m;
+        if (int rc = compile_source(dev, p->r.source, m)) return rc;
+        if (int rc = get_function(dev, *m, p->r.main.entry, &p->main)) return rc;
+        if (p->r.klass == KC_REDUCE_SPLIT)
+            if (int rc = get_function(dev, *m, p->r.finish.entry, &p->finish)) return rc;
+    }
+    dev->plans[key] = p;
+    out = p;
+    return ANL_OK;
+}
+
+static int launch_one(anl_device* dev, CUfunction fn, const Launch& l, int64_t sym, std::vector<void*>& args, cudaStream_t stream) {
+    int64_t work = l.sym_trailing > 0 ? sym * l.sym_trailing : l.static_outputs;
+    if (work <= 0) return ANL_OK;
+    int64_t grid = (work + l.outputs_per_block - 1) / l.outputs_per_block;
+    if (grid > 0x7fffffffLL) return dev->fail(ANL_ERR_LIMIT, "cuda: grid too large");
+    CUresult cr = dev->drv.LaunchKernel(fn, (unsigned)grid, 1, 1, l.block, 1, 1, l.smem_bytes, (CUstream)stream, args.data(), nullptr);
+    if (cr != CUDA_SUCCESS) { const char* s = nullptr; dev->drv.GetErrorString(cr, &s); return dev->fail(ANL_ERR_CUDA, std::string("cuda: cuLaunchKernel(") + l.entry + "): " + (s ? s : "?")); }
+    dev->stats.kernels_launched++;
+    return ANL_OK;
+}
+
+int launch_plan(anl_device* dev, const Plan& plan, const Item& item, void* const* bufs, int64_t sym_value, cudaStream_t stream,
+                std::vector<void*>* keep_scratch) {
+    if (plan.r.klass == KC_GEMM) return launch_gemm(dev, plan, bufs, stream);
+    int nb = (int)item.bufs.size();
+    std::vector<void*> ptrs(bufs, bufs + nb);
+    int n0 = (int)sym_value;
+    void* scratch = nullptr;
+    std::vector<void*> args;
+    for (int b = 0; b < nb; b++) args.push_back(&ptrs[b]);
+    if (plan.r.klass == KC_REDUCE_SPLIT) {
+        // partials travel through global scratch memory owned by the pool for the duration of the
+        // two launches; stream order makes re-use by a later kernel safe
+        if (int rc = dev->alloc((size_t)plan.r.scratch_elems * 4, &scratch)) return rc;
+        args.push_back(&scratch);
+    }
+    if (plan.r.uses_sym) args.push_back(&n0);
+    int rc = launch_one(dev, plan.main, plan.r.main, sym_value, args, stream);
+    if (rc == ANL_OK && plan.r.klass == KC_REDUCE_SPLIT) rc = launch_one(dev, plan.finish, plan.r.finish, sym_value, args, stream);
+    if (scratch) { if (keep_scratch) keep_scratch->push_back(scratch); else dev->release(scratch); }
+    return rc;
+}
+
+int upload_f32(anl_device* dev, void* dst, int dtype, const float* host, int64_t elems, cudaStream_t s) {
+    if (elems <= 0) return ANL_OK;
+    dev->stats.h2d_bytes += (uint64_t)elems * 4;
+    if (dtype != DT_F16 && dtype != DT_BF16) {
+        CK(dev, cudaMemcpyAsync(dst, host, (size_t)elems * 4, cudaMemcpyHostToDevice, s));
+        return ANL_OK;
+    }
+    void* stage = nullptr;
+    if (int rc = dev->alloc((size_t)elems * 4, &stage)) return rc;
+    cudaError_t e = cudaMemcpyAsync(stage, host, (size_t)elems * 4, cudaMemcpyHostToDevice, s);
+    if (e == cudaSuccess) {
+        unsigned g = grid_for(elems, 256, dev->prop.multiProcessorCount);
+        if (dtype == DT_F16) cvt_f32_to_f16<<<g, 256, 0, s>>>((const float*)stage, (__half*)dst, elems);
+        else cvt_f32_to_bf16slot<<<g, 256, 0, s>>>((const float*)stage, (float*)dst, elems);
+        e = cudaGetLastError();
+        dev->stats.kernels_launched++;
+    }
+    dev->release(stage);   // stream-ordered: later users of the block run after the conversion
+    if (e != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("cuda: upload: ") + cudaGetErrorString(e));
+    return ANL_OK;
+}
+
+int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64_t elems, cudaStream_t s) {
+    if (elems <= 0) return ANL_OK;
+    dev->stats.d2h_bytes += (uint64_t)elems * 4;
+    if (dtype != DT_F16) {
+        CK(dev, cudaMemcpyAsync(host, src, (size_t)elems * 4, cudaMemcpyDeviceToHost, s));
+        return ANL_OK;
+    }
+    void* stage = nullptr;
+    if (int rc = dev->alloc((size_t)elems * 4, &stage)) return rc;
+    cvt_f16_to_f32<<<grid_for(elems, 256, dev->prop.multiProcessorCount), 256, 0, s>>>((const __half*)src, (float*)stage, elems);
+    dev->stats.kernels_launched++;
+    cudaError_t e = cudaGetLastError();
+    if (e == cudaSuccess) e = cudaMemcpyAsync(host, stage, (size_t)elems * 4, cudaMemcpyDeviceToHost, s);
+    dev->release(stage);
+    if (e != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("cuda: download: ") + cudaGetErrorString(e));
+    return ANL_OK;
+}
+
+}  // namespace anl
+
+// ── schedule execution ───────────────────────────────────────────────────────────────────────
+namespace {
+
+struct DevBuf { void* ptr = nullptr; size_t bytes = 0; int dtype = DT_F32; int64_t elems = 0; bool owned = false; };
+
+struct Bindings {
+    std::vector<std::pair<std::string, int64_t>> v;
+    int64_t get(const std::string& name, int64_t dflt) const { for (auto& p : v) if (p.first == name) return p.second; return dflt; }
+    int64_t any() const { return v.empty() ? -1 : v[0].second; }
+};
+
+int64_t item_sym(const Item& it, const Bindings& b) {
+    if (!it.sym_vars.empty()) return b.get(it.sym_vars[0], b.any());
+    return b.any();
+}
+
+// Buffer table of one schedule: slot-shared intermediates, dedicated outputs, leaves
+// (backend/webgpu/executor.go:66-151).
+struct Table {
+    std::unordered_map<uint32_t, DevBuf> bufs;
+    std::vector<void*> owned;
+    std::set<uint32_t> written, read;
+    std::vector<uint32_t> finals;      // in schedule order
+};
+
+int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings& binds,
+                const anl_input* inputs, int n_inputs, const anl_output* placed, int n_placed, Table& t) {
+    for (auto& it : items) { t.written.insert(it.bufs[0].id); for (size_t b = 1; b < it.bufs.size(); b++) t.read.insert(it.bufs[b].id); }
+    std::map<int, size_t> slot_bytes;
+    for (auto& it : items) {
+        const BufDesc& o = it.bufs[0];
+        if (o.slot >= 0) { size_t by = (size_t)o.elems(item_sym(it, binds)) * dt_storage_bytes(o.dtype); slot_bytes[o.slot] = std::max(slot_bytes[o.slot], by); }
+    }
+    std::map<int, void*> slot_ptr;
+    for (auto& kv : slot_bytes) { void* p; if (int rc = dev->alloc(kv.second, &p)) return rc; slot_ptr[kv.first] = p; t.owned.push_back(p); }
+    for (auto& it : items) {
+        const BufDesc& o = it.bufs[0];
+        int64_t sym = item_sym(it, binds);
+        DevBuf d; d.dtype = o.dtype; d.elems = o.elems(sym); d.bytes = (size_t)d.elems * dt_storage_bytes(o.dtype);
+        if (o.slot >= 0) d.ptr = slot_ptr[o.slot];
+        else {
+            bool is_final = !t.read.count(o.id);
+            const anl_output* pl = nullptr;
+            for (int k = 0; k < n_placed; k++) if (placed[k].uop_idx == o.id && placed[k].resident) pl = &placed[k];
+            if (is_final && pl) {
+                if (pl->resident->elems < d.elems || pl->resident->dtype != o.dtype) return dev->fail(ANL_ERR_INVALID, "run: resident output buffer has the wrong size or dtype");
+                d.ptr = pl->resident->ptr;
+            } else if (!t.bufs.count(o.id)) {
+                if (int rc = dev->alloc(d.bytes, &d.ptr)) return rc;
+                t.owned.push_back(d.ptr); d.owned = true;
+            } else d.ptr = t.bufs[o.id].ptr;
+        }
+        t.bufs[o.id] = d;
+    }
+    for (auto& it : items) {
+        int64_t sym = item_sym(it, binds);
+        for (size_t b = 1; b < it.bufs.size(); b++) {
+            const BufDesc& bd = it.bufs[b];
+            if (t.written.count(bd.id) || t.bufs.count(bd.id)) continue;
+            DevBuf d; d.dtype = bd.dtype; d.elems = bd.elems(sym); d.bytes = (size_t)d.elems * dt_storage_bytes(bd.dtype);
+            const anl_input* in = nullptr;
+            for (int k = 0; k < n_inputs; k++) if (inputs[k].uop_idx == bd.id) in = &inputs[k];
+            if (in && in->resident) {
+                if (in->resident->elems < d.elems) return dev->fail(ANL_ERR_INVALID, "run: resident input " + std::to_string(bd.id) + " is smaller than the schedule expects");
+                d.ptr = in->resident->ptr;
+            } else {
+                if (int rc = dev->alloc(d.bytes, &d.ptr)) return rc;
+                t.owned.push_back(d.ptr); d.owned = true;
+                if (in && in->data) {
+                    if (in->elems < d.elems) return dev->fail(ANL_ERR_INVALID, "run: input " + std::to_string(bd.id) + " has " + std::to_string(in->elems) + " values, schedule expects " + std::to_string(d.elems));
+                    if (int rc = upload_f32(dev, d.ptr, bd.dtype, in->data, d.elems, dev->stream)) return rc;
+                } else {
+                    CK(dev, cudaMemsetAsync(d.ptr, 0, d.bytes ? d.bytes : 4, dev->stream));
+                }
+            }
+            t.bufs[bd.id] = d;
+        }
+    }
+    for (auto& it : items) if (!t.read.count(it.bufs[0].id)) t.finals.push_back(it.bufs[0].id);
+    return ANL_OK;
+}
+
+int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& binds, Table& t, cudaStream_t stream, bool keep_scratch = false) {
+    CodegenOpts opts; opts.debug_bounds = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;
+    for (size_t i = 0; i < items.size(); i++) {
+        const Item& it = items[i];
+        std::shared_ptr<Plan> plan;
+        if (int rc = get_plan(dev, it, opts, plan)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
+        std::vector<void*> ptrs;
+        for (auto& b : it.bufs) ptrs.push_back(t.bufs[b.id].ptr);
+        if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
+    }
+    return ANL_OK;
+}
+
+int collect_outputs(anl_device* dev, Table& t, const anl_output* placed, int n_placed, anl_output* outs, int* n_outs, cudaStream_t stream) {
+    int cap = *n_outs, n = 0;
+    std::vector<float*> mine;
+    int rc = ANL_OK;
+    for (uint32_t id : t.finals) {
+        if (n >= cap) { rc = dev->fail(ANL_ERR_LIMIT, "run: more final outputs than the caller made room for"); break; }
+        DevBuf& d = t.bufs[id];
+        anl_output o{}; o.uop_idx = id; o.elems = d.elems;
+        const anl_output* pl = nullptr;
+        for (int k = 0; k < n_placed; k++) if (placed[k].uop_idx == id) pl = &placed[k];
+        if (pl && pl->resident) { o.resident = pl->resident; }
+        else {
+            if (pl && pl->data) {
+                if (pl->elems < d.elems) { rc = dev->fail(ANL_ERR_INVALID, "run: placed output array is too small"); break; }
+                o.data = pl->data;
+            } else {
+                o.data = (float*)std::malloc((size_t)std::max<int64_t>(d.elems, 1) * 4);
+                if (!o.data) { rc = dev->fail(ANL_ERR_LIMIT, "run: out of host memory"); break; }
+                mine.push_back(o.data);
+            }
+            if ((rc = download_f32(dev, o.data, d.ptr, d.dtype, d.elems, stream))) break;
+        }
+        outs[n++] = o;
+    }
+    cudaError_t e = cudaStreamSynchronize(stream);
+    if (rc == ANL_OK && e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("cuda: ") + cudaGetErrorString(e));
+    if (rc != ANL_OK) { for (float* p : mine) std::free(p); n = 0; }
+    *n_outs = n;
+    return rc;
+}
+
+Bindings make_bindings(const anl_binding* binds, int n) {
+    Bindings b;
+    for (int i = 0; i < n; i++) b.v.push_back({binds[i].name ? binds[i].name : "", binds[i].value});
+    return b;
+}
+
+CodegenOpts opts_from(const int* o, unsigned flags) {
+    CodegenOpts c;
+    if (o) { c.block_threads = o[0]; c.reduce_lanes = o[1]; c.vector_width = o[2]; c.split = o[3]; c.debug_bounds = o[4] != 0; }
+    if (flags & ANL_OPEN_DEBUG_BOUNDS) c.debug_bounds = true;
+    return c;
+}
+
+}  // namespace
+
+struct anl_graph {
+    anl_device* dev = nullptr;
+    std::vector<Item> items;
+    Table table;
+    bool built = false;
+    int64_t built_sym = -2;
+    cudaGraphExec_t exec = nullptr;
+    std::vector<std::pair<uint32_t, anl_buffer*>> resident_in, resident_out;
+};
+
+extern "C" {
+
+int anl_open(int ordinal, unsigned flags, anl_device** out) {
+    if (!out) return ANL_ERR_INVALID;
+    *out = nullptr;
+    int count = 0;
+    if (cudaGetDeviceCount(&count) != cudaSuccess || ordinal < 0 || ordinal >= count) return ANL_ERR_NO_DEVICE;
+    auto* d = new anl_device();
+    d->ordinal = ordinal; d->flags = flags;
+    if (cudaSetDevice(ordinal) != cudaSuccess || cudaFree(0) != cudaSuccess || cudaGetDeviceProperties(&d->prop, ordinal) != cudaSuccess) { delete d; return ANL_ERR_NO_DEVICE; }
+    if (d->prop.major < 10) { delete d; return ANL_ERR_NO_DEVICE; }   // kernels are built for sm_100a only
+    if (cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking) != cudaSuccess) { delete d; return ANL_ERR_CUDA; }
+    cudaStreamCreateWithFlags(&d->comm_stream, cudaStreamNonBlocking);
+    cudaEventCreateWithFlags(&d->comm_event, cudaEventDisableTiming);
+    cudaEventCreateWithFlags(&d->comm_done, cudaEventDisableTiming);
+    if (ensure_driver(d) != ANL_OK) { delete d; return ANL_ERR_CUDA; }
+    *out = d;
+    return ANL_OK;
+}
+
+void anl_close(anl_device* dev) {
+    if (!dev) return;
+    cudaSetDevice(dev->ordinal);
+    cudaStreamSynchronize(dev->stream);
+    anl_comm_destroy(dev);
+    for (auto& kv : dev->modules) if (kv.second->mod && dev->drv.ModuleUnload) dev->drv.ModuleUnload(kv.second->mod);
+    dev->trim();
+    for (auto& kv : dev->live) cudaFree(kv.first);
+    if (dev->comm_event) cudaEventDestroy(dev->comm_event);
+    if (dev->comm_done) cudaEventDestroy(dev->comm_done);
+    if (dev->comm_stream) cudaStreamDestroy(dev->comm_stream);
+    if (dev->stream) cudaStreamDestroy(dev->stream);
+    delete dev;
+}
+
+int anl_device_info(anl_device* dev, anl_info* info) {
+    if (!dev || !info) return ANL_ERR_INVALID;
+    std::memset(info, 0, sizeof *info);
+    std::snprintf(info->name, sizeof info->name, "%s", dev->prop.name);
+    info->sm_major = dev->prop.major; info->sm_minor = dev->prop.minor; info->sm_count = dev->prop.multiProcessorCount;
+    info->total_mem = dev->prop.totalGlobalMem;
+    info->has_f16 = 1; info->has_bf16 = 1; info->has_tcgen05 = dev->prop.major == 10;
+    return ANL_OK;
+}
+
+const char* anl_last_error(anl_device* dev) { return dev ? dev->err.c_str() : "no device"; }
+
+int anl_get_stats(anl_device* dev, anl_stats* out) { if (!dev || !out) return ANL_ERR_INVALID; *out = dev->stats; return ANL_OK; }
+
+int anl_synchronize(anl_device* dev) {
+    if (!dev) return ANL_ERR_INVALID;
+    CK(dev, cudaStreamSynchronize(dev->stream));
+    if (dev->comm_stream) CK(dev, cudaStreamSynchronize(dev->comm_stream));
+    return ANL_OK;
+}
+
+int anl_run(anl_device* dev, const uint8_t* blob, size_t blob_len, const anl_input* inputs, int n_inputs,
+            const anl_binding* binds, int n_binds, const anl_output* placed, int n_placed, anl_output* outs, int* n_outs) {
+    if (!dev || !n_outs) return ANL_ERR_INVALID;
+    cudaSetDevice(dev->ordinal);
+    std::vector<Item> items; std::string perr;
+    if (!parse_kir(blob, blob_len, items, perr)) return dev->fail(ANL_ERR_INVALID, perr);
+    if (items.empty()) { *n_outs = 0; return ANL_OK; }     // empty schedule → (nil, nil), backend/webgpu/executor.go:27-29
+    for (auto& it : items) if (it.bufs.empty()) return dev->fail(ANL_ERR_INVALID, "run: item without buffers");
+    Bindings b = make_bindings(binds, n_binds);
+    Table t;
+    int rc = build_table(dev, items, b, inputs, n_inputs, placed, n_placed, t);
+    if (rc == ANL_OK) rc = run_items(dev, items, b, t, dev->stream);
+    if (rc == ANL_OK) rc = collect_outputs(dev, t, placed, n_placed, outs, n_outs, dev->stream);
+    else { cudaStreamSynchronize(dev->stream); *n_outs = 0; }
+    for (void* p : t.owned) dev->release(p);
+    return rc;
+}
+
+void anl_outputs_free(anl_output* outs, int n_outs) {
+    if (!outs) return;
+    for (int i = 0; i < n_outs; i++) { if (!outs[i].resident && outs[i].data) std::free(outs[i].data); outs[i].data = nullptr; }
+}
+
+int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o,
+              char* src, size_t src_cap, size_t* src_len, int* klass, int* block, int64_t* opb, char* note, size_t note_cap) {
+    std::vector<Item> items; std::string err;
+    if (!parse_kir(blob, blob_len, items, err)) { if (dev) dev->err = err; return ANL_ERR_INVALID; }
+    if (index < 0 || index >= (int)items.size()) return ANL_ERR_INVALID;
+    Rendered r;
+    if (!render_cuda(items[index], opts_from(o, dev ? dev->flags : 0), r, err)) {
+        if (dev) dev->err = err;
+        if (note && note_cap) std::snprintf(note, note_cap, "%s", err.c_str());
+        return ANL_ERR_UNSUPPORTED;
+    }
+    if (src && src_cap) { size_t n = std::min(src_cap - 1, r.source.size()); std::memcpy(src, r.source.data(), n); src[n] = 0; }
+    if (src_len) *src_len = r.source.size();
+    if (klass) *klass = r.klass;
+    if (block) *block = (int)r.main.block;
+    if (opb) *opb = r.main.outputs_per_block;
+    if (note && note_cap) std::snprintf(note, note_cap, "%s", r.note.c_str());
+    return ANL_OK;
+}
+
+int anl_compile_check(const char* src, char* log, size_t log_cap) {
+    std::vector<char> cubin; std::string l;
+    int rc = nvrtc_compile(src ? src : "", cubin, l);
+    if (log && log_cap) std::snprintf(log, log_cap, "%s", l.c_str());
+    return rc;
+}
+
+// Benchmarker.Benchmark (backend/webgpu/benchmark.go:18-208): the reference times submit+wait with
+// the host clock and reports min/median/max/mean/stddev/CV; here each iteration is bracketed by CUDA
+// events on the launching stream.  Inputs are zero-filled device buffers, as the reference's are.
+int anl_benchmark(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o, int warmup, int iterations, anl_bench_result* out) {
+    if (!dev || !out || iterations <= 0) return ANL_ERR_INVALID;
+    cudaSetDevice(dev->ordinal);
+    std::vector<Item> items; std::string perr;
+    if (!parse_kir(blob, blob_len, items, perr)) return dev->fail(ANL_ERR_INVALID, perr);
+    if (index < 0 || index >= (int)items.size()) return dev->fail(ANL_ERR_INVALID, "benchmark: item index out of range");
+    const Item& it = items[index];
+    for (auto& b : it.bufs) if (b.symbolic()) return dev->fail(ANL_ERR_UNSUPPORTED, "benchmark: symbolic kernels are not timed");
+    std::shared_ptr<Plan> plan;
+    if (int rc = get_plan(dev, it, opts_from(o, dev->flags), plan)) return rc;
+    std::vector<void*> ptrs;
+    int rc = ANL_OK;
+    for (auto& b : it.bufs) {
+        void* p = nullptr; size_t by = (size_t)b.elems(0) * dt_storage_bytes(b.dtype);
+        if ((rc = dev->alloc(by, &p))) break;
+        cudaMemsetAsync(p, 0, by ? by : 4, dev->stream);
+        ptrs.push_back(p);
+    }
+    std::vector<double> us;
+    if (rc == ANL_OK) {
+        cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
+        for (int i = 0; i < warmup + iterations && rc == ANL_OK; i++) {
+            cudaEventRecord(e0, dev->stream);
+            rc = launch_plan(dev, *plan, it, ptrs.data(), 0, dev->stream, nullptr);
+            cudaEventRecord(e1, dev->stream);
+            if (cudaEventSynchronize(e1) != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, "benchmark: kernel failed");
+            float ms = 0; cudaEventElapsedTime(&ms, e0, e1);
+            if (i >= warmup) us.push_back(ms * 1000.0);
+        }
+        cudaEventDestroy(e0); cudaEventDestroy(e1);
+    }
+    for (void* p : ptrs) dev->release(p);
+    if (rc != ANL_OK) return rc;
+    std::sort(us.begin(), us.end());
+    double sum = 0; for (double v : us) sum += v;
+    double mean = sum / us.size(), var = 0;
+    for (double v : us) var += (v - mean) * (v - mean);
+    out->min_us = us.front(); out->max_us = us.back(); out->median_us = us[us.size() / 2];
+    out->mean_us = mean; out->stddev_us = std::sqrt(var / us.size()); out->cv = mean > 0 ? out->stddev_us / mean : 0;
+    return ANL_OK;
+}
+
+int anl_buffer_create(anl_device* dev, int dtype, int64_t elems, anl_buffer** out) {
+    if (!dev || !out || elems < 0) return ANL_ERR_INVALID;
+    cudaSetDevice(dev->ordinal);
+    auto* b = new anl_buffer();
+    b->dev = dev; b->dtype = dtype; b->elems = elems; b->bytes = (size_t)elems * dt_storage_bytes(dtype);
+    if (int rc = dev->alloc(b->bytes, &b->ptr)) { delete b; return rc; }
+    cudaMemsetAsync(b->ptr, 0, b->bytes ? b->bytes : 4, dev->stream);
+    *out = b;
+    return ANL_OK;
+}
+int anl_buffer_upload(anl_buffer* buf, const float* data, int64_t elems) {
+    if (!buf || !data || elems > buf->elems) return ANL_ERR_INVALID;
+    cudaSetDevice(buf->dev->ordinal);
+    if (int rc = upload_f32(buf->dev, buf->ptr, buf->dtype, data, elems, buf->dev->stream)) return rc;
+    CK(buf->dev, cudaStreamSynchronize(buf->dev->stream));
+    return ANL_OK;
+}
+int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems) {
+    if (!buf || !data || elems > buf->elems) return ANL_ERR_INVALID;
+    cudaSetDevice(buf->dev->ordinal);
+    if (int rc = download_f32(buf->dev, data, buf->ptr, buf->dtype, elems, buf->dev->stream)) return rc;
+    CK(buf->dev, cudaStreamSynchronize(buf->dev->stream));
+    return ANL_OK;
+}
+void anl_buffer_release(anl_buffer* buf) { if (!buf) return; cudaStreamSynchronize(buf->dev->stream); buf->dev->release(buf->ptr); delete buf; }
+void* anl_buffer_device_ptr(anl_buffer* buf) { return buf ? buf->ptr : nullptr; }
+int64_t anl_buffer_elems(anl_buffer* buf) { return buf ? buf->elems : 0; }
+
+int anl_sgd_step(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale) {
+    if (!dev || !master || !param || !grad) return ANL_ERR_INVALID;
+    if (master->dtype != ANL_F32) return dev->fail(ANL_ERR_INVALID, "sgd: master weights must be f32");
+    if (grad->elems < master->elems || param->elems < master->elems) return dev->fail(ANL_ERR_INVALID, "sgd: gradient length != parameter length");
+    cudaSetDevice(dev->ordinal);
+    long long n = master->elems;
+    unsigned g = grid_for(n, 256, dev->prop.multiProcessorCount);
+    float* m = (float*)master->ptr;
+    bool gh = grad->dtype == ANL_F16, ph = param->dtype == ANL_F16;
+    int bf = param->dtype == ANL_BF16;
+    if (gh && ph) sgd_kernel<__half, __half><<<g, 256, 0, dev->stream>>>(m, (__half*)param->ptr, (const __half*)grad->ptr, lr, scale, n, 0);
+    else if (gh) sgd_kernel<__half, float><<<g, 256, 0, dev->stream>>>(m, (float*)param->ptr, (const __half*)grad->ptr, lr, scale, n, bf);
+    else if (ph) sgd_kernel<float, __half><<<g, 256, 0, dev->stream>>>(m, (__half*)param->ptr, (const float*)grad->ptr, lr, scale, n, 0);
+    else sgd_kernel<float, float><<<g, 256, 0, dev->stream>>>(m, (float*)param->ptr, (const float*)grad->ptr, lr, scale, n, bf);
+    dev->stats.kernels_launched++;
+    CK(dev, cudaGetLastError());
+    return ANL_OK;
+}
+
+int anl_host_alloc(size_t bytes, void** out) { return cudaMallocHost(out, bytes ? bytes : 4) == cudaSuccess ? ANL_OK : ANL_ERR_CUDA; }
+void anl_host_free(void* p) { if (p) cudaFreeHost(p); }
+
+// ── JIT replay through a CUDA graph ──────────────────────────────────────────────────────────
+int anl_graph_create(anl_device* dev, const uint8_t* blob, size_t blob_len, anl_graph** out) {
+    if (!dev || !out) return ANL_ERR_INVALID;
+    auto* g = new anl_graph();
+    g->dev = dev;
+    std::string perr;
+    if (!parse_kir(blob, blob_len, g->items, perr)) { delete g; return dev->fail(ANL_ERR_INVALID, perr); }
+    for (auto& it : g->items) if (it.bufs.empty()) { delete g; return dev->fail(ANL_ERR_INVALID, "graph: item without buffers"); }
+    *out = g;
+    return ANL_OK;
+}
+
+static void graph_drop(anl_graph* g) {
+    if (g->exec) { cudaGraphExecDestroy(g->exec); g->exec = nullptr; }
+    for (void* p : g->table.owned) g->dev->release(p);
+    g->table = Table();
+    g->built = false;
+}
+
+int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs, const anl_binding* binds, int n_binds,
+                     const anl_output* placed, int n_placed, anl_output* outs, int* n_outs) {
+    if (!g || !n_outs) return ANL_ERR_INVALID;
+    anl_device* dev = g->dev;
+    cudaSetDevice(dev->ordinal);
+    if (g->items.empty()) { *n_outs = 0; return ANL_OK; }
+    Bindings b = make_bindings(binds, n_binds);
+    int64_t sym = b.any();
+    // resident placements are baked into the captured pointers: any change rebuilds
+    std::vector<std::pair<uint32_t, anl_buffer*>> rin, rout;
+    for (int k = 0; k < n_inputs; k++) if (inputs[k].resident) rin.push_back({inputs[k].uop_idx, inputs[k].resident});
+    for (int k = 0; k < n_placed; k++) if (placed[k].resident) rout.push_back({placed[k].uop_idx, placed[k].resident});
+    if (g->built && (sym != g->built_sym || rin != g->resident_in || rout != g->resident_out)) graph_drop(g);
+    int rc = ANL_OK;
+    if (!g->built) {
+        // first call for this binding: allocate persistent buffers (uploading the inputs as a side
+        // effect), compile every kernel eagerly, then capture the launches
+        rc = build_table(dev, g->items, b, inputs, n_inputs, placed, n_placed, g->table);
+        CodegenOpts opts; opts.debug_bounds = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;
+        for (size_t i = 0; i < g->items.size() && rc == ANL_OK; i++) { std::shared_ptr<Plan> p; rc = get_plan(dev, g->items[i], opts, p); }
+        if (rc == ANL_OK) {
+            cudaGraph_t graph = nullptr;
+            cudaError_t e = cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeRelaxed);
+            if (e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("graph: begin capture: ") + cudaGetErrorString(e));
+            if (rc == ANL_OK) {
+                int rrc = run_items(dev, g->items, b, g->table, dev->stream, true);   // scratch stays with the graph
+                e = cudaStreamEndCapture(dev->stream, &graph);
+                if (rrc != ANL_OK) rc = rrc;
+                else if (e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("graph: end capture: ") + cudaGetErrorString(e));
+            }
+            if (rc == ANL_OK) {
+                e = cudaGraphInstantiate(&g->exec, graph, 0);
+                if (e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("graph: instantiate: ") + cudaGetErrorString(e));
+            }
+            if (graph) cudaGraphDestroy(graph);
+        }
+        if (rc != ANL_OK) { graph_drop(g); *n_outs = 0; return rc; }
+        g->built = true; g->built_sym = sym; g->resident_in = rin; g->resident_out = rout;
+        dev->stats.graph_captures++;
+    } else {
+        // replay: refresh host-fed leaves in place
+        for (int k = 0; k < n_inputs && rc == ANL_OK; k++) {
+            if (inputs[k].resident || !inputs[k].data) continue;
+            auto f = g->table.bufs.find(inputs[k].uop_idx);
+            if (f == g->table.bufs.end() || g->table.written.count(inputs[k].uop_idx)) continue;
+            if (inputs[k].elems < f->second.elems) { rc = dev->fail(ANL_ERR_INVALID, "graph: input smaller than captured buffer"); break; }
+            rc = upload_f32(dev, f->second.ptr, f->second.dtype, inputs[k].data, f->second.elems, dev->stream);
+        }
+        if (rc != ANL_OK) { *n_outs = 0; return rc; }
+    }
+    cudaError_t e = cudaGraphLaunch(g->exec, dev->stream);
+    if (e != cudaSuccess) { *n_outs = 0; return dev->fail(ANL_ERR_CUDA, std::string("graph: launch: ") + cudaGetErrorString(e)); }
+    dev->stats.graph_replays++;
+    return collect_outputs(dev, g->table, placed, n_placed, outs, n_outs, dev->stream);
+}
+
+void anl_graph_release(anl_graph* g) {
+    if (!g) return;
+    cudaStreamSynchronize(g->dev->stream);
+    graph_drop(g);
+    delete g;
+}
+
+}  // extern "C"

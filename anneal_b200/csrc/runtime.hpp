@@ -1,0 +1,97 @@
+// Device runtime behind the C ABI: context, stream, buffer pool, NVRTC module cache, schedule
+// execution.  Replaces backend/webgpu/{open,executor,benchmark}.go of the reference.
+#pragma once
+#include <cuda.h>
+#include <cuda_runtime.h>
+
+#include <cstdint>
+#include <map>
+#include <memory>
+#include <string>
+#include <unordered_map>
+#include <vector>
+
+#include "../../include/anneal_cuda.h"
+#include "codegen.hpp"
+#include "kir.hpp"
+
+namespace anl {
+
+struct DriverApi {
+    CUresult (*ModuleLoadData)(CUmodule*, const void*) = nullptr;
+    CUresult (*ModuleUnload)(CUmodule) = nullptr;
+    CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
+    CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
+    CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                     const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                     CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
+    bool loaded = false;
+};
+
+struct Module {
+    CUmodule mod = nullptr;
+    std::unordered_map<std::string, CUfunction> fn;
+};
+
+// One item ready to launch: rendered source, compiled entry points, or a GEMM route.
+struct GemmPlan;
+struct Plan {
+    Rendered r;
+    CUfunction main = nullptr, finish = nullptr;
+    std::shared_ptr<GemmPlan> gemm;
+};
+
+}  // namespace anl
+
+struct anl_buffer {
+    anl_device* dev = nullptr;
+    int dtype = ANL_F32;
+    int64_t elems = 0;
+    void* ptr = nullptr;
+    size_t bytes = 0;
+};
+
+struct anl_device {
+    int ordinal = 0;
+    unsigned flags = 0;
+    cudaStream_t stream = nullptr;
+    cudaStream_t comm_stream = nullptr;
+    cudaEvent_t comm_event = nullptr, comm_done = nullptr;
+    std::string err;
+    cudaDeviceProp prop{};
+    anl::DriverApi drv;
+    std::unordered_map<uint64_t, std::shared_ptr<anl::Plan>> plans;   // structure hash ^ opts → plan
+    std::unordered_map<uint64_t, std::shared_ptr<anl::Module>> modules;  // source hash → module
+    std::multimap<size_t, void*> pool;                                // free device blocks by size
+    std::unordered_map<void*, size_t> live;                           // blocks handed out
+    anl_stats stats{};
+    void* nccl_comm = nullptr;
+    int rank = 0, nranks = 1;
+
+    int fail(int code, const std::string& m) { err = m; return code; }
+    int alloc(size_t bytes, void** out);
+    void release(void* p);
+    void trim();
+};
+
+namespace anl {
+
+int ensure_driver(anl_device* dev);
+int compile_source(anl_device* dev, const std::string& src, std::shared_ptr<Module>& out);
+int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::shared_ptr<Plan>& out);
+// keep_scratch: when not null, scratch blocks a launch needs are appended there (the caller releases
+// them) instead of going back to the pool at once
+int launch_plan(anl_device* dev, const Plan& plan, const Item& item, void* const* bufs, int64_t sym_value, cudaStream_t stream,
+                std::vector<void*>* keep_scratch);
+
+// dtype conversion at the boundary (backend/webgpu/executor.go:161-179, 457-519)
+int upload_f32(anl_device* dev, void* dst, int dtype, const float* host, int64_t elems, cudaStream_t s);
+int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64_t elems, cudaStream_t s);
+
+// hand-written contraction kernels (gemm.cu); returns ANL_OK and fills plan.gemm if the item is a
+// dense SUM-of-products over buffers that they cover, ANL_ERR_UNSUPPORTED otherwise
+int plan_gemm(anl_device* dev, const Item& item, Plan& plan);
+int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream);
+
+}  // namespace anl

@@ -1,0 +1,166 @@
+/*
+ * anneal_cuda.h — C ABI of the B200 device backend for anneal.
+ *
+ * This is what a Go `backend/cuda` package binds (through cgo or a dlopen-style FFI) to provide
+ * anneal's device interfaces, backend/device.go:10-37:
+ *
+ *     Executor.Run / Close, SymbolicExecutor.RunSymbolic, Benchmarker.Benchmark
+ *
+ * plus the optional residency, optimiser and data-parallel calls that a CUDA device needs to keep
+ * parameters on the GPU between steps.  Every function returns 0 on success and a non-zero
+ * anl_status otherwise; none throws, aborts or allocates on behalf of the caller except where
+ * stated.  After a failure anl_last_error(dev) describes it.  A schedule crosses the boundary as one
+ * kernel-IR blob: the serialised []schedule.ExecItem (schedule/exec.go:6-32); its byte layout is
+ * documented in anneal_b200/kir.py.
+ *
+ * Threading: calls on one anl_device must not overlap (the reference funnels every device call
+ * through one owner goroutine, backend/webgpu/open.go:63-82); different devices are independent.
+ */
+#ifndef ANNEAL_CUDA_H
+#define ANNEAL_CUDA_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct anl_device anl_device;
+typedef struct anl_buffer anl_buffer;
+typedef struct anl_graph anl_graph;
+
+typedef enum {
+    ANL_OK = 0,
+    ANL_ERR_INVALID = 1,      /* malformed blob or argument */
+    ANL_ERR_CUDA = 2,         /* a CUDA runtime / driver call failed */
+    ANL_ERR_COMPILE = 3,      /* NVRTC rejected generated or supplied source */
+    ANL_ERR_UNSUPPORTED = 4,  /* valid request this backend cannot serve */
+    ANL_ERR_NO_DEVICE = 5,    /* no usable GPU, or the GPU lacks a required feature */
+    ANL_ERR_COMM = 6,         /* NCCL failure or timeout */
+    ANL_ERR_LIMIT = 7         /* a stated size limit was exceeded */
+} anl_status;
+
+/* storage dtypes, numbered as the kernel-IR numbers them */
+enum { ANL_BOOL = 1, ANL_I32 = 6, ANL_U32 = 7, ANL_F16 = 10, ANL_BF16 = 11, ANL_F32 = 12 };
+
+typedef struct {
+    char name[128];
+    int sm_major, sm_minor, sm_count;
+    size_t total_mem;
+    int has_f16, has_bf16, has_tcgen05;
+} anl_info;
+
+/* A leaf input of a schedule.  Values travel as float32 whatever the storage dtype and are
+ * quantised on upload (backend/webgpu/executor.go:161-179); `resident`, when not NULL, names a
+ * device buffer that already holds the data and `data` is ignored. */
+typedef struct {
+    uint32_t uop_idx;
+    const float* data;
+    int64_t elems;
+    anl_buffer* resident;
+} anl_input;
+
+typedef struct { const char* name; int64_t value; } anl_binding;
+
+/* A final output.  In `outs` (filled by the library): `data` is a float32 array of `elems` values
+ * that the library allocated, released with anl_outputs_free, unless the output was placed.  In
+ * `placed` (filled by the caller): where one output should go instead: `resident` keeps it on the
+ * device in that buffer (nothing is copied back), `data` names a caller-owned host array with room
+ * for `elems` values (for instance pinned memory). */
+typedef struct {
+    uint32_t uop_idx;
+    float* data;
+    int64_t elems;
+    anl_buffer* resident;
+} anl_output;
+
+/* Benchmarker result: backend/device.go:30-37 BenchmarkResult, microseconds. */
+typedef struct { double min_us, median_us, max_us, mean_us, stddev_us, cv; } anl_bench_result;
+
+/* counters since open: the CUDA-side extension of schedule.CompilerStats (schedule/stats.go:3-18) */
+typedef struct {
+    uint64_t kernels_launched, gemm_launched, nvrtc_compiles, nvrtc_cache_hits, lower_cache_hits;
+    uint64_t h2d_bytes, d2h_bytes, graph_replays, graph_captures, device_allocs;
+} anl_stats;
+
+/* ── lifecycle: webgpu.Open / Device.Close / AdapterName / HasShaderF16 (backend/webgpu/open.go:89-175) ── */
+int anl_open(int ordinal, unsigned flags, anl_device** out);
+void anl_close(anl_device* dev);
+int anl_device_info(anl_device* dev, anl_info* info);
+const char* anl_last_error(anl_device* dev);
+int anl_get_stats(anl_device* dev, anl_stats* out);
+/* flags for anl_open */
+#define ANL_OPEN_DEBUG_BOUNDS 1u   /* clamp and check every generated load */
+#define ANL_OPEN_NO_GEMM 2u        /* never route contractions to the tensor-core kernels */
+
+/* ── Executor.Run / SymbolicExecutor.RunSymbolic (backend/device.go:10-28; backend/webgpu/executor.go:26-240, 576-810) ──
+ * Runs the items of `blob` in order.  `outs` has room for `*n_outs` entries on entry; on return
+ * `*n_outs` is the number of final outputs (buffers no later item reads) and the first entries of
+ * `outs` describe them.  Inputs with unknown ids are ignored; an empty schedule returns 0 outputs.
+ * `binds` gives the value of each symbolic variable; pass n_binds = 0 for a static schedule.
+ * `placed` (may be NULL) redirects chosen outputs, see anl_output. */
+int anl_run(anl_device* dev, const uint8_t* blob, size_t blob_len,
+            const anl_input* inputs, int n_inputs,
+            const anl_binding* binds, int n_binds,
+            const anl_output* placed, int n_placed,
+            anl_output* outs, int* n_outs);
+void anl_outputs_free(anl_output* outs, int n_outs);
+
+/* ── codegen.Lower + RenderWGSL (codegen/lower.go:98-105, codegen/wgsl.go:36-39), CUDA flavour ──
+ * Renders item `index` of the blob to CUDA C without touching the GPU.  `opts` is 5 ints:
+ * {block_threads, reduce_lanes, vector_width, split, debug_bounds}; 0 means "choose".  The
+ * source is copied to `src` (capacity src_cap, always NUL-terminated) and its full length is
+ * returned in *src_len; `klass`, `block`, `outputs_per_block` describe the launch. */
+int anl_lower(anl_device* dev_or_null, const uint8_t* blob, size_t blob_len, int index, const int* opts,
+              char* src, size_t src_cap, size_t* src_len, int* klass, int* block, int64_t* outputs_per_block,
+              char* note, size_t note_cap);
+
+/* NVRTC-compiles CUDA C for sm_100a; needs no GPU.  Returns ANL_ERR_COMPILE with the log in `log`. */
+int anl_compile_check(const char* src, char* log, size_t log_cap);
+
+/* ── Benchmarker.Benchmark (backend/webgpu/benchmark.go:18-208): CUDA-event timing of one item ── */
+int anl_benchmark(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* opts,
+                  int warmup, int iterations, anl_bench_result* out);
+
+/* ── JIT replay (tensor/jit.go:179-246): a schedule frozen into a CUDA graph ──
+ * anl_graph_create runs nothing; the first anl_graph_replay instantiates buffers, compiles the
+ * kernels and captures them on the device stream; later replays with the same bindings relaunch
+ * the captured graph.  Inputs and outputs follow anl_run. */
+int anl_graph_create(anl_device* dev, const uint8_t* blob, size_t blob_len, anl_graph** out);
+int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs,
+                     const anl_binding* binds, int n_binds,
+                     const anl_output* placed, int n_placed, anl_output* outs, int* n_outs);
+void anl_graph_release(anl_graph* g);
+
+/* ── resident buffers: Parameter.Load / Value without the per-step round trip (tensor/nn/nn.go:56-61) ── */
+int anl_buffer_create(anl_device* dev, int dtype, int64_t elems, anl_buffer** out);
+int anl_buffer_upload(anl_buffer* buf, const float* data, int64_t elems);
+int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems);
+void anl_buffer_release(anl_buffer* buf);
+void* anl_buffer_device_ptr(anl_buffer* buf);
+int64_t anl_buffer_elems(anl_buffer* buf);
+
+/* ── Parameter.SGDStep / SGD.Step on the device (tensor/nn/nn.go:69-76, 98-106) ──
+ * master[i] -= lr * grad[i] * grad_scale in f32 (master is an F32 buffer), then param[i] =
+ * quantise(master[i]) into `param` (F16/BF16/F32 storage; may equal master). */
+int anl_sgd_step(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float grad_scale);
+
+/* ── data parallelism (no counterpart in the reference, which is single-device: README.md:109-111) ──
+ * One process per GPU.  Rank 0 obtains an id, every rank passes the same 128 bytes to init. */
+int anl_comm_unique_id(uint8_t id[128]);
+int anl_comm_init(anl_device* dev, int rank, int nranks, const uint8_t id[128]);
+int anl_allreduce_sum(anl_device* dev, anl_buffer* buf);     /* in place, on the comm stream, ordered after prior work */
+int anl_comm_destroy(anl_device* dev);
+
+/* host staging memory that the GPU can copy from directly */
+int anl_host_alloc(size_t bytes, void** out);
+void anl_host_free(void* p);
+
+/* blocks until all work queued on the device has finished */
+int anl_synchronize(anl_device* dev);
+
+#ifdef __cplusplus
+}
+#endif
+#endif
