@@ -1102,6 +1102,56 @@ struct Gen {
 
 }  // namespace
 
+bool match_contraction(const Item& item, Contraction& c) {
+    CodegenOpts o;
+    Gen g(item, o);
+    if (!g.analyse() || g.has_sym) return false;
+    if (g.reduces.size() != 1 || g.reduces[0] != g.body) return false;
+    const Node& red = g.N(g.body);
+    if ((int)red.aux != OP_ADD) return false;
+    std::vector<int> rr;
+    for (size_t s = 1; s < red.src.size(); s++) if (g.N(red.src[s]).op == OP_RANGE) rr.push_back(red.src[s]);
+    if (rr.size() != 1) return false;
+    int k = rr[0];
+    const Node& mul = g.N(red.src[0]);
+    if (mul.op != OP_MUL || mul.src.size() != 2) return false;
+    int ia = mul.src[0], ib = mul.src[1];
+    if (g.N(ia).op != OP_INDEX || g.N(ib).op != OP_INDEX) return false;
+    if (g.loop_ranges.empty() || g.loop_ranges.size() > 3) return false;
+    // output = [..m ranges.., n]: n is the innermost loop range read by exactly one operand
+    int pa = (int)g.N(g.N(ia).src[0]).arg, pb = (int)g.N(g.N(ib).src[0]).arg;
+    if (g.N(g.N(ia).src[0]).op != OP_PARAM || g.N(g.N(ib).src[0]).op != OP_PARAM) return false;
+    Lin fa = g.flat_index(ia), fb = g.flat_index(ib);
+    if (!g.in_bounds(fa, pa) || !g.in_bounds(fb, pb)) return false;
+    auto only_ranges = [&](const Lin& l) { for (auto& t : l.t) if (g.atoms[t.first].kind != Atom::RANGE) return false; return true; };
+    if (!only_ranges(fa) || !only_ranges(fb)) return false;
+    auto coef = [&](const Lin& l, int r) { bool ok; return g.lin_coef(l, r, ok); };
+    // decide which operand carries n (the innermost output range)
+    int n_range = g.loop_ranges.back();
+    if (coef(fa, n_range) != 0 && coef(fb, n_range) == 0) { std::swap(ia, ib); std::swap(pa, pb); std::swap(fa, fb); }
+    if (coef(fa, n_range) != 0 || coef(fb, n_range) == 0) return false;
+    // remaining output ranges form M; they must index only A, with nested strides
+    int64_t M = 1, a_sm = 0;
+    for (int i = (int)g.loop_ranges.size() - 2; i >= 0; i--) {
+        int r = g.loop_ranges[i];
+        if (coef(fb, r) != 0) return false;
+        int64_t ca = coef(fa, r);
+        if (M == 1) a_sm = ca;
+        else if (ca != a_sm * M) return false;
+        M *= g.N(r).arg;
+    }
+    if (g.loop_ranges.size() == 1) { M = 1; a_sm = 0; }
+    c.a_param = pa; c.b_param = pb;
+    c.M = M; c.N = g.N(n_range).arg; c.K = g.N(k).arg;
+    c.a_sm = a_sm; c.a_sk = coef(fa, k); c.a_off = fa.c;
+    c.b_sn = coef(fb, n_range); c.b_sk = coef(fb, k); c.b_off = fb.c;
+    if (c.a_sk == 0 || c.b_sk == 0 || c.b_sn == 0 || (M > 1 && a_sm == 0)) return false;
+    c.in_dtype = item.bufs[pa].dtype;
+    if (item.bufs[pb].dtype != c.in_dtype) return false;
+    c.out_dtype = item.bufs[0].dtype;
+    return true;
+}
+
 bool render_cuda(const Item& item, const CodegenOpts& opts, Rendered& out, std::string& err) {
     Gen g(item, opts);
     bool ok = g.run(out);

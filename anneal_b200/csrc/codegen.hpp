@@ -53,6 +53,21 @@ struct Rendered {
 
 bool render_cuda(const Item& item, const CodegenOpts& opts, Rendered& out, std::string& err);
 
+// A kernel whose body is exactly SUM_k a[..] * b[..] over two buffers with affine indices:
+//   out[m, n] = sum_k A[a_off + m*a_sm + k*a_sk] * B[b_off + n*b_sn + k*b_sk],  out row-major [M, N].
+// This is the pattern Tensor.Matmul, nn.Linear and their gradients schedule to
+// (tensor/reduce.go:105-166, tensor/nn/nn.go:154-162, tensor/gradient_ruleset.go:137-140, 207-233).
+struct Contraction {
+    int a_param = 0, b_param = 0;
+    int64_t M = 0, N = 0, K = 0;
+    int64_t a_sm = 0, a_sk = 0, a_off = 0;
+    int64_t b_sn = 0, b_sk = 0, b_off = 0;
+    int in_dtype = DT_F32, out_dtype = DT_F32;
+};
+// Contraction selection (the schedule/kernels.go hook the CUDA device adds): true when `item`
+// is such a kernel.  Leading output ranges are folded into M when they are contiguous with it.
+bool match_contraction(const Item& item, Contraction& out);
+
 // Hash of everything that determines the rendered source (node table, buffer dtypes and
 // shapes) and nothing that does not (buffer ids, slots).
 uint64_t structure_hash(const Item& item);

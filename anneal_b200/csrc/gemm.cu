@@ -1,6 +1,343 @@
+// Dense contractions on the 5th-generation tensor cores: D[M,N] = sum_k A[m,k] * B[n,k], f16
+// operands, f32 accumulation in tensor memory, one rounding to f16 at the store — the arithmetic
+// the reference specifies for an f16 REDUCE (f32 accumulator, operands widened, narrowed once:
+// codegen/lower.go:654-719), reached through tcgen05.mma instead of its one-thread-per-output loop.
+//
+// One persistent CTA per SM, warp-specialised:
+//   warp 0      TMA producer: cp.async.bulk.tensor loads of the A and B k-blocks into a 4-stage
+//               shared-memory ring (128-byte swizzle), completion on an mbarrier per stage;
+//   warp 1      MMA issuer: one lane issues tcgen05.mma (M=128, N=256, K=16) four times per stage
+//               and commits to the stage's "empty" barrier; owns the TMEM allocation;
+//   warps 2-5   epilogue: tcgen05.ld the 128x256 f32 accumulator, convert, store.  Two accumulators
+//               (2 x 256 TMEM columns) let the epilogue of tile i overlap the main loop of tile i+1.
+// Either operand may be K-major (k contiguous) or MN-major (m / n contiguous): the forward pass
+// x·Wᵀ is K/K, the input gradient dY·W is K/MN, the weight gradient dYᵀ·X is MN/MN.  No operand
+// is transposed in memory; the layout goes into the shared-memory and instruction descriptors.
+// No multicast is used anywhere: every CTA issues its own loads.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records a code in a host-visible
+// status word and the CTA drains and frees its tensor memory instead of spinning.
+#include <cuda_fp16.h>
+
+#include <cstring>
+
 #include "runtime.hpp"
+
 namespace anl {
-struct GemmPlan {};
-int plan_gemm(anl_device*, const Item&, Plan&) { return ANL_ERR_UNSUPPORTED; }
-int launch_gemm(anl_device* dev, const Plan&, void* const*, cudaStream_t) { return dev->fail(ANL_ERR_UNSUPPORTED, "gemm: not built"); }
+
+constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
+constexpr int A_TILE_BYTES = BM * BK * 2;          // 16 KiB
+constexpr int B_TILE_BYTES = BN * BK * 2;          // 32 KiB
+constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
+constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
+constexpr int GEMM_THREADS = 192;
+constexpr unsigned WAIT_LIMIT = 1u << 20;
+
+struct GemmPlan {
+    Contraction c;
+    bool a_mn = false, b_mn = false;     // MN-major operands
+    int64_t lda = 0, ldb = 0;            // elements between consecutive rows of the 2-D global views
+    int* status_host = nullptr;          // mapped, host-visible
+    int* status_dev = nullptr;
+};
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
 }
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+// Bounded wait: false when the phase did not complete within WAIT_LIMIT polls, or when another
+// role of this CTA has already given up (`failed`, in shared memory).
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, const volatile int* failed = nullptr) {
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        if (failed && (i & 255u) == 255u && *failed) return false;
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(bar) : "memory");
+}
+
+// Shared-memory matrix descriptor for tcgen05.mma, 128-byte swizzle.
+//   bits [0,14) start address >> 4, [16,30) leading byte offset >> 4, [32,46) stride byte offset >> 4,
+//   [46,48) descriptor version 1, [61,64) layout type 2 (128-byte swizzle).
+__device__ __forceinline__ uint64_t make_desc(uint32_t saddr, uint32_t lbo_bytes, uint32_t sbo_bytes) {
+    uint64_t d = 0;
+    d |= (uint64_t)((saddr >> 4) & 0x3FFF);
+    d |= (uint64_t)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (uint64_t)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (uint64_t)1 << 46;
+    d |= (uint64_t)2 << 61;
+    return d;
+}
+
+__device__ __forceinline__ void umma_f16(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit(uint32_t bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
+struct GemmArgs {
+    __half* d;
+    int M, N, K, ldd;
+    int tiles_m, tiles_n;
+    int* status;
+};
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int failed;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1 KiB alignment
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int num_tiles = g.tiles_m * g.tiles_n;
+    const int kblocks = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 4); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // 512 columns: two 128x256 f32 accumulators
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ── producer ──
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            int issued = 0;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                const int m0 = (t % g.tiles_m) * BM, n0 = (t / g.tiles_m) * BN;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 1; break; }
+                    const uint32_t fb = smem_u32(&full_bar[stage]);
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_TILE_BYTES;
+                    mbar_expect_tx(fb, STAGE_BYTES);
+                    const int k0 = kb * BK;
+                    if (A_MN) { for (int j = 0; j < BM / 64; j++) tma_load_2d(sa + j * (BK * 128), &map_a, m0 + 64 * j, k0, fb); }
+                    else tma_load_2d(sa, &map_a, k0, m0, fb);
+                    if (B_MN) { for (int j = 0; j < BN / 64; j++) tma_load_2d(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
+                    else tma_load_2d(sb, &map_b, k0, n0, fb);
+                    issued++;
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) {
+                failed = 1;
+                // let copies already in flight land before the CTA goes away
+                int pending = issued < STAGES ? issued : STAGES;
+                for (int i = 0; i < pending; i++) { stage = stage == 0 ? STAGES - 1 : stage - 1; mbar_wait(smem_u32(&full_bar[stage]), 0); mbar_wait(smem_u32(&full_bar[stage]), 1); }
+            }
+        }
+    } else if (warp == 1) {
+        // ── MMA issuer ──
+        if (lane == 0) {
+            // instruction descriptor: f32 accumulate, f16 x f16, majors, N >> 3 at bit 17, M >> 4 at bit 24
+            const uint32_t idesc = (1u << 4) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+                if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 2; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 3; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_base + stage * STAGE_BYTES, sb = sa + A_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        // K-major: 16 k-elements = 32 bytes inside the 128-byte row, 8-row groups 1 KiB apart.
+                        // MN-major: 16 k-rows = two 1 KiB atoms, 64-wide m/n groups one box (BK*128 B) apart.
+                        const uint64_t ad = A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
+                        const uint64_t bd = B_MN ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+                        umma_f16(tmem_d, ad, bd, idesc, (kb | k) != 0);
+                    }
+                    umma_commit(smem_u32(&empty_bar[stage]));      // frees the stage when these MMAs retire
+                    if (++stage == STAGES) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                umma_commit(smem_u32(&acc_full[acc]));             // accumulator complete
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+            if (!ok) failed = 1;
+        }
+    } else {
+        // ── epilogue: warps 2..5, TMEM lane quadrant = warp % 4 ──
+        const int quad = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            const int m0 = (t % g.tiles_m) * BM, n0 = (t / g.tiles_m) * BN;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 4; failed = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quad * 32 + lane;
+            __half* drow = g.d + (size_t)row * g.ldd + n0;
+            const bool row_ok = row < g.M;
+            const bool vec_ok = (g.ldd % 8 == 0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col = n0 + c * 32;
+                if (!row_ok || col >= g.N) continue;
+                if (vec_ok && col + 32 <= g.N) {
+                    uint4* dst = reinterpret_cast<uint4*>(drow + c * 32);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        __half2 h0 = __floats2half2_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+                        __half2 h1 = __floats2half2_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+                        __half2 h2 = __floats2half2_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+                        __half2 h3 = __floats2half2_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+                        uint4 o;
+                        o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                        o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                        dst[q] = o;
+                    }
+                } else {
+                    for (int j = 0; j < 32 && col + j < g.N; j++) drow[c * 32 + j] = __float2half_rn(__uint_as_float(v[j]));
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&acc_empty[acc]));
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+static int encode_map(anl_device* dev, CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
+                      uint32_t box_inner, uint32_t box_outer) {
+    cuuint64_t dims[2] = {inner, outer};
+    cuuint64_t strides[1] = {row_stride_elems * 2};
+    cuuint32_t box[2] = {box_inner, box_outer};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = dev->drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                                               CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                               CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) { const char* s = nullptr; dev->drv.GetErrorString(r, &s); return dev->fail(ANL_ERR_CUDA, std::string("gemm: cuTensorMapEncodeTiled: ") + (s ? s : "?")); }
+    return ANL_OK;
+}
+
+int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
+    Contraction c;
+    if (!match_contraction(item, c)) return ANL_ERR_UNSUPPORTED;
+    if (c.in_dtype != DT_F16 || c.out_dtype != DT_F16) return ANL_ERR_UNSUPPORTED;
+    if (c.M < 64 || c.N < 64 || c.K < 32) return ANL_ERR_UNSUPPORTED;          // not worth a 128x256 tile
+    auto gp = std::make_shared<GemmPlan>();
+    gp->c = c;
+    // A: either k contiguous (K-major, row stride a_sm) or m contiguous (MN-major, row stride a_sk)
+    if (c.a_sk == 1 && c.a_sm >= c.K) { gp->a_mn = false; gp->lda = c.a_sm; }
+    else if (c.a_sm == 1 && c.a_sk >= c.M) { gp->a_mn = true; gp->lda = c.a_sk; }
+    else return ANL_ERR_UNSUPPORTED;
+    if (c.b_sk == 1 && c.b_sn >= c.K) { gp->b_mn = false; gp->ldb = c.b_sn; }
+    else if (c.b_sn == 1 && c.b_sk >= c.N) { gp->b_mn = true; gp->ldb = c.b_sk; }
+    else return ANL_ERR_UNSUPPORTED;
+    // TMA: 16-byte aligned bases and row strides
+    if (gp->lda % 8 || gp->ldb % 8 || c.a_off % 8 || c.b_off % 8) return ANL_ERR_UNSUPPORTED;
+    if (c.M >= (1ll << 31) || c.N >= (1ll << 31) || c.K >= (1ll << 31)) return ANL_ERR_UNSUPPORTED;
+    static int* status_host = nullptr;
+    static int* status_dev = nullptr;
+    if (!status_host) {
+        if (cudaHostAlloc((void**)&status_host, 64, cudaHostAllocMapped) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
+        *status_host = 0;
+        if (cudaHostGetDevicePointer((void**)&status_dev, status_host, 0) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
+    }
+    gp->status_host = status_host; gp->status_dev = status_dev;
+    static bool attr_set = false;
+    if (!attr_set) {
+        cudaFuncSetAttribute(gemm_f16_tcgen05<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        attr_set = true;
+    }
+    plan.gemm = gp;
+    plan.r.klass = KC_GEMM;
+    plan.r.note = std::string("gemm tcgen05 ") + (gp->a_mn ? "A:MN" : "A:K") + (gp->b_mn ? " B:MN" : " B:K") + " M=" + std::to_string(c.M) + " N=" + std::to_string(c.N) + " K=" + std::to_string(c.K);
+    return ANL_OK;
+}
+
+double gemm_flops(const Plan& plan) { const Contraction& c = plan.gemm->c; return 2.0 * (double)c.M * (double)c.N * (double)c.K; }
+
+int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream) {
+    const GemmPlan& gp = *plan.gemm;
+    const Contraction& c = gp.c;
+    if (*gp.status_host != 0) return dev->fail(ANL_ERR_CUDA, "gemm: an earlier launch timed out on a barrier (code " + std::to_string(*gp.status_host) + ")");
+    const __half* a = (const __half*)bufs[c.a_param] + c.a_off;
+    const __half* b = (const __half*)bufs[c.b_param] + c.b_off;
+    CUtensorMap ma, mb;
+    int rc;
+    if (gp.a_mn) rc = encode_map(dev, &ma, a, (uint64_t)c.M, (uint64_t)c.K, (uint64_t)gp.lda, 64, BK);
+    else rc = encode_map(dev, &ma, a, (uint64_t)c.K, (uint64_t)c.M, (uint64_t)gp.lda, BK, BM);
+    if (rc) return rc;
+    if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
+    else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, BN);
+    if (rc) return rc;
+    GemmArgs g;
+    g.d = (__half*)bufs[0];
+    g.M = (int)c.M; g.N = (int)c.N; g.K = (int)c.K; g.ldd = (int)c.N;
+    g.tiles_m = (int)((c.M + BM - 1) / BM); g.tiles_n = (int)((c.N + BN - 1) / BN);
+    g.status = gp.status_dev;
+    int tiles = g.tiles_m * g.tiles_n;
+    int grid = std::min(tiles, dev->prop.multiProcessorCount);
+    if (gp.a_mn && gp.b_mn) gemm_f16_tcgen05<true, true><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
+    else if (gp.a_mn) gemm_f16_tcgen05<true, false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
+    else if (gp.b_mn) gemm_f16_tcgen05<false, true><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
+    else gemm_f16_tcgen05<false, false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm: launch: ") + cudaGetErrorString(e));
+    dev->stats.kernels_launched++;
+    dev->stats.gemm_launched++;
+    return ANL_OK;
+}
+
+}  // namespace anl

@@ -212,8 +212,24 @@ static int launch_one(anl_device* dev, CUfunction fn, const Launch& l, int64_t s
     return ANL_OK;
 }
 
+static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item, void* const* bufs, int64_t sym_value, cudaStream_t stream,
+                             std::vector<void*>* keep_scratch);
+
 int launch_plan(anl_device* dev, const Plan& plan, const Item& item, void* const* bufs, int64_t sym_value, cudaStream_t stream,
                 std::vector<void*>* keep_scratch) {
+    if (!dev->profiling) return launch_plan_inner(dev, plan, item, bufs, sym_value, stream, keep_scratch);
+    anl_device::ProfRec r{};
+    cudaEventCreate(&r.e0); cudaEventCreate(&r.e1);
+    r.klass = plan.r.klass; r.flops = plan.r.klass == KC_GEMM ? gemm_flops(plan) : 0.0;
+    cudaEventRecord(r.e0, stream);
+    int rc = launch_plan_inner(dev, plan, item, bufs, sym_value, stream, keep_scratch);
+    cudaEventRecord(r.e1, stream);
+    dev->prof.push_back(r);
+    return rc;
+}
+
+static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item, void* const* bufs, int64_t sym_value, cudaStream_t stream,
+                             std::vector<void*>* keep_scratch) {
     if (plan.r.klass == KC_GEMM) return launch_gemm(dev, plan, bufs, stream);
     int nb = (int)item.bufs.size();
     std::vector<void*> ptrs(bufs, bufs + nb);
@@ -455,6 +471,8 @@ void anl_close(anl_device* dev) {
     for (auto& kv : dev->modules) if (kv.second->mod && dev->drv.ModuleUnload) dev->drv.ModuleUnload(kv.second->mod);
     dev->trim();
     for (auto& kv : dev->live) cudaFree(kv.first);
+    for (auto& r : dev->prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+    if (dev->timer0) { cudaEventDestroy(dev->timer0); cudaEventDestroy(dev->timer1); }
     if (dev->comm_event) cudaEventDestroy(dev->comm_event);
     if (dev->comm_done) cudaEventDestroy(dev->comm_done);
     if (dev->comm_stream) cudaStreamDestroy(dev->comm_stream);
@@ -602,7 +620,17 @@ int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems) {
     CK(buf->dev, cudaStreamSynchronize(buf->dev->stream));
     return ANL_OK;
 }
-void anl_buffer_release(anl_buffer* buf) { if (!buf) return; cudaStreamSynchronize(buf->dev->stream); buf->dev->release(buf->ptr); delete buf; }
+void anl_buffer_release(anl_buffer* buf) { if (!buf) return; cudaStreamSynchronize(buf->dev->stream); if (!buf->view) buf->dev->release(buf->ptr); delete buf; }
+int anl_buffer_view(anl_buffer* parent, int64_t offset, int64_t elems, anl_buffer** out) {
+    if (!parent || !out || offset < 0 || elems < 0 || offset + elems > parent->elems) return ANL_ERR_INVALID;
+    if (offset % 128) return parent->dev->fail(ANL_ERR_INVALID, "buffer view: offset must be a multiple of 128 elements");
+    auto* b = new anl_buffer();
+    b->dev = parent->dev; b->dtype = parent->dtype; b->elems = elems; b->view = true;
+    b->bytes = (size_t)elems * dt_storage_bytes(parent->dtype);
+    b->ptr = (char*)parent->ptr + (size_t)offset * dt_storage_bytes(parent->dtype);
+    *out = b;
+    return ANL_OK;
+}
 void* anl_buffer_device_ptr(anl_buffer* buf) { return buf ? buf->ptr : nullptr; }
 int64_t anl_buffer_elems(anl_buffer* buf) { return buf ? buf->elems : 0; }
 
@@ -622,6 +650,43 @@ int anl_sgd_step(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buf
     else sgd_kernel<float, float><<<g, 256, 0, dev->stream>>>(m, (float*)param->ptr, (const float*)grad->ptr, lr, scale, n, bf);
     dev->stats.kernels_launched++;
     CK(dev, cudaGetLastError());
+    return ANL_OK;
+}
+
+int anl_timer_start(anl_device* dev) {
+    if (!dev) return ANL_ERR_INVALID;
+    cudaSetDevice(dev->ordinal);
+    if (!dev->timer0) { CK(dev, cudaEventCreate(&dev->timer0)); CK(dev, cudaEventCreate(&dev->timer1)); }
+    CK(dev, cudaEventRecord(dev->timer0, dev->stream));
+    return ANL_OK;
+}
+int anl_timer_stop(anl_device* dev, float* ms) {
+    if (!dev || !ms || !dev->timer0) return ANL_ERR_INVALID;
+    CK(dev, cudaEventRecord(dev->timer1, dev->stream));
+    CK(dev, cudaEventSynchronize(dev->timer1));
+    CK(dev, cudaEventElapsedTime(ms, dev->timer0, dev->timer1));
+    return ANL_OK;
+}
+int anl_profile_enable(anl_device* dev, int on) {
+    if (!dev) return ANL_ERR_INVALID;
+    cudaStreamSynchronize(dev->stream);
+    for (auto& r : dev->prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
+    dev->prof.clear();
+    dev->profiling = on != 0;
+    return ANL_OK;
+}
+int anl_profile_read(anl_device* dev, anl_profile_entry* out, int cap, int* n) {
+    if (!dev || !out || !n) return ANL_ERR_INVALID;
+    CK(dev, cudaStreamSynchronize(dev->stream));
+    std::map<int, anl_profile_entry> acc;
+    for (auto& r : dev->prof) {
+        float ms = 0; cudaEventElapsedTime(&ms, r.e0, r.e1);
+        anl_profile_entry& e = acc[r.klass];
+        e.klass = r.klass; e.launches++; e.total_ms += ms; e.flops += r.flops;
+    }
+    int k = 0;
+    for (auto& kv : acc) { if (k >= cap) break; out[k++] = kv.second; }
+    *n = k;
     return ANL_OK;
 }
 

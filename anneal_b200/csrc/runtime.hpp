@@ -50,6 +50,7 @@ struct anl_buffer {
     int64_t elems = 0;
     void* ptr = nullptr;
     size_t bytes = 0;
+    bool view = false;      // a window of another buffer: the memory is not ours to release
 };
 
 struct anl_device {
@@ -66,6 +67,10 @@ struct anl_device {
     std::multimap<size_t, void*> pool;                                // free device blocks by size
     std::unordered_map<void*, size_t> live;                           // blocks handed out
     anl_stats stats{};
+    cudaEvent_t timer0 = nullptr, timer1 = nullptr;
+    bool profiling = false;
+    struct ProfRec { cudaEvent_t e0, e1; int klass; double flops; };
+    std::vector<ProfRec> prof;
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
 
@@ -93,5 +98,6 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 // dense SUM-of-products over buffers that they cover, ANL_ERR_UNSUPPORTED otherwise
 int plan_gemm(anl_device* dev, const Item& item, Plan& plan);
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream);
+double gemm_flops(const Plan& plan);   // 2*M*N*K of a routed contraction
 
 }  // namespace anl

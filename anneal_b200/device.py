@@ -48,6 +48,10 @@ class _Stats(C.Structure):
                                           "graph_captures", "device_allocs")]
 
 
+class _Prof(C.Structure):
+    _fields_ = [("klass", C.c_int), ("launches", C.c_int), ("total_ms", C.c_double), ("flops", C.c_double)]
+
+
 class _Info(C.Structure):
     _fields_ = [("name", C.c_char * 128), ("sm_major", C.c_int), ("sm_minor", C.c_int), ("sm_count", C.c_int),
                 ("total_mem", C.c_size_t), ("has_f16", C.c_int), ("has_bf16", C.c_int), ("has_tcgen05", C.c_int)]
@@ -91,6 +95,7 @@ def load_library():
     L.anl_buffer_download.argtypes = [vp, vp, C.c_int64]
     L.anl_buffer_release.argtypes = [vp]
     L.anl_buffer_release.restype = None
+    L.anl_buffer_view.argtypes = [vp, C.c_int64, C.c_int64, C.POINTER(vp)]
     L.anl_buffer_device_ptr.argtypes = [vp]
     L.anl_buffer_device_ptr.restype = vp
     L.anl_buffer_elems.argtypes = [vp]
@@ -100,6 +105,10 @@ def load_library():
     L.anl_comm_init.argtypes = [vp, i, i, C.c_char_p]
     L.anl_allreduce_sum.argtypes = [vp, vp]
     L.anl_comm_destroy.argtypes = [vp]
+    L.anl_timer_start.argtypes = [vp]
+    L.anl_timer_stop.argtypes = [vp, C.POINTER(C.c_float)]
+    L.anl_profile_enable.argtypes = [vp, i]
+    L.anl_profile_read.argtypes = [vp, C.POINTER(_Prof), i, C.POINTER(i)]
     L.anl_host_alloc.argtypes = [C.c_size_t, C.POINTER(vp)]
     L.anl_host_free.argtypes = [vp]
     L.anl_host_free.restype = None
@@ -112,8 +121,9 @@ ABI_SYMBOLS = [
     "anl_open", "anl_close", "anl_device_info", "anl_last_error", "anl_get_stats", "anl_run", "anl_outputs_free",
     "anl_lower", "anl_compile_check", "anl_benchmark", "anl_graph_create", "anl_graph_replay", "anl_graph_release",
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
-    "anl_buffer_elems", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
-    "anl_comm_destroy", "anl_host_alloc", "anl_host_free", "anl_synchronize",
+    "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
+    "anl_comm_destroy", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
+    "anl_profile_enable", "anl_profile_read",
 ]
 
 KERNEL_CLASSES = {0: "elementwise", 1: "reduce", 2: "reduce_split", 3: "gemm", 4: "raw"}
@@ -155,11 +165,18 @@ def compile_check(source: str) -> str:
 class ResidentBuffer:
     """A device buffer that outlives a run: parameters, master weights, gradients."""
 
-    def __init__(self, dev: "Device", dtype, elems: int):
+    def __init__(self, dev: "Device", dtype, elems: int, _handle=None):
         self.dev, self.dtype, self.elems = dev, dtype, int(elems)
+        if _handle is None:
+            _handle = C.c_void_p()
+            dev._check(dev.L.anl_buffer_create(dev.h, dtype.code, self.elems, C.byref(_handle)))
+        self.h = _handle
+
+    def view(self, offset: int, elems: int) -> "ResidentBuffer":
+        """A window of this buffer (offset a multiple of 128 elements); no copy."""
         h = C.c_void_p()
-        dev._check(dev.L.anl_buffer_create(dev.h, dtype.code, self.elems, C.byref(h)))
-        self.h = h
+        self.dev._check(self.dev.L.anl_buffer_view(self.h, int(offset), int(elems), C.byref(h)))
+        return ResidentBuffer(self.dev, self.dtype, elems, h)
 
     def upload(self, data):
         a = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
@@ -326,6 +343,25 @@ class Device:
 
     def allreduce_sum(self, buf: ResidentBuffer):
         self._check(self.L.anl_allreduce_sum(self.h, buf.h))
+
+    def timer_start(self):
+        self._check(self.L.anl_timer_start(self.h))
+
+    def timer_stop(self) -> float:
+        """Milliseconds between timer_start and now on the compute stream (CUDA events)."""
+        ms = C.c_float()
+        self._check(self.L.anl_timer_stop(self.h, C.byref(ms)))
+        return ms.value
+
+    def profile(self, on: bool):
+        self._check(self.L.anl_profile_enable(self.h, 1 if on else 0))
+
+    def profile_read(self):
+        arr = (_Prof * 8)()
+        n = C.c_int()
+        self._check(self.L.anl_profile_read(self.h, arr, 8, C.byref(n)))
+        return {KERNEL_CLASSES.get(arr[k].klass, str(arr[k].klass)): {"launches": arr[k].launches, "total_ms": arr[k].total_ms,
+                                                                       "flops": arr[k].flops} for k in range(n.value)}
 
     def synchronize(self):
         self._check(self.L.anl_synchronize(self.h))

@@ -64,10 +64,14 @@ def tanh(x: Tensor) -> Tensor:
 
 def gelu_tanh(x: Tensor) -> Tensor:
     """0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), composed from the
-    reference's primitives only (it has no GELU of its own)."""
+    reference's primitives only (it has no GELU of its own). The sigmoid inside
+    tanh sees max(2u, -10): in f16 storage exp(-2u) would otherwise overflow to
+    inf for u < -5.5 and the backward pass would form 0 * inf."""
     k = lambda v: Tensor.full(x.shape, v, x.dtype)
-    inner = k(math.sqrt(2.0 / math.pi)).mul(x.add(k(0.044715).mul(x.mul(x).mul(x))))
-    return k(0.5).mul(x).mul(k(1.0).add(tanh(inner)))
+    u = k(math.sqrt(2.0 / math.pi)).mul(x.add(k(0.044715).mul(x.mul(x).mul(x))))
+    v = k(2.0).mul(u).maximum(k(-10.0))
+    th = k(2.0).mul(sigmoid(v)).sub(k(1.0))
+    return k(0.5).mul(x).mul(k(1.0).add(th))
 
 
 class Linear:
@@ -165,12 +169,15 @@ def softmax_rows(x: Tensor):
     return e.div(s)
 
 
-def cross_entropy_onehot(logits: Tensor, onehot: Tensor) -> Tensor:
-    """-sum(onehot * (x - m - log s)) / B, a scalar."""
+def cross_entropy_onehot(logits: Tensor, onehot: Tensor, reduction: str = "mean") -> Tensor:
+    """Softmax cross-entropy against one-hot rows, a scalar:
+    -sum(onehot * (x - m - log s)) / B for "mean", without the division for "sum".
+    The mean scales each term before summing, so an f16 result cannot overflow."""
     n, c = logits.shape
     m = logits.max([1]).reshape((n, 1)).expand((n, c))
     z = logits.sub(m)
     s = z.exp().sum([1]).reshape((n, 1)).expand((n, c))
-    logp = z.sub(s.log())
-    total = onehot.mul(logp).sum()
-    return total.neg().div(Tensor.full((), float(n), total.dtype))
+    terms = onehot.mul(z.sub(s.log()))
+    if reduction == "mean":
+        terms = terms.mul(Tensor.full((n, c), 1.0 / n, terms.dtype))
+    return terms.sum().neg()

@@ -1,0 +1,110 @@
+"""Training loop with device-resident parameters.
+
+The reference's loop (examples/mlp.go:111-142, tensor/nn/nn.go:56-106) rebuilds
+the graph every step, re-uploads every weight through ``Parameter.Load`` and
+applies SGD on the host. ``ResidentTrainer`` keeps that loop's meaning — f32
+master weights, storage-dtype copies re-quantised after each update, plain SGD —
+but builds the schedule once (the JIT's job, tensor/jit.go:86-118), keeps
+parameters, masters and gradients in three contiguous device buckets, replays
+the step as one CUDA graph, all-reduces the gradient bucket across ranks and
+updates on the device. Per step only the batch goes up and the loss comes down.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional
+
+import numpy as np
+
+from . import realize as R
+from .device import Device, ResidentBuffer, pinned_array
+from .uop import dtypes
+
+
+def _round_up(n: int, m: int = 128) -> int:
+    return (n + m - 1) // m * m
+
+
+class ResidentTrainer:
+    def __init__(self, dev: Device, model, lr: float, world: int = 1, use_graph: bool = True,
+                 materialize: bool = True, resident_inputs: bool = False):
+        self.dev, self.model, self.lr, self.world, self.use_graph = dev, model, float(lr), world, use_graph
+        prev = R.MATERIALIZE_CONTRACTION_OPERANDS
+        R.MATERIALIZE_CONTRACTION_OPERANDS = materialize
+        try:
+            g = model.graph()
+            self.items, out_ids = R.build_schedule(g.targets())
+        finally:
+            R.MATERIALIZE_CONTRACTION_OPERANDS = prev
+        self.loss_id, self.grad_ids = out_ids[0], out_ids[1:]
+        self.grad_scale = float(g.grad_scale)
+        self.x_id, self.y_id = g.inputs["x"].node.idx, g.inputs["y"].node.idx
+        self.x_elems = int(np.prod(g.inputs["x"].shape))
+        self.y_elems = int(np.prod(g.inputs["y"].shape))
+        self.in_dtype = g.inputs["x"].dtype
+        params = g.params
+        self.params = params
+        sdt = params[0].dtype
+        offs, total = [], 0
+        for p in params:
+            offs.append(total)
+            total += _round_up(p.value.size)
+        self.total = total
+        self.master = dev.buffer(dtypes.float32, total)
+        self.store = self.master if sdt is dtypes.float32 else dev.buffer(sdt, total)
+        self.grad = dev.buffer(sdt, total)
+        flat = np.zeros(total, dtype=np.float32)
+        for p, o in zip(params, offs):
+            flat[o:o + p.value.size] = p.value
+        self.master.upload(flat)
+        if self.store is not self.master:
+            self.store.upload(flat)
+        self.offsets = offs
+        self.inputs: Dict[int, object] = {}
+        self.placed: Dict[int, object] = {}
+        self._views = []
+        for p, o, gid in zip(params, offs, self.grad_ids):
+            pv = self.store.view(o, p.value.size)
+            gv = self.grad.view(o, p.value.size)
+            self._views += [pv, gv]
+            self.inputs[p.t.node.idx] = pv
+            self.placed[gid] = gv
+        self.loss_host = pinned_array(1)
+        self.placed[self.loss_id] = self.loss_host
+        self.resident_inputs = resident_inputs
+        if resident_inputs:
+            self.x_res = dev.buffer(self.in_dtype, self.x_elems)
+            self.y_res = dev.buffer(self.in_dtype, self.y_elems)
+            self.loss_res = dev.buffer(g.loss.dtype, 1)
+            self.placed[self.loss_id] = self.loss_res
+
+    def load_batch(self, x: np.ndarray, y: np.ndarray) -> None:
+        """Resident-input mode: stage one batch on the device ahead of the timed region."""
+        self.x_res.upload(x)
+        self.y_res.upload(y)
+
+    def step(self, x: Optional[np.ndarray] = None, y: Optional[np.ndarray] = None) -> Optional[float]:
+        inputs = dict(self.inputs)
+        if self.resident_inputs:
+            inputs[self.x_id], inputs[self.y_id] = self.x_res, self.y_res
+        else:
+            inputs[self.x_id], inputs[self.y_id] = x, y
+        run = self.dev.replay if self.use_graph else self.dev.run
+        run(self.items, inputs, None, self.placed)
+        if self.world > 1:
+            self.dev.allreduce_sum(self.grad)
+        self.dev.sgd_step(self.master, self.store, self.grad, self.lr, self.grad_scale / self.world)
+        return None if self.resident_inputs else float(self.loss_host[0])
+
+    def loss(self) -> float:
+        if self.resident_inputs:
+            return float(self.loss_res.download()[0])
+        return float(self.loss_host[0])
+
+    def parameters(self) -> List[np.ndarray]:
+        """Master weights back on the host, one array per parameter (for checkpoints and tests)."""
+        flat = self.master.download()
+        return [flat[o:o + p.value.size].copy() for p, o in zip(self.params, self.offsets)]
+
+    def gradients(self) -> List[np.ndarray]:
+        flat = self.grad.download()
+        return [flat[o:o + p.value.size].copy() for p, o in zip(self.params, self.offsets)]

@@ -73,6 +73,7 @@ class TrainGraph:
     params: List[nn.Parameter]
     grads: List[Tensor]
     inputs: Dict[str, Tensor]
+    grad_scale: float = 1.0      # multiply gradients by this before the update (loss scaling)
 
     def targets(self) -> List[Tensor]:
         return [self.loss] + self.grads
@@ -197,9 +198,11 @@ class WideMLP:
         for l in self.layers[:-1]:
             h = nn.gelu_tanh(l.forward(h))
         logits = self.layers[-1].forward(h)
-        loss = nn.cross_entropy_onehot(logits, y)
-        g = backward(loss, leaves)
-        return TrainGraph(loss, self.params, [g[l] for l in leaves], {"x": x, "y": y})
+        # f16 gradients of a batch mean underflow (softmax/B ~ 1e-7): differentiate the batch SUM
+        # and fold 1/B into the optimiser step; report the mean
+        loss = nn.cross_entropy_onehot(logits, y, "mean")
+        g = backward(nn.cross_entropy_onehot(logits, y, "sum"), leaves)
+        return TrainGraph(loss, self.params, [g[l] for l in leaves], {"x": x, "y": y}, 1.0 / self.batch)
 
 
 # ── C5: symbolic-batch MLP under JIT (shape of examples/dynmlp.go) ───────────

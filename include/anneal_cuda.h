@@ -138,6 +138,11 @@ int anl_buffer_create(anl_device* dev, int dtype, int64_t elems, anl_buffer** ou
 int anl_buffer_upload(anl_buffer* buf, const float* data, int64_t elems);
 int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems);
 void anl_buffer_release(anl_buffer* buf);
+/* A window [offset, offset+elems) of `parent` as a buffer of its own (same dtype, no copy).  Used
+ * to lay all parameters, or all gradients, out in one contiguous bucket so that one all-reduce and
+ * one optimiser launch cover them.  `offset` must be a multiple of 128 elements.  Release the view
+ * before the parent. */
+int anl_buffer_view(anl_buffer* parent, int64_t offset, int64_t elems, anl_buffer** out);
 void* anl_buffer_device_ptr(anl_buffer* buf);
 int64_t anl_buffer_elems(anl_buffer* buf);
 
@@ -156,6 +161,18 @@ int anl_comm_destroy(anl_device* dev);
 /* host staging memory that the GPU can copy from directly */
 int anl_host_alloc(size_t bytes, void** out);
 void anl_host_free(void* p);
+
+/* ── timing (Benchmarker's clock, for whole steps): CUDA events on the compute stream ── */
+int anl_timer_start(anl_device* dev);
+int anl_timer_stop(anl_device* dev, float* elapsed_ms);   /* waits for the stop event */
+
+/* Per-kernel-class breakdown.  While enabled every launch is bracketed by an event pair (this
+ * perturbs back-to-back launches slightly, so do not take whole-step times with it on).
+ * anl_profile_read waits for the device, then returns one entry per kernel class seen since the
+ * last anl_profile_enable(dev, 1). */
+typedef struct { int klass; int launches; double total_ms; double flops; } anl_profile_entry;
+int anl_profile_enable(anl_device* dev, int on);
+int anl_profile_read(anl_device* dev, anl_profile_entry* out, int cap, int* n);
 
 /* blocks until all work queued on the device has finished */
 int anl_synchronize(anl_device* dev);
