@@ -367,6 +367,8 @@ struct Gen {
     Block* cur_top = nullptr;
     std::map<int, std::vector<bool>> atom_dep_memo;
 
+    Block& T() { return cur_top ? *cur_top : top; }
+
     void stmt(int ctx, const std::string& s) {
         Block& b = ctx < 0 ? (cur_top ? *cur_top : top) : loop[ctx];
         b.code += std::string((ctx < 0 ? 1 : 2) * 2, ' ') + s + "\n";
@@ -582,20 +584,20 @@ struct Gen {
                 tot += ")";
                 hdr = "for (int q = RED_BEGIN" + tot + "; q < RED_END" + tot + "; q += RED_STEP) {";
             }
-            top.code += "  " + hdr + "\n";
+            T().code += "  " + hdr + "\n";
             if (rr.size() > 1) {
                 // decompose q, last range fastest
                 std::string stride = "1";
                 for (int k = (int)rr.size() - 1; k >= 0; k--) {
                     std::string rn = "r" + std::to_string(N(rr[k]).aux);
                     std::string b = range_bound(rr[k]);
-                    top.code += "    const int " + rn + " = " + (k == 0 ? "q / (" + stride + ")" : "(q / (" + stride + ")) % " + b) + ";\n";
+                    T().code += "    const int " + rn + " = " + (k == 0 ? "q / (" + stride + ")" : "(q / (" + stride + ")) % " + b) + ";\n";
                     stride = stride + " * " + b;
                 }
             }
-            top.code += loop[i].code;
-            top.code += "    " + acc + " = " + combine(rop, acc_c, acc, ef) + ";\n";
-            top.code += "  }\n";
+            T().code += loop[i].code;
+            T().code += "    " + acc + " = " + combine(rop, acc_c, acc, ef) + ";\n";
+            T().code += "  }\n";
             if (reduce_combine_mode == "group")
                 stmt(-1, acc + " = group_" + rop_tag(rop) + "_" + (isf ? "f" : "i") + "(" + acc + ", lane, grp, red_smem);");
             else if (reduce_combine_mode == "partial")
@@ -621,6 +623,16 @@ struct Gen {
         std::string e;
         auto a = [&](int k) { return val(nd.src[k], ctx); };
         auto af = [&](int k) { return to_float(nd.src[k], val(nd.src[k], ctx)); };
+        // operand k in this node's own compute class: a node shared between an f16 reduction (where it
+        // is evaluated widened) and f16 code outside it is narrowed at the point of use
+        auto ac = [&](int k) {
+            std::string v = val(nd.src[k], ctx);
+            Cls sc = cls(nd.src[k]);
+            if (sc == c) return v;
+            if (c == CF16 && sc == CF32) return "__float2half_rn(" + v + ")";
+            if (c == CF32 && sc == CF16) return "__half2float(" + v + ")";
+            return v;
+        };
         bool h = (c == CF16);
         auto wrap = [&](const std::string& fexpr) { return h ? "__float2half_rn(" + fexpr + ")" : fexpr; };
         if (c == CBOOL) {
@@ -652,22 +664,22 @@ struct Gen {
                 case OP_INDEX: e = load_expr(i, ctx); break;
                 case OP_REDUCE: if (ctx >= 0) { fail("codegen: nested REDUCE"); return "0.0f"; } e = reduce_expr(i); break;
                 case OP_CAST: case OP_BITCAST: e = cast_expr(i, ctx); break;
-                case OP_WHERE: { std::string cnd = a(0); if (cnd == "true") return a(1); if (cnd == "false") return a(2); e = "(" + cnd + " ? " + a(1) + " : " + a(2) + ")"; break; }
+                case OP_WHERE: { std::string cnd = a(0); if (cnd == "true") return ac(1); if (cnd == "false") return ac(2); e = "(" + cnd + " ? " + ac(1) + " : " + ac(2) + ")"; break; }
                 case OP_EXP2: e = wrap("exp2f(" + af(0) + ")"); break;
                 case OP_LOG2: e = wrap("log2f(" + af(0) + ")"); break;
                 case OP_SIN: e = wrap("sinf(" + af(0) + ")"); break;
                 case OP_SQRT: e = wrap("sqrtf(" + af(0) + ")"); break;
                 case OP_RECIP: e = wrap("(1.0f / " + af(0) + ")"); break;
                 case OP_TRUNC: e = wrap("truncf(" + af(0) + ")"); break;
-                case OP_NEG: e = h ? "__hneg(" + a(0) + ")" : "(-" + a(0) + ")"; break;
-                case OP_ADD: e = h ? "__hadd(" + a(0) + ", " + a(1) + ")" : "(" + a(0) + " + " + a(1) + ")"; break;
-                case OP_SUB: e = h ? "__hsub(" + a(0) + ", " + a(1) + ")" : "(" + a(0) + " - " + a(1) + ")"; break;
-                case OP_MUL: e = h ? "__hmul(" + a(0) + ", " + a(1) + ")" : "(" + a(0) + " * " + a(1) + ")"; break;
+                case OP_NEG: e = h ? "__hneg(" + ac(0) + ")" : "(-" + ac(0) + ")"; break;
+                case OP_ADD: e = h ? "__hadd(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " + " + ac(1) + ")"; break;
+                case OP_SUB: e = h ? "__hsub(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " - " + ac(1) + ")"; break;
+                case OP_MUL: e = h ? "__hmul(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " * " + ac(1) + ")"; break;
                 case OP_FDIV: e = wrap("(" + af(0) + " / " + af(1) + ")"); break;
-                case OP_MAX: e = h ? "__hmax(" + a(0) + ", " + a(1) + ")" : "fmaxf(" + a(0) + ", " + a(1) + ")"; break;
+                case OP_MAX: e = h ? "__hmax(" + ac(0) + ", " + ac(1) + ")" : "fmaxf(" + ac(0) + ", " + ac(1) + ")"; break;
                 case OP_POW: e = wrap("powf(" + af(0) + ", " + af(1) + ")"); break;
                 case OP_MOD: e = wrap("fmodf(" + af(0) + ", " + af(1) + ")"); break;
-                case OP_MULACC: e = h ? "__hadd(" + a(0) + ", __hmul(" + a(1) + ", " + a(2) + "))" : "(" + a(0) + " + (" + a(1) + " * " + a(2) + "))"; break;
+                case OP_MULACC: e = h ? "__hadd(" + ac(0) + ", __hmul(" + ac(1) + ", " + ac(2) + "))" : "(" + ac(0) + " + (" + ac(1) + " * " + ac(2) + "))"; break;
                 default: fail("codegen: unhandled op " + std::to_string(nd.op)); return "0.0f";
             }
         }
@@ -777,16 +789,17 @@ struct Gen {
         return sym_output() ? "((long long)n0 * " + std::to_string(static_total()) + ")" : std::to_string(static_total()) + "LL";
     }
 
-    // r_i = (g / stride_i) % size_i for every loop range, innermost last
-    std::string decompose(const std::string& g) {
+    // r_i = (g / stride_i) % size_i for loop ranges [first, last), innermost last
+    std::string decompose(const std::string& g, size_t first = 0, size_t last = (size_t)-1, const std::string& indent = "  ") {
+        if (last == (size_t)-1) last = loop_ranges.size();
         std::string s;
         int64_t stride = 1;
-        for (int k = (int)loop_ranges.size() - 1; k >= 0; k--) {
+        for (int k = (int)last - 1; k >= (int)first; k--) {
             int r = loop_ranges[k];
             std::string rn = "r" + std::to_string(N(r).aux);
             std::string e = stride == 1 ? g : "(" + g + " / " + std::to_string(stride) + ")";
-            if (k == 0 || N(r).symbolic()) s += "  const int " + rn + " = (int)" + e + ";\n";
-            else s += "  const int " + rn + " = (int)(" + e + " % " + std::to_string(N(r).arg) + ");\n";
+            if (k == (int)first || N(r).symbolic()) s += indent + "const int " + rn + " = (int)" + e + ";\n";
+            else s += indent + "const int " + rn + " = (int)(" + e + " % " + std::to_string(N(r).arg) + ");\n";
             if (!N(r).symbolic()) stride *= N(r).arg;
         }
         return s;
@@ -978,7 +991,63 @@ struct Gen {
         return m.str();
     }
 
+    // Every REDUCE is invariant along the trailing `ninv` output ranges (a row statistic consumed by
+    // an elementwise expression over the row, the shape epilogue fusion produces for softmax-like
+    // graphs, schedule/schedule.go:197-233).  The reference re-runs the reduction for every output
+    // element; here one block owns one outer index, all threads cooperate on each reduction once,
+    // then sweep the invariant ranges.
+    bool build_rowbcast(Rendered& out, size_t ninv, int64_t inner) {
+        threads = opts.block_threads > 0 ? opts.block_threads : 256;
+        lanes = threads; touts = 1; rc_layout = true;
+        size_t nouter = loop_ranges.size() - ninv;
+        int64_t outer = 1; bool osym = false;
+        for (size_t k = 0; k < nouter; k++) { if (N(loop_ranges[k]).symbolic()) osym = true; else outer *= N(loop_ranges[k]).arg; }
+        reset_emit();
+        reduce_combine_mode = "group";
+        std::ostringstream k;
+        k << reduce_macros(false) << preamble();
+        std::string name = "reduce_rowbcast";
+        k << signature(name, false, threads) << " {\n";
+        k << "  __shared__ float red_smem[" << std::max(threads / 32, 1) << "];\n";
+        k << "  const int lane = threadIdx.x, grp = 0;\n";
+        k << "  const long long go = blockIdx.x;\n";
+        k << decompose("go", 0, nouter);
+        cur_top = &prelude;
+        for (int r : reduces) { val(r, -1); if (!err.empty()) return false; }
+        cur_top = nullptr;
+        std::string v = val(body, -1);
+        if (!err.empty()) return false;
+        k << prelude.code;
+        k << "  for (int gi = threadIdx.x; gi < " << inner << "; gi += " << threads << ") {\n";
+        k << decompose("gi", nouter, loop_ranges.size(), "    ");
+        k << top.code;
+        k << "    data0[go * " << inner << "LL + gi] = " << store_value(v, body) << ";\n";
+        k << "  }\n}\n";
+        out.klass = KC_REDUCE;
+        out.source = k.str();
+        out.main.entry = name;
+        out.main.block = threads;
+        out.main.outputs_per_block = 1;
+        out.main.static_outputs = outer;
+        out.main.sym_trailing = osym ? outer : 0;
+        out.uses_sym = has_sym;
+        out.note = "reduce row-broadcast inner=" + std::to_string(inner) + " lanes=" + std::to_string(lanes);
+        return true;
+    }
+
     bool build_reduce(Rendered& out) {
+        if (opts.reduce_lanes == 0 && opts.split <= 1) {
+            size_t ninv = 0; int64_t inner = 1;
+            for (int k = (int)loop_ranges.size() - 1; k >= 0; k--) {
+                int r = loop_ranges[k];
+                if (N(r).symbolic()) break;
+                bool used = false;
+                for (int red : reduces) if (dep[red][range_slot[r]]) used = true;
+                if (used) break;
+                ninv++; inner *= N(r).arg;
+            }
+            if (ninv > 0 && inner >= 64) return build_rowbcast(out, ninv, inner);
+        }
         int64_t total = static_total();
         int64_t rmax = 0; bool rsym = false;
         for (int r : reduces) { int64_t t = reduce_total(r); if (t == 0) rsym = true; rmax = std::max(rmax, t); }

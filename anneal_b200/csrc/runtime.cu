@@ -11,7 +11,9 @@
 #include <cmath>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 #include <set>
+#include <unordered_set>
 
 using namespace anl;
 
@@ -295,6 +297,11 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 // ── schedule execution ───────────────────────────────────────────────────────────────────────
 namespace {
 
+// host arrays handed out through anl_output.data; anl_outputs_free releases only these, never a
+// caller-placed array
+std::mutex g_owned_mu;
+std::unordered_set<float*> g_owned_outputs;
+
 struct DevBuf { void* ptr = nullptr; size_t bytes = 0; int dtype = DT_F32; int64_t elems = 0; bool owned = false; };
 
 struct Bindings {
@@ -406,6 +413,7 @@ int collect_outputs(anl_device* dev, Table& t, const anl_output* placed, int n_p
                 o.data = (float*)std::malloc((size_t)std::max<int64_t>(d.elems, 1) * 4);
                 if (!o.data) { rc = dev->fail(ANL_ERR_LIMIT, "run: out of host memory"); break; }
                 mine.push_back(o.data);
+                { std::lock_guard<std::mutex> lk(g_owned_mu); g_owned_outputs.insert(o.data); }
             }
             if ((rc = download_f32(dev, o.data, d.ptr, d.dtype, d.elems, stream))) break;
         }
@@ -413,7 +421,11 @@ int collect_outputs(anl_device* dev, Table& t, const anl_output* placed, int n_p
     }
     cudaError_t e = cudaStreamSynchronize(stream);
     if (rc == ANL_OK && e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("cuda: ") + cudaGetErrorString(e));
-    if (rc != ANL_OK) { for (float* p : mine) std::free(p); n = 0; }
+    if (rc != ANL_OK) {
+        std::lock_guard<std::mutex> lk(g_owned_mu);
+        for (float* p : mine) { g_owned_outputs.erase(p); std::free(p); }
+        n = 0;
+    }
     *n_outs = n;
     return rc;
 }
@@ -438,6 +450,7 @@ struct anl_graph {
     std::vector<Item> items;
     Table table;
     bool built = false;
+    uint64_t kernels_per_replay = 0, gemms_per_replay = 0;
     int64_t built_sym = -2;
     cudaGraphExec_t exec = nullptr;
     std::vector<std::pair<uint32_t, anl_buffer*>> resident_in, resident_out;
@@ -521,7 +534,12 @@ int anl_run(anl_device* dev, const uint8_t* blob, size_t blob_len, const anl_inp
 
 void anl_outputs_free(anl_output* outs, int n_outs) {
     if (!outs) return;
-    for (int i = 0; i < n_outs; i++) { if (!outs[i].resident && outs[i].data) std::free(outs[i].data); outs[i].data = nullptr; }
+    std::lock_guard<std::mutex> lk(g_owned_mu);
+    for (int i = 0; i < n_outs; i++) {
+        auto it = outs[i].data ? g_owned_outputs.find(outs[i].data) : g_owned_outputs.end();
+        if (it != g_owned_outputs.end()) { std::free(outs[i].data); g_owned_outputs.erase(it); }
+        outs[i].data = nullptr;
+    }
 }
 
 int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o,
@@ -737,7 +755,11 @@ int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs, const 
             cudaError_t e = cudaStreamBeginCapture(dev->stream, cudaStreamCaptureModeRelaxed);
             if (e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("graph: begin capture: ") + cudaGetErrorString(e));
             if (rc == ANL_OK) {
+                uint64_t k0 = dev->stats.kernels_launched, g0 = dev->stats.gemm_launched;
                 int rrc = run_items(dev, g->items, b, g->table, dev->stream, true);   // scratch stays with the graph
+                g->kernels_per_replay = dev->stats.kernels_launched - k0;
+                g->gemms_per_replay = dev->stats.gemm_launched - g0;
+                dev->stats.kernels_launched = k0; dev->stats.gemm_launched = g0;        // counted per replay below
                 e = cudaStreamEndCapture(dev->stream, &graph);
                 if (rrc != ANL_OK) rc = rrc;
                 else if (e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("graph: end capture: ") + cudaGetErrorString(e));
@@ -765,6 +787,8 @@ int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs, const 
     cudaError_t e = cudaGraphLaunch(g->exec, dev->stream);
     if (e != cudaSuccess) { *n_outs = 0; return dev->fail(ANL_ERR_CUDA, std::string("graph: launch: ") + cudaGetErrorString(e)); }
     dev->stats.graph_replays++;
+    dev->stats.kernels_launched += g->kernels_per_replay;
+    dev->stats.gemm_launched += g->gemms_per_replay;
     return collect_outputs(dev, g->table, placed, n_placed, outs, n_outs, dev->stream);
 }
 

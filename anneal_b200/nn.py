@@ -172,7 +172,14 @@ def softmax_rows(x: Tensor):
 def cross_entropy_onehot(logits: Tensor, onehot: Tensor, reduction: str = "mean") -> Tensor:
     """Softmax cross-entropy against one-hot rows, a scalar:
     -sum(onehot * (x - m - log s)) / B for "mean", without the division for "sum".
-    The mean scales each term before summing, so an f16 result cannot overflow."""
+    The mean scales each term before summing, so an f16 result cannot overflow.
+
+    The logits are materialised first. The backward of the row max compares each logit with the
+    max; if the logits were an inlined f16 expression (matmul + bias) the max kernel would evaluate
+    it widened to f32 inside its reduction (codegen/lower.go:158-171) while the stored max is
+    rounded to f16, no element would compare equal, the tie count would be 0 and the gradient
+    inf. Reading one stored copy makes both sides the same value."""
+    logits = logits.contiguous()
     n, c = logits.shape
     m = logits.max([1]).reshape((n, 1)).expand((n, c))
     z = logits.sub(m)

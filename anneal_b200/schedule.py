@@ -267,54 +267,52 @@ def _is_view_of_buffer(u: U.UOp, realized) -> bool:
 
 
 def materialize_contraction_operands(roots: List[U.UOp]) -> List[U.UOp]:
-    """Rewrite ``SUM(MUL(a, b))`` so that a and b are views of buffers.
+    """Rewrite the graph so that both operands of every ``SUM(MUL(a, b))`` are views of buffers.
 
-    An operand that is an expression (an activation of the previous layer's
-    output, a masked adjoint) is wrapped in CONTIGUOUS *below* its movement ops,
-    at the point where it still has its own un-broadcast shape, so that it is
-    computed once instead of once per multiply. Not part of the reference
-    scheduler; its only existing use of CONTIGUOUS as a materialisation barrier
-    is tensor/gradient_ruleset.go:309-312."""
-    memo: Dict[int, U.UOp] = {}
+    An operand that is an expression (an activation of the previous layer's output, a masked
+    adjoint) is wrapped in CONTIGUOUS *below* its movement ops, at the point where it still has its
+    own un-broadcast shape, so that it is computed once instead of once per multiply — and every
+    other consumer of that expression reads the same buffer instead of recomputing it. Not part of
+    the reference scheduler; its only existing use of CONTIGUOUS as a materialisation barrier is
+    tensor/gradient_ruleset.go:309-312."""
+    sink = U.new(Op.SINK, dtypes.void, tuple(roots))
+    topo = U.toposort(sink)[:-1]
+    chosen = set()
+    for u in topo:
+        if u.op == Op.REDUCE_AXIS and u.arg[0] == Op.ADD and u.src[0].op == Op.MUL:
+            for o in u.src[0].src:
+                while o.op in U.MOVEMENT:
+                    o = o.src[0]
+                if o.op not in (Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS, Op.CONST):
+                    chosen.add(o.idx)
+    if not chosen:
+        return list(roots)
+    out: Dict[int, U.UOp] = {}
+    for u in topo:
+        srcs = tuple(out[s.idx] for s in u.src)
+        v = u if all(a is b for a, b in zip(srcs, u.src)) else U.new(u.op, u.dtype, srcs, u.arg, u.tag)
+        if u.idx in chosen:
+            v = U.new(Op.CONTIGUOUS, v.dtype, (v,))
+        out[u.idx] = v
+    return [out[r.idx] for r in roots]
 
-    def wrap(u: U.UOp) -> U.UOp:
-        chain = []
-        while u.op in U.MOVEMENT:
-            chain.append(u)
-            u = u.src[0]
-        if u.op in (Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS, Op.CONST):
-            return None
-        v = U.new(Op.CONTIGUOUS, u.dtype, (u,))
-        for m in reversed(chain):
-            v = U.new(m.op, m.dtype, (v,), m.arg, m.tag)
-        return v
 
-    def rec(u: U.UOp) -> U.UOp:
-        r = memo.get(u.idx)
-        if r is not None:
-            return r
-        srcs = tuple(rec(s) for s in u.src)
-        if u.op == Op.REDUCE_AXIS and u.arg[0] == Op.ADD and srcs[0].op == Op.MUL:
-            m = srcs[0]
-            ops = [wrap(o) or o for o in m.src]
-            if any(a is not b for a, b in zip(ops, m.src)):
-                srcs = (U.new(Op.MUL, m.dtype, tuple(ops), m.arg, m.tag),)
-        r = u if all(a is b for a, b in zip(srcs, u.src)) else U.new(u.op, u.dtype, srcs, u.arg, u.tag)
-        memo[u.idx] = r
-        return r
-
-    import sys
-    sys.setrecursionlimit(max(sys.getrecursionlimit(), 100000))
-    return [rec(r) for r in roots]
+def _is_dense_contraction(body: U.UOp) -> bool:
+    return (body.op == Op.REDUCE and body.arg == Op.ADD and body.src[0].op == Op.MUL
+            and all(o.op == Op.INDEX for o in body.src[0].src))
 
 
 def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
-                    fusion: Optional[bool] = None) -> Tuple[List[ExecItem], Dict[int, int]]:
+                    fusion: Optional[bool] = None, keep_contractions: bool = False) -> Tuple[List[ExecItem], Dict[int, int]]:
     """Schedule the tensor-graph nodes ``outputs``.
 
     Returns the ordered items and a map from each output node's idx to the
     ``uop_idx`` of the buffer that holds it (the reference matches outputs to
-    tensors by schedule order instead, tensor/realize.go:152-181)."""
+    tensors by schedule order instead, tensor/realize.go:152-181).
+
+    ``keep_contractions`` leaves a dense SUM-of-products over two buffers as a kernel of its own
+    instead of splicing it into an elementwise consumer, so that it reaches the device as a plain
+    GEMM (used together with ``materialize_contraction_operands``)."""
     import sys
     sys.setrecursionlimit(max(sys.getrecursionlimit(), 100000))
     max_bufs = MAX_KERNEL_BUFFERS if max_bufs is None else max_bufs
@@ -377,6 +375,11 @@ def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
             if len(cons) != 1 or cons[0] == -1:
                 continue
             c = kernels[cons[0]]
+            if keep_contractions and _is_dense_contraction(k.body):
+                # a consumer that only re-indexes the contraction (a permuted copy of a weight
+                # gradient) folds into it and leaves a contraction; anything else stays separate
+                if not (c.body.op == Op.INDEX and c.body.src[0].idx == kid):
+                    continue
             if c.has_reduce or kid in reads_in_reduce[cons[0]]:
                 continue
             combined = (cur[cons[0]] - {kid}) | cur[kid]

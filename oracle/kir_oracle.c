@@ -324,7 +324,7 @@ static val eval(ectx *c, int i) {
     switch (n->op) {
     case OP_INDEX: r = eval_index(c, n); break;
     case OP_REDUCE: r = eval_reduce(c, n); break;
-    case OP_WHERE: r = eval(c, s[0]).i ? eval(c, s[1]) : eval(c, s[2]); break;
+    case OP_WHERE: r = eval(c, s[0]).i ? eval(c, s[1]) : eval(c, s[2]); if (n->cls == C_F16 && !n->widen) r.f = f16_round_f(r.f); break;
     case OP_CAST: {
         const node *sn = &nodes[s[0]]; val a = eval(c, s[0]);
         if (isf) { float x = as_f(sn, a); r.f = (n->cls == C_F16 && !n->widen) ? f16_round_f(x) : x; }
@@ -338,13 +338,15 @@ static val eval(ectx *c, int i) {
     case OP_SIN: r.f = fin(n, sinf(eval(c, s[0]).f)); break;
     case OP_SQRT: r.f = fin(n, n->cls == C_F16 && !n->widen ? sqrt((double)eval(c, s[0]).f) : (double)sqrtf(eval(c, s[0]).f)); break;
     case OP_RECIP: { float x = eval(c, s[0]).f; r.f = fin(n, n->cls == C_F16 && !n->widen ? 1.0 / (double)x : (double)(1.0f / x)); break; }
-    case OP_NEG: if (isf) r.f = -eval(c, s[0]).f; else r.i = -eval(c, s[0]).i; break;
+    case OP_NEG: if (isf) { float x = eval(c, s[0]).f; r.f = (n->cls == C_F16 && !n->widen) ? -f16_round_f(x) : -x; } else r.i = -eval(c, s[0]).i; break;
     case OP_TRUNC: r.f = truncf(eval(c, s[0]).f); break;
     case OP_ADD: case OP_SUB: case OP_MUL: case OP_FDIV: case OP_MAX: case OP_POW: {
         val a = eval(c, s[0]), b = eval(c, s[1]);
         if (isf) {
             if (n->cls == C_F16 && !n->widen) {
-                double x = a.f, y = b.f, z;
+                /* an operand shared with an f16 reduction carries its widened (f32) value: it is
+                 * narrowed where f16 code uses it */
+                double x = f16_round_f(a.f), y = f16_round_f(b.f), z;
                 switch (n->op) { case OP_ADD: z = x + y; break; case OP_SUB: z = x - y; break; case OP_MUL: z = x * y; break;
                                  case OP_FDIV: z = x / y; break; case OP_MAX: z = (x != x) ? y : (y != y) ? x : (x < y ? y : x); break; default: z = pow(x, y); }
                 r.f = f16_round_d(z);
@@ -362,7 +364,7 @@ static val eval(ectx *c, int i) {
         break; }
     case OP_MULACC: { /* (s0 + (s1 * s2)), codegen/wgsl.go:303-304 */
         val a = eval(c, s[0]), b = eval(c, s[1]), d = eval(c, s[2]);
-        if (isf) { if (n->cls == C_F16 && !n->widen) r.f = f16_round_d((double)a.f + (double)f16_round_d((double)b.f * (double)d.f)); else { float m = b.f * d.f; r.f = a.f + m; } }
+        if (isf) { if (n->cls == C_F16 && !n->widen) r.f = f16_round_d((double)f16_round_f(a.f) + (double)f16_round_d((double)f16_round_f(b.f) * (double)f16_round_f(d.f))); else { float m = b.f * d.f; r.f = a.f + m; } }
         else r.i = a.i + b.i * d.i;
         break; }
     case OP_IDIV: { val a = eval(c, s[0]), b = eval(c, s[1]);
