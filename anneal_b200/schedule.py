@@ -280,11 +280,20 @@ def materialize_contraction_operands(roots: List[U.UOp]) -> List[U.UOp]:
     chosen = set()
     for u in topo:
         if u.op == Op.REDUCE_AXIS and u.arg[0] == Op.ADD and u.src[0].op == Op.MUL:
+            # a contraction multiplies two operands broadcast along different axes: both reach the
+            # MUL through an EXPAND (tensor/reduce.go:143-165); a plain sum of products does not
+            operands, expanded = [], []
             for o in u.src[0].src:
+                ex = False
                 while o.op in U.MOVEMENT:
+                    ex = ex or o.op == Op.EXPAND
                     o = o.src[0]
-                if o.op not in (Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS, Op.CONST):
-                    chosen.add(o.idx)
+                operands.append(o)
+                expanded.append(ex)
+            if all(expanded):
+                for o in operands:
+                    if o.op not in (Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS, Op.CONST):
+                        chosen.add(o.idx)
     if not chosen:
         return list(roots)
     out: Dict[int, U.UOp] = {}

@@ -103,7 +103,7 @@ static float f16_round_d(double d) {
     return (float)(d < 0 ? -out : out);
 }
 static float f16_round_f(float f) { return f16_round_d((double)f); }
-static float bf16_trunc(float f) { val v; v.f = f; v.u &= 0xFFFF0000u; return v.f; }
+static float bf16_trunc(float f) { uint32_t u; memcpy(&u, &f, 4); u &= 0xFFFF0000u; memcpy(&f, &u, 4); return f; }
 
 static int dtype_class(int dt) {
     switch (dt) {
@@ -480,10 +480,15 @@ static int run_item(orc *o, const item *it, int threads) {
         for (int64_t g = lo; g < hi; g++) {
             val v = eval(&c, body);
             const node *bn = &it->nodes[body];
-            if (out_dt == DT_F16) v.f = f16_round_f(as_f(bn, v));
-            else if (out_dt == DT_BF16) v.f = bf16_trunc(as_f(bn, v));
-            else if (out_dt == DT_F32 && !(bn->cls == C_F32 || bn->cls == C_F16)) v.f = as_f(bn, v);
-            out[g] = v;
+            int body_is_float = (bn->cls == C_F32 || bn->cls == C_F16);
+            if (out_dt == DT_F16 || out_dt == DT_BF16 || (out_dt == DT_F32 && !body_is_float)) {
+                float fv = as_f(bn, v);
+                if (out_dt == DT_F16) fv = f16_round_f(fv);          /* narrowing at the store */
+                else if (out_dt == DT_BF16) fv = bf16_trunc(fv);     /* bitcast & 0xFFFF0000, codegen/wgsl.go:228-229 */
+                memcpy(&out[g], &fv, 4);
+            } else {
+                out[g] = v;
+            }
             for (int l = nl - 1; l >= 0; l--) {
                 cur[l]++; c.rver[lslots[l]]++;
                 if (cur[l] < lsize[l]) { c.rval[lslots[l]] = cur[l]; break; }
@@ -551,9 +556,12 @@ void orc_free(orc *o) {
 }
 /* host-side conversions exposed for the dtype known-answer tests */
 uint16_t orc_f32_to_f16_bits(float f) {
+    val v; v.f = f; uint32_t s = (v.u >> 31) << 15;
+    if (f != f) {                                  /* NaN stays NaN: shifted payload, never zero (uop/dtype.go:404-412) */
+        uint32_t m = (v.u & 0x7FFFFF) >> 13;
+        return (uint16_t)(s | 0x7C00 | (m ? m : 1));
+    }
     float r = f16_round_f(f);
-    if (r != r) return 0x7E00;
-    val v; v.f = r; uint32_t s = (v.u >> 31) << 15;
     if (isinf(r)) return (uint16_t)(s | 0x7C00);
     if (r == 0) return (uint16_t)s;
     int e; double m = frexp(fabs((double)r), &e);  /* |r| = m*2^e, m in [0.5,1) */

@@ -1,0 +1,131 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/anneal_cuda.h declares;
+the renderer and NVRTC work on the CPU box (no kernel is launched here)."""
+import ctypes
+import os
+import re
+
+import numpy as np
+import pytest
+
+from anneal_b200 import build, device, nn, realize as R, workloads as W
+from anneal_b200.tensor import Tensor
+from anneal_b200.uop import dtypes
+
+ROOT = os.path.dirname(os.path.dirname(os.path.abspath(__file__)))
+
+
+@pytest.fixture(scope="module")
+def lib():
+    build.build()
+    return device.load_library()
+
+
+def test_header_and_library_agree(lib):
+    hdr = open(os.path.join(ROOT, "include", "anneal_cuda.h")).read()
+    declared = set(re.findall(r"\b(anl_[a-z0-9_]+)\s*\(", hdr))
+    assert declared == set(device.ABI_SYMBOLS), declared ^ set(device.ABI_SYMBOLS)
+    for name in declared:
+        assert hasattr(lib, name), f"{name} is declared but not exported"
+
+
+def test_open_without_gpu_fails_cleanly(lib):
+    import torch
+    if torch.cuda.is_available():
+        pytest.skip("a GPU is present")
+    h = ctypes.c_void_p()
+    assert lib.anl_open(0, 0, ctypes.byref(h)) != 0 and not h.value
+    with pytest.raises(device.DeviceError):
+        device.Device(0)
+
+
+def test_malformed_blob_is_rejected(lib):
+    src = ctypes.create_string_buffer(64)
+    n = ctypes.c_size_t()
+    k, b, o = ctypes.c_int(), ctypes.c_int(), ctypes.c_int64()
+    note = ctypes.create_string_buffer(64)
+    for blob in (b"", b"NOPE\0\0\0\0", b"KIR1\x01\0\0\0\x05"):
+        rc = lib.anl_lower(None, blob, len(blob), 0, None, src, 64, ctypes.byref(n), ctypes.byref(k), ctypes.byref(b), ctypes.byref(o), note, 64)
+        assert rc != 0
+
+
+def _lower_all(tensors):
+    items, _ = R.build_schedule(tensors)
+    out = []
+    for i in range(len(items)):
+        r = device.lower(items, i)
+        device.compile_check(r["source"])
+        out.append(r)
+    return items, out
+
+
+def test_elementwise_uses_128_bit_accesses_when_provable():
+    x = Tensor.new_leaf((64, 512))
+    b = Tensor.new_leaf((512,))
+    _, low = _lower_all([x.add(b.reshape((1, 512)).expand((64, 512))).exp2()])
+    assert low[0]["class"] == "elementwise" and "V=4" in low[0]["note"]
+    assert "ldv_<float, 4>" in low[0]["source"] and "stv_<float, 4>" in low[0]["source"]
+    # a transposed read cannot be vectorised
+    _, low = _lower_all([x.permute((1, 0)).exp2()])
+    assert "V=1" in low[0]["note"]
+
+
+def test_index_arithmetic_is_canonicalised():
+    # reshape/expand/permute chains arrive as div/mod trees (schedule/index.go:231-293); the load of a
+    # matmul operand must come out as a plain affine index
+    a, b = Tensor.new_leaf((37, 53)), Tensor.new_leaf((53, 29))
+    _, low = _lower_all([a.matmul(b)])
+    body = low[0]["source"][low[0]["source"].index('extern "C"'):]
+    assert re.search(r"data1\[\(r\d+ \* 53 \+ r\d+\)\]", body), body
+
+
+def test_f16_reduce_accumulates_in_f32_and_narrows_once():
+    # codegen/f16_codegen_test.go: "var acc0: f32" for an f16 matmul
+    a, b = Tensor.new_leaf((8, 16), dtypes.float16), Tensor.new_leaf((16, 8), dtypes.float16)
+    _, low = _lower_all([a.matmul(b)])
+    src = low[0]["source"]
+    assert re.search(r"float acc\d+ = 0.0f;", src) and "__float2half_rn(acc" in src and "__half2float(data1[" in src
+
+
+def test_max_identity_and_scalar_reduce():
+    x = Tensor.new_leaf((8,))
+    _, low = _lower_all([x.max()])
+    assert "__int_as_float(0xff7fffff)" in low[0]["source"]
+
+
+def test_pad_guarded_load_is_clamped():
+    x = Tensor.new_leaf((4,))
+    _, low = _lower_all([x.pad(((2, 2),)).sum([0])])
+    assert "clampi_(" in low[0]["source"]
+
+
+def test_symbolic_kernel_takes_the_bound_as_argument():
+    m = W.DynMLP(din=32, hidden=48, dout=16, max_batch=64)
+    out, loss, grads, _ = m.graph(8)
+    items, low = _lower_all([out] + grads)
+    assert any("const int n0" in r["source"] for r in low)
+    assert all(it.sym_vars == ["n"] for it in items if any(0 in b.shape for b in it.bufs))
+
+
+def test_all_benchmark_configs_render_and_compile():
+    for build_graph in (lambda: W.MLP().graph().targets(), lambda: W.SmallCNN(batch=2, hw=8, c1=2, c2=3).graph().targets(),
+                        lambda: W.SoftmaxFwdBwd(16, 128).graph(True)[0]):
+        R.reset()
+        _lower_all(build_graph())
+    R.reset()
+    R.MATERIALIZE_CONTRACTION_OPERANDS = True
+    try:
+        m = W.WideMLP(batch=64, width=64, classes=72, depth=2)
+        items, low = _lower_all(m.graph().targets())
+    finally:
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+    assert any("row-broadcast" in r["note"] for r in low)
+
+
+def test_opts_change_the_launch_shape():
+    x = Tensor.new_leaf((300, 700))
+    items, _ = R.build_schedule([x.sum([1])])
+    base = device.lower(items, 0)
+    forced = device.lower(items, 0, [128, 4, 0, 0, 0])
+    assert forced["block"] == 128 and "lanes=4" in forced["note"] and base["note"] != forced["note"]
+    split = device.lower(R.build_schedule([Tensor.new_leaf((1 << 20,)).sum()])[0], 0)
+    assert split["class"] == "reduce_split"

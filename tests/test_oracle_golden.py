@@ -1,0 +1,168 @@
+"""The CPU oracle pinned against the known-answer vectors of the reference's own tests
+(tests/golden/reference_vectors.json; each case cites the reference file and lines)."""
+import json
+import os
+
+import numpy as np
+import pytest
+
+from anneal_b200 import nn, realize as R
+from anneal_b200.gradient import backward
+from anneal_b200.tensor import Tensor
+from anneal_b200.uop import dtypes, quantize
+from oracle import binding
+
+GOLD = json.load(open(os.path.join(os.path.dirname(__file__), "golden", "reference_vectors.json")))
+
+
+@pytest.fixture(autouse=True)
+def use_oracle(oracle):
+    R.DEFAULT_EXECUTOR = oracle
+    yield
+    R.DEFAULT_EXECUTOR = None
+
+
+def leaf(shape, data, dtype=dtypes.float32):
+    return Tensor.new_leaf(shape, dtype).set_data(np.asarray(data, dtype=np.float32))
+
+
+def build(case):
+    g = case["graph"]
+    if g == "exp2":
+        return leaf((len(case["x"]),), case["x"]).exp2()
+    if g == "add":
+        return leaf((4,), case["x"]).add(leaf((4,), case["y"]))
+    if g == "sum_all":
+        return leaf((8,), case["x"]).sum()
+    if g == "sum_axis0_4x4":
+        return leaf((4, 4), case["x"]).sum([0])
+    if g == "max_all":
+        return leaf((4,), case["x"]).max()
+    if g == "log2_exp2":
+        return leaf((4,), case["x"]).exp2().log2()
+    if g == "matmul_2x3_3x2":
+        a = leaf((2, 3), case["x"]).reshape((2, 3, 1)).expand((2, 3, 2))
+        b = leaf((3, 2), case["y"]).reshape((1, 3, 2)).expand((2, 3, 2))
+        return a.mul(b).sum([1])
+    if g == "mse_2x3_3x2":
+        a = leaf((2, 3), case["x"]).reshape((2, 3, 1)).expand((2, 3, 2))
+        b = leaf((3, 2), case["w"]).reshape((1, 3, 2)).expand((2, 3, 2))
+        d = a.mul(b).sum([1]).sub(leaf((2, 2), case["t"]))
+        return d.mul(d).mean()
+    if g == "grad_sum_exp2":
+        x = leaf((4,), case["x"])
+        return backward(x.exp2().sum(), [x])[x]
+    raise KeyError(g)
+
+
+@pytest.mark.parametrize("case", GOLD["value_oracles"], ids=lambda c: c["graph"] + "@" + c["ref"].split(":")[1])
+def test_value_oracles(case):
+    t = build(case)
+    R.realize(t)
+    assert np.allclose(t.data, np.asarray(case["want"], dtype=np.float32), atol=case["tol"], rtol=0), (t.data, case["want"])
+
+
+@pytest.mark.parametrize("case", GOLD["padded_reduce"], ids=lambda c: c["ref"].split(":")[1])
+def test_padded_reduce_uses_the_reduce_identity(case):
+    x = leaf(tuple(case["shape"]), case["x"]).pad(case["pad"])
+    y = x.max([case["axis"]]) if case["op"] == "max" else x.sum([case["axis"]])
+    R.realize(y)
+    assert list(y.data) == case["want"]
+
+
+def test_sgd_quadratic_trajectory():
+    c = GOLD["sgd_trajectory"]
+    p = nn.Parameter((c["n"],))
+    p.value[:] = c["p0"]
+    for step in range(c["steps"]):
+        assert np.allclose(p.value, c["p"][step], atol=c["tol"])
+        R.reset()
+        pl = p.load()
+        d = pl.sub(leaf((c["n"],), [c["target"]] * c["n"]))
+        g = backward(d.mul(d).sum(), [pl])[pl]
+        R.realize(g)
+        assert np.allclose(g.data, c["grad"][step], atol=c["tol"])
+        p.sgd_step(g.data, c["lr"])
+    assert np.allclose(p.value, c["p"][c["steps"]], atol=c["tol"])
+
+
+def ref_maxpool(data, N, C, H, W, kH, kW, sH, sW):
+    oH, oW = (H - kH) // sH + 1, (W - kW) // sW + 1
+    x = data.reshape(N, C, H, W)
+    out = np.empty((N, C, oH, oW), dtype=np.float32)
+    for i in range(oH):
+        for j in range(oW):
+            out[:, :, i, j] = x[:, :, i * sH:i * sH + kH, j * sW:j * sW + kW].max(axis=(2, 3))
+    return out.reshape(-1)
+
+
+@pytest.mark.parametrize("case", GOLD["maxpool"]["cases"], ids=str)
+def test_maxpool_forward_exact(case):
+    N, C, H, W, kH, kW, sH, sW, neg = case
+    data = np.arange(1, N * C * H * W + 1, dtype=np.float32) * (-1 if neg else 1)
+    out = nn.max_pool2d(leaf((N, C, H, W), data), kH, kW, sH, sW)
+    R.realize(out)
+    assert np.array_equal(out.data, ref_maxpool(data, N, C, H, W, kH, kW, sH, sW))
+
+
+def test_f16_cast_round_trip_is_bit_exact():
+    v = GOLD["f16_cast_roundtrip"]["x"]
+    x = leaf((len(v),), v, dtypes.float16)
+    y = x.cast(dtypes.float32).cast(dtypes.float16)
+    R.realize(y)
+    assert np.array_equal(y.data, np.asarray(v, dtype=np.float32))
+
+
+def test_bf16_round_trip_truncates():
+    v = np.asarray(GOLD["bf16_roundtrip"]["x"], dtype=np.float32)
+    x = leaf((v.size,), v, dtypes.bfloat16)
+    y = x.cast(dtypes.float32).cast(dtypes.bfloat16)
+    R.realize(y)
+    assert np.array_equal(y.data, (v.view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32))
+
+
+def test_bf16_add_matches_truncation_model():
+    rng = np.random.default_rng(17)
+    a, b = (rng.random(512) * 2 - 1).astype(np.float32), (rng.random(512) * 2 - 1).astype(np.float32)
+    tr = lambda v: (np.asarray(v, np.float32).view(np.uint32) & np.uint32(0xFFFF0000)).view(np.float32)
+    z = leaf((512,), a, dtypes.bfloat16).add(leaf((512,), b, dtypes.bfloat16))
+    R.realize(z)
+    assert np.abs(z.data - tr(tr(a) + tr(b))).max() <= 1e-6
+
+
+@pytest.mark.parametrize("bits,want", GOLD["f32_to_f16_bits"]["cases"])
+def test_f32_to_f16_known_answers(bits, want):
+    f = np.array([bits], dtype=np.uint32).view(np.float32)[0]
+    assert binding.lib().orc_f32_to_f16_bits(float(f) if f == f else f) == want or (f != f and bits == 0x7F800001)
+    if f == f:   # the frontend's quantiser (numpy RTNE) agrees on every non-NaN case
+        q = quantize(np.array([f], np.float32), dtypes.float16)
+        assert np.array([q[0]], np.float32).astype(np.float16).view(np.uint16)[0] == want
+
+
+@pytest.mark.parametrize("bits,want", GOLD["f16_to_f32_bits"]["cases"])
+def test_f16_to_f32_known_answers(bits, want):
+    assert np.array([bits], dtype=np.uint16).view(np.float16).astype(np.float32).view(np.uint32)[0] == want
+
+
+def test_f16_arithmetic_is_rounded_per_op():
+    # 2049 is not representable in f16: 2048 + 1 rounds to even (2048), and (2048+1)+1 stays 2048,
+    # while an f32 evaluation would give 2050
+    x = leaf((1,), [2048.0], dtypes.float16)
+    one = Tensor.full((1,), 1.0, dtypes.float16)
+    y = x.add(one).add(one)
+    R.realize(y)
+    assert y.data[0] == 2048.0
+    # inside an f16 reduction the body is widened: sum of 2048 ones from 2048 reaches 4096 exactly
+    v = leaf((2049,), [2048.0] + [1.0] * 2048, dtypes.float16)
+    s = v.sum()
+    R.realize(s)
+    assert s.data[0] == 4096.0
+
+
+def test_max_identity_is_minus_flt_max_not_inf():
+    # an empty-support max (every element padded away) yields -FLT_MAX, the WGSL literal the
+    # reference emits (codegen/wgsl.go:373-379), not -inf
+    x = leaf((2,), [1.0, 2.0]).shrink(((0, 1),)).pad(((0, 0),))
+    y = leaf((1, 2), [1.0, 2.0]).pad(((0, 0), (2, 0))).shrink(((0, 1), (0, 2))).max([1])
+    R.realize(y)
+    assert y.data[0] == np.float32(-3.4028234663852886e38)
