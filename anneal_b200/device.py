@@ -109,6 +109,7 @@ def load_library():
     L.anl_timer_stop.argtypes = [vp, C.POINTER(C.c_float)]
     L.anl_profile_enable.argtypes = [vp, i]
     L.anl_profile_read.argtypes = [vp, C.POINTER(_Prof), i, C.POINTER(i)]
+    L.anl_sum_f32_static.argtypes = [vp, C.c_int64, vp, vp, C.c_char_p, C.c_size_t]
     L.anl_host_alloc.argtypes = [C.c_size_t, C.POINTER(vp)]
     L.anl_host_free.argtypes = [vp]
     L.anl_host_free.restype = None
@@ -123,7 +124,7 @@ ABI_SYMBOLS = [
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
     "anl_comm_destroy", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
-    "anl_profile_enable", "anl_profile_read",
+    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static",
 ]
 
 KERNEL_CLASSES = {0: "elementwise", 1: "reduce", 2: "reduce_split", 3: "gemm", 4: "raw"}

@@ -174,6 +174,17 @@ typedef struct { int klass; int launches; double total_ms; double flops; } anl_p
 int anl_profile_enable(anl_device* dev, int on);
 int anl_profile_read(anl_device* dev, anl_profile_entry* out, int cap, int* n);
 
+/* ── sum of an f32 device array without touching the allocator (no counterpart in the reference) ──
+ * For callers that cannot allocate: a host whose own pool already owns all device memory, or a loop
+ * that cannot take cudaMalloc's device-wide synchronisation.  `x` (n values) and `out` (1 value) are
+ * device pointers the caller owns; the work is queued on `stream` (a cudaStream_t, NULL for the
+ * default stream) and is not waited for.  The two-stage reduction keeps its partials in a 4 KiB
+ * array that is part of the library image on every GPU, so n is limited to [1, 2^30]; other sizes
+ * return ANL_ERR_LIMIT with the reason in `err`.  The first call on each device also looks up that
+ * array's address, so make it before starting any stream capture.  All calls on a device share the
+ * array: two calls whose kernels can overlap (different streams) race; calls on one stream do not. */
+int anl_sum_f32_static(const float* x, int64_t n, float* out, void* stream, char* err, size_t err_cap);
+
 /* blocks until all work queued on the device has finished */
 int anl_synchronize(anl_device* dev);
 
