@@ -1,0 +1,215 @@
+// Autotuning of generated kernels: the reference's BEAM search (codegen/beam.go:271-406) over the
+// retargeted transform space.  The reference widens a frontier of at most `width` candidates by
+// applying one more opt (Local / Tile / Upcast / Vectorize on some axis) per depth level, rejects
+// any candidate whose output differs from the untransformed kernel's, times the rest (min of 5
+// after 2 warm-ups, codegen/beam.go:241) and stops when a level brings no improvement.  Here a
+// candidate is a CodegenOpts tuple {threads per block, lanes per reduction, vector width, split}
+// and one step changes one knob.  Two differences, both forced by parallel reductions: timing
+// uses CUDA events, and the guard is bit-identity only for kernels without a REDUCE; kernels with
+// one are compared to 1e-4 of the output's largest magnitude, because lanes change the order of
+// the f32 additions.  Results persist in a line-per-entry JSON file keyed by the kernel's
+// structure hash and guarded by the hash of its default source (codegen/beam.go:147-190).
+#include <algorithm>
+#include <cmath>
+#include <cstdio>
+#include <cstdlib>
+#include <cstring>
+#include <fstream>
+#include <sstream>
+
+#include "runtime.hpp"
+
+namespace anl {
+
+namespace {
+
+struct Cand { int o[4]; double us; };
+
+std::string default_cache_path() {
+    const char* x = std::getenv("ANNEAL_BEAM_CACHE");
+    if (x && *x) return x;
+    const char* c = std::getenv("XDG_CACHE_HOME");
+    std::string base = (c && *c) ? c : (std::string(std::getenv("HOME") ? std::getenv("HOME") : "/tmp") + "/.cache");
+    return base + "/anneal/beam_cache_cuda.json";
+}
+
+CodegenOpts to_opts(const int* o, bool debug) {
+    CodegenOpts c; c.block_threads = o[0]; c.reduce_lanes = o[1]; c.vector_width = o[2]; c.split = o[3]; c.debug_bounds = debug;
+    return c;
+}
+
+// deterministic inputs of the reference's search: ((j + i*17) % 13 + 1) * 0.01 (codegen/beam.go:410-420)
+void fill(std::vector<float>& v, int buf_index) {
+    for (size_t j = 0; j < v.size(); j++) v[j] = (float)(((long long)j + (long long)buf_index * 17) % 13 + 1) * 0.01f;
+}
+
+int time_plan(anl_device* dev, const Plan& plan, const Item& it, std::vector<void*>& ptrs, double* us) {
+    cudaEvent_t e0, e1;
+    cudaEventCreate(&e0); cudaEventCreate(&e1);
+    double best = 1e30;
+    int rc = ANL_OK;
+    for (int i = 0; i < 7 && rc == ANL_OK; i++) {
+        cudaEventRecord(e0, dev->stream);
+        rc = launch_plan(dev, plan, it, ptrs.data(), 0, dev->stream, nullptr);
+        cudaEventRecord(e1, dev->stream);
+        if (cudaEventSynchronize(e1) != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, "beam: kernel failed");
+        float ms = 0; cudaEventElapsedTime(&ms, e0, e1);
+        if (i >= 2) best = std::min(best, (double)ms * 1000.0);
+    }
+    cudaEventDestroy(e0); cudaEventDestroy(e1);
+    *us = best;
+    return rc;
+}
+
+}  // namespace
+
+bool beam_cache_lookup(anl_device* dev, uint64_t key, uint64_t src_hash, int* opts) {
+    auto it = dev->beam_cache.find(key);
+    if (it == dev->beam_cache.end() || it->second.src_hash != src_hash) return false;   // collision guard
+    std::memcpy(opts, it->second.opts, sizeof(int) * 4);
+    return true;
+}
+
+void beam_cache_load(anl_device* dev, const std::string& path_in) {
+    std::string path = path_in.empty() ? default_cache_path() : path_in;
+    dev->beam_cache_path = path;
+    std::ifstream f(path);
+    std::string line;
+    while (std::getline(f, line)) {
+        unsigned long long k = 0, s = 0; int o[4]; double us = 0;
+        if (std::sscanf(line.c_str(), "{\"key\":\"%llx\",\"src\":\"%llx\",\"opts\":[%d,%d,%d,%d],\"us\":%lf}", &k, &s, &o[0], &o[1], &o[2], &o[3], &us) == 7) {
+            anl_device::BeamEntry e; e.src_hash = s; std::memcpy(e.opts, o, sizeof o); e.us = us;
+            dev->beam_cache[k] = e;
+        }
+    }
+}
+
+static void beam_cache_store(anl_device* dev, uint64_t key, uint64_t src_hash, const int* o, double us) {
+    anl_device::BeamEntry e; e.src_hash = src_hash; std::memcpy(e.opts, o, sizeof(int) * 4); e.us = us;
+    dev->beam_cache[key] = e;
+    if (dev->beam_cache_path.empty()) dev->beam_cache_path = default_cache_path();
+    std::string dir = dev->beam_cache_path.substr(0, dev->beam_cache_path.find_last_of('/'));
+    std::string cmd = "mkdir -p '" + dir + "'";
+    if (std::system(cmd.c_str()) != 0) return;
+    std::ofstream f(dev->beam_cache_path, std::ios::trunc);
+    for (auto& kv : dev->beam_cache) {
+        char b[256];
+        std::snprintf(b, sizeof b, "{\"key\":\"%016llx\",\"src\":\"%016llx\",\"opts\":[%d,%d,%d,%d],\"us\":%.3f}\n",
+                      (unsigned long long)kv.first, (unsigned long long)kv.second.src_hash, kv.second.opts[0], kv.second.opts[1], kv.second.opts[2], kv.second.opts[3], kv.second.us);
+        f << b;
+    }
+}
+
+int beam_search(anl_device* dev, const Item& it, int width, int depth, anl_beam_result* out) {
+    std::memset(out, 0, sizeof *out);
+    for (auto& b : it.bufs) if (b.symbolic()) return dev->fail(ANL_ERR_UNSUPPORTED, "beam: symbolic ranges are not searched (codegen/opt.go:108-111)");
+    if (!it.source.empty()) return dev->fail(ANL_ERR_UNSUPPORTED, "beam: pre-rendered items are not searched");
+    bool debug = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;
+    if (width <= 0) width = 4;
+    if (depth <= 0) depth = 4;
+    int base_o[4] = {0, 0, 0, 0};
+    Rendered base_r; std::string err;
+    if (!render_cuda(it, to_opts(base_o, debug), base_r, err)) return dev->fail(ANL_ERR_UNSUPPORTED, err);
+    uint64_t key = structure_hash(it), src_hash = fnv1a(base_r.source.data(), base_r.source.size());
+    int cached[4];
+    if (beam_cache_lookup(dev, key, src_hash, cached)) {
+        std::memcpy(out->opts, cached, sizeof cached);
+        out->from_cache = 1; out->best_us = dev->beam_cache[key].us;
+        return ANL_OK;
+    }
+    bool has_reduce = base_r.klass != KC_ELEMENTWISE;
+
+    // buffers: inputs filled deterministically, one output per candidate run
+    std::vector<void*> ptrs(it.bufs.size(), nullptr);
+    int rc = ANL_OK;
+    for (size_t b = 0; b < it.bufs.size() && rc == ANL_OK; b++) {
+        int64_t n = it.bufs[b].elems(0);
+        rc = dev->alloc((size_t)n * dt_storage_bytes(it.bufs[b].dtype), &ptrs[b]);
+        if (rc == ANL_OK && b > 0) {
+            std::vector<float> h((size_t)n); fill(h, (int)b);
+            rc = upload_f32(dev, ptrs[b], it.bufs[b].dtype, h.data(), n, dev->stream);
+            cudaStreamSynchronize(dev->stream);
+        }
+    }
+    int64_t on = it.bufs[0].elems(0);
+    std::vector<float> ref((size_t)on), got((size_t)on);
+    auto run_one = [&](const int* o, double* us, std::vector<float>& result) -> int {
+        std::shared_ptr<Plan> p;
+        unsigned saved = dev->flags; dev->flags |= ANL_OPEN_NO_GEMM;      // search the generated kernel, not the routing
+        int r = get_plan(dev, it, to_opts(o, debug), p);
+        dev->flags = saved;
+        if (r) return r;
+        cudaMemsetAsync(ptrs[0], 0xFF, (size_t)on * dt_storage_bytes(it.bufs[0].dtype), dev->stream);
+        if ((r = time_plan(dev, *p, it, ptrs, us))) return r;
+        if ((r = download_f32(dev, result.data(), ptrs[0], it.bufs[0].dtype, on, dev->stream))) return r;
+        return cudaStreamSynchronize(dev->stream) == cudaSuccess ? ANL_OK : dev->fail(ANL_ERR_CUDA, "beam: sync failed");
+    };
+    double base_us = 0;
+    if (rc == ANL_OK) rc = run_one(base_o, &base_us, ref);
+    if (rc == ANL_OK) {
+        double scale = 0;
+        for (float v : ref) scale = std::max(scale, (double)std::fabs(v));
+        auto accept = [&](const std::vector<float>& g) {
+            if (!has_reduce) return std::memcmp(g.data(), ref.data(), g.size() * 4) == 0;
+            double worst = 0;
+            for (size_t i = 0; i < g.size(); i++) { double d = std::fabs((double)g[i] - ref[i]); if (!(d <= worst)) worst = d; }
+            return worst <= 1e-4 * std::max(scale, 1e-30);
+        };
+        const int threads_v[] = {64, 128, 256, 512, 1024};
+        const int lanes_v[] = {1, 2, 4, 8, 16, 32, 64, 128, 256, 512, 1024};
+        const int vec_v[] = {1, 4, 8};
+        const int split_v[] = {1, 2, 8, 32, 128, 512};
+        std::vector<Cand> frontier = {Cand{{0, 0, 0, 0}, base_us}};
+        Cand best = frontier[0];
+        std::vector<std::string> seen = {"0,0,0,0"};
+        for (int d = 0; d < depth; d++) {
+            std::vector<Cand> next;
+            for (const Cand& c : frontier) {
+                auto try_set = [&](int knob, int value) {
+                    Cand n = c; n.o[knob] = value;
+                    if (n.o[1] > 0 && n.o[0] > 0 && n.o[1] > n.o[0]) return;
+                    char k[64]; std::snprintf(k, sizeof k, "%d,%d,%d,%d", n.o[0], n.o[1], n.o[2], n.o[3]);
+                    if (std::find(seen.begin(), seen.end(), k) != seen.end()) return;
+                    seen.push_back(k);
+                    out->candidates_tried++;
+                    double us = 0;
+                    if (run_one(n.o, &us, got) != ANL_OK || !accept(got)) { out->candidates_rejected++; return; }
+                    n.us = us;
+                    next.push_back(n);
+                };
+                for (int v : threads_v) try_set(0, v);
+                if (has_reduce) { for (int v : lanes_v) try_set(1, v); for (int v : split_v) try_set(3, v); }
+                else for (int v : vec_v) try_set(2, v);
+            }
+            if (next.empty()) break;
+            std::sort(next.begin(), next.end(), [](const Cand& a, const Cand& b) { return a.us < b.us; });
+            if ((int)next.size() > width) next.resize(width);
+            if (next[0].us >= best.us) break;              // no improvement at this depth
+            best = next[0];
+            frontier = next;
+        }
+        std::memcpy(out->opts, best.o, sizeof best.o);
+        out->base_us = base_us; out->best_us = best.us;
+        beam_cache_store(dev, key, src_hash, best.o, best.us);
+        dev->err.clear();
+    }
+    for (void* p : ptrs) dev->release(p);
+    return rc;
+}
+
+}  // namespace anl
+
+extern "C" int anl_beam_search(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, int width, int depth,
+                               const char* cache_path, anl_beam_result* out) {
+    if (!dev || !out) return ANL_ERR_INVALID;
+    cudaSetDevice(dev->ordinal);
+    std::vector<anl::Item> items; std::string perr;
+    if (!anl::parse_kir(blob, blob_len, items, perr)) return dev->fail(ANL_ERR_INVALID, perr);
+    if (index < 0 || index >= (int)items.size()) return dev->fail(ANL_ERR_INVALID, "beam: item index out of range");
+    if (!dev->beam_loaded || (cache_path && dev->beam_cache_path != cache_path)) {
+        dev->beam_cache.clear();
+        anl::beam_cache_load(dev, cache_path ? cache_path : "");
+        dev->beam_loaded = true;
+    }
+    return anl::beam_search(dev, items[index], width, depth, out);
+}

@@ -817,6 +817,8 @@ struct Gen {
         for (int i = 0; i < n; i++) if (N(i).op == OP_INDEX && i != dst && is_live(i)) idx_nodes.push_back(i);
         for (int i : idx_nodes) if (dt_storage_bytes(it.bufs[(int)N(N(i).src[0]).arg].dtype) != 2) { all16 = false; }
         int V = opts.vector_width > 1 ? opts.vector_width : (all16 ? 8 : 4);
+        if (!all16 && V > 4) V = 4;            // one access is at most 128 bits
+        if (V != 4 && V != 8 && V != 2) V = all16 ? 8 : 4;
         if (N(rv).arg % V != 0) return 1;
         vloads.clear();
         for (int i : idx_nodes) {

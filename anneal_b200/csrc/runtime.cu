@@ -340,7 +340,7 @@ int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings&
         DevBuf d; d.dtype = o.dtype; d.elems = o.elems(sym); d.bytes = (size_t)d.elems * dt_storage_bytes(o.dtype);
         if (o.slot >= 0) d.ptr = slot_ptr[o.slot];
         else {
-            bool is_final = !t.read.count(o.id);
+            bool is_final = true;
             const anl_output* pl = nullptr;
             for (int k = 0; k < n_placed; k++) if (placed[k].uop_idx == o.id && placed[k].resident) pl = &placed[k];
             if (is_final && pl) {
@@ -377,7 +377,8 @@ int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings&
             t.bufs[bd.id] = d;
         }
     }
-    for (auto& it : items) if (!t.read.count(it.bufs[0].id)) t.finals.push_back(it.bufs[0].id);
+    // final outputs: never read again, or read again but deliberately left un-aliased by the planner
+    for (auto& it : items) if (!t.read.count(it.bufs[0].id) || it.bufs[0].slot < 0) t.finals.push_back(it.bufs[0].id);
     return ANL_OK;
 }
 
@@ -386,7 +387,23 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
     for (size_t i = 0; i < items.size(); i++) {
         const Item& it = items[i];
         std::shared_ptr<Plan> plan;
-        if (int rc = get_plan(dev, it, opts, plan)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
+        CodegenOpts use = opts;
+        if ((dev->flags & ANL_OPEN_BEAM) && it.source.empty()) {
+            // BeamApplyToItems (codegen/beam.go:470-541): cached winner, else search now
+            bool sym = false; for (auto& b : it.bufs) if (b.symbolic()) sym = true;
+            Contraction c;
+            bool gemm = !(dev->flags & ANL_OPEN_NO_GEMM) && match_contraction(it, c) && c.in_dtype == DT_F16;
+            if (!sym && !gemm) {
+                if (!dev->beam_loaded) { beam_cache_load(dev, ""); dev->beam_loaded = true; }
+                anl_beam_result br;
+                cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
+                cudaStreamIsCapturing(stream, &cs);
+                if (cs == cudaStreamCaptureStatusNone && beam_search(dev, it, 0, 0, &br) == ANL_OK) {
+                    use.block_threads = br.opts[0]; use.reduce_lanes = br.opts[1]; use.vector_width = br.opts[2]; use.split = br.opts[3];
+                }
+            }
+        }
+        if (int rc = get_plan(dev, it, use, plan)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
         std::vector<void*> ptrs;
         for (auto& b : it.bufs) ptrs.push_back(t.bufs[b.id].ptr);
         if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }

@@ -71,6 +71,10 @@ struct anl_device {
     bool profiling = false;
     struct ProfRec { cudaEvent_t e0, e1; int klass; double flops; };
     std::vector<ProfRec> prof;
+    struct BeamEntry { uint64_t src_hash = 0; int opts[4] = {0, 0, 0, 0}; double us = 0; };
+    std::unordered_map<uint64_t, BeamEntry> beam_cache;
+    std::string beam_cache_path;
+    bool beam_loaded = false;
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
 
@@ -98,6 +102,11 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 // dense SUM-of-products over buffers that they cover, ANL_ERR_UNSUPPORTED otherwise
 int plan_gemm(anl_device* dev, const Item& item, Plan& plan);
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream);
-double gemm_flops(const Plan& plan);   // 2*M*N*K of a routed contraction
+double gemm_flops(const Plan& plan);
+
+// autotuning (beam.cpp)
+int beam_search(anl_device* dev, const Item& it, int width, int depth, anl_beam_result* out);
+void beam_cache_load(anl_device* dev, const std::string& path);
+bool beam_cache_lookup(anl_device* dev, uint64_t key, uint64_t src_hash, int* opts);   // 2*M*N*K of a routed contraction
 
 }  // namespace anl

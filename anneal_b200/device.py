@@ -52,6 +52,11 @@ class _Prof(C.Structure):
     _fields_ = [("klass", C.c_int), ("launches", C.c_int), ("total_ms", C.c_double), ("flops", C.c_double)]
 
 
+class _Beam(C.Structure):
+    _fields_ = [("opts", C.c_int * 4), ("base_us", C.c_double), ("best_us", C.c_double), ("tried", C.c_int),
+                ("rejected", C.c_int), ("from_cache", C.c_int)]
+
+
 class _Info(C.Structure):
     _fields_ = [("name", C.c_char * 128), ("sm_major", C.c_int), ("sm_minor", C.c_int), ("sm_count", C.c_int),
                 ("total_mem", C.c_size_t), ("has_f16", C.c_int), ("has_bf16", C.c_int), ("has_tcgen05", C.c_int)]
@@ -110,6 +115,7 @@ def load_library():
     L.anl_profile_enable.argtypes = [vp, i]
     L.anl_profile_read.argtypes = [vp, C.POINTER(_Prof), i, C.POINTER(i)]
     L.anl_sum_f32_static.argtypes = [vp, C.c_int64, vp, vp, C.c_char_p, C.c_size_t]
+    L.anl_beam_search.argtypes = [vp, u8p, C.c_size_t, i, i, i, C.c_char_p, C.POINTER(_Beam)]
     L.anl_host_alloc.argtypes = [C.c_size_t, C.POINTER(vp)]
     L.anl_host_free.argtypes = [vp]
     L.anl_host_free.restype = None
@@ -124,7 +130,7 @@ ABI_SYMBOLS = [
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
     "anl_comm_destroy", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
-    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static",
+    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search",
 ]
 
 KERNEL_CLASSES = {0: "elementwise", 1: "reduce", 2: "reduce_split", 3: "gemm", 4: "raw"}
@@ -204,6 +210,7 @@ class Device:
 
     DEBUG_BOUNDS = 1
     NO_GEMM = 2
+    BEAM = 4
 
     def __init__(self, ordinal: Optional[int] = None, flags: int = 0):
         self.L = load_library()
@@ -211,6 +218,8 @@ class Device:
             ordinal = int(os.environ.get("ANNEAL_CUDA_DEVICE", os.environ.get("LOCAL_RANK", "0")))
         if os.environ.get("ANNEAL_CUDA_DEBUG_BOUNDS") == "1":
             flags |= self.DEBUG_BOUNDS
+        if os.environ.get("ANNEAL_BEAM") == "1":      # the reference's switch (codegen/beam.go:471)
+            flags |= self.BEAM
         h = C.c_void_p()
         rc = self.L.anl_open(ordinal, flags, C.byref(h))
         if rc:
@@ -325,6 +334,15 @@ class Device:
         o = (C.c_int * 5)(*(list(opts) + [0] * 5)[:5]) if opts else None
         self._check(self.L.anl_benchmark(self.h, blob, len(blob), 0, o, warmup, iterations, C.byref(r)))
         return {n: getattr(r, n) for n, _ in _Bench._fields_}
+
+    def beam_search(self, item, width: int = 4, depth: int = 4, cache_path: Optional[str] = None):
+        """codegen.BeamSearch for one kernel; returns the winning transform and its timing."""
+        blob = kir.serialize([item])
+        r = _Beam()
+        self._check(self.L.anl_beam_search(self.h, blob, len(blob), 0, width, depth,
+                                           cache_path.encode() if cache_path else None, C.byref(r)))
+        return {"opts": list(r.opts), "base_us": r.base_us, "best_us": r.best_us, "tried": r.tried,
+                "rejected": r.rejected, "from_cache": bool(r.from_cache)}
 
     # ── residency / optimiser / data parallel ────────────────────────────
     def buffer(self, dtype, elems) -> ResidentBuffer:

@@ -497,7 +497,8 @@ def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
                 ready.append(j)
         ready.sort()
     assert len(ordered) == n, "schedule: dependency cycle"
-    memory_plan(ordered)
+    out_map_ids = {out_buf[placeholders[o.idx].idx].idx for o in outputs}
+    memory_plan(ordered, out_map_ids)
     out_map = {o.idx: out_buf[placeholders[o.idx].idx].idx for o in outputs}
     return ordered, out_map
 
@@ -516,14 +517,17 @@ def _substitute_bufs(root: U.UOp, pmap: Dict[int, U.UOp]) -> U.UOp:
     return out[root.idx]
 
 
-def memory_plan(items: List[ExecItem]) -> None:
+def memory_plan(items: List[ExecItem], keep: Optional[set] = None) -> None:
     """Greedy slot sharing for intermediates; leaves and final outputs keep
-    slot -1 (schedule/kernels.go:365-463)."""
+    slot -1 (schedule/kernels.go:365-463). ``keep`` names requested outputs that a
+    later kernel also reads: they keep slot -1 too, so the device hands them back
+    (the reference would alias them away, tensor/realize.go:147-151)."""
+    keep = keep or set()
     written = {it.bufs[0].uop_idx: i for i, it in enumerate(items)}
     last_read: Dict[int, int] = {}
     for i, it in enumerate(items):
         for b in it.bufs[1:]:
-            if b.uop_idx in written:
+            if b.uop_idx in written and b.uop_idx not in keep:
                 last_read[b.uop_idx] = max(last_read.get(b.uop_idx, -1), i)
     inter = sorted((written[b], b) for b in last_read)
     slots: List[int] = []

@@ -93,11 +93,13 @@ int anl_get_stats(anl_device* dev, anl_stats* out);
 /* flags for anl_open */
 #define ANL_OPEN_DEBUG_BOUNDS 1u   /* clamp and check every generated load */
 #define ANL_OPEN_NO_GEMM 2u        /* never route contractions to the tensor-core kernels */
+#define ANL_OPEN_BEAM 4u           /* apply / search autotuned transforms (the reference's ANNEAL_BEAM=1) */
 
 /* ── Executor.Run / SymbolicExecutor.RunSymbolic (backend/device.go:10-28; backend/webgpu/executor.go:26-240, 576-810) ──
  * Runs the items of `blob` in order.  `outs` has room for `*n_outs` entries on entry; on return
- * `*n_outs` is the number of final outputs (buffers no later item reads) and the first entries of
- * `outs` describe them.  Inputs with unknown ids are ignored; an empty schedule returns 0 outputs.
+ * `*n_outs` is the number of final outputs (buffers no later item reads, plus written buffers the
+ * planner left with slot -1 although a later item reads them) and the first entries of `outs`
+ * describe them.  Inputs with unknown ids are ignored; an empty schedule returns 0 outputs.
  * `binds` gives the value of each symbolic variable; pass n_binds = 0 for a static schedule.
  * `placed` (may be NULL) redirects chosen outputs, see anl_output. */
 int anl_run(anl_device* dev, const uint8_t* blob, size_t blob_len,
@@ -122,6 +124,19 @@ int anl_compile_check(const char* src, char* log, size_t log_cap);
 /* ── Benchmarker.Benchmark (backend/webgpu/benchmark.go:18-208): CUDA-event timing of one item ── */
 int anl_benchmark(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* opts,
                   int warmup, int iterations, anl_bench_result* out);
+
+/* ── codegen.BeamSearch / BeamApplyToItems (codegen/beam.go:271-406, 470-541) ──
+ * Searches the transform space of one generated kernel {threads per block, lanes per reduction,
+ * vector width, split}: beam of `width` (default 4), at most `depth` levels (default 4), one knob
+ * changed per level, candidates timed with CUDA events (min of 5 after 2 warm-ups) on the
+ * reference's deterministic test inputs, rejected unless the output matches the default kernel's
+ * (bit-identical without a REDUCE, 1e-4 relative with one).  The winner is stored in a disk cache
+ * (`cache_path`, or $ANNEAL_BEAM_CACHE, or ~/.cache/anneal/beam_cache_cuda.json) keyed by the
+ * kernel's structure hash and guarded by its default source hash.  A device opened with
+ * ANL_OPEN_BEAM applies cached winners in anl_run and searches on a miss. */
+typedef struct { int opts[4]; double base_us, best_us; int candidates_tried, candidates_rejected, from_cache; } anl_beam_result;
+int anl_beam_search(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, int width, int depth,
+                    const char* cache_path, anl_beam_result* out);
 
 /* ── JIT replay (tensor/jit.go:179-246): a schedule frozen into a CUDA graph ──
  * anl_graph_create runs nothing; the first anl_graph_replay instantiates buffers, compiles the

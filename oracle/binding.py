@@ -88,7 +88,7 @@ class OracleExecutor:
             out = {}
             for it in items:
                 ob = it.bufs[0]
-                if ob.uop_idx in read and not want_all:
+                if ob.uop_idx in read and ob.slot >= 0 and not want_all:
                     continue
                 n = L.orc_buffer_elems(h, ob.uop_idx)
                 a = np.empty(n, dtype=np.float32)

@@ -1,0 +1,144 @@
+"""The benchmark configurations at (or near) full size on the GPU: trajectories, size-independent
+properties, replay and residency paths."""
+import numpy as np
+import pytest
+
+from anneal_b200 import nn, realize as R, workloads as W
+from anneal_b200.tensor import Tensor
+from anneal_b200.train import ResidentTrainer
+from anneal_b200.uop import dtypes
+from util import compare, rel_err, schedule
+
+pytestmark = pytest.mark.gpu
+
+
+def test_c1_loss_trajectory_100_steps(cuda, oracle):
+    """MLP 784→128→10, batch 64, lr 0.01: device-resident training (graph replay, on-device SGD)
+    against the host loop of the reference (fresh graph, oracle, numpy SGD). Bound from the task:
+    loss trajectories within 1e-3 over 100 steps."""
+    m = W.MLP()
+    tr = ResidentTrainer(cuda, m, m.lr, use_graph=True, materialize=False)
+    ref = W.MLP()
+    dev_losses, ref_losses = [], []
+    for step in range(100):
+        dev_losses.append(tr.step(m.x, m.y))
+        R.reset()
+        g = ref.graph()
+        items, out_ids, inputs = schedule(g.targets())
+        out = oracle.run(items, inputs)
+        ref_losses.append(float(out[out_ids[0]][0]))
+        for p, gid in zip(ref.params, out_ids[1:]):
+            p.sgd_step(out[gid], ref.lr)
+    d = np.abs(np.array(dev_losses) - np.array(ref_losses))
+    assert d.max() < 1e-3, (d.max(), dev_losses[-1], ref_losses[-1])
+    assert ref_losses[-1] < ref_losses[0]
+    for a, p in zip(tr.parameters(), ref.params):
+        assert rel_err(a, p.value) < 1e-4
+
+
+def test_c2_cnn_full_size_step(cuda, oracle):
+    m = W.SmallCNN()
+    g = m.graph()
+    compare(cuda, oracle, g.targets(), 1e-4, what="cnn 32x1x28x28")
+
+
+def test_c3_softmax_full_size_properties(cuda):
+    """8192×8192 cannot be checked element by element against the CPU oracle in seconds; check the
+    closed form on sampled rows and the invariants of a softmax gradient on all rows."""
+    s = W.SoftmaxFwdBwd(8192, 8192)
+    ts, _ = s.graph()
+    items, out_ids, inputs = schedule(ts)
+    dx = cuda.run(items, inputs)[out_ids[0]].reshape(8192, 8192)
+    assert np.isfinite(dx).all()
+    # rows of dx sum to zero: sum_j y_j (g_j - <y,g>) = 0
+    assert np.abs(dx.sum(1, dtype=np.float64)).max() < 1e-5
+    rows = [0, 1, 4095, 8191]
+    x = s.x.reshape(8192, 8192)[rows].astype(np.float64)
+    g = s.g.reshape(8192, 8192)[rows].astype(np.float64)
+    e = np.exp(x - x.max(1, keepdims=True))
+    y = e / e.sum(1, keepdims=True)
+    want = y * (g - (y * g).sum(1, keepdims=True))
+    assert rel_err(dx[rows], want) < 1e-4
+
+
+def test_c5_symbolic_replay_compiles_once(cuda, oracle):
+    """One schedule, many batch sizes: kernels compile on the first binding only
+    (backend/webgpu/executor.go:949-952 SymCompiledCount semantics)."""
+    m = W.DynMLP(din=64, hidden=128, dout=32, max_batch=4096)
+    x0, y0 = m.inputs(8)
+    out, loss, grads, ins = m.graph(8, x0, y0)
+    jit = R.JIT()
+    R.DEFAULT_EXECUTOR = cuda
+    try:
+        jit.realize_with_binding({"n": 8}, out, *grads)
+        compiles = cuda.stats()["nvrtc_compiles"]
+        for b in (1, 17, 256, 4096):
+            R.reset()
+            xb, yb = m.inputs(b)
+            out, loss, grads, ins = m.graph(b, xb, yb)
+            jit.realize_with_binding({"n": b}, out, *grads)
+            items, out_ids, inputs = schedule([out] + grads)
+            want = oracle.run(items, inputs, {"n": b})
+            assert rel_err(out.data, want[out_ids[0]]) < 1e-4
+            for gt, oid in zip(grads, out_ids[1:]):
+                assert rel_err(gt.data, want[oid]) < 1e-4
+        assert cuda.stats()["nvrtc_compiles"] == compiles
+        assert jit.stats() == (1, 4)
+    finally:
+        R.DEFAULT_EXECUTOR = None
+
+
+def test_graph_replay_equals_run(cuda):
+    m = W.MLP(batch=32, dims=(64, 48, 10))
+    g = m.graph()
+    items, out_ids, inputs = schedule(g.targets())
+    a = cuda.run(items, inputs)
+    for _ in range(3):
+        b = cuda.replay(items, inputs)
+        for k in a:
+            assert np.array_equal(a[k], b[k])
+    assert cuda.stats()["graph_replays"] >= 3
+
+
+def test_benchmarker_reports_statistics(cuda):
+    x = Tensor.new_leaf((1024, 1024))
+    items, _ = R.build_schedule([x.exp2().sum([1])])
+    r = cuda.benchmark(items[0], warmup=2, iterations=5)
+    assert 0 < r["min_us"] <= r["median_us"] <= r["max_us"] and r["cv"] >= 0
+    forced = cuda.benchmark(items[0], warmup=2, iterations=5, opts=[128, 32, 0, 0, 0])
+    assert forced["min_us"] > 0
+
+
+def test_resident_sgd_matches_host_sgd(cuda):
+    rng = np.random.default_rng(0)
+    w = rng.standard_normal(1000).astype(np.float32)
+    g = rng.standard_normal(1000).astype(np.float32)
+    master = cuda.buffer(dtypes.float32, 1000).upload(w)
+    param = cuda.buffer(dtypes.float16, 1000).upload(w)
+    grad = cuda.buffer(dtypes.float16, 1000).upload(g)
+    cuda.sgd_step(master, param, grad, 0.1, 0.5)
+    cuda.synchronize()
+    gq = g.astype(np.float16).astype(np.float32)
+    want = w - np.float32(0.1) * (gq * np.float32(0.5))
+    assert np.allclose(master.download(), want, rtol=0, atol=1e-6)
+    assert np.array_equal(param.download(), want.astype(np.float16).astype(np.float32))
+
+
+def test_bf16_store_truncates(cuda, oracle):
+    rng = np.random.default_rng(17)
+    a = Tensor.new_leaf((512,), dtypes.bfloat16).set_data(rng.random(512) * 2 - 1)
+    b = Tensor.new_leaf((512,), dtypes.bfloat16).set_data(rng.random(512) * 2 - 1)
+    worst, got, want, ids = compare(cuda, oracle, [a.add(b)], 0.0, what="bf16 add")
+    assert np.array_equal(got[ids[0]].view(np.uint32) & 0xFFFF, np.zeros(512, np.uint32))
+
+
+def test_pre_rendered_source_item_runs(cuda):
+    """An item that arrives with source and launch shape but no AST (schedule/cache.go:80-88; the
+    reference injects a hand-written kernel this way in diag_test.go:76-125)."""
+    from anneal_b200.schedule import Buffer, ExecItem
+    src = 'extern "C" __global__ void main_kernel(float* out, const float* in) { int i = blockIdx.x * blockDim.x + threadIdx.x; if (i < 1000) out[i] = in[i] * 2.0f + 1.0f; }'
+    it = ExecItem(None, [Buffer(900001, 1000, (1000,), dtypes.float32), Buffer(900002, 1000, (1000,), dtypes.float32)],
+                  source=src, local_size=(128, 1, 1), grid=(8, 1, 1))
+    x = np.arange(1000, dtype=np.float32)
+    out = cuda.run([it], {900002: x})
+    assert np.array_equal(out[900001], x * 2 + 1)
