@@ -669,7 +669,7 @@ struct Gen {
                 case OP_LOG2: e = wrap("log2f(" + af(0) + ")"); break;
                 case OP_SIN: e = wrap("sinf(" + af(0) + ")"); break;
                 case OP_SQRT: e = wrap("sqrtf(" + af(0) + ")"); break;
-                case OP_RECIP: e = wrap("(1.0f / " + af(0) + ")"); break;
+                case OP_RECIP: e = wrap("__frcp_rn(" + af(0) + ")"); break;
                 case OP_TRUNC: e = wrap("truncf(" + af(0) + ")"); break;
                 case OP_NEG: e = h ? "__hneg(" + ac(0) + ")" : "(-" + ac(0) + ")"; break;
                 case OP_ADD: e = h ? "__hadd(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " + " + ac(1) + ")"; break;

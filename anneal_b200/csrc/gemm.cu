@@ -31,6 +31,7 @@ constexpr int B_TILE_BYTES = BN * BK * 2;          // 32 KiB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
 constexpr int GEMM_THREADS = 192;
+constexpr int TQ = 4;                               // depth of the per-CTA tile queue
 constexpr unsigned WAIT_LIMIT = 1u << 20;
 
 struct GemmPlan {
@@ -111,6 +112,7 @@ struct GemmArgs {
     int M, N, K, ldd;
     int tiles_m, tiles_n;
     int* status;
+    int* tile_counter;      // zeroed before the launch; CTAs draw tile numbers from it
 };
 
 template <bool A_MN, bool B_MN>
@@ -118,6 +120,10 @@ __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES], empty_bar[STAGES], acc_full[2], acc_empty[2];
+    // tile queue: the producer draws tile numbers from a global counter and hands them to the MMA
+    // and epilogue roles, so a CTA that starts late (SMs busy with a collective) simply takes fewer
+    __shared__ __align__(8) uint64_t tq_full[TQ], tq_empty[TQ];
+    __shared__ int tile_ring[TQ];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int failed;
 
@@ -129,6 +135,7 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 4); }
+        for (int q = 0; q < TQ; q++) { mbar_init(smem_u32(&tq_full[q]), 1); mbar_init(smem_u32(&tq_empty[q]), 5); }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -148,7 +155,17 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             uint32_t stage = 0, phase = 0;
             bool ok = true;
             int issued = 0;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            uint32_t qs = 0, qphase = 0;
+            int next = atomicAdd(g.tile_counter, 1);
+            while (ok) {
+                if (!mbar_wait(smem_u32(&tq_empty[qs]), qphase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 5; break; }
+                int t = next;
+                if (t >= num_tiles) t = -1;
+                else next = atomicAdd(g.tile_counter, 1);      // drawn one tile ahead: its latency hides behind this tile's loads
+                tile_ring[qs] = t;
+                mbar_arrive(smem_u32(&tq_full[qs]));
+                if (++qs == TQ) { qs = 0; qphase ^= 1; }
+                if (t < 0) break;
                 const int m0 = (t % g.tiles_m) * BM, n0 = (t / g.tiles_m) * BN;
                 for (int kb = 0; kb < kblocks; kb++) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 1; break; }
@@ -178,7 +195,13 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
             const uint32_t idesc = (1u << 4) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)(BM >> 4) << 24);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+            uint32_t qs = 0, qphase = 0;
+            while (ok) {
+                if (!mbar_wait(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; *(volatile int*)g.status = 6; break; }
+                const int t = tile_ring[qs];
+                mbar_arrive(smem_u32(&tq_empty[qs]));
+                if (++qs == TQ) { qs = 0; qphase ^= 1; }
+                if (t < 0) break;
                 if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 2; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + acc * BN;
@@ -208,7 +231,14 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
         const int quad = warp & 3;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        for (int t = blockIdx.x; t < num_tiles && ok; t += gridDim.x) {
+        uint32_t qs = 0, qphase = 0;
+        while (ok) {
+            if (!mbar_wait(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 7; failed = 1; } break; }
+            const int t = tile_ring[qs];
+            __syncwarp();
+            if (lane == 0) mbar_arrive(smem_u32(&tq_empty[qs]));
+            if (++qs == TQ) { qs = 0; qphase ^= 1; }
+            if (t < 0) break;
             const int m0 = (t % g.tiles_m) * BM, n0 = (t / g.tiles_m) * BN;
             if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 4; failed = 1; } break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
@@ -237,7 +267,10 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                         dst[q] = o;
                     }
                 } else {
-                    for (int j = 0; j < 32 && col + j < g.N; j++) drow[c * 32 + j] = __float2half_rn(__uint_as_float(v[j]));
+                    // ragged right edge: constant indices keep v[] in registers
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (col + j < g.N) drow[c * 32 + j] = __float2half_rn(__uint_as_float(v[j]));
                 }
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
@@ -292,6 +325,7 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
         if (cudaHostGetDevicePointer((void**)&status_dev, status_host, 0) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
     }
     gp->status_host = status_host; gp->status_dev = status_dev;
+    if (!dev->gemm_tile_counter && cudaMalloc((void**)&dev->gemm_tile_counter, 256) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(gemm_f16_tcgen05<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -327,6 +361,8 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream
     g.M = (int)c.M; g.N = (int)c.N; g.K = (int)c.K; g.ldd = (int)c.N;
     g.tiles_m = (int)((c.M + BM - 1) / BM); g.tiles_n = (int)((c.N + BN - 1) / BN);
     g.status = gp.status_dev;
+    g.tile_counter = dev->gemm_tile_counter;
+    if (cudaMemsetAsync(g.tile_counter, 0, 4, stream) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot reset the tile counter");
     int tiles = g.tiles_m * g.tiles_n;
     int grid = std::min(tiles, dev->prop.multiProcessorCount);
     if (gp.a_mn && gp.b_mn) gemm_f16_tcgen05<true, true><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);

@@ -322,6 +322,7 @@ struct Table {
     std::vector<void*> owned;
     std::set<uint32_t> written, read;
     std::vector<uint32_t> finals;      // in schedule order
+    std::unordered_map<uint32_t, anl_buffer*> reduce_after;   // output id → resident buffer to all-reduce once produced
 };
 
 int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings& binds,
@@ -346,6 +347,7 @@ int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings&
             if (is_final && pl) {
                 if (pl->resident->elems < d.elems || pl->resident->dtype != o.dtype) return dev->fail(ANL_ERR_INVALID, "run: resident output buffer has the wrong size or dtype");
                 d.ptr = pl->resident->ptr;
+                if (pl->allreduce) t.reduce_after[o.id] = pl->resident;
             } else if (!t.bufs.count(o.id)) {
                 if (int rc = dev->alloc(d.bytes, &d.ptr)) return rc;
                 t.owned.push_back(d.ptr); d.owned = true;
@@ -407,8 +409,11 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         std::vector<void*> ptrs;
         for (auto& b : it.bufs) ptrs.push_back(t.bufs[b.id].ptr);
         if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
+        auto ra = t.reduce_after.find(it.bufs[0].id);
+        if (ra != t.reduce_after.end())
+            if (int rc = comm_allreduce_async(dev, ra->second->ptr, ra->second->elems, ra->second->dtype, stream)) return rc;
     }
-    return ANL_OK;
+    return comm_join(dev, stream);
 }
 
 int collect_outputs(anl_device* dev, Table& t, const anl_output* placed, int n_placed, anl_output* outs, int* n_outs, cudaStream_t stream) {
@@ -501,6 +506,7 @@ void anl_close(anl_device* dev) {
     for (auto& kv : dev->modules) if (kv.second->mod && dev->drv.ModuleUnload) dev->drv.ModuleUnload(kv.second->mod);
     dev->trim();
     for (auto& kv : dev->live) cudaFree(kv.first);
+    if (dev->gemm_tile_counter) cudaFree(dev->gemm_tile_counter);
     for (auto& r : dev->prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
     if (dev->timer0) { cudaEventDestroy(dev->timer0); cudaEventDestroy(dev->timer1); }
     if (dev->comm_event) cudaEventDestroy(dev->comm_event);
@@ -758,7 +764,7 @@ int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs, const 
     // resident placements are baked into the captured pointers: any change rebuilds
     std::vector<std::pair<uint32_t, anl_buffer*>> rin, rout;
     for (int k = 0; k < n_inputs; k++) if (inputs[k].resident) rin.push_back({inputs[k].uop_idx, inputs[k].resident});
-    for (int k = 0; k < n_placed; k++) if (placed[k].resident) rout.push_back({placed[k].uop_idx, placed[k].resident});
+    for (int k = 0; k < n_placed; k++) if (placed[k].resident) rout.push_back({placed[k].uop_idx + (placed[k].allreduce ? 0x80000000u : 0u), placed[k].resident});
     if (g->built && (sym != g->built_sym || rin != g->resident_in || rout != g->resident_out)) graph_drop(g);
     int rc = ANL_OK;
     if (!g->built) {

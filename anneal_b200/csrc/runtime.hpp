@@ -75,8 +75,10 @@ struct anl_device {
     std::unordered_map<uint64_t, BeamEntry> beam_cache;
     std::string beam_cache_path;
     bool beam_loaded = false;
+    int* gemm_tile_counter = nullptr;     // device word the persistent GEMM draws tile numbers from
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
+    bool comm_pending = false;
 
     int fail(int code, const std::string& m) { err = m; return code; }
     int alloc(size_t bytes, void** out);
@@ -103,6 +105,11 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 int plan_gemm(anl_device* dev, const Item& item, Plan& plan);
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream);
 double gemm_flops(const Plan& plan);
+
+// data parallel (comm.cpp): queue an all-reduce of [ptr, ptr+elems) on the communication stream after
+// everything queued so far on `stream`; comm_join makes `stream` wait for all of them
+int comm_allreduce_async(anl_device* dev, void* ptr, int64_t elems, int dtype, cudaStream_t stream);
+int comm_join(anl_device* dev, cudaStream_t stream);
 
 // autotuning (beam.cpp)
 int beam_search(anl_device* dev, const Item& it, int width, int depth, anl_beam_result* out);

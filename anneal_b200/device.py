@@ -35,7 +35,8 @@ class _Binding(C.Structure):
 
 
 class _Output(C.Structure):
-    _fields_ = [("uop_idx", C.c_uint32), ("data", C.POINTER(C.c_float)), ("elems", C.c_int64), ("resident", C.c_void_p)]
+    _fields_ = [("uop_idx", C.c_uint32), ("data", C.POINTER(C.c_float)), ("elems", C.c_int64), ("resident", C.c_void_p),
+                ("allreduce", C.c_int)]
 
 
 class _Bench(C.Structure):
@@ -264,17 +265,17 @@ class Device:
         return arr, len(binding)
 
     @staticmethod
-    def _placed(placed):
+    def _placed(placed, allreduce=()):
         placed = placed or {}
         keep = []
         arr = (_Output * max(len(placed), 1))()
         for k, (idx, v) in enumerate(placed.items()):
             if isinstance(v, ResidentBuffer):
-                arr[k] = _Output(idx, None, v.elems, v.h)
+                arr[k] = _Output(idx, None, v.elems, v.h, 1 if idx in allreduce else 0)
             else:
                 assert v.dtype == np.float32 and v.flags["C_CONTIGUOUS"]
                 keep.append(v)
-                arr[k] = _Output(idx, v.ctypes.data_as(C.POINTER(C.c_float)), v.size, None)
+                arr[k] = _Output(idx, v.ctypes.data_as(C.POINTER(C.c_float)), v.size, None, 0)
         return arr, len(placed), keep
 
     def _collect(self, outs, n, placed):
@@ -290,13 +291,15 @@ class Device:
         return res
 
     # ── Executor / SymbolicExecutor ───────────────────────────────────────
-    def run(self, items, inputs, binding=None, placed=None):
+    def run(self, items, inputs, binding=None, placed=None, allreduce=()):
+        """``allreduce``: ids of placed resident outputs to sum across ranks as soon as they are
+        produced, overlapped with the rest of the schedule."""
         if not items:
             return {}
         blob = self._blob(items)
         ia, ni, keep_i = self._inputs(inputs)
         ba, nb = self._binds(binding)
-        pa, npl, keep_p = self._placed(placed)
+        pa, npl, keep_p = self._placed(placed, allreduce)
         cap = len(items)
         outs = (_Output * cap)()
         n = C.c_int(cap)
@@ -306,7 +309,7 @@ class Device:
     def run_symbolic(self, items, inputs, binding):
         return self.run(items, inputs, binding)
 
-    def replay(self, items, inputs, binding=None, placed=None):
+    def replay(self, items, inputs, binding=None, placed=None, allreduce=()):
         """Run through a CUDA graph captured on first use of this item list."""
         if not items:
             return {}
@@ -320,7 +323,7 @@ class Device:
             self._graphs[key] = g
         ia, ni, keep_i = self._inputs(inputs)
         ba, nb = self._binds(binding)
-        pa, npl, keep_p = self._placed(placed)
+        pa, npl, keep_p = self._placed(placed, allreduce)
         cap = len(items)
         outs = (_Output * cap)()
         n = C.c_int(cap)

@@ -59,7 +59,8 @@ def build_schedule(tensors: Sequence[Tensor]):
     nodes = [t.node for t in tensors]
     if MATERIALIZE_CONTRACTION_OPERANDS:
         nodes = S.materialize_contraction_operands(nodes)
-    items, out_map = S.create_schedule(nodes, keep_contractions=MATERIALIZE_CONTRACTION_OPERANDS)
+    items, out_map = S.create_schedule(nodes, keep_contractions=MATERIALIZE_CONTRACTION_OPERANDS,
+                                       outputs_first=MATERIALIZE_CONTRACTION_OPERANDS)
     return items, [out_map[n.idx] for n in nodes]
 
 

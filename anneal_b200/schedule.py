@@ -312,7 +312,8 @@ def _is_dense_contraction(body: U.UOp) -> bool:
 
 
 def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
-                    fusion: Optional[bool] = None, keep_contractions: bool = False) -> Tuple[List[ExecItem], Dict[int, int]]:
+                    fusion: Optional[bool] = None, keep_contractions: bool = False,
+                    outputs_first: bool = False) -> Tuple[List[ExecItem], Dict[int, int]]:
     """Schedule the tensor-graph nodes ``outputs``.
 
     Returns the ordered items and a map from each output node's idx to the
@@ -321,7 +322,9 @@ def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
 
     ``keep_contractions`` leaves a dense SUM-of-products over two buffers as a kernel of its own
     instead of splicing it into an elementwise consumer, so that it reaches the device as a plain
-    GEMM (used together with ``materialize_contraction_operands``)."""
+    GEMM (used together with ``materialize_contraction_operands``). ``outputs_first`` lets a ready
+    kernel that produces a requested output run before other ready kernels, so gradients finish as
+    early as the dependencies allow and their all-reduce can overlap the rest of the backward pass."""
     import sys
     sys.setrecursionlimit(max(sys.getrecursionlimit(), 100000))
     max_bufs = MAX_KERNEL_BUFFERS if max_bufs is None else max_bufs
@@ -486,7 +489,9 @@ def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
             if w is not None and w != i:
                 users[w].append(i)
                 indeg[i] += 1
-    ready = sorted(i for i in range(n) if indeg[i] == 0)
+    wanted = {out_buf[placeholders[o.idx].idx].idx for o in outputs}
+    prio = (lambda i: (0 if items[i].bufs[0].uop_idx in wanted else 1, i)) if outputs_first else (lambda i: (0, i))
+    ready = sorted((i for i in range(n) if indeg[i] == 0), key=prio)
     ordered = []
     while ready:
         i = ready.pop(0)
@@ -495,7 +500,7 @@ def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
             indeg[j] -= 1
             if indeg[j] == 0:
                 ready.append(j)
-        ready.sort()
+        ready.sort(key=prio)
     assert len(ordered) == n, "schedule: dependency cycle"
     out_map_ids = {out_buf[placeholders[o.idx].idx].idx for o in outputs}
     memory_plan(ordered, out_map_ids)

@@ -26,8 +26,9 @@ def _round_up(n: int, m: int = 128) -> int:
 
 class ResidentTrainer:
     def __init__(self, dev: Device, model, lr: float, world: int = 1, use_graph: bool = True,
-                 materialize: bool = True, resident_inputs: bool = False):
+                 materialize: bool = True, resident_inputs: bool = False, overlap: bool = True):
         self.dev, self.model, self.lr, self.world, self.use_graph = dev, model, float(lr), world, use_graph
+        self.overlap = overlap
         prev = R.MATERIALIZE_CONTRACTION_OPERANDS
         R.MATERIALIZE_CONTRACTION_OPERANDS = materialize
         try:
@@ -89,9 +90,13 @@ class ResidentTrainer:
         else:
             inputs[self.x_id], inputs[self.y_id] = x, y
         run = self.dev.replay if self.use_graph else self.dev.run
-        run(self.items, inputs, None, self.placed)
-        if self.world > 1:
-            self.dev.allreduce_sum(self.grad)
+        if self.world > 1 and self.overlap:
+            # each gradient is summed across ranks as soon as its kernel is queued
+            run(self.items, inputs, None, self.placed, self.grad_ids)
+        else:
+            run(self.items, inputs, None, self.placed)
+            if self.world > 1:
+                self.dev.allreduce_sum(self.grad)
         self.dev.sgd_step(self.master, self.store, self.grad, self.lr, self.grad_scale / self.world)
         return None if self.resident_inputs else float(self.loss_host[0])
 

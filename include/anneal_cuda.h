@@ -73,6 +73,9 @@ typedef struct {
     float* data;
     int64_t elems;
     anl_buffer* resident;
+    int allreduce;   /* placed + resident only: sum this output over all ranks as soon as its kernel
+                        has been queued, on the communication stream, overlapping the rest of the
+                        schedule; the run (or graph replay) completes after the reduction */
 } anl_output;
 
 /* Benchmarker result: backend/device.go:30-37 BenchmarkResult, microseconds. */
