@@ -86,11 +86,16 @@ int anl_allreduce_sum(anl_device* dev, anl_buffer* buf) {
 }  // extern "C"
 
 namespace anl {
+int comm_fork(anl_device* dev, cudaStream_t stream) {
+    cudaEventRecord(dev->comm_event, stream);
+    cudaStreamWaitEvent(dev->comm_stream, dev->comm_event, 0);
+    dev->comm_pending = true;
+    return ANL_OK;
+}
 int comm_allreduce_async(anl_device* dev, void* ptr, int64_t elems, int dtype, cudaStream_t stream) {
     if (dev->nranks == 1 || !dev->nccl_comm) return ANL_OK;
     Nccl& n = nccl();
-    cudaEventRecord(dev->comm_event, stream);
-    cudaStreamWaitEvent(dev->comm_stream, dev->comm_event, 0);
+    comm_fork(dev, stream);
     int r = n.AllReduce(ptr, ptr, (size_t)elems, dtype == ANL_F16 ? NCCL_FLOAT16 : NCCL_FLOAT32, NCCL_SUM, dev->nccl_comm, dev->comm_stream);
     if (r != 0) return dev->fail(ANL_ERR_COMM, std::string("nccl: ncclAllReduce: ") + (n.GetErrorString ? n.GetErrorString(r) : "?"));
     dev->comm_pending = true;

@@ -252,6 +252,24 @@ static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item
     return rc;
 }
 
+int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream) {
+    if (master->dtype != ANL_F32) return dev->fail(ANL_ERR_INVALID, "sgd: master weights must be f32");
+    if (grad->elems < master->elems || param->elems < master->elems) return dev->fail(ANL_ERR_INVALID, "sgd: gradient length != parameter length");
+    long long n = master->elems;
+    if (n == 0) return ANL_OK;
+    unsigned g = grid_for(n, 256, dev->prop.multiProcessorCount);
+    float* m = (float*)master->ptr;
+    bool gh = grad->dtype == ANL_F16, ph = param->dtype == ANL_F16;
+    int bf = param->dtype == ANL_BF16;
+    if (gh && ph) sgd_kernel<__half, __half><<<g, 256, 0, stream>>>(m, (__half*)param->ptr, (const __half*)grad->ptr, lr, scale, n, 0);
+    else if (gh) sgd_kernel<__half, float><<<g, 256, 0, stream>>>(m, (float*)param->ptr, (const __half*)grad->ptr, lr, scale, n, bf);
+    else if (ph) sgd_kernel<float, __half><<<g, 256, 0, stream>>>(m, (__half*)param->ptr, (const float*)grad->ptr, lr, scale, n, 0);
+    else sgd_kernel<float, float><<<g, 256, 0, stream>>>(m, (float*)param->ptr, (const float*)grad->ptr, lr, scale, n, bf);
+    dev->stats.kernels_launched++;
+    CK(dev, cudaGetLastError());
+    return ANL_OK;
+}
+
 int upload_f32(anl_device* dev, void* dst, int dtype, const float* host, int64_t elems, cudaStream_t s) {
     if (elems <= 0) return ANL_OK;
     dev->stats.h2d_bytes += (uint64_t)elems * 4;
@@ -322,7 +340,7 @@ struct Table {
     std::vector<void*> owned;
     std::set<uint32_t> written, read;
     std::vector<uint32_t> finals;      // in schedule order
-    std::unordered_map<uint32_t, anl_buffer*> reduce_after;   // output id → resident buffer to all-reduce once produced
+    std::unordered_map<uint32_t, anl_output> after;   // output id → placed entry asking for an all-reduce and/or an SGD update
 };
 
 int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings& binds,
@@ -347,7 +365,7 @@ int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings&
             if (is_final && pl) {
                 if (pl->resident->elems < d.elems || pl->resident->dtype != o.dtype) return dev->fail(ANL_ERR_INVALID, "run: resident output buffer has the wrong size or dtype");
                 d.ptr = pl->resident->ptr;
-                if (pl->allreduce) t.reduce_after[o.id] = pl->resident;
+                if (pl->allreduce || pl->sgd_master) t.after[o.id] = *pl;
             } else if (!t.bufs.count(o.id)) {
                 if (int rc = dev->alloc(d.bytes, &d.ptr)) return rc;
                 t.owned.push_back(d.ptr); d.owned = true;
@@ -386,6 +404,23 @@ int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings&
 
 int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& binds, Table& t, cudaStream_t stream, bool keep_scratch = false) {
     CodegenOpts opts; opts.debug_bounds = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;
+    // A parameter may only be updated once every kernel of this schedule that reads it has been
+    // queued: the update of output X waits for max(producer of X, last reader of its parameter).
+    std::unordered_map<size_t, std::vector<uint32_t>> sgd_at;
+    for (auto& kv : t.after) {
+        if (!kv.second.sgd_master) continue;
+        const void* pp = (kv.second.sgd_param ? kv.second.sgd_param : kv.second.sgd_master)->ptr;
+        const void* mp = kv.second.sgd_master->ptr;
+        size_t at = 0;
+        for (size_t i = 0; i < items.size(); i++) {
+            if (items[i].bufs[0].id == kv.first) at = std::max(at, i);
+            for (size_t b = 1; b < items[i].bufs.size(); b++) {
+                const void* q = t.bufs[items[i].bufs[b].id].ptr;
+                if (q == pp || q == mp) at = std::max(at, i);
+            }
+        }
+        sgd_at[at].push_back(kv.first);
+    }
     for (size_t i = 0; i < items.size(); i++) {
         const Item& it = items[i];
         std::shared_ptr<Plan> plan;
@@ -409,9 +444,19 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         std::vector<void*> ptrs;
         for (auto& b : it.bufs) ptrs.push_back(t.bufs[b.id].ptr);
         if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
-        auto ra = t.reduce_after.find(it.bufs[0].id);
-        if (ra != t.reduce_after.end())
-            if (int rc = comm_allreduce_async(dev, ra->second->ptr, ra->second->elems, ra->second->dtype, stream)) return rc;
+        // side stream: [all-reduce this gradient] behind the producing kernel ...
+        auto ra = t.after.find(it.bufs[0].id);
+        if (ra != t.after.end() && ra->second.allreduce)
+            if (int rc = comm_allreduce_async(dev, ra->second.resident->ptr, ra->second.resident->elems, ra->second.resident->dtype, stream)) return rc;
+        // ... [update the parameter] once its last reader has been queued as well
+        auto sg = sgd_at.find(i);
+        if (sg != sgd_at.end()) {
+            comm_fork(dev, stream);
+            for (uint32_t id : sg->second) {
+                const anl_output& a = t.after[id];
+                if (int rc = launch_sgd(dev, a.sgd_master, a.sgd_param ? a.sgd_param : a.sgd_master, a.resident, a.sgd_lr, a.sgd_scale, dev->comm_stream)) return rc;
+            }
+        }
     }
     return comm_join(dev, stream);
 }
@@ -490,7 +535,11 @@ int anl_open(int ordinal, unsigned flags, anl_device** out) {
     if (cudaSetDevice(ordinal) != cudaSuccess || cudaFree(0) != cudaSuccess || cudaGetDeviceProperties(&d->prop, ordinal) != cudaSuccess) { delete d; return ANL_ERR_NO_DEVICE; }
     if (d->prop.major < 10) { delete d; return ANL_ERR_NO_DEVICE; }   // kernels are built for sm_100a only
     if (cudaStreamCreateWithFlags(&d->stream, cudaStreamNonBlocking) != cudaSuccess) { delete d; return ANL_ERR_CUDA; }
-    cudaStreamCreateWithFlags(&d->comm_stream, cudaStreamNonBlocking);
+    {   // collectives get the highest priority so their blocks are placed as soon as an SM frees up
+        int lo = 0, hi = 0;
+        cudaDeviceGetStreamPriorityRange(&lo, &hi);
+        cudaStreamCreateWithPriority(&d->comm_stream, cudaStreamNonBlocking, hi);
+    }
     cudaEventCreateWithFlags(&d->comm_event, cudaEventDisableTiming);
     cudaEventCreateWithFlags(&d->comm_done, cudaEventDisableTiming);
     if (ensure_driver(d) != ANL_OK) { delete d; return ANL_ERR_CUDA; }
@@ -677,21 +726,8 @@ int64_t anl_buffer_elems(anl_buffer* buf) { return buf ? buf->elems : 0; }
 
 int anl_sgd_step(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale) {
     if (!dev || !master || !param || !grad) return ANL_ERR_INVALID;
-    if (master->dtype != ANL_F32) return dev->fail(ANL_ERR_INVALID, "sgd: master weights must be f32");
-    if (grad->elems < master->elems || param->elems < master->elems) return dev->fail(ANL_ERR_INVALID, "sgd: gradient length != parameter length");
     cudaSetDevice(dev->ordinal);
-    long long n = master->elems;
-    unsigned g = grid_for(n, 256, dev->prop.multiProcessorCount);
-    float* m = (float*)master->ptr;
-    bool gh = grad->dtype == ANL_F16, ph = param->dtype == ANL_F16;
-    int bf = param->dtype == ANL_BF16;
-    if (gh && ph) sgd_kernel<__half, __half><<<g, 256, 0, dev->stream>>>(m, (__half*)param->ptr, (const __half*)grad->ptr, lr, scale, n, 0);
-    else if (gh) sgd_kernel<__half, float><<<g, 256, 0, dev->stream>>>(m, (float*)param->ptr, (const __half*)grad->ptr, lr, scale, n, bf);
-    else if (ph) sgd_kernel<float, __half><<<g, 256, 0, dev->stream>>>(m, (__half*)param->ptr, (const float*)grad->ptr, lr, scale, n, 0);
-    else sgd_kernel<float, float><<<g, 256, 0, dev->stream>>>(m, (float*)param->ptr, (const float*)grad->ptr, lr, scale, n, bf);
-    dev->stats.kernels_launched++;
-    CK(dev, cudaGetLastError());
-    return ANL_OK;
+    return anl::launch_sgd(dev, master, param, grad, lr, scale, dev->stream);
 }
 
 int anl_timer_start(anl_device* dev) {
@@ -764,7 +800,7 @@ int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs, const 
     // resident placements are baked into the captured pointers: any change rebuilds
     std::vector<std::pair<uint32_t, anl_buffer*>> rin, rout;
     for (int k = 0; k < n_inputs; k++) if (inputs[k].resident) rin.push_back({inputs[k].uop_idx, inputs[k].resident});
-    for (int k = 0; k < n_placed; k++) if (placed[k].resident) rout.push_back({placed[k].uop_idx + (placed[k].allreduce ? 0x80000000u : 0u), placed[k].resident});
+    for (int k = 0; k < n_placed; k++) if (placed[k].resident) rout.push_back({placed[k].uop_idx + (placed[k].allreduce ? 0x80000000u : 0u) + (placed[k].sgd_master ? 0x40000000u : 0u), placed[k].resident});
     if (g->built && (sym != g->built_sym || rin != g->resident_in || rout != g->resident_out)) graph_drop(g);
     int rc = ANL_OK;
     if (!g->built) {

@@ -36,7 +36,8 @@ class _Binding(C.Structure):
 
 class _Output(C.Structure):
     _fields_ = [("uop_idx", C.c_uint32), ("data", C.POINTER(C.c_float)), ("elems", C.c_int64), ("resident", C.c_void_p),
-                ("allreduce", C.c_int)]
+                ("allreduce", C.c_int), ("sgd_master", C.c_void_p), ("sgd_param", C.c_void_p), ("sgd_lr", C.c_float),
+                ("sgd_scale", C.c_float)]
 
 
 class _Bench(C.Structure):
@@ -170,6 +171,14 @@ def compile_check(source: str) -> str:
     return log.value.decode()
 
 
+class GradientTarget:
+    """Where a gradient output goes and what happens right behind it: optional all-reduce across
+    ranks, optional SGD update of its parameter (master f32 + storage copy)."""
+
+    def __init__(self, grad, master=None, param=None, lr: float = 0.0, scale: float = 1.0, allreduce: bool = False):
+        self.grad, self.master, self.param, self.lr, self.scale, self.allreduce = grad, master, param, lr, scale, allreduce
+
+
 class ResidentBuffer:
     """A device buffer that outlives a run: parameters, master weights, gradients."""
 
@@ -270,12 +279,16 @@ class Device:
         keep = []
         arr = (_Output * max(len(placed), 1))()
         for k, (idx, v) in enumerate(placed.items()):
-            if isinstance(v, ResidentBuffer):
-                arr[k] = _Output(idx, None, v.elems, v.h, 1 if idx in allreduce else 0)
+            if isinstance(v, GradientTarget):
+                arr[k] = _Output(idx, None, v.grad.elems, v.grad.h, 1 if v.allreduce else 0,
+                                 v.master.h if v.master is not None else None, v.param.h if v.param is not None else None,
+                                 v.lr, v.scale)
+            elif isinstance(v, ResidentBuffer):
+                arr[k] = _Output(idx, None, v.elems, v.h, 1 if idx in allreduce else 0, None, None, 0.0, 0.0)
             else:
                 assert v.dtype == np.float32 and v.flags["C_CONTIGUOUS"]
                 keep.append(v)
-                arr[k] = _Output(idx, v.ctypes.data_as(C.POINTER(C.c_float)), v.size, None, 0)
+                arr[k] = _Output(idx, v.ctypes.data_as(C.POINTER(C.c_float)), v.size, None, 0, None, None, 0.0, 0.0)
         return arr, len(placed), keep
 
     def _collect(self, outs, n, placed):

@@ -16,7 +16,7 @@ from typing import Dict, List, Optional
 import numpy as np
 
 from . import realize as R
-from .device import Device, ResidentBuffer, pinned_array
+from .device import Device, GradientTarget, ResidentBuffer, pinned_array
 from .uop import dtypes
 
 
@@ -63,12 +63,16 @@ class ResidentTrainer:
         self.inputs: Dict[int, object] = {}
         self.placed: Dict[int, object] = {}
         self._views = []
+        self.fused: Dict[int, object] = {}
         for p, o, gid in zip(params, offs, self.grad_ids):
             pv = self.store.view(o, p.value.size)
             gv = self.grad.view(o, p.value.size)
-            self._views += [pv, gv]
+            mv = self.master.view(o, p.value.size)
+            self._views += [pv, gv, mv]
             self.inputs[p.t.node.idx] = pv
             self.placed[gid] = gv
+            # overlapped mode: each gradient is all-reduced and applied right behind its kernel
+            self.fused[gid] = GradientTarget(gv, mv, pv, self.lr, self.grad_scale / world, allreduce=world > 1)
         self.loss_host = pinned_array(1)
         self.placed[self.loss_id] = self.loss_host
         self.resident_inputs = resident_inputs
@@ -90,14 +94,15 @@ class ResidentTrainer:
         else:
             inputs[self.x_id], inputs[self.y_id] = x, y
         run = self.dev.replay if self.use_graph else self.dev.run
-        if self.world > 1 and self.overlap:
-            # each gradient is summed across ranks as soon as its kernel is queued
-            run(self.items, inputs, None, self.placed, self.grad_ids)
+        if self.overlap:
+            placed = dict(self.placed)
+            placed.update(self.fused)
+            run(self.items, inputs, None, placed)
         else:
             run(self.items, inputs, None, self.placed)
             if self.world > 1:
                 self.dev.allreduce_sum(self.grad)
-        self.dev.sgd_step(self.master, self.store, self.grad, self.lr, self.grad_scale / self.world)
+            self.dev.sgd_step(self.master, self.store, self.grad, self.lr, self.grad_scale / self.world)
         return None if self.resident_inputs else float(self.loss_host[0])
 
     def loss(self) -> float:

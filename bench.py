@@ -135,7 +135,8 @@ def run_ours(args):
     from anneal_b200.device import Device
     from anneal_b200.train import ResidentTrainer
 
-    os.environ.setdefault("NCCL_DEBUG_FILE", "/dev/stderr")   # keep NCCL's banner off stdout: rank 0 prints one JSON line
+    if not args.nccl_debug:
+        os.environ.pop("NCCL_DEBUG", None)       # NCCL prints its banner on stdout; rank 0 prints one JSON line
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -154,7 +155,8 @@ def run_ours(args):
     model = W.WideMLP(rank=rank, **CFG)
     x, y = model.make_inputs()
     R.reset()
-    tr = ResidentTrainer(dev, model, model.lr, world=world, use_graph=True, resident_inputs=True)
+    tr = ResidentTrainer(dev, model, model.lr, world=world, use_graph=not args.no_graph, resident_inputs=True,
+                         overlap=not args.no_overlap)
     tr.load_batch(x, y)
     for _ in range(args.warmup):
         tr.step()
@@ -188,7 +190,7 @@ def run_ours(args):
         tr_prof.step()
     prof = dev.profile_read()
     dev.profile(False)
-    tr_prof.use_graph = True
+    tr_prof.use_graph = not args.no_graph
     pk, pk_kind = peaks()
     roof = None
     if "gemm" in prof and prof["gemm"]["total_ms"] > 0:
@@ -204,7 +206,8 @@ def run_ours(args):
     # end to end: batch in pinned host memory, uploaded every step, loss read back every step
     R.reset()
     from anneal_b200.device import pinned_array
-    tr2 = ResidentTrainer(dev, model, model.lr, world=world, use_graph=True, resident_inputs=False)
+    tr2 = ResidentTrainer(dev, model, model.lr, world=world, use_graph=not args.no_graph, resident_inputs=False,
+                          overlap=not args.no_overlap)
     xh, yh = pinned_array(x.size), pinned_array(y.size)
     xh[:] = x
     yh[:] = y
@@ -262,6 +265,9 @@ def main():
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
+    ap.add_argument("--no-overlap", action="store_true", help="all-reduce the whole gradient bucket after the backward pass")
+    ap.add_argument("--nccl-debug", action="store_true", help="leave NCCL_DEBUG as set in the environment")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -76,6 +76,13 @@ typedef struct {
     int allreduce;   /* placed + resident only: sum this output over all ranks as soon as its kernel
                         has been queued, on the communication stream, overlapping the rest of the
                         schedule; the run (or graph replay) completes after the reduction */
+    /* placed + resident only, optional: treat this output as the gradient of a parameter and apply
+     * anl_sgd_step(sgd_master, sgd_param, this output, sgd_lr, sgd_scale) right behind it (after the
+     * all-reduce when one is requested) on the same side stream, so the update of early-finished
+     * gradients overlaps the rest of the backward pass.  NULL sgd_master = no update. */
+    anl_buffer* sgd_master;
+    anl_buffer* sgd_param;
+    float sgd_lr, sgd_scale;
 } anl_output;
 
 /* Benchmarker result: backend/device.go:30-37 BenchmarkResult, microseconds. */

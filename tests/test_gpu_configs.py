@@ -142,3 +142,21 @@ def test_pre_rendered_source_item_runs(cuda):
     x = np.arange(1000, dtype=np.float32)
     out = cuda.run([it], {900002: x})
     assert np.array_equal(out[900001], x * 2 + 1)
+
+
+def test_fused_update_equals_separate_update(cuda):
+    """Per-gradient [all-reduce →] SGD on the side stream, deferred past the parameter's last reader,
+    must leave exactly the parameters that one SGD launch after the backward pass leaves."""
+    res = []
+    for overlap in (True, False):
+        R.reset()
+        m = W.WideMLP(batch=256, width=256, classes=72, depth=3)
+        x, y = m.make_inputs()
+        tr = ResidentTrainer(cuda, m, 0.05, use_graph=overlap, resident_inputs=True, overlap=overlap)
+        tr.load_batch(x, y)
+        for _ in range(4):
+            tr.step()
+        res.append((tr.parameters(), tr.loss()))
+    for a, b in zip(res[0][0], res[1][0]):
+        assert np.array_equal(a, b)
+    assert res[0][1] == res[1][1]
