@@ -19,6 +19,7 @@
 // status word and the CTA drains and frees its tensor memory instead of spinning.
 #include <cuda_fp16.h>
 
+#include <cstdlib>
 #include <cstring>
 
 #include "runtime.hpp"
@@ -287,6 +288,186 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
+// ── two-CTA variant ─────────────────────────────────────────────────────────────────────────────
+// A pair of CTAs on neighbouring SMs (a cluster of 2) computes one 256x256 tile with
+// tcgen05.mma.cta_group::2: each CTA holds 128 rows of A, HALF of B (128 of the 256 columns) and
+// the 128x256 accumulator of its own rows; the tensor cores of both SMs read both halves of B.  Per
+// k-block a CTA therefore moves 32 KiB through shared memory instead of 48 KiB for the same math,
+// which is what the one-CTA kernel is short of (shared-memory bandwidth, not DRAM).  The even CTA
+// leads: it owns the "full" barriers (both CTAs' loads complete on them) and issues the MMAs; its
+// commits release the stage and publish the accumulator in both CTAs.  No load is multicast.
+constexpr int STAGES2 = 6;
+constexpr int B2_TILE_BYTES = (BN / 2) * BK * 2;               // 16 KiB: this CTA's half of B
+constexpr int STAGE2_BYTES = A_TILE_BYTES + B2_TILE_BYTES;     // 32 KiB
+constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar) : "memory");
+}
+__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+
+template <bool A_MN, bool B_MN>
+__global__ void __launch_bounds__(GEMM_THREADS, 1)
+gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
+    extern __shared__ uint8_t smem_raw[];
+    __shared__ __align__(8) uint64_t full_bar[STAGES2], empty_bar[STAGES2], acc_full[2], acc_empty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ volatile int failed;
+
+    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();            // 0 leads
+    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
+    const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
+    const int num_tiles = tiles_m * g.tiles_n;
+    const int kblocks = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES2; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 8); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                  // both CTAs' barriers exist before any remote signal
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            uint32_t stage = 0, phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += npairs) {
+                const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;          // this CTA's rows of A
+                const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);          // this CTA's half of B
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
+                    const uint32_t own_fb = smem_u32(&full_bar[stage]);
+                    const uint32_t fb = map_to_cta(own_fb, 0);                     // loads of both CTAs complete on the leader's barrier
+                    const uint32_t sa = smem_base + stage * STAGE2_BYTES, sb = sa + A_TILE_BYTES;
+                    if (rank == 0) mbar_expect_tx(own_fb, 2 * STAGE2_BYTES);
+                    const int k0 = kb * BK;
+                    if (A_MN) { for (int j = 0; j < BM / 64; j++) tma_load_2d_pair(sa + j * (BK * 128), &map_a, m0 + 64 * j, k0, fb); }
+                    else tma_load_2d_pair(sa, &map_a, k0, m0, fb);
+                    if (B_MN) { for (int j = 0; j < BN / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
+                    else tma_load_2d_pair(sb, &map_b, k0, n0, fb);
+                    if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) failed = 1;
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            // M = 256 across the pair (M >> 4 = 16 at bit 24), N = 256
+            const uint32_t idesc = (1u << 4) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = pair; t < num_tiles && ok; t += npairs) {
+                if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const uint32_t tmem_d = tmem_base + acc * BN;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 13; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const uint32_t sa = smem_base + stage * STAGE2_BYTES, sb = sa + A_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        const uint64_t ad = A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
+                        const uint64_t bd = B_MN ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+                        umma_f16_pair(tmem_d, ad, bd, idesc, (kb | k) != 0);
+                    }
+                    const uint32_t eb = smem_u32(&empty_bar[stage]);
+                    umma_commit_pair(map_to_cta(eb, 0));       // frees the stage here ...
+                    umma_commit_pair(map_to_cta(eb, 1));       // ... and in the partner CTA
+                    if (++stage == STAGES2) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                const uint32_t af = smem_u32(&acc_full[acc]);
+                umma_commit_pair(map_to_cta(af, 0));
+                umma_commit_pair(map_to_cta(af, 1));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+            if (!ok) failed = 1;
+        }
+    } else {
+        const int quad = warp & 3;
+        uint32_t acc = 0, acc_phase = 0;
+        bool ok = true;
+        for (int t = pair; t < num_tiles && ok; t += npairs) {
+            const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / tiles_m) * BN;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quad * 32 + lane;
+            __half* drow = g.d + (size_t)row * g.ldd + n0;
+            const bool row_ok = row < g.M;
+            const bool vec_ok = (g.ldd % 8 == 0);
+#pragma unroll 1
+            for (int c = 0; c < BN / 32; c++) {
+                uint32_t v[32];
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col = n0 + c * 32;
+                if (!row_ok || col >= g.N) continue;
+                if (vec_ok && col + 32 <= g.N) {
+                    uint4* dst = reinterpret_cast<uint4*>(drow + c * 32);
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        __half2 h0 = __floats2half2_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
+                        __half2 h1 = __floats2half2_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
+                        __half2 h2 = __floats2half2_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
+                        __half2 h3 = __floats2half2_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
+                        uint4 o;
+                        o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
+                        o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
+                        dst[q] = o;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j++)
+                        if (col + j < g.N) drow[c * 32 + j] = __float2half_rn(__uint_as_float(v[j]));
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));   // the leader waits for both CTAs' epilogues
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                  // the leader's MMAs read the partner's shared memory: leave together
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
 static int encode_map(anl_device* dev, CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
                       uint32_t box_inner, uint32_t box_outer) {
     cuuint64_t dims[2] = {inner, outer};
@@ -332,6 +513,10 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
         cudaFuncSetAttribute(gemm_f16_tcgen05<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_f16_tcgen05<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_f16_tcgen05<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
         attr_set = true;
     }
     plan.gemm = gp;
@@ -363,6 +548,29 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream
     g.status = gp.status_dev;
     g.tile_counter = dev->gemm_tile_counter;
     if (cudaMemsetAsync(g.tile_counter, 0, 4, stream) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot reset the tile counter");
+    static const bool pair_ok = std::getenv("ANNEAL_GEMM_PAIR") ? std::atoi(std::getenv("ANNEAL_GEMM_PAIR")) != 0 : true;
+    if (pair_ok && c.M >= 2 * BM && c.N >= BN / 2) {
+        // two-CTA tiles: B is loaded in halves of 128 columns, so its tensor map gets a 128-row box
+        if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
+        else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, BN / 2);
+        if (rc) return rc;
+        int tiles2 = (int)((c.M + 2 * BM - 1) / (2 * BM)) * g.tiles_n;
+        int pairs = std::min(tiles2, dev->prop.multiProcessorCount / 2);
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.stream = stream;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        cudaError_t le;
+        if (gp.a_mn && gp.b_mn) le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<true, true>, ma, mb, g);
+        else if (gp.a_mn) le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<true, false>, ma, mb, g);
+        else if (gp.b_mn) le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<false, true>, ma, mb, g);
+        else le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<false, false>, ma, mb, g);
+        if (le != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm: pair launch: ") + cudaGetErrorString(le));
+        dev->stats.kernels_launched++;
+        dev->stats.gemm_launched++;
+        return ANL_OK;
+    }
     int tiles = g.tiles_m * g.tiles_n;
     int grid = std::min(tiles, dev->prop.multiProcessorCount);
     if (gp.a_mn && gp.b_mn) gemm_f16_tcgen05<true, true><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);

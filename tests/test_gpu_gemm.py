@@ -22,7 +22,8 @@ def gemm_count(cuda, fn):
     return cuda.stats()["gemm_launched"] - before
 
 
-@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 328, 136), (64, 1000, 520), (384, 72, 2048)])
+@pytest.mark.parametrize("M,N,K", [(128, 256, 64), (256, 512, 256), (200, 328, 136), (64, 1000, 520), (384, 72, 2048),
+                                   (512, 512, 320), (1000, 328, 136), (2304, 1000, 520)])
 @pytest.mark.parametrize("layout", ["KK", "KM", "MM", "MK"])
 def test_gemm_layouts(cuda, oracle, M, N, K, layout):
     # A is [M,K] (K-major) or stored [K,M] (M-major); B is [N,K] (K-major) or stored [K,N] (N-major)
