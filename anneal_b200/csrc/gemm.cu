@@ -327,18 +327,37 @@ __device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
 }
 
+__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const volatile int* failed) {
+    // like mbar_wait, but acquires at cluster scope: the data guarded by the barrier was written by the partner CTA
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        if (failed && (i & 255u) == 255u && *failed) return false;
+        uint32_t done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, int v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+
 template <bool A_MN, bool B_MN>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
     __shared__ __align__(8) uint64_t full_bar[STAGES2], empty_bar[STAGES2], acc_full[2], acc_empty[2];
+    // tile queue: the leader's producer draws tile numbers from the global counter and publishes each
+    // one in both CTAs; a slot is recycled once all ten consumers of the pair have read it
+    __shared__ __align__(8) uint64_t tq_full[TQ], tq_empty[TQ];
+    __shared__ int tile_ring[TQ];
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int failed;
 
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0 leads
-    const int pair = blockIdx.x >> 1, npairs = gridDim.x >> 1;
     const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
     const int num_tiles = tiles_m * g.tiles_n;
     const int kblocks = (g.K + BK - 1) / BK;
@@ -346,6 +365,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES2; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
         for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 8); }
+        for (int q = 0; q < TQ; q++) { mbar_init(smem_u32(&tq_full[q]), 1); mbar_init(smem_u32(&tq_empty[q]), 10); }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -363,7 +383,26 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
         if (lane == 0) {
             uint32_t stage = 0, phase = 0;
             bool ok = true;
-            for (int t = pair; t < num_tiles && ok; t += npairs) {
+            uint32_t qs = 0, qphase = 0;
+            int next = rank == 0 ? atomicAdd(g.tile_counter, 1) : 0;
+            while (ok) {
+                int t;
+                if (rank == 0) {
+                    if (!mbar_wait(smem_u32(&tq_empty[qs]), qphase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 15; break; }
+                    t = next;
+                    if (t >= num_tiles) t = -1;
+                    else next = atomicAdd(g.tile_counter, 1);
+                    tile_ring[qs] = t;
+                    st_cluster_u32(map_to_cta(smem_u32(&tile_ring[qs]), 1), t);
+                    mbar_arrive(smem_u32(&tq_full[qs]));
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&tq_full[qs]), 1));
+                } else {
+                    if (!mbar_wait_cluster(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; *(volatile int*)g.status = 16; break; }
+                    t = *(volatile int*)&tile_ring[qs];
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
+                }
+                if (++qs == TQ) { qs = 0; qphase ^= 1; }
+                if (t < 0) break;
                 const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;          // this CTA's rows of A
                 const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);          // this CTA's half of B
                 for (int kb = 0; kb < kblocks; kb++) {
@@ -388,7 +427,13 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const uint32_t idesc = (1u << 4) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
-            for (int t = pair; t < num_tiles && ok; t += npairs) {
+            uint32_t qs = 0, qphase = 0;
+            while (ok) {
+                if (!mbar_wait(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; *(volatile int*)g.status = 17; break; }
+                const int t = tile_ring[qs];
+                mbar_arrive(smem_u32(&tq_empty[qs]));
+                if (++qs == TQ) { qs = 0; qphase ^= 1; }
+                if (t < 0) break;
                 if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const uint32_t tmem_d = tmem_base + acc * BN;
@@ -419,7 +464,14 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
         const int quad = warp & 3;
         uint32_t acc = 0, acc_phase = 0;
         bool ok = true;
-        for (int t = pair; t < num_tiles && ok; t += npairs) {
+        uint32_t qs = 0, qphase = 0;
+        while (ok) {
+            if (!mbar_wait_cluster(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 18; failed = 1; } break; }
+            const int t = *(volatile int*)&tile_ring[qs];
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
+            if (++qs == TQ) { qs = 0; qphase ^= 1; }
+            if (t < 0) break;
             const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / tiles_m) * BN;
             if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
