@@ -298,8 +298,7 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 // commits release the stage and publish the accumulator in both CTAs.  No load is multicast.
 constexpr int STAGES2 = 6;
 constexpr int B2_TILE_BYTES = (BN / 2) * BK * 2;               // 16 KiB: this CTA's half of B
-constexpr int STAGE2_BYTES = A_TILE_BYTES + B2_TILE_BYTES;     // 32 KiB
-constexpr int SMEM2_BYTES = STAGES2 * STAGE2_BYTES + 1024;
+constexpr int SMEM2_BYTES = STAGES2 * (A_TILE_BYTES + B2_TILE_BYTES) + 1024;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
 __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
@@ -343,7 +342,8 @@ __device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, int v) {
     asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
 }
 
-template <bool A_MN, bool B_MN>
+// BNT = tile width in columns (256, or 128 when that fills the last wave of tiles better)
+template <bool A_MN, bool B_MN, int BNT>
 __global__ void __launch_bounds__(GEMM_THREADS, 1)
 gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
     extern __shared__ uint8_t smem_raw[];
@@ -355,6 +355,8 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
     __shared__ uint32_t tmem_base_slot;
     __shared__ volatile int failed;
 
+    constexpr int BHALF_BYTES = (BNT / 2) * BK * 2;            // this CTA's half of the B tile
+    constexpr int STAGE_B = A_TILE_BYTES + BHALF_BYTES;
     const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const uint32_t rank = cluster_ctarank();            // 0 leads
@@ -404,17 +406,17 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
                 if (t < 0) break;
                 const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;          // this CTA's rows of A
-                const int n0 = (t / tiles_m) * BN + (int)rank * (BN / 2);          // this CTA's half of B
+                const int n0 = (t / tiles_m) * BNT + (int)rank * (BNT / 2);          // this CTA's half of B
                 for (int kb = 0; kb < kblocks; kb++) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
                     const uint32_t own_fb = smem_u32(&full_bar[stage]);
                     const uint32_t fb = map_to_cta(own_fb, 0);                     // loads of both CTAs complete on the leader's barrier
-                    const uint32_t sa = smem_base + stage * STAGE2_BYTES, sb = sa + A_TILE_BYTES;
-                    if (rank == 0) mbar_expect_tx(own_fb, 2 * STAGE2_BYTES);
+                    const uint32_t sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
+                    if (rank == 0) mbar_expect_tx(own_fb, 2 * STAGE_B);
                     const int k0 = kb * BK;
                     if (A_MN) { for (int j = 0; j < BM / 64; j++) tma_load_2d_pair(sa + j * (BK * 128), &map_a, m0 + 64 * j, k0, fb); }
                     else tma_load_2d_pair(sa, &map_a, k0, m0, fb);
-                    if (B_MN) { for (int j = 0; j < BN / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
+                    if (B_MN) { for (int j = 0; j < BNT / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
                     else tma_load_2d_pair(sb, &map_b, k0, n0, fb);
                     if (++stage == STAGES2) { stage = 0; phase ^= 1; }
                 }
@@ -424,7 +426,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             // M = 256 across the pair (M >> 4 = 16 at bit 24), N = 256
-            const uint32_t idesc = (1u << 4) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BN >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
+            const uint32_t idesc = (1u << 4) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
             uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             uint32_t qs = 0, qphase = 0;
@@ -436,11 +438,11 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
                 if (t < 0) break;
                 if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + acc * BN;
+                const uint32_t tmem_d = tmem_base + acc * BNT;
                 for (int kb = 0; kb < kblocks; kb++) {
                     if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 13; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sa = smem_base + stage * STAGE2_BYTES, sb = sa + A_TILE_BYTES;
+                    const uint32_t sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
 #pragma unroll
                     for (int k = 0; k < BK / 16; k++) {
                         const uint64_t ad = A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
@@ -472,7 +474,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
             if (++qs == TQ) { qs = 0; qphase ^= 1; }
             if (t < 0) break;
-            const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / tiles_m) * BN;
+            const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / tiles_m) * BNT;
             if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quad * 32 + lane;
@@ -480,9 +482,9 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
             const bool row_ok = row < g.M;
             const bool vec_ok = (g.ldd % 8 == 0);
 #pragma unroll 1
-            for (int c = 0; c < BN / 32; c++) {
+            for (int c = 0; c < BNT / 32; c++) {
                 uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BN + c * 32, v);
+                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BNT + c * 32, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int col = n0 + c * 32;
                 if (!row_ok || col >= g.N) continue;
@@ -565,10 +567,11 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
         cudaFuncSetAttribute(gemm_f16_tcgen05<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_f16_tcgen05<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
         cudaFuncSetAttribute(gemm_f16_tcgen05<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
-        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
-        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
-        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+#define ANL_PAIR_ATTR(AM, BM_) \
+        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<AM, BM_, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES); \
+        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<AM, BM_, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
+        ANL_PAIR_ATTR(false, false) ANL_PAIR_ATTR(false, true) ANL_PAIR_ATTR(true, false) ANL_PAIR_ATTR(true, true)
+#undef ANL_PAIR_ATTR
         attr_set = true;
     }
     plan.gemm = gp;
@@ -602,22 +605,39 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream
     if (cudaMemsetAsync(g.tile_counter, 0, 4, stream) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot reset the tile counter");
     static const bool pair_ok = std::getenv("ANNEAL_GEMM_PAIR") ? std::atoi(std::getenv("ANNEAL_GEMM_PAIR")) != 0 : true;
     if (pair_ok && c.M >= 2 * BM && c.N >= BN / 2) {
-        // two-CTA tiles: B is loaded in halves of 128 columns, so its tensor map gets a 128-row box
+        // two-CTA tiles, 256 rows by 256 or 128 columns.  The narrow tile fills the last wave of tiles
+        // better but stages 1.5x the bytes per flop and measured 25% slower on 4096x4096x8192 (it
+        // becomes L2-bound), so it is only taken when the wide tile would leave most pairs idle.
+        const int npairs = dev->prop.multiProcessorCount / 2;
+        const int tm2 = (int)((c.M + 2 * BM - 1) / (2 * BM));
+        auto fill = [&](int bnt) { long long t = (long long)tm2 * ((c.N + bnt - 1) / bnt); long long w = (t + npairs - 1) / npairs; return (double)t / (double)(w * npairs); };
+        const int bnt = (fill(128) * 0.7 > fill(256)) ? 128 : 256;
+        // B is loaded in halves of bnt/2 columns, so its tensor map gets a box of that many rows
         if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
-        else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, BN / 2);
+        else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, bnt / 2);
         if (rc) return rc;
-        int tiles2 = (int)((c.M + 2 * BM - 1) / (2 * BM)) * g.tiles_n;
-        int pairs = std::min(tiles2, dev->prop.multiProcessorCount / 2);
+        g.tiles_n = (int)((c.N + bnt - 1) / bnt);
+        int tiles2 = tm2 * g.tiles_n;
+        int pairs = std::min(tiles2, npairs);
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.stream = stream;
         cudaLaunchAttribute at[1];
         at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
         cudaError_t le;
-        if (gp.a_mn && gp.b_mn) le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<true, true>, ma, mb, g);
-        else if (gp.a_mn) le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<true, false>, ma, mb, g);
-        else if (gp.b_mn) le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<false, true>, ma, mb, g);
-        else le = cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<false, false>, ma, mb, g);
+#define ANL_PAIR_LAUNCH(AM, BM_, W) cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<AM, BM_, W>, ma, mb, g)
+        if (bnt == 256) {
+            if (gp.a_mn && gp.b_mn) le = ANL_PAIR_LAUNCH(true, true, 256);
+            else if (gp.a_mn) le = ANL_PAIR_LAUNCH(true, false, 256);
+            else if (gp.b_mn) le = ANL_PAIR_LAUNCH(false, true, 256);
+            else le = ANL_PAIR_LAUNCH(false, false, 256);
+        } else {
+            if (gp.a_mn && gp.b_mn) le = ANL_PAIR_LAUNCH(true, true, 128);
+            else if (gp.a_mn) le = ANL_PAIR_LAUNCH(true, false, 128);
+            else if (gp.b_mn) le = ANL_PAIR_LAUNCH(false, true, 128);
+            else le = ANL_PAIR_LAUNCH(false, false, 128);
+        }
+#undef ANL_PAIR_LAUNCH
         if (le != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm: pair launch: ") + cudaGetErrorString(le));
         dev->stats.kernels_launched++;
         dev->stats.gemm_launched++;
