@@ -510,6 +510,10 @@ struct Gen {
         }
     }
 
+    bool unroll_short_loops = false;
+    std::string dp = "data";                         // name prefix of the buffer pointers
+    std::map<int, std::string> chain_subst;          // row chain: parameter → register holding this row's value
+
     std::string load_expr(int i, int ctx) {
         if (vec_load.count(i)) return vec_load[i] + "[u]";
         const Node& nd = N(i);
@@ -517,13 +521,28 @@ struct Gen {
         int p = (int)N(nd.src[0]).arg;
         if (p < 0 || p >= (int)it.bufs.size()) { fail("codegen: PARAM number out of range"); return "0"; }
         Lin f = flat_index(i);
+        auto cs = chain_subst.find(p);
+        if (cs != chain_subst.end()) {
+            // produced by an earlier stage of the same row chain: only this row's element is available
+            bool row_only = f.c == 0 && f.t.size() == 1 && f.t[0].second == 1 && atoms[f.t[0].first].kind == Atom::RANGE &&
+                            !loop_ranges.empty() && atoms[f.t[0].first].node == loop_ranges[0];
+            if (!row_only) { fail("chain: a stage reads another row of an earlier stage's output"); return "0"; }
+            std::string e = cs->second;
+            Cls bc = dtype_cls(it.bufs[p].dtype), want = cls(i);
+            if (dtype_cls(nd.dtype) == CBOOL) return "(" + e + " != 0u)";
+            if (bc == CF16 && want == CF32) return "__half2float(" + e + ")";
+            if (bc == CF32 && want == CF16) return "__float2half_rn(" + e + ")";
+            if (bc != want && (want == CINT || want == CUINT)) return std::string("(") + cls_ctype(want) + ")" + e;
+            if (bc != want && want == CF32) return "(float)" + e;
+            return e;
+        }
         std::string idx = render(f, ctx);
         if (opts.debug_bounds || !in_bounds(f, p)) {
             const BufDesc& b = it.bufs[p];
             std::string hi = b.symbolic() ? "(n0 * " + std::to_string(b.trailing()) + " - 1)" : std::to_string(std::max<int64_t>(b.elems(0) - 1, 0));
             idx = "clampi_(" + idx + ", " + hi + ")";
         }
-        std::string e = "data" + std::to_string(p) + "[" + idx + "]";
+        std::string e = dp + std::to_string(p) + "[" + idx + "]";
         Cls bc = dtype_cls(it.bufs[p].dtype);
         Cls want = cls(i);
         if (dtype_cls(nd.dtype) == CBOOL) return "(" + e + " != 0u)";
@@ -578,6 +597,9 @@ struct Gen {
             } else if (rr.size() == 1) {
                 std::string rn = "r" + std::to_string(N(rr[0]).aux);
                 hdr = "for (int " + rn + " = RED_BEGIN(" + range_bound(rr[0]) + "); " + rn + " < RED_END(" + range_bound(rr[0]) + "); " + rn + " += RED_STEP) {";
+                // short trip counts are unrolled: the loads of one stage of a row chain can then stay in
+                // registers for the next stage instead of being fetched from L1 again
+                if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) hdr = "_Pragma(\"unroll\") " + hdr;
             } else {
                 std::string tot = "(";
                 for (size_t k = 0; k < rr.size(); k++) tot += (k ? " * " : "") + range_bound(rr[k]);
@@ -993,6 +1015,63 @@ struct Gen {
         return m.str();
     }
 
+    // One stage of a row chain.  Requirements: static ranges, the first loop range is the row, every
+    // REDUCE is invariant along the other loop ranges (they are swept after the reductions).  Emits
+    //   <decl>  : declaration of the stage's per-row result (when the stage has no inner ranges)
+    //   <code>  : a braced block computing it for row `row`
+    bool build_chain_stage(int k, int threads_, std::string& decl, std::string& code, std::string& result_var, int64_t& rows, bool& has_inner) {
+        if (!analyse()) return false;
+        if (has_sym || loop_ranges.empty()) return fail("chain: symbolic or scalar kernel");
+        rows = N(loop_ranges[0]).arg;
+        for (size_t r = 1; r < loop_ranges.size(); r++)
+            for (int red : reduces) if (dep[red][range_slot[loop_ranges[r]]]) return fail("chain: a reduction depends on an inner output range");
+        // every load must be unit-stride (or constant) along the innermost range it sweeps inside the row,
+        // otherwise one block per row would stride through memory (a column sum is not a row chain)
+        for (int i = 0; i < n; i++) {
+            if (N(i).op != OP_INDEX || i == dst || !is_live(i)) continue;
+            int innermost = -1;
+            for (int r : all_ranges) if (r != loop_ranges[0] && dep[i][range_slot[r]]) innermost = std::max(innermost, r);
+            if (innermost < 0) continue;
+            bool ok; int64_t c = lin_coef(flat_index(i), innermost, ok);
+            if (!ok || std::llabs(c) > 1) return fail("chain: strided access inside the row");
+        }
+        has_inner = loop_ranges.size() > 1;
+        int64_t inner = 1;
+        for (size_t r = 1; r < loop_ranges.size(); r++) inner *= N(loop_ranges[r]).arg;
+        threads = threads_; lanes = threads; touts = 1; rc_layout = true;
+        reset_emit();
+        reduce_combine_mode = "group";
+        unroll_short_loops = true;
+        dp = "s" + std::to_string(k) + "_data";
+        std::ostringstream c;
+        std::string bt = buf_ctype(it.bufs[0].dtype);
+        result_var = "stage" + std::to_string(k);
+        if (!has_inner) decl = "  " + bt + " " + result_var + ";\n";
+        c << "  {   // stage " << k << "\n";
+        c << "  const int r" << N(loop_ranges[0]).aux << " = row;\n";
+        cur_top = &prelude;
+        for (int r : reduces) { val(r, -1); if (!err.empty()) return false; }
+        cur_top = nullptr;
+        std::string v = val(body, -1);
+        if (!err.empty()) return false;
+        c << prelude.code;
+        if (has_inner) {
+            c << (inner <= (int64_t)threads * 32 ? "  _Pragma(\"unroll\")\n" : "");
+            c << "  for (int gi = threadIdx.x; gi < " << inner << "; gi += " << threads << ") {\n";
+            c << decompose("gi", 1, loop_ranges.size(), "    ");
+            c << top.code;
+            c << "    " << dp << "0[(long long)row * " << inner << "LL + gi] = " << store_value(v, body) << ";\n";
+            c << "  }\n";
+        } else {
+            c << top.code;
+            c << "  " << result_var << " = " << store_value(v, body) << ";\n";
+            c << "  if (threadIdx.x == 0) " << dp << "0[row] = " << result_var << ";\n";
+        }
+        c << "  }\n";
+        code = c.str();
+        return true;
+    }
+
     // Every REDUCE is invariant along the trailing `ninv` output ranges (a row statistic consumed by
     // an elementwise expression over the row, the shape epilogue fusion produces for softmax-like
     // graphs, schedule/schedule.go:197-233).  The reference re-runs the reduction for every output
@@ -1220,6 +1299,53 @@ bool match_contraction(const Item& item, Contraction& c) {
     c.in_dtype = item.bufs[pa].dtype;
     if (item.bufs[pb].dtype != c.in_dtype) return false;
     c.out_dtype = item.bufs[0].dtype;
+    return true;
+}
+
+bool render_row_chain(const std::vector<const Item*>& items, const std::vector<std::vector<std::pair<int, int>>>& chain_reads,
+                      const CodegenOpts& opts, ChainRendered& out, std::string& err) {
+    if (items.size() < 2 || chain_reads.size() != items.size()) { err = "chain: needs at least two stages"; return false; }
+    const int threads = opts.block_threads > 0 ? opts.block_threads : 512;
+    std::ostringstream k, sig, body;
+    std::vector<std::string> result(items.size());
+    std::vector<bool> inner(items.size(), false);
+    int64_t rows = -1;
+    sig << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") row_chain(";
+    bool first_arg = true;
+    std::string decls;
+    for (size_t s = 0; s < items.size(); s++) {
+        Gen g(*items[s], opts);
+        for (auto& pr : chain_reads[s]) {
+            if (pr.second < 0 || pr.second >= (int)s || inner[pr.second]) { err = "chain: stage input is not a per-row result of an earlier stage"; return false; }
+            g.chain_subst[pr.first] = result[pr.second];
+        }
+        std::string decl, code; int64_t r = 0; bool has_inner = false;
+        if (!g.build_chain_stage((int)s, threads, decl, code, result[s], r, has_inner)) { err = g.err.empty() ? "chain: stage rejected" : g.err; return false; }
+        if (rows >= 0 && r != rows) { err = "chain: stages iterate different row counts"; return false; }
+        rows = r;
+        inner[s] = has_inner;
+        if (has_inner && s + 1 != items.size()) { err = "chain: only the last stage may produce a full row"; return false; }
+        decls += decl;
+        body << code;
+        for (size_t b = 0; b < items[s]->bufs.size(); b++) {
+            bool is_chain_out = b == 0;      // written by this kernel: never const/restrict
+            sig << (first_arg ? "" : ", ") << (is_chain_out ? "" : "const ") << buf_ctype(items[s]->bufs[b].dtype) << "* __restrict__ s" << s << "_data" << b;
+            first_arg = false;
+        }
+    }
+    sig << ")";
+    k << "#define LANES " << threads << "\n#define TOUTS 1\n#define RC_LAYOUT 1\n";
+    k << "#define RED_BEGIN(n) lane\n#define RED_END(n) (n)\n#define RED_STEP LANES\n";
+    k << Gen::preamble();
+    k << sig.str() << " {\n";
+    k << "  __shared__ float red_smem[" << std::max(threads / 32, 1) << "];\n";
+    k << "  const int lane = threadIdx.x, grp = 0;\n  (void)grp;\n";
+    k << "  const int row = blockIdx.x;\n";
+    k << decls << body.str() << "}\n";
+    out.source = k.str();
+    out.block = (unsigned)threads;
+    out.rows = rows;
+    out.note = "row chain of " + std::to_string(items.size()) + " stages, " + std::to_string(rows) + " rows";
     return true;
 }
 

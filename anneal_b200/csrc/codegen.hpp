@@ -68,6 +68,23 @@ struct Contraction {
 // is such a kernel.  Leading output ranges are folded into M when they are contiguous with it.
 bool match_contraction(const Item& item, Contraction& out);
 
+// Row chain: consecutive kernels that all iterate the same outer ("row") range, reduce only over
+// ranges inside the row, and hand each other one value per row (a softmax forward+backward is five
+// such kernels).  Rendered as ONE kernel with one block per row: the stages run back to back, each
+// stage's per-row result stays in a register for the later stages (and is still written to its
+// buffer), and the row's operands are read from DRAM once and from L1/L2 afterwards.  The reference
+// launches each stage separately and re-reads every operand from memory each time.
+struct ChainRendered {
+    std::string source, entry = "row_chain", note;
+    unsigned block = 256;
+    int64_t rows = 0;
+};
+// True when `items` (in schedule order, at least two) form such a chain.  `ext_reads[k]` must list,
+// for stage k, which of its input parameters are outputs of EARLIER stages of the chain, as
+// (parameter number, producing stage).  Kernel arguments: every stage's buffers in order.
+bool render_row_chain(const std::vector<const Item*>& items, const std::vector<std::vector<std::pair<int, int>>>& chain_reads,
+                      const CodegenOpts& opts, ChainRendered& out, std::string& err);
+
 // Hash of everything that determines the rendered source (node table, buffer dtypes and
 // shapes) and nothing that does not (buffer ids, slots).
 uint64_t structure_hash(const Item& item);

@@ -580,6 +580,17 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
     return ANL_OK;
 }
 
+// SMs the persistent GEMM may occupy.  When gradients are reduced while the backward pass is still
+// running, a few SMs are left free so that the collective's blocks (and the update kernels behind
+// them) find a place at once instead of waiting for a 150-SM persistent grid to drain.
+static int gemm_sm_budget(anl_device* dev) {
+    static const int env = std::getenv("ANNEAL_GEMM_SMS") ? std::atoi(std::getenv("ANNEAL_GEMM_SMS")) : 0;
+    int sms = dev->prop.multiProcessorCount;
+    int want = env > 0 ? env : (dev->nranks > 1 ? sms - dev->comm_reserved_sms : sms);
+    want = std::max(2, std::min(want, sms));
+    return want & ~1;
+}
+
 double gemm_flops(const Plan& plan) { const Contraction& c = plan.gemm->c; return 2.0 * (double)c.M * (double)c.N * (double)c.K; }
 
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream) {
@@ -608,7 +619,7 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream
         // two-CTA tiles, 256 rows by 256 or 128 columns.  The narrow tile fills the last wave of tiles
         // better but stages 1.5x the bytes per flop and measured 25% slower on 4096x4096x8192 (it
         // becomes L2-bound), so it is only taken when the wide tile would leave most pairs idle.
-        const int npairs = dev->prop.multiProcessorCount / 2;
+        const int npairs = gemm_sm_budget(dev) / 2;
         const int tm2 = (int)((c.M + 2 * BM - 1) / (2 * BM));
         auto fill = [&](int bnt) { long long t = (long long)tm2 * ((c.N + bnt - 1) / bnt); long long w = (t + npairs - 1) / npairs; return (double)t / (double)(w * npairs); };
         const int bnt = (fill(128) * 0.7 > fill(256)) ? 128 : 256;
@@ -644,7 +655,7 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream
         return ANL_OK;
     }
     int tiles = g.tiles_m * g.tiles_n;
-    int grid = std::min(tiles, dev->prop.multiProcessorCount);
+    int grid = std::min(tiles, gemm_sm_budget(dev));
     if (gp.a_mn && gp.b_mn) gemm_f16_tcgen05<true, true><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
     else if (gp.a_mn) gemm_f16_tcgen05<true, false><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
     else if (gp.b_mn) gemm_f16_tcgen05<false, true><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);

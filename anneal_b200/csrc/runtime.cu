@@ -402,6 +402,82 @@ int build_table(anl_device* dev, const std::vector<Item>& items, const Bindings&
     return ANL_OK;
 }
 
+// Row chains: greedily take the longest run of items starting at `first` that iterate the same row
+// count, produce one value per row (the last may produce a whole row) and are not wanted by an
+// all-reduce / update hook; render them as one kernel (cached, negative results included).
+int try_row_chain(anl_device* dev, const std::vector<Item>& items, size_t first, Table& t, cudaStream_t stream, size_t* used) {
+    *used = 0;
+    auto rows_of = [&](const Item& it, bool& full_row) -> int64_t {
+        const BufDesc& o = it.bufs[0];
+        if (!it.source.empty() || !it.sym_vars.empty() || o.shape.empty() || o.symbolic()) return -1;
+        for (auto& b : it.bufs) if (b.symbolic()) return -1;
+        full_row = o.shape.size() > 1;
+        return o.shape[0];
+    };
+    bool full = false;
+    int64_t rows = rows_of(items[first], full);
+    if (rows < 128 || full) return ANL_OK;
+    std::vector<const Item*> members;
+    std::vector<std::vector<std::pair<int, int>>> reads;
+    uint64_t key = 0x9E3779B97F4A7C15ull;
+    for (size_t j = first; j < items.size(); j++) {
+        const Item& it = items[j];
+        bool f = false;
+        if (rows_of(it, f) != rows || t.after.count(it.bufs[0].id)) break;
+        Contraction c;
+        if (match_contraction(it, c) && c.in_dtype == DT_F16 && !(dev->flags & ANL_OPEN_NO_GEMM)) break;
+        std::vector<std::pair<int, int>> rd;
+        for (size_t b = 1; b < it.bufs.size(); b++)
+            for (size_t m = 0; m < members.size(); m++)
+                if (members[m]->bufs[0].id == it.bufs[b].id) rd.push_back({(int)b, (int)m});
+        members.push_back(&it);
+        reads.push_back(rd);
+        uint64_t h = structure_hash(it);
+        key = fnv1a(&h, sizeof h, key);
+        for (auto& pr : rd) key = fnv1a(&pr, sizeof pr, key);
+        if (f) break;               // a full-row producer ends the chain
+    }
+    // try the longest run first, then shorter prefixes
+    while (members.size() >= 2) {
+        uint64_t k2 = fnv1a(&key, sizeof key, members.size());
+        for (auto* m : members) { uint64_t h = structure_hash(*m); k2 = fnv1a(&h, sizeof h, k2); }
+        auto f = dev->chains.find(k2);
+        std::shared_ptr<ChainPlan> cp;
+        if (f != dev->chains.end()) cp = f->second;
+        else {
+            cp = std::make_shared<ChainPlan>();
+            CodegenOpts o; std::string err;
+            static const int chain_threads = std::getenv("ANNEAL_CHAIN_THREADS") ? std::atoi(std::getenv("ANNEAL_CHAIN_THREADS")) : 0;
+            o.block_threads = chain_threads;
+            if (!render_row_chain(members, reads, o, cp->r, err)) cp.reset();
+            else {
+                std::shared_ptr<Module> mod;
+                if (int rc = compile_source(dev, cp->r.source, mod)) return rc;
+                CUresult cr = dev->drv.ModuleGetFunction(&cp->fn, mod->mod, cp->r.entry.c_str());
+                if (cr != CUDA_SUCCESS) return dev->fail(ANL_ERR_CUDA, "cuda: row_chain entry point missing");
+            }
+            dev->chains[k2] = cp;
+        }
+        if (cp) {
+            std::vector<void*> ptrs;
+            for (auto* m : members) for (auto& b : m->bufs) ptrs.push_back(t.bufs[b.id].ptr);
+            std::vector<void*> args;
+            for (auto& p : ptrs) args.push_back(&p);
+            cudaEvent_t e0 = nullptr, e1 = nullptr;
+            if (dev->profiling) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, stream); }
+            CUresult cr = dev->drv.LaunchKernel(cp->fn, (unsigned)cp->r.rows, 1, 1, cp->r.block, 1, 1, 0, (CUstream)stream, args.data(), nullptr);
+            if (dev->profiling) { cudaEventRecord(e1, stream); dev->prof.push_back({e0, e1, KC_REDUCE, 0.0}); }
+            if (cr != CUDA_SUCCESS) { const char* s = nullptr; dev->drv.GetErrorString(cr, &s); return dev->fail(ANL_ERR_CUDA, std::string("cuda: cuLaunchKernel(row_chain): ") + (s ? s : "?")); }
+            dev->stats.kernels_launched++;
+            *used = members.size();
+            return ANL_OK;
+        }
+        members.pop_back();
+        reads.pop_back();
+    }
+    return ANL_OK;
+}
+
 int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& binds, Table& t, cudaStream_t stream, bool keep_scratch = false) {
     CodegenOpts opts; opts.debug_bounds = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;
     // A parameter may only be updated once every kernel of this schedule that reads it has been
@@ -421,8 +497,15 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         }
         sgd_at[at].push_back(kv.first);
     }
+    const bool chains_on = !(dev->flags & ANL_OPEN_NO_ROW_CHAIN) && !(dev->flags & ANL_OPEN_BEAM);
     for (size_t i = 0; i < items.size(); i++) {
         const Item& it = items[i];
+        if (chains_on) {
+            size_t used = 0;
+            int rc = try_row_chain(dev, items, i, t, stream, &used);
+            if (rc != ANL_OK) return rc;
+            if (used > 0) { i += used - 1; continue; }
+        }
         std::shared_ptr<Plan> plan;
         CodegenOpts use = opts;
         if ((dev->flags & ANL_OPEN_BEAM) && it.source.empty()) {
@@ -630,6 +713,30 @@ int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, 
     if (klass) *klass = r.klass;
     if (block) *block = (int)r.main.block;
     if (opb) *opb = r.main.outputs_per_block;
+    if (note && note_cap) std::snprintf(note, note_cap, "%s", r.note.c_str());
+    return ANL_OK;
+}
+
+int anl_lower_chain(const uint8_t* blob, size_t blob_len, int first, int count, char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap) {
+    std::vector<Item> items; std::string err;
+    if (!parse_kir(blob, blob_len, items, err) || first < 0 || count < 2 || first + count > (int)items.size()) {
+        if (note && note_cap) std::snprintf(note, note_cap, "%s", err.empty() ? "chain: bad item range" : err.c_str());
+        return ANL_ERR_INVALID;
+    }
+    std::vector<const Item*> members;
+    std::vector<std::vector<std::pair<int, int>>> reads;
+    for (int j = first; j < first + count; j++) {
+        std::vector<std::pair<int, int>> rd;
+        for (size_t b = 1; b < items[j].bufs.size(); b++)
+            for (size_t m = 0; m < members.size(); m++)
+                if (members[m]->bufs[0].id == items[j].bufs[b].id) rd.push_back({(int)b, (int)m});
+        members.push_back(&items[j]);
+        reads.push_back(rd);
+    }
+    ChainRendered r; CodegenOpts o;
+    if (!render_row_chain(members, reads, o, r, err)) { if (note && note_cap) std::snprintf(note, note_cap, "%s", err.c_str()); return ANL_ERR_UNSUPPORTED; }
+    if (src && src_cap) { size_t n = std::min(src_cap - 1, r.source.size()); std::memcpy(src, r.source.data(), n); src[n] = 0; }
+    if (src_len) *src_len = r.source.size();
     if (note && note_cap) std::snprintf(note, note_cap, "%s", r.note.c_str());
     return ANL_OK;
 }

@@ -36,6 +36,12 @@ struct Module {
 
 // One item ready to launch: rendered source, compiled entry points, or a GEMM route.
 struct GemmPlan;
+// Several consecutive items rendered as one row-chain kernel (codegen.hpp ChainRendered).
+struct ChainPlan {
+    ChainRendered r;
+    CUfunction fn = nullptr;
+};
+
 struct Plan {
     Rendered r;
     CUfunction main = nullptr, finish = nullptr;
@@ -64,6 +70,7 @@ struct anl_device {
     anl::DriverApi drv;
     std::unordered_map<uint64_t, std::shared_ptr<anl::Plan>> plans;   // structure hash ^ opts → plan
     std::unordered_map<uint64_t, std::shared_ptr<anl::Module>> modules;  // source hash → module
+    std::unordered_map<uint64_t, std::shared_ptr<anl::ChainPlan>> chains; // hash of member items → fused kernel, or null if they do not fuse
     std::multimap<size_t, void*> pool;                                // free device blocks by size
     std::unordered_map<void*, size_t> live;                           // blocks handed out
     anl_stats stats{};
@@ -79,6 +86,7 @@ struct anl_device {
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
     bool comm_pending = false;
+    int comm_reserved_sms = 0;            // SMs the persistent GEMM leaves to collectives when nranks > 1
 
     int fail(int code, const std::string& m) { err = m; return code; }
     int alloc(size_t bytes, void** out);

@@ -90,6 +90,7 @@ def load_library():
     L.anl_outputs_free.restype = None
     L.anl_lower.argtypes = [vp, u8p, C.c_size_t, i, C.POINTER(i), C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t),
                             C.POINTER(i), C.POINTER(i), C.POINTER(C.c_int64), C.c_char_p, C.c_size_t]
+    L.anl_lower_chain.argtypes = [u8p, C.c_size_t, i, i, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t), C.c_char_p, C.c_size_t]
     L.anl_compile_check.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t]
     L.anl_benchmark.argtypes = [vp, u8p, C.c_size_t, i, C.POINTER(i), i, i, C.POINTER(_Bench)]
     L.anl_graph_create.argtypes = [vp, u8p, C.c_size_t, C.POINTER(vp)]
@@ -128,7 +129,7 @@ def load_library():
 #: every symbol include/anneal_cuda.h declares
 ABI_SYMBOLS = [
     "anl_open", "anl_close", "anl_device_info", "anl_last_error", "anl_get_stats", "anl_run", "anl_outputs_free",
-    "anl_lower", "anl_compile_check", "anl_benchmark", "anl_graph_create", "anl_graph_replay", "anl_graph_release",
+    "anl_lower", "anl_lower_chain", "anl_compile_check", "anl_benchmark", "anl_graph_create", "anl_graph_replay", "anl_graph_release",
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
     "anl_comm_destroy", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
@@ -159,6 +160,20 @@ def lower(items, index: int = 0, opts: Optional[Sequence[int]] = None):
         raise DeviceError(f"cuda: lower: {note.value.decode()} (status {rc})")
     return {"source": src.value.decode(), "class": KERNEL_CLASSES.get(klass.value, "?"), "block": block.value,
             "outputs_per_block": opb.value, "note": note.value.decode()}
+
+
+def lower_chain(items, first: int, count: int) -> dict:
+    """CUDA C of items[first:first+count] fused into one row-chain kernel; raises if they do not qualify."""
+    L = load_library()
+    blob = kir.serialize(items)
+    cap = 1 << 18
+    src = C.create_string_buffer(cap)
+    note = C.create_string_buffer(512)
+    n = C.c_size_t()
+    rc = L.anl_lower_chain(blob, len(blob), first, count, src, cap, C.byref(n), note, 512)
+    if rc:
+        raise DeviceError(f"cuda: lower_chain: {note.value.decode()} (status {rc})")
+    return {"source": src.value.decode(), "note": note.value.decode()}
 
 
 def compile_check(source: str) -> str:
@@ -221,6 +236,7 @@ class Device:
     DEBUG_BOUNDS = 1
     NO_GEMM = 2
     BEAM = 4
+    NO_ROW_CHAIN = 8
 
     def __init__(self, ordinal: Optional[int] = None, flags: int = 0):
         self.L = load_library()

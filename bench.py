@@ -258,12 +258,97 @@ def run_ours(args):
     dev.close()
 
 
+def run_other(args):
+    """The other four configurations, one GPU: samples/s (or GB/s for the bandwidth-bound one) with
+    inputs resident, timed with CUDA events over graph replays."""
+    from anneal_b200 import realize as R, workloads as W
+    from anneal_b200.device import Device
+    from anneal_b200.realize import leaf_inputs
+    from anneal_b200.train import ResidentTrainer
+    from anneal_b200.uop import dtypes
+    dev = Device(int(os.environ.get("LOCAL_RANK", "0")))
+    out = {"data": "synthetic", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True}
+    if args.workload in ("mlp", "cnn"):
+        m = W.MLP() if args.workload == "mlp" else W.SmallCNN()
+        tr = ResidentTrainer(dev, m, m.lr, use_graph=True, materialize=False, resident_inputs=True)
+        tr.load_batch(m.x, m.y)
+        for _ in range(args.warmup):
+            tr.step()
+        dev.synchronize()
+        dev.timer_start()
+        for _ in range(args.steps):
+            tr.step()
+        ms = dev.timer_stop()
+        out.update(metric=METRIC, unit=UNIT, value=m.batch * args.steps / (ms / 1e3), ms_per_step=ms / args.steps, dtype="f32",
+                   config={"workload": args.workload + "_train_step", "batch": m.batch, "kernels_per_step": len(tr.items), "loss": tr.loss()})
+    elif args.workload == "softmax":
+        s = W.SoftmaxFwdBwd(8192, 8192)
+        ts, ins = s.graph()
+        items, out_ids = R.build_schedule(ts)
+        xb = dev.buffer(dtypes.float32, s.x.size).upload(s.x)
+        gb = dev.buffer(dtypes.float32, s.g.size).upload(s.g)
+        ob = dev.buffer(dtypes.float32, s.x.size)
+        inputs = {ins["x"].node.idx: xb, ins["g"].node.idx: gb}
+        placed = {out_ids[0]: ob}
+        for _ in range(args.warmup):
+            dev.replay(items, inputs, None, placed)
+        dev.synchronize()
+        dev.timer_start()
+        for _ in range(args.steps):
+            dev.replay(items, inputs, None, placed)
+        ms = dev.timer_stop()
+        algo = 3 * s.x.size * 4
+        pk, kind = peaks()
+        gbs = algo * args.steps / (ms / 1e3) / 1e9
+        out.update(metric="softmax_fwd_bwd_hbm_gbs", unit="GB/s", value=gbs, ms_per_step=ms / args.steps, dtype="f32",
+                   config={"workload": "softmax_fwd_bwd_8192x8192", "kernels_per_step": len(items), "algorithmic_bytes": algo},
+                   roofline={"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                             "traffic": None, "peak_kind": kind + " copy", "note": "whole schedule, not one kernel"})
+    elif args.workload == "dynmlp":
+        m = W.DynMLP()
+        res = {}
+        R.DEFAULT_EXECUTOR = dev
+        for b in (1, 17, 256, 4096, 65536):
+            R.reset()
+            x, y = m.inputs(b)
+            outt, loss, grads, ins = m.graph(b)
+            items, out_ids = R.build_schedule([outt] + grads)
+            bufs = {}
+            for t, d in ((ins["x"], x), (ins["y"], y)):
+                bufs[t.node.idx] = dev.buffer(dtypes.float32, d.size).upload(d)
+            for p in m.params:
+                bufs[p.t.node.idx] = dev.buffer(dtypes.float32, p.value.size).upload(p.value)
+            placed = {}
+            for oid, it in ((o, next(i for i in items if i.bufs[0].uop_idx == o)) for o in out_ids):
+                n = int(np.prod([d if d else b for d in it.bufs[0].shape])) if it.bufs[0].shape else 1
+                placed[oid] = dev.buffer(dtypes.float32, n)
+            steps = max(2, args.steps if b <= 4096 else 2)
+            for _ in range(2):
+                dev.replay(items, bufs, {"n": b}, placed)
+            dev.synchronize()
+            dev.timer_start()
+            for _ in range(steps):
+                dev.replay(items, bufs, {"n": b}, placed)
+            ms = dev.timer_stop() / steps
+            res[str(b)] = {"us_per_replay": ms * 1e3, "samples_per_s": b / (ms / 1e3), "tflops": 42e6 * b / (ms / 1e3) / 1e12}
+            for v in list(bufs.values()) + list(placed.values()):
+                v.release()
+        R.DEFAULT_EXECUTOR = None
+        out.update(metric=METRIC, unit=UNIT, value=res["65536"]["samples_per_s"], ms_per_step=res["65536"]["us_per_replay"] / 1e3, dtype="f32",
+                   config={"workload": "dynmlp_symbolic_batch", "per_batch": res, "nvrtc_compiles": dev.stats()["nvrtc_compiles"]})
+    out["gpu_launches"] = int(dev.stats()["kernels_launched"])
+    print(json.dumps(out))
+    dev.close()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--workload", default="wide_mlp", choices=["wide_mlp", "mlp", "cnn", "softmax", "dynmlp"],
+                    help="wide_mlp is the headline configuration; the others print a one-GPU line for the remaining configurations")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="all-reduce the whole gradient bucket after the backward pass")
@@ -271,6 +356,8 @@ def main():
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)
+    elif args.workload != "wide_mlp":
+        run_other(args)
     else:
         run_ours(args)
 

@@ -103,6 +103,7 @@ int anl_get_stats(anl_device* dev, anl_stats* out);
 /* flags for anl_open */
 #define ANL_OPEN_DEBUG_BOUNDS 1u   /* clamp and check every generated load */
 #define ANL_OPEN_NO_GEMM 2u        /* never route contractions to the tensor-core kernels */
+#define ANL_OPEN_NO_ROW_CHAIN 8u    /* launch every item on its own instead of fusing per-row kernel chains */
 #define ANL_OPEN_BEAM 4u           /* apply / search autotuned transforms (the reference's ANNEAL_BEAM=1) */
 
 /* ── Executor.Run / SymbolicExecutor.RunSymbolic (backend/device.go:10-28; backend/webgpu/executor.go:26-240, 576-810) ──
@@ -127,6 +128,12 @@ void anl_outputs_free(anl_output* outs, int n_outs);
 int anl_lower(anl_device* dev_or_null, const uint8_t* blob, size_t blob_len, int index, const int* opts,
               char* src, size_t src_cap, size_t* src_len, int* klass, int* block, int64_t* outputs_per_block,
               char* note, size_t note_cap);
+
+/* Renders items [first, first+count) of the blob as one row-chain kernel (one block per row, the
+ * stages back to back, per-row results in registers) if they qualify; ANL_ERR_UNSUPPORTED with the
+ * reason in `note` otherwise.  anl_run does this by itself; the call exists for inspection. */
+int anl_lower_chain(const uint8_t* blob, size_t blob_len, int first, int count,
+                    char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap);
 
 /* NVRTC-compiles CUDA C for sm_100a; needs no GPU.  Returns ANL_ERR_COMPILE with the log in `log`. */
 int anl_compile_check(const char* src, char* log, size_t log_cap);

@@ -160,3 +160,26 @@ def test_fused_update_equals_separate_update(cuda):
     for a, b in zip(res[0][0], res[1][0]):
         assert np.array_equal(a, b)
     assert res[0][1] == res[1][1]
+
+
+def test_row_chain_fuses_softmax_fwd_bwd_into_one_kernel(cuda, oracle):
+    s = W.SoftmaxFwdBwd(256, 512)
+    ts, _ = s.graph()
+    items, out_ids, inputs = schedule(ts)
+    assert len(items) == 5
+    before = cuda.stats()["kernels_launched"]
+    got = cuda.run(items, inputs)[out_ids[0]]
+    assert cuda.stats()["kernels_launched"] - before == 1        # five scheduled kernels, one launch
+    want = oracle.run(items, inputs)[out_ids[0]]
+    assert rel_err(got, want) < 1e-4
+    assert rel_err(got, s.reference_dx().reshape(-1)) < 1e-4
+    # the unfused route gives the same answer to the same tolerance
+    from anneal_b200.device import Device
+    plain = Device(0, flags=Device.NO_ROW_CHAIN)
+    try:
+        b0 = plain.stats()["kernels_launched"]
+        ref = plain.run(items, inputs)[out_ids[0]]
+        assert plain.stats()["kernels_launched"] - b0 == 5
+    finally:
+        plain.close()
+    assert rel_err(got, ref) < 1e-5
