@@ -511,6 +511,7 @@ struct Gen {
     }
 
     bool unroll_short_loops = false;
+    int chain_vec = 1;
     std::string dp = "data";                         // name prefix of the buffer pointers
     std::map<int, std::string> chain_subst;          // row chain: parameter → register holding this row's value
 
@@ -599,7 +600,15 @@ struct Gen {
                 hdr = "for (int " + rn + " = RED_BEGIN(" + range_bound(rr[0]) + "); " + rn + " < RED_END(" + range_bound(rr[0]) + "); " + rn + " += RED_STEP) {";
                 // short trip counts are unrolled: the loads of one stage of a row chain can then stay in
                 // registers for the next stage instead of being fetched from L1 again
-                if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) hdr = "_Pragma(\"unroll\") " + hdr;
+                if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) {
+                    if (chain_vec > 1 && N(rr[0]).arg % chain_vec == 0) {
+                        // each lane takes chain_vec consecutive elements per trip: with 16-byte aligned bases the
+                        // compiler turns the unrolled scalar loads into one 128-bit access
+                        std::string V = std::to_string(chain_vec), nb = range_bound(rr[0]);
+                        hdr = "_Pragma(\"unroll\") for (int " + rn + "b = lane * " + V + "; " + rn + "b < " + nb + "; " + rn + "b += LANES * " + V + ") "
+                              "_Pragma(\"unroll\") for (int " + rn + "v = 0; " + rn + "v < " + V + "; " + rn + "v++) { const int " + rn + " = " + rn + "b + " + rn + "v;";
+                    } else hdr = "_Pragma(\"unroll\") " + hdr;
+                }
             } else {
                 std::string tot = "(";
                 for (size_t k = 0; k < rr.size(); k++) tot += (k ? " * " : "") + range_bound(rr[k]);
@@ -1042,6 +1051,7 @@ struct Gen {
         reset_emit();
         reduce_combine_mode = "group";
         unroll_short_loops = true;
+        chain_vec = 1;      // 4-element chunks per lane measured slower: nvcc keeps the loads scalar, and they lose coalescing
         dp = "s" + std::to_string(k) + "_data";
         std::ostringstream c;
         std::string bt = buf_ctype(it.bufs[0].dtype);
@@ -1056,8 +1066,13 @@ struct Gen {
         if (!err.empty()) return false;
         c << prelude.code;
         if (has_inner) {
-            c << (inner <= (int64_t)threads * 32 ? "  _Pragma(\"unroll\")\n" : "");
-            c << "  for (int gi = threadIdx.x; gi < " << inner << "; gi += " << threads << ") {\n";
+            if (inner <= (int64_t)threads * 32 && inner % chain_vec == 0 && chain_vec > 1) {
+                c << "  _Pragma(\"unroll\") for (int gb = threadIdx.x * " << chain_vec << "; gb < " << inner << "; gb += " << threads * chain_vec << ")\n";
+                c << "  _Pragma(\"unroll\") for (int gv = 0; gv < " << chain_vec << "; gv++) { const int gi = gb + gv;\n";
+            } else {
+                c << (inner <= (int64_t)threads * 32 ? "  _Pragma(\"unroll\")\n" : "");
+                c << "  for (int gi = threadIdx.x; gi < " << inner << "; gi += " << threads << ") {\n";
+            }
             c << decompose("gi", 1, loop_ranges.size(), "    ");
             c << top.code;
             c << "    " << dp << "0[(long long)row * " << inner << "LL + gi] = " << store_value(v, body) << ";\n";
@@ -1306,7 +1321,7 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
                       const CodegenOpts& opts, ChainRendered& out, std::string& err) {
     if (items.size() < 2 || chain_reads.size() != items.size()) { err = "chain: needs at least two stages"; return false; }
     const int threads = opts.block_threads > 0 ? opts.block_threads : 512;
-    std::ostringstream k, sig, body;
+    std::ostringstream k, sig, body, aligned;
     std::vector<std::string> result(items.size());
     std::vector<bool> inner(items.size(), false);
     int64_t rows = -1;
@@ -1329,7 +1344,10 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
         body << code;
         for (size_t b = 0; b < items[s]->bufs.size(); b++) {
             bool is_chain_out = b == 0;      // written by this kernel: never const/restrict
-            sig << (first_arg ? "" : ", ") << (is_chain_out ? "" : "const ") << buf_ctype(items[s]->bufs[b].dtype) << "* __restrict__ s" << s << "_data" << b;
+            std::string ty = std::string(is_chain_out ? "" : "const ") + buf_ctype(items[s]->bufs[b].dtype) + "*";
+            sig << (first_arg ? "" : ", ") << ty << " __restrict__ s" << s << "_data" << b << "_";
+            // device blocks are 256-byte aligned (pool granularity, 128-element view offsets)
+            aligned << "  " << ty << " __restrict__ s" << s << "_data" << b << " = (" << ty << ")__builtin_assume_aligned(s" << s << "_data" << b << "_, 16);\n";
             first_arg = false;
         }
     }
@@ -1341,6 +1359,7 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
     k << "  __shared__ float red_smem[" << std::max(threads / 32, 1) << "];\n";
     k << "  const int lane = threadIdx.x, grp = 0;\n  (void)grp;\n";
     k << "  const int row = blockIdx.x;\n";
+    k << aligned.str();
     k << decls << body.str() << "}\n";
     out.source = k.str();
     out.block = (unsigned)threads;
