@@ -9,7 +9,7 @@ HERE = os.path.dirname(os.path.abspath(__file__))
 CSRC = os.path.join(HERE, "csrc")
 LIBDIR = os.path.join(HERE, "lib")
 SO = os.path.join(LIBDIR, "libanneal_cuda.so")
-SOURCES = ["kir.cpp", "codegen.cpp", "comm.cpp", "runtime.cu", "gemm.cu", "static_sum.cu", "beam.cpp"]
+SOURCES = ["kir.cpp", "codegen.cpp", "comm.cpp", "runtime.cu", "gemm.cu", "gemm_f32.cu", "static_sum.cu", "beam.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
 FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
          "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-cudart", "static"]

@@ -1270,7 +1270,7 @@ struct Gen {
 bool match_contraction(const Item& item, Contraction& c) {
     CodegenOpts o;
     Gen g(item, o);
-    if (!g.analyse() || g.has_sym) return false;
+    if (!g.analyse()) return false;
     if (g.reduces.size() != 1 || g.reduces[0] != g.body) return false;
     const Node& red = g.N(g.body);
     if ((int)red.aux != OP_ADD) return false;
@@ -1296,21 +1296,29 @@ bool match_contraction(const Item& item, Contraction& c) {
     if (coef(fa, n_range) != 0 && coef(fb, n_range) == 0) { std::swap(ia, ib); std::swap(pa, pb); std::swap(fa, fb); }
     if (coef(fa, n_range) != 0 || coef(fb, n_range) == 0) return false;
     // remaining output ranges form M; they must index only A, with nested strides
+    // a symbolic extent (the bound batch) may be all of M or all of K; its value arrives at launch
+    if (g.N(n_range).symbolic()) return false;
     int64_t M = 1, a_sm = 0;
+    c.m_sym = false; c.k_sym = g.N(k).symbolic();
     for (int i = (int)g.loop_ranges.size() - 2; i >= 0; i--) {
         int r = g.loop_ranges[i];
         if (coef(fb, r) != 0) return false;
         int64_t ca = coef(fa, r);
+        if (g.N(r).symbolic()) {
+            if (g.loop_ranges.size() != 2) return false;
+            c.m_sym = true; a_sm = ca; M = 0;
+            break;
+        }
         if (M == 1) a_sm = ca;
         else if (ca != a_sm * M) return false;
         M *= g.N(r).arg;
     }
     if (g.loop_ranges.size() == 1) { M = 1; a_sm = 0; }
     c.a_param = pa; c.b_param = pb;
-    c.M = M; c.N = g.N(n_range).arg; c.K = g.N(k).arg;
+    c.M = M; c.N = g.N(n_range).arg; c.K = c.k_sym ? 0 : g.N(k).arg;
     c.a_sm = a_sm; c.a_sk = coef(fa, k); c.a_off = fa.c;
     c.b_sn = coef(fb, n_range); c.b_sk = coef(fb, k); c.b_off = fb.c;
-    if (c.a_sk == 0 || c.b_sk == 0 || c.b_sn == 0 || (M > 1 && a_sm == 0)) return false;
+    if (c.a_sk == 0 || c.b_sk == 0 || c.b_sn == 0 || ((M > 1 || c.m_sym) && a_sm == 0)) return false;
     c.in_dtype = item.bufs[pa].dtype;
     if (item.bufs[pb].dtype != c.in_dtype) return false;
     c.out_dtype = item.bufs[0].dtype;

@@ -63,6 +63,7 @@ struct Contraction {
     int64_t a_sm = 0, a_sk = 0, a_off = 0;
     int64_t b_sn = 0, b_sk = 0, b_off = 0;
     int in_dtype = DT_F32, out_dtype = DT_F32;
+    bool m_sym = false, k_sym = false;   // M (or K) is the symbolic batch: 0 here, bound at launch
 };
 // Contraction selection (the schedule/kernels.go hook the CUDA device adds): true when `item`
 // is such a kernel.  Leading output ranges are folded into M when they are contiguous with it.

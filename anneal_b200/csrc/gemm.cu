@@ -39,6 +39,7 @@ struct GemmPlan {
     Contraction c;
     bool a_mn = false, b_mn = false;     // MN-major operands
     int64_t lda = 0, ldb = 0;            // elements between consecutive rows of the 2-D global views
+    bool f32 = false;                    // f32 operands: the FP32-pipe kernel instead of tcgen05
     int* status_host = nullptr;          // mapped, host-visible
     int* status_dev = nullptr;
 };
@@ -538,7 +539,24 @@ static int encode_map(anl_device* dev, CUtensorMap* map, const void* base, uint6
 int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
     Contraction c;
     if (!match_contraction(item, c)) return ANL_ERR_UNSUPPORTED;
+    const bool dynamic = c.m_sym || c.k_sym;
+    if (c.in_dtype == DT_F32 && c.out_dtype == DT_F32) {
+        if (c.a_sk != 1 && c.a_sm != 1) return ANL_ERR_UNSUPPORTED;
+        if (c.b_sk != 1 && c.b_sn != 1) return ANL_ERR_UNSUPPORTED;
+        if (!dynamic && !gemm_f32_worth(c.M, c.N, c.K)) return ANL_ERR_UNSUPPORTED;
+        if (c.N < 64) return ANL_ERR_UNSUPPORTED;
+        auto gp = std::make_shared<GemmPlan>();
+        gp->c = c; gp->f32 = true;
+        plan.gemm = gp;
+        plan.gemm_dynamic = dynamic;
+        if (!dynamic) {
+            plan.r.klass = KC_GEMM;
+            plan.r.note = "gemm f32 M=" + std::to_string(c.M) + " N=" + std::to_string(c.N) + " K=" + std::to_string(c.K);
+        }
+        return ANL_OK;
+    }
     if (c.in_dtype != DT_F16 || c.out_dtype != DT_F16) return ANL_ERR_UNSUPPORTED;
+    if (dynamic) return ANL_ERR_UNSUPPORTED;                                   // tcgen05 path: static extents only
     if (c.M < 64 || c.N < 64 || c.K < 32) return ANL_ERR_UNSUPPORTED;          // not worth a 128x256 tile
     auto gp = std::make_shared<GemmPlan>();
     gp->c = c;
@@ -591,11 +609,24 @@ static int gemm_sm_budget(anl_device* dev) {
     return want & ~1;
 }
 
-double gemm_flops(const Plan& plan) { const Contraction& c = plan.gemm->c; return 2.0 * (double)c.M * (double)c.N * (double)c.K; }
+double gemm_flops(const Plan& plan, int64_t sym_value) {
+    const Contraction& c = plan.gemm->c;
+    return 2.0 * (double)(c.m_sym ? sym_value : c.M) * (double)c.N * (double)(c.k_sym ? sym_value : c.K);
+}
 
-int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream) {
+bool gemm_taken(const Plan& plan, int64_t sym_value) {
+    if (!plan.gemm) return false;
+    if (!plan.gemm_dynamic) return plan.r.klass == KC_GEMM;
+    const Contraction& c = plan.gemm->c;
+    return gemm_f32_worth(c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K);
+}
+
+int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream) {
     const GemmPlan& gp = *plan.gemm;
     const Contraction& c = gp.c;
+    if (gp.f32)
+        return launch_gemm_f32(dev, (const float*)bufs[c.a_param] + c.a_off, (const float*)bufs[c.b_param] + c.b_off, (float*)bufs[0],
+                               c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K, c.a_sm, c.a_sk, c.b_sn, c.b_sk, stream);
     if (*gp.status_host != 0) return dev->fail(ANL_ERR_CUDA, "gemm: an earlier launch timed out on a barrier (code " + std::to_string(*gp.status_host) + ")");
     const __half* a = (const __half*)bufs[c.a_param] + c.a_off;
     const __half* b = (const __half*)bufs[c.b_param] + c.b_off;

@@ -1,0 +1,233 @@
+// f32 contraction kernel: D[m, n] = sum_k A[m, k] * B[n, k] with f32 operands, f32 accumulation in
+// ascending k, f32 result.  The reference lowers such a kernel to one thread per output element
+// that walks k serially (codegen/lower.go:158-171 and the REDUCE loop of codegen/wgsl.go); this is
+// the same sum in the same order per output element (fused multiply-add instead of multiply then
+// add, so results differ from the reference by rounding only), tiled through shared memory so that
+// every operand element is read from HBM once per tile row/column instead of once per output.
+//
+// There is no single-precision tensor-core mode on sm_100 that keeps f32 products exact (TF32 drops
+// 13 mantissa bits), so this path stays on the FP32 pipes: 128x128 output tile per CTA, 16-deep k
+// slices double-buffered in shared memory, 8x8 outputs per thread.  Either operand may have k or
+// its row index contiguous; both are staged k-major so the inner loop reads 128-bit vectors.
+#include <cuda_runtime.h>
+
+#include <algorithm>
+#include <cstdint>
+#include <string>
+
+#include "runtime.hpp"
+
+namespace anl {
+
+// Unroll factor of the 16-step inner product and CTAs per SM.  Two CTAs of 128 registers per
+// thread hide each other's barriers; unrolling by 2 keeps the register allocator under that cap
+// without spills and measured fastest (45-50 TFLOP/s on 8192x4096x1024 against 40-47 unrolled
+// fully, 34-44 with one 255-register CTA per SM).
+#ifndef ANL_F32_UNROLL
+#define ANL_F32_UNROLL 2
+#endif
+#ifndef ANL_F32_MINBLOCKS
+#define ANL_F32_MINBLOCKS 2
+#endif
+constexpr int F_UNROLL = ANL_F32_UNROLL;
+constexpr int F_BM = 128, F_BN = 128, F_BK = 16, F_THREADS = 256, F_LD = F_BM + 4;
+
+struct GemmF32Args {
+    const float* a; const float* b; float* d;
+    int M, N, K;
+    long long a_sm, a_sk, b_sn, b_sk;
+    int ldd, tiles_m, tiles_n;
+};
+
+// Fetches this thread's 8 elements (two groups of 4) of each [128 rows x 16 k] operand slice.
+// KC: the groups run along k (element (r, k) at base[r * s_r + k * s_k], s_k == 1 when VEC);
+// otherwise along the row index (s_r == 1 when VEC).  The pointer walks down k by one slice per
+// load, so the loop carries one pointer per operand instead of recomputing 64-bit products.
+// VEC: 128-bit loads are legal (alignment and extents checked by the host), and a group is then
+// either fully inside the operand or fully outside.
+template <bool KC, bool VEC>
+struct SliceFetch {
+    const float* p;
+    long long second, step, sg;    // offset of the second group, one slice along k, stride inside a group
+    int kofs, fc0, fc1;            // k offset of the first group; valid elements along the fixed index
+
+    __device__ __forceinline__ void init(const float* base, long long s_r, long long s_k, int r0, int R, int tid) {
+        if (KC) {
+            const int row = tid >> 2;
+            kofs = (tid & 3) * 4;
+            p = base + (long long)(r0 + row) * s_r + (long long)kofs * s_k;
+            second = 64 * s_r; sg = s_k;
+            fc0 = r0 + row < R ? 4 : 0; fc1 = r0 + row + 64 < R ? 4 : 0;
+        } else {
+            const int rq = (tid & 31) * 4;
+            kofs = tid >> 5;
+            p = base + (long long)kofs * s_k + (long long)(r0 + rq) * s_r;
+            second = 8 * s_k; sg = s_r;
+            fc0 = fc1 = max(0, min(4, R - (r0 + rq)));
+        }
+        step = F_BK * s_k;
+    }
+
+    __device__ __forceinline__ void load(int k0, int K, float (&v)[8]) {
+#pragma unroll
+        for (int j = 0; j < 2; j++) {
+            const float* q = j ? p + second : p;
+            const int kv = K - (k0 + kofs + (KC ? 0 : 8 * j));
+            const int fc = j ? fc1 : fc0;
+            const int cnt = KC ? min(fc, max(kv, 0)) : (kv > 0 ? fc : 0);
+            if (VEC) {
+                float4 x = make_float4(0.f, 0.f, 0.f, 0.f);
+                if (cnt >= 4) x = *reinterpret_cast<const float4*>(q);
+                v[j * 4 + 0] = x.x; v[j * 4 + 1] = x.y; v[j * 4 + 2] = x.z; v[j * 4 + 3] = x.w;
+            } else {
+#pragma unroll
+                for (int i = 0; i < 4; i++) v[j * 4 + i] = i < cnt ? q[i * sg] : 0.f;
+            }
+        }
+        p += step;
+    }
+};
+
+// Store the fetched elements k-major: slice[k][row].
+template <bool KC>
+__device__ __forceinline__ void stage_slice(float (*slice)[F_LD], int tid, const float (&v)[8]) {
+#pragma unroll
+    for (int j = 0; j < 2; j++) {
+        const int f = tid + j * F_THREADS;
+        if (KC) {
+            const int row = f >> 2, kq = (f & 3) * 4;
+#pragma unroll
+            for (int i = 0; i < 4; i++) slice[kq + i][row] = v[j * 4 + i];
+        } else {
+            const int kk = f >> 5, rq = (f & 31) * 4;
+            *reinterpret_cast<float4*>(&slice[kk][rq]) = make_float4(v[j * 4 + 0], v[j * 4 + 1], v[j * 4 + 2], v[j * 4 + 3]);
+        }
+    }
+}
+
+template <bool A_KC, bool B_KC, bool VEC>
+__global__ void __launch_bounds__(F_THREADS, ANL_F32_MINBLOCKS) gemm_f32_simt(const GemmF32Args g) {
+    __shared__ __align__(16) float As[2][F_BK][F_LD];
+    __shared__ __align__(16) float Bs[2][F_BK][F_LD];
+    const int tid = threadIdx.x;
+    // tiles are numbered so that consecutive CTAs share one column panel of B and walk down M in
+    // groups of 8 row tiles: the group's A panels and the B panel stay in L2 while they are reused
+    const int group = 8;
+    const int per_group = group * g.tiles_n;
+    const int bid = blockIdx.x;
+    const int g0 = (bid / per_group) * group;
+    const int gsz = min(group, g.tiles_m - g0);
+    const int tm = g0 + (bid % per_group) % gsz;
+    const int tn = (bid % per_group) / gsz;
+    const int m0 = tm * F_BM, n0 = tn * F_BN;
+    const int tx = tid & 15, ty = tid >> 4;
+
+    float acc[8][8];
+#pragma unroll
+    for (int i = 0; i < 8; i++)
+#pragma unroll
+        for (int j = 0; j < 8; j++) acc[i][j] = 0.f;
+
+    float ra[8], rb[8];
+    const int nk = (g.K + F_BK - 1) / F_BK;
+    SliceFetch<A_KC, VEC> fa;
+    SliceFetch<B_KC, VEC> fb;
+    fa.init(g.a, g.a_sm, g.a_sk, m0, g.M, tid);
+    fb.init(g.b, g.b_sn, g.b_sk, n0, g.N, tid);
+    fa.load(0, g.K, ra);
+    fb.load(0, g.K, rb);
+    stage_slice<A_KC>(As[0], tid, ra);
+    stage_slice<B_KC>(Bs[0], tid, rb);
+    __syncthreads();
+    for (int kt = 0; kt < nk; kt++) {
+        const int cur = kt & 1;
+        if (kt + 1 < nk) {
+            fa.load((kt + 1) * F_BK, g.K, ra);
+            fb.load((kt + 1) * F_BK, g.K, rb);
+        }
+#pragma unroll F_UNROLL
+        for (int k = 0; k < F_BK; k++) {
+            const float4 a0 = *reinterpret_cast<const float4*>(&As[cur][k][ty * 4]);
+            const float4 a1 = *reinterpret_cast<const float4*>(&As[cur][k][64 + ty * 4]);
+            const float4 b0 = *reinterpret_cast<const float4*>(&Bs[cur][k][tx * 4]);
+            const float4 b1 = *reinterpret_cast<const float4*>(&Bs[cur][k][64 + tx * 4]);
+            const float av[8] = {a0.x, a0.y, a0.z, a0.w, a1.x, a1.y, a1.z, a1.w};
+            const float bv[8] = {b0.x, b0.y, b0.z, b0.w, b1.x, b1.y, b1.z, b1.w};
+#pragma unroll
+            for (int i = 0; i < 8; i++)
+#pragma unroll
+                for (int j = 0; j < 8; j++) acc[i][j] = fmaf(av[i], bv[j], acc[i][j]);
+        }
+        if (kt + 1 < nk) {
+            stage_slice<A_KC>(As[cur ^ 1], tid, ra);
+            stage_slice<B_KC>(Bs[cur ^ 1], tid, rb);
+        }
+        __syncthreads();
+    }
+    const bool vec_out = VEC && (g.ldd & 3) == 0 && (g.N & 3) == 0;
+#pragma unroll
+    for (int i = 0; i < 8; i++) {
+        const int m = m0 + (i < 4 ? ty * 4 + i : 64 + ty * 4 + (i - 4));
+        if (m >= g.M) continue;
+        float* drow = g.d + (long long)m * g.ldd;
+#pragma unroll
+        for (int h = 0; h < 2; h++) {
+            const int n = n0 + h * 64 + tx * 4;
+            if (vec_out) {
+                if (n < g.N) *reinterpret_cast<float4*>(drow + n) = make_float4(acc[i][h * 4 + 0], acc[i][h * 4 + 1], acc[i][h * 4 + 2], acc[i][h * 4 + 3]);
+            } else {
+#pragma unroll
+                for (int j = 0; j < 4; j++) if (n + j < g.N) drow[n + j] = acc[i][h * 4 + j];
+            }
+        }
+    }
+}
+
+// Whether a contraction of these extents is worth the tiled kernel: below this the generated
+// one-thread-per-output kernel finishes sooner (a 128x128 tile would leave most SMs idle).
+bool gemm_f32_worth(int64_t M, int64_t N, int64_t K) {
+    if (M <= 0 || N <= 0 || K <= 0) return false;
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return false;
+    const int64_t tiles = ((M + F_BM - 1) / F_BM) * ((N + F_BN - 1) / F_BN);
+    return tiles >= 16 && K >= 64 && tiles < (1ll << 31);
+}
+
+int launch_gemm_f32(anl_device* dev, const float* a, const float* b, float* d, int64_t M, int64_t N, int64_t K,
+                    int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk, cudaStream_t stream) {
+    GemmF32Args g;
+    g.a = a; g.b = b; g.d = d;
+    g.M = (int)M; g.N = (int)N; g.K = (int)K;
+    g.a_sm = a_sm; g.a_sk = a_sk; g.b_sn = b_sn; g.b_sk = b_sk;
+    g.ldd = (int)N;
+    g.tiles_m = (int)((M + F_BM - 1) / F_BM); g.tiles_n = (int)((N + F_BN - 1) / F_BN);
+    // staged "k contiguous" unless the row index is the contiguous one; an operand with neither
+    // contiguous still works through the scalar loads of the k-contiguous form
+    const bool a_kc = a_sm != 1 || M == 1, b_kc = b_sn != 1;
+    auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    // 128-bit loads: aligned bases, the strided index a multiple of 4 elements, and the contiguous
+    // extent a multiple of 4 so that no vector straddles the edge
+    bool vec = al16(a) && al16(b) && al16(d);
+    vec = vec && (a_kc ? (a_sk == 1 && a_sm % 4 == 0 && K % 4 == 0) : (a_sk % 4 == 0 && M % 4 == 0));
+    vec = vec && (b_kc ? (b_sk == 1 && b_sn % 4 == 0 && K % 4 == 0) : (b_sk % 4 == 0 && N % 4 == 0));
+    const unsigned grid = (unsigned)(g.tiles_m * g.tiles_n);
+#define ANL_F32_LAUNCH(AK, BK_, V) gemm_f32_simt<AK, BK_, V><<<grid, F_THREADS, 0, stream>>>(g)
+    if (vec) {
+        if (a_kc && b_kc) ANL_F32_LAUNCH(true, true, true);
+        else if (a_kc) ANL_F32_LAUNCH(true, false, true);
+        else if (b_kc) ANL_F32_LAUNCH(false, true, true);
+        else ANL_F32_LAUNCH(false, false, true);
+    } else {
+        if (a_kc && b_kc) ANL_F32_LAUNCH(true, true, false);
+        else if (a_kc) ANL_F32_LAUNCH(true, false, false);
+        else if (b_kc) ANL_F32_LAUNCH(false, true, false);
+        else ANL_F32_LAUNCH(false, false, false);
+    }
+#undef ANL_F32_LAUNCH
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm f32: launch: ") + cudaGetErrorString(e));
+    dev->stats.kernels_launched++;
+    dev->stats.gemm_launched++;
+    return ANL_OK;
+}
+
+}  // namespace anl

@@ -186,7 +186,7 @@ int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::sh
     } else {
         bool routed = false;
         if (opts_default(opts) && !(dev->flags & ANL_OPEN_NO_GEMM)) routed = plan_gemm(dev, item, *p) == ANL_OK;
-        if (!routed) {
+        if (!routed || p->gemm_dynamic) {
             std::string err;
             if (!render_cuda(item, opts, p->r, err)) return dev->fail(ANL_ERR_UNSUPPORTED, err);
         }
@@ -222,7 +222,8 @@ int launch_plan(anl_device* dev, const Plan& plan, const Item& item, void* const
     if (!dev->profiling) return launch_plan_inner(dev, plan, item, bufs, sym_value, stream, keep_scratch);
     anl_device::ProfRec r{};
     cudaEventCreate(&r.e0); cudaEventCreate(&r.e1);
-    r.klass = plan.r.klass; r.flops = plan.r.klass == KC_GEMM ? gemm_flops(plan) : 0.0;
+    const bool gemm = gemm_taken(plan, sym_value);
+    r.klass = gemm ? KC_GEMM : plan.r.klass; r.flops = gemm ? gemm_flops(plan, sym_value) : 0.0;
     cudaEventRecord(r.e0, stream);
     int rc = launch_plan_inner(dev, plan, item, bufs, sym_value, stream, keep_scratch);
     cudaEventRecord(r.e1, stream);
@@ -232,7 +233,7 @@ int launch_plan(anl_device* dev, const Plan& plan, const Item& item, void* const
 
 static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item, void* const* bufs, int64_t sym_value, cudaStream_t stream,
                              std::vector<void*>* keep_scratch) {
-    if (plan.r.klass == KC_GEMM) return launch_gemm(dev, plan, bufs, stream);
+    if (gemm_taken(plan, sym_value)) return launch_gemm(dev, plan, bufs, sym_value, stream);
     int nb = (int)item.bufs.size();
     std::vector<void*> ptrs(bufs, bufs + nb);
     int n0 = (int)sym_value;
@@ -713,6 +714,14 @@ int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, 
     if (klass) *klass = r.klass;
     if (block) *block = (int)r.main.block;
     if (opb) *opb = r.main.outputs_per_block;
+    {   // say when the device would route this item to a contraction kernel instead of this source
+        Contraction c;
+        if (match_contraction(items[index], c)) {
+            auto ext = [](int64_t v, bool sym) { return sym ? std::string("n") : std::to_string(v); };
+            r.note += (r.note.empty() ? "" : "; ") + std::string("contraction ") + (c.in_dtype == DT_F16 ? "f16" : c.in_dtype == DT_F32 ? "f32" : "other") +
+                      " M=" + ext(c.M, c.m_sym) + " N=" + std::to_string(c.N) + " K=" + ext(c.K, c.k_sym);
+        }
+    }
     if (note && note_cap) std::snprintf(note, note_cap, "%s", r.note.c_str());
     return ANL_OK;
 }

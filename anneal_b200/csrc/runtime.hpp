@@ -46,6 +46,7 @@ struct Plan {
     Rendered r;
     CUfunction main = nullptr, finish = nullptr;
     std::shared_ptr<GemmPlan> gemm;
+    bool gemm_dynamic = false;   // a symbolic extent decides per launch between `gemm` and the rendered kernel
 };
 
 }  // namespace anl
@@ -111,8 +112,13 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 // hand-written contraction kernels (gemm.cu); returns ANL_OK and fills plan.gemm if the item is a
 // dense SUM-of-products over buffers that they cover, ANL_ERR_UNSUPPORTED otherwise
 int plan_gemm(anl_device* dev, const Item& item, Plan& plan);
-int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, cudaStream_t stream);
-double gemm_flops(const Plan& plan);
+int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream);
+double gemm_flops(const Plan& plan, int64_t sym_value);
+// true when this launch (with the symbolic extent bound to sym_value) goes to the contraction kernel
+bool gemm_taken(const Plan& plan, int64_t sym_value);
+bool gemm_f32_worth(int64_t M, int64_t N, int64_t K);
+int launch_gemm_f32(anl_device* dev, const float* a, const float* b, float* d, int64_t M, int64_t N, int64_t K,
+                    int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk, cudaStream_t stream);
 
 // data parallel (comm.cpp): queue an all-reduce of [ptr, ptr+elems) on the communication stream after
 // everything queued so far on `stream`; comm_join makes `stream` wait for all of them

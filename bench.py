@@ -308,6 +308,7 @@ def run_other(args):
         m = W.DynMLP()
         res = {}
         R.DEFAULT_EXECUTOR = dev
+        R.MATERIALIZE_CONTRACTION_OPERANDS = True
         for b in (1, 17, 256, 4096, 65536):
             R.reset()
             x, y = m.inputs(b)
@@ -334,6 +335,7 @@ def run_other(args):
             for v in list(bufs.values()) + list(placed.values()):
                 v.release()
         R.DEFAULT_EXECUTOR = None
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
         out.update(metric=METRIC, unit=UNIT, value=res["65536"]["samples_per_s"], ms_per_step=res["65536"]["us_per_replay"] / 1e3, dtype="f32",
                    config={"workload": "dynmlp_symbolic_batch", "per_batch": res, "nvrtc_compiles": dev.stats()["nvrtc_compiles"]})
     out["gpu_launches"] = int(dev.stats()["kernels_launched"])

@@ -45,3 +45,63 @@ def test_linear_forward_backward_routes_to_gemm(cuda, oracle):
     finally:
         R.MATERIALIZE_CONTRACTION_OPERANDS = False
     assert n == 8      # 3 forward, 2 input-gradient, 3 weight-gradient contractions
+
+
+# ── f32 contractions: the FP32-pipe tiled kernel ────────────────────────────────────────────────
+F32 = 1e-5
+
+
+def fleaf(shape, seed):
+    n = int(np.prod(shape))
+    return Tensor.new_leaf(shape, dtypes.float32).set_data(W.normal(12, seed, n) * np.float32(0.5))
+
+
+@pytest.mark.parametrize("M,N,K", [(512, 640, 136), (515, 601, 131), (2048, 1024, 64), (130, 2100, 1000)])
+@pytest.mark.parametrize("layout", ["KK", "KM", "MM", "MK"])
+def test_gemm_f32_layouts(cuda, oracle, M, N, K, layout):
+    a = fleaf((M, K), 1) if layout[0] == "K" else fleaf((K, M), 1).permute((1, 0))
+    b = fleaf((N, K), 2).permute((1, 0)) if layout[1] == "K" else fleaf((K, N), 2)
+    out = a.matmul(b)
+    n = gemm_count(cuda, lambda: compare(cuda, oracle, [out], F32, what=f"gemm f32 {layout} {M}x{N}x{K}"))
+    assert n == 1, "f32 contraction was not routed to the tiled kernel"
+
+
+def test_gemm_f32_small_stays_on_generated_kernel(cuda, oracle):
+    out = fleaf((64, 784), 1).matmul(fleaf((128, 784), 2).permute((1, 0)))
+    n = gemm_count(cuda, lambda: compare(cuda, oracle, [out], F32, what="small f32 matmul"))
+    assert n == 0
+
+
+@pytest.mark.parametrize("b,gemms", [(3, 0), (300, 4), (2100, 5)])
+def test_gemm_f32_symbolic_batch(cuda, oracle, b, gemms):
+    """The bound batch is M of the forward/input-gradient contractions and K of the weight-gradient
+    ones; one compiled plan serves every binding and picks the kernel per launch.
+
+    The tiled kernel accumulates with fused multiply-adds, the oracle rounds the product first, so a
+    hidden pre-activation within rounding distance of zero can land on the other side of the ReLU
+    and switch that unit's gradient on or off for one sample.  Hidden units with such a sample are
+    left out of the comparison of the first layer's gradients; everything else is continuous in the
+    pre-activation and is compared in full."""
+    from anneal_b200 import realize as R
+    from util import rel_err, schedule
+    R.MATERIALIZE_CONTRACTION_OPERANDS = True
+    try:
+        m = W.DynMLP(din=512, hidden=1024, dout=256, max_batch=4096)
+        x, y = m.inputs(b)
+        out, loss, grads, ins = m.graph(b, x, y)
+        items, out_ids, inputs = schedule([out] + grads)
+        before = cuda.stats()["gemm_launched"]
+        got = cuda.run(items, inputs, {"n": b})
+        n = cuda.stats()["gemm_launched"] - before
+        want = oracle.run(items, inputs, {"n": b})
+    finally:
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+    assert n == gemms
+    z = x.reshape(b, 512).astype(np.float64) @ m.params[0].value.reshape(1024, 512).astype(np.float64).T + m.params[1].value
+    steady = ~(np.abs(z) < 1e-5).any(axis=0)            # hidden units whose ReLU masks do not hang on rounding
+    assert steady.sum() >= 1000
+    o_id, dw1, db1, dw2, db2 = out_ids
+    for k in (o_id, dw2, db2):
+        assert rel_err(got[k], want[k]) <= 2e-5, (b, k)
+    assert rel_err(got[dw1].reshape(1024, 512)[steady], want[dw1].reshape(1024, 512)[steady]) <= 2e-5
+    assert rel_err(got[db1][steady], want[db1][steady]) <= 2e-5
