@@ -58,6 +58,12 @@ struct anl_buffer {
     void* ptr = nullptr;
     size_t bytes = 0;
     bool view = false;      // a window of another buffer: the memory is not ours to release
+    // pipelined upload: an f32 block the copy stream fills while the compute stream still works on
+    // the buffer's current contents
+    void* stage = nullptr;
+    int64_t staged_elems = 0;
+    cudaEvent_t stage_ready = nullptr, stage_free = nullptr;
+    bool stage_free_recorded = false;
 };
 
 struct anl_device {
@@ -65,6 +71,7 @@ struct anl_device {
     unsigned flags = 0;
     cudaStream_t stream = nullptr;
     cudaStream_t comm_stream = nullptr;
+    cudaStream_t copy_stream = nullptr;   // host-to-device staging of the next batch, created on first use
     cudaEvent_t comm_event = nullptr, comm_done = nullptr;
     std::string err;
     cudaDeviceProp prop{};

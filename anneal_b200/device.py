@@ -100,6 +100,8 @@ def load_library():
     L.anl_graph_release.restype = None
     L.anl_buffer_create.argtypes = [vp, i, C.c_int64, C.POINTER(vp)]
     L.anl_buffer_upload.argtypes = [vp, vp, C.c_int64]
+    L.anl_buffer_upload_begin.argtypes = [vp, vp, C.c_int64]
+    L.anl_buffer_upload_commit.argtypes = [vp]
     L.anl_buffer_download.argtypes = [vp, vp, C.c_int64]
     L.anl_buffer_release.argtypes = [vp]
     L.anl_buffer_release.restype = None
@@ -130,7 +132,7 @@ def load_library():
 ABI_SYMBOLS = [
     "anl_open", "anl_close", "anl_device_info", "anl_last_error", "anl_get_stats", "anl_run", "anl_outputs_free",
     "anl_lower", "anl_lower_chain", "anl_compile_check", "anl_benchmark", "anl_graph_create", "anl_graph_replay", "anl_graph_release",
-    "anl_buffer_create", "anl_buffer_upload", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
+    "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
     "anl_comm_destroy", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
     "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search",
@@ -213,6 +215,19 @@ class ResidentBuffer:
     def upload(self, data):
         a = np.ascontiguousarray(data, dtype=np.float32).reshape(-1)
         self.dev._check(self.dev.L.anl_buffer_upload(self.h, a.ctypes.data, a.size))
+        return self
+
+    def upload_begin(self, data: np.ndarray):
+        """Start copying `data` (contiguous float32, ideally pinned) on the copy stream; the buffer keeps
+        its contents until `upload_commit`.  The array is held until then."""
+        if data.dtype != np.float32 or not data.flags["C_CONTIGUOUS"]:
+            raise ValueError("upload_begin: a contiguous float32 array is required (no hidden copy may outlive the call)")
+        self._staged = data
+        self.dev._check(self.dev.L.anl_buffer_upload_begin(self.h, data.ctypes.data, data.size))
+        return self
+
+    def upload_commit(self):
+        self.dev._check(self.dev.L.anl_buffer_upload_commit(self.h))
         return self
 
     def download(self) -> np.ndarray:

@@ -87,8 +87,21 @@ class ResidentTrainer:
         self.x_res.upload(x)
         self.y_res.upload(y)
 
+    def prefetch(self, x: np.ndarray, y: np.ndarray) -> None:
+        """Resident-input mode: start moving the NEXT batch to the device on the copy stream while
+        the steps already queued run; the following ``step`` picks it up. ``x`` and ``y`` are
+        contiguous float32 host arrays (pinned for a truly asynchronous copy) that stay untouched
+        until that step has been issued."""
+        self.x_res.upload_begin(x)
+        self.y_res.upload_begin(y)
+        self._staged = True
+
     def step(self, x: Optional[np.ndarray] = None, y: Optional[np.ndarray] = None) -> Optional[float]:
         inputs = dict(self.inputs)
+        if self.resident_inputs and getattr(self, "_staged", False):
+            self.x_res.upload_commit()
+            self.y_res.upload_commit()
+            self._staged = False
         if self.resident_inputs:
             inputs[self.x_id], inputs[self.y_id] = self.x_res, self.y_res
         else:

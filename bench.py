@@ -203,22 +203,35 @@ def run_ours(args):
                 "share_of_kernel_time": gp["total_ms"] / sum(v["total_ms"] for v in prof.values()),
                 "how": "instrumented eager re-run of the same steps, CUDA event pair around every launch"}
 
-    # end to end: batch in pinned host memory, uploaded every step, loss read back every step
+    # end to end: every step's batch starts in pinned host memory and its loss is read back on the
+    # host.  The copy of batch i+1 is issued on the copy stream right after step i is queued (what a
+    # data loader does), so it overlaps step i's kernels; the loss read-back then blocks the host.
     R.reset()
     from anneal_b200.device import pinned_array
-    tr2 = ResidentTrainer(dev, model, model.lr, world=world, use_graph=not args.no_graph, resident_inputs=False,
+    tr2 = ResidentTrainer(dev, model, model.lr, world=world, use_graph=not args.no_graph, resident_inputs=True,
                           overlap=not args.no_overlap)
-    xh, yh = pinned_array(x.size), pinned_array(y.size)
-    xh[:] = x
-    yh[:] = y
-    for _ in range(max(args.warmup, 1)):
-        tr2.step(xh, yh)
+    host = []
+    for _ in range(2):
+        xh, yh = pinned_array(x.size), pinned_array(y.size)
+        xh[:] = x
+        yh[:] = y
+        host.append((xh, yh))
+    e2e_loss = None
+
+    def e2e_steps(n):
+        nonlocal e2e_loss
+        for i in range(n):
+            tr2.step()                       # commits the staged batch, then the captured step
+            tr2.prefetch(*host[(i + 1) % 2])  # next batch: host -> device behind this step
+            e2e_loss = tr2.loss()            # device -> host, waits for the step
+
+    tr2.prefetch(*host[0])
+    e2e_steps(max(args.warmup, 1))
     dev.synchronize()
     barrier()
     t0 = time.perf_counter()
     dev.timer_start()
-    for _ in range(args.steps):
-        tr2.step(xh, yh)
+    e2e_steps(args.steps)
     ms2 = dev.timer_stop()
     dev.synchronize()
     wall2 = (time.perf_counter() - t0) * 1e3
@@ -229,7 +242,9 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms2 = float(t[0])
     e2e = {"value": CFG["batch"] * world * args.steps / (ms2 / 1e3), "unit": UNIT,
-           "h2d_bytes_per_step": int((x.size + y.size) * 4), "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps}
+           "h2d_bytes_per_step": int((x.size + y.size) * 4), "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps,
+           "how": "batch i+1 copied from pinned host memory on a copy stream while step i runs; loss read back every step",
+           "loss": e2e_loss}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
@@ -270,7 +285,10 @@ def run_other(args):
     out = {"data": "synthetic", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True}
     if args.workload in ("mlp", "cnn"):
         m = W.MLP() if args.workload == "mlp" else W.SmallCNN()
-        tr = ResidentTrainer(dev, m, m.lr, use_graph=True, materialize=False, resident_inputs=True)
+        # the im2col of a convolution is a 9- or 72-term padded sum: as an operand expression it is
+        # re-evaluated inside every step of the contraction's reduce loop, as a buffer it is written once
+        mat = True if args.materialize < 0 else bool(args.materialize)
+        tr = ResidentTrainer(dev, m, m.lr, use_graph=True, materialize=mat, resident_inputs=True)
         tr.load_batch(m.x, m.y)
         for _ in range(args.warmup):
             tr.step()
@@ -280,7 +298,8 @@ def run_other(args):
             tr.step()
         ms = dev.timer_stop()
         out.update(metric=METRIC, unit=UNIT, value=m.batch * args.steps / (ms / 1e3), ms_per_step=ms / args.steps, dtype="f32",
-                   config={"workload": args.workload + "_train_step", "batch": m.batch, "kernels_per_step": len(tr.items), "loss": tr.loss()})
+                   config={"workload": args.workload + "_train_step", "batch": m.batch, "kernels_per_step": len(tr.items), "loss": tr.loss(),
+                           "contraction_operands_materialized": mat})
     elif args.workload == "softmax":
         s = W.SoftmaxFwdBwd(8192, 8192)
         ts, ins = s.graph()
@@ -351,6 +370,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="wide_mlp", choices=["wide_mlp", "mlp", "cnn", "softmax", "dynmlp"],
                     help="wide_mlp is the headline configuration; the others print a one-GPU line for the remaining configurations")
+    ap.add_argument("--materialize", type=int, default=-1, help="mlp/cnn: 1/0 forces contraction operands to be buffers or expressions")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="all-reduce the whole gradient bucket after the backward pass")

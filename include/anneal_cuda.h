@@ -158,7 +158,9 @@ int anl_beam_search(anl_device* dev, const uint8_t* blob, size_t blob_len, int i
 /* ── JIT replay (tensor/jit.go:179-246): a schedule frozen into a CUDA graph ──
  * anl_graph_create runs nothing; the first anl_graph_replay instantiates buffers, compiles the
  * kernels and captures them on the device stream; later replays with the same bindings relaunch
- * the captured graph.  Inputs and outputs follow anl_run. */
+ * the captured graph.  Inputs and outputs follow anl_run, with one difference: a replay of a built
+ * graph whose inputs and outputs are all resident buffers returns as soon as the graph is queued,
+ * without waiting for the GPU (the next download, anl_synchronize or host-bound output waits). */
 int anl_graph_create(anl_device* dev, const uint8_t* blob, size_t blob_len, anl_graph** out);
 int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs,
                      const anl_binding* binds, int n_binds,
@@ -169,6 +171,14 @@ void anl_graph_release(anl_graph* g);
 int anl_buffer_create(anl_device* dev, int dtype, int64_t elems, anl_buffer** out);
 int anl_buffer_upload(anl_buffer* buf, const float* data, int64_t elems);
 int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems);
+/* Pipelined upload of the next batch (the data-loader side of examples/mlp.go:111-142, where the
+ * reference re-uploads x and y inside Run every step).  `upload_begin` queues the host-to-device
+ * copy on a copy stream into a staging block and returns; the buffer still holds the previous
+ * contents and kernels already queued keep reading them.  `upload_commit` makes the compute stream
+ * wait for that copy and convert it into the buffer, in order with the launches around it.  `data`
+ * should be pinned (anl_host_alloc) and must stay unchanged until the commit has executed. */
+int anl_buffer_upload_begin(anl_buffer* buf, const float* data, int64_t elems);
+int anl_buffer_upload_commit(anl_buffer* buf);
 void anl_buffer_release(anl_buffer* buf);
 /* A window [offset, offset+elems) of `parent` as a buffer of its own (same dtype, no copy).  Used
  * to lay all parameters, or all gradients, out in one contiguous bucket so that one all-reduce and

@@ -183,3 +183,65 @@ def test_row_chain_fuses_softmax_fwd_bwd_into_one_kernel(cuda, oracle):
     finally:
         plain.close()
     assert rel_err(got, ref) < 1e-5
+
+
+def test_pipelined_upload_begin_commit(cuda):
+    """upload_begin leaves the buffer untouched; upload_commit installs the staged batch in the
+    buffer's storage dtype; a second round reuses the staging block."""
+    from anneal_b200.device import pinned_array
+    rng = np.random.default_rng(5)
+    for dt in (dtypes.float32, dtypes.float16):
+        buf = cuda.buffer(dt, 5000)
+        first = rng.standard_normal(5000).astype(np.float32)
+        buf.upload(first)
+        q = (lambda a: a.astype(np.float16).astype(np.float32)) if dt is dtypes.float16 else (lambda a: a)
+        for _ in range(3):
+            h = pinned_array(5000)
+            h[:] = rng.standard_normal(5000).astype(np.float32)
+            before = buf.download()
+            buf.upload_begin(h)
+            cuda.synchronize()
+            assert np.array_equal(buf.download(), before)
+            buf.upload_commit()
+            assert np.array_equal(buf.download(), q(h))
+        with pytest.raises(Exception):
+            buf.upload_commit()          # nothing staged
+        buf.release()
+
+
+def test_prefetched_batches_train_like_loaded_batches(cuda):
+    """Feeding each step through prefetch (copy stream, staged) gives the trajectory of feeding it
+    through load_batch (compute stream, synchronous), with a different batch every step."""
+    from anneal_b200.device import pinned_array
+    res = []
+    batches = []
+    for s in range(4):
+        mm = W.WideMLP(batch=256, width=256, classes=72, depth=2, rank=s)
+        batches.append(mm.make_inputs())
+    for mode in ("prefetch", "load"):
+        R.reset()
+        m = W.WideMLP(batch=256, width=256, classes=72, depth=2)
+        tr = ResidentTrainer(cuda, m, 0.05, use_graph=True, resident_inputs=True)
+        losses = []
+        if mode == "prefetch":
+            host = []
+            for x, y in batches:
+                xh, yh = pinned_array(x.size), pinned_array(y.size)
+                xh[:] = x
+                yh[:] = y
+                host.append((xh, yh))
+            tr.prefetch(*host[0])
+            for i in range(4):
+                tr.step()
+                if i + 1 < 4:
+                    tr.prefetch(*host[i + 1])
+                losses.append(tr.loss())
+        else:
+            for x, y in batches:
+                tr.load_batch(x, y)
+                tr.step()
+                losses.append(tr.loss())
+        res.append((losses, tr.parameters()))
+    assert res[0][0] == res[1][0]
+    for a, b in zip(res[0][1], res[1][1]):
+        assert np.array_equal(a, b)
