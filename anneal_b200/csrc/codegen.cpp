@@ -696,11 +696,11 @@ struct Gen {
                 case OP_REDUCE: if (ctx >= 0) { fail("codegen: nested REDUCE"); return "0.0f"; } e = reduce_expr(i); break;
                 case OP_CAST: case OP_BITCAST: e = cast_expr(i, ctx); break;
                 case OP_WHERE: { std::string cnd = a(0); if (cnd == "true") return ac(1); if (cnd == "false") return ac(2); e = "(" + cnd + " ? " + ac(1) + " : " + ac(2) + ")"; break; }
-                case OP_EXP2: e = wrap("exp2f(" + af(0) + ")"); break;
+                case OP_EXP2: e = h ? "__float2half_rn(ex2_h_(" + af(0) + "))" : "exp2f(" + af(0) + ")"; break;
                 case OP_LOG2: e = wrap("log2f(" + af(0) + ")"); break;
                 case OP_SIN: e = wrap("sinf(" + af(0) + ")"); break;
                 case OP_SQRT: e = wrap("sqrtf(" + af(0) + ")"); break;
-                case OP_RECIP: e = wrap("__frcp_rn(" + af(0) + ")"); break;
+                case OP_RECIP: e = h ? "__float2half_rn(rcp_h_(" + af(0) + "))" : "__frcp_rn(" + af(0) + ")"; break;
                 case OP_TRUNC: e = wrap("truncf(" + af(0) + ")"); break;
                 case OP_NEG: e = h ? "__hneg(" + ac(0) + ")" : "(-" + ac(0) + ")"; break;
                 case OP_ADD: e = h ? "__hadd(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " + " + ac(1) + ")"; break;
@@ -716,6 +716,95 @@ struct Gen {
         }
         std::string name = "t" + std::to_string(i);
         stmt(ctx, std::string("const ") + cls_ctype(c) + " " + name + " = " + e + ";");
+        memo[key] = name;
+        return name;
+    }
+
+    // ── paired f16 evaluation ────────────────────────────────────────────────────────────────
+    // An elementwise kernel whose values are all f16 (or comparisons of f16 values) is evaluated two
+    // elements at a time in __half2: every arithmetic instruction then serves two outputs, which is
+    // what an instruction-bound GELU needs to get back under the memory roofline.  Each lane
+    // computes exactly what the one-element form computes (the *2 intrinsics round per lane, exp2 and
+    // the reciprocal go through the same f32 approximations), so the two forms agree bit for bit.
+    bool h2 = false;
+
+    bool h2_node_ok(int i, std::vector<char>& seen) {
+        if (seen[i]) return seen[i] == 1;
+        seen[i] = 1;
+        const Node& nd = N(i);
+        Cls c = cls(i);
+        auto fail_ = [&]() { seen[i] = 2; return false; };
+        if (nd.op == OP_CONST) return (nd.dtype == DT_F16 && c == CF16) ? true : fail_();
+        if (nd.op == OP_INDEX) {
+            if (c != CF16 || N(nd.src[0]).op != OP_PARAM) return fail_();
+            int p = (int)N(nd.src[0]).arg;
+            if (p < 0 || p >= (int)it.bufs.size() || it.bufs[p].dtype != DT_F16) return fail_();
+            return true;                                   // the index subtree is integer code, rendered as usual
+        }
+        if (c == CF16) {
+            switch (nd.op) {
+                case OP_NEG: case OP_ADD: case OP_SUB: case OP_MUL: case OP_MAX: case OP_MULACC:
+                case OP_EXP2: case OP_LOG2: case OP_SQRT: case OP_RECIP: case OP_SIN: break;
+                case OP_WHERE: if (cls(nd.src[0]) != CBOOL) return fail_(); break;
+                default: return fail_();
+            }
+        } else if (c == CBOOL) {
+            switch (nd.op) {
+                case OP_CMPLT: case OP_CMPNE: case OP_CMPEQ:
+                    if (cls(nd.src[0]) != CF16 || cls(nd.src[1]) != CF16) return fail_();
+                    break;
+                case OP_AND: case OP_OR: case OP_XOR: case OP_WHERE: break;
+                default: return fail_();
+            }
+        } else return fail_();
+        for (int sidx : nd.src) if (!h2_node_ok(sidx, seen)) return fail_();
+        return true;
+    }
+    bool h2_eligible(int V) {
+        if (V < 2 || (V & 1) || it.bufs[0].dtype != DT_F16 || cls(body) != CF16) return false;
+        std::vector<char> seen(n, 0);
+        return h2_node_ok(body, seen);
+    }
+
+    std::string val_h2(int i) {
+        const Node& nd = N(i);
+        auto key = std::make_pair(i, -1);
+        auto f = memo.find(key);
+        if (f != memo.end()) return f->second;
+        if (nd.op == OP_CONST) {
+            double d; std::memcpy(&d, &nd.arg, 8);
+            if (std::isinf(d)) d = d < 0 ? -65504.0 : 65504.0;
+            return "__float2half2_rn(" + flit(d) + ")";
+        }
+        Cls c = cls(i);
+        auto a = [&](int k) { return val_h2(nd.src[k]); };
+        std::string e;
+        switch (nd.op) {
+            case OP_INDEX: e = vec_load.count(i) ? vec_load[i] + "[u]" : "__half2half2(" + load_expr(i, -1) + ")"; break;
+            case OP_NEG: e = "__hneg2(" + a(0) + ")"; break;
+            case OP_ADD: e = "__hadd2(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_SUB: e = "__hsub2(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_MUL: e = "__hmul2(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_MAX: e = "__hmax2(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_MULACC: e = "__hadd2(" + a(0) + ", __hmul2(" + a(1) + ", " + a(2) + "))"; break;
+            case OP_EXP2: e = "h2_ex2_(" + a(0) + ")"; break;
+            case OP_RECIP: e = "h2_rcp_(" + a(0) + ")"; break;
+            case OP_LOG2: e = "h2_log2_(" + a(0) + ")"; break;
+            case OP_SQRT: e = "h2_sqrt_(" + a(0) + ")"; break;
+            case OP_SIN: e = "h2_sin_(" + a(0) + ")"; break;
+            case OP_CMPLT: e = "__hlt2_mask(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_CMPEQ: e = "__heq2_mask(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_CMPNE: e = "__hneu2_mask(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_AND: e = "(" + a(0) + " & " + a(1) + ")"; break;
+            case OP_OR: e = "(" + a(0) + " | " + a(1) + ")"; break;
+            case OP_XOR: e = "(" + a(0) + " ^ " + a(1) + ")"; break;
+            case OP_WHERE:
+                e = c == CBOOL ? "((" + a(0) + " & " + a(1) + ") | (~" + a(0) + " & " + a(2) + "))" : "h2_sel_(" + a(0) + ", " + a(1) + ", " + a(2) + ")";
+                break;
+            default: fail("codegen: paired f16 form met op " + std::to_string(nd.op)); return "__float2half2_rn(0.0f)";
+        }
+        std::string name = "t" + std::to_string(i);
+        stmt(-1, std::string("const ") + (c == CBOOL ? "unsigned" : "__half2") + " " + name + " = " + e + ";");
         memo[key] = name;
         return name;
     }
@@ -754,6 +843,20 @@ struct Gen {
             "template <class T, int V> __device__ __forceinline__ void stv_(T* p, const T* in) {\n"
             "  typedef typename vec_t_<sizeof(T) * V>::type W;\n"
             "  *reinterpret_cast<W*>(p) = *reinterpret_cast<const W*>(in);\n"
+            "}\n"
+            // f16-class exp2 and reciprocal: one MUFU on the widened value, rounded back to f16.  The
+            // f32 approximation is within 2 ulp (f32), far below the f16 rounding that follows.
+            "__device__ __forceinline__ float ex2_h_(float x) { float r; asm(\"ex2.approx.ftz.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n"
+            "__device__ __forceinline__ float rcp_h_(float x) { float r; asm(\"rcp.approx.ftz.f32 %0, %1;\" : \"=f\"(r) : \"f\"(x)); return r; }\n"
+            "#define DEF_H2MAP_(NAME, F) __device__ __forceinline__ __half2 NAME(__half2 x) { return __floats2half2_rn(F(__low2float(x)), F(__high2float(x))); }\n"
+            "DEF_H2MAP_(h2_ex2_, ex2_h_)\n"
+            "DEF_H2MAP_(h2_rcp_, rcp_h_)\n"
+            "DEF_H2MAP_(h2_log2_, log2f)\n"
+            "DEF_H2MAP_(h2_sqrt_, sqrtf)\n"
+            "DEF_H2MAP_(h2_sin_, sinf)\n"
+            "__device__ __forceinline__ __half2 h2_sel_(unsigned m, __half2 a, __half2 b) {\n"
+            "  unsigned x = *reinterpret_cast<unsigned*>(&a), y = *reinterpret_cast<unsigned*>(&b), r = (x & m) | (y & ~m);\n"
+            "  return *reinterpret_cast<__half2*>(&r);\n"
             "}\n"
             "__device__ __forceinline__ float op_add_f(float a, float b) { return a + b; }\n"
             "__device__ __forceinline__ float op_mul_f(float a, float b) { return a * b; }\n"
@@ -900,6 +1003,8 @@ struct Gen {
             k << "  data0[g] = " << store_value(v, body) << ";\n";
         } else {
             int rv = loop_ranges.back();
+            h2 = opts.vector_width >= 0 && h2_eligible(V);
+            const int U = h2 ? V / 2 : V;                  // iterations of the unrolled loop
             k << "  const long long base = g * " << V << ";\n";
             k << "  if (base >= " << total_expr() << ") return;\n";
             k << decompose("base");
@@ -913,6 +1018,12 @@ struct Gen {
                 std::string arr = "v" + std::to_string(vi++);
                 std::string bt = buf_ctype(it.bufs[p].dtype), VS = std::to_string(V);
                 std::string idx = render(f, -1);
+                if (h2) {
+                    stmt(-1, "__half2 " + arr + "_raw[" + std::to_string(U) + "];");
+                    stmt(-1, "ldv_<__half2, " + std::to_string(U) + ">(reinterpret_cast<const __half2*>(data" + std::to_string(p) + " + " + idx + "), " + arr + "_raw);");
+                    vec_load[i] = arr + "_raw";
+                    continue;
+                }
                 stmt(-1, bt + " " + arr + "_raw[" + VS + "];");
                 stmt(-1, "ldv_<" + bt + ", " + VS + ">(data" + std::to_string(p) + " + " + idx + ", " + arr + "_raw);");
                 // convert to the compute class of the INDEX node
@@ -931,15 +1042,17 @@ struct Gen {
             }
             cur_top = nullptr;
             vec_range = rv;
-            std::string v = val(body, -1);
+            std::string v = h2 ? val_h2(body) : val(body, -1);
             if (!err.empty()) return false;
             k << prelude.code;
-            k << "  " << buf_ctype(it.bufs[0].dtype) << " outv[" << V << "];\n";
-            k << "  _Pragma(\"unroll\") for (int u = 0; u < " << V << "; u++) {\n";
+            const std::string ot = h2 ? "__half2" : buf_ctype(it.bufs[0].dtype);
+            k << "  " << ot << " outv[" << U << "];\n";
+            k << "  _Pragma(\"unroll\") for (int u = 0; u < " << U << "; u++) {\n";
             k << top.code;
-            k << "    outv[u] = " << store_value(v, body) << ";\n";
+            k << "    outv[u] = " << (h2 ? v : store_value(v, body)) << ";\n";
             k << "  }\n";
-            k << "  stv_<" << buf_ctype(it.bufs[0].dtype) << ", " << V << ">(data0 + base, outv);\n";
+            if (h2) k << "  stv_<__half2, " << U << ">(reinterpret_cast<__half2*>(data0 + base), outv);\n";
+            else k << "  stv_<" << ot << ", " << V << ">(data0 + base, outv);\n";
         }
         k << "}\n";
         out.klass = KC_ELEMENTWISE;
@@ -951,7 +1064,7 @@ struct Gen {
         out.main.static_outputs = static_total();
         out.main.sym_trailing = sym_output() ? static_total() : 0;
         out.uses_sym = has_sym;
-        out.note = "elementwise V=" + std::to_string(V);
+        out.note = "elementwise V=" + std::to_string(V) + (h2 ? " paired f16" : "");
         return true;
     }
 

@@ -614,6 +614,12 @@ double gemm_flops(const Plan& plan, int64_t sym_value) {
     return 2.0 * (double)(c.m_sym ? sym_value : c.M) * (double)c.N * (double)(c.k_sym ? sym_value : c.K);
 }
 
+int64_t gemm_window_rows(const Plan& plan, int64_t* row_elems) {
+    if (!plan.gemm || plan.gemm_dynamic || plan.r.klass != KC_GEMM || plan.gemm->f32) return 0;
+    if (row_elems) *row_elems = plan.gemm->c.N;
+    return plan.gemm->c.M;
+}
+
 bool gemm_taken(const Plan& plan, int64_t sym_value) {
     if (!plan.gemm) return false;
     if (!plan.gemm_dynamic) return plan.r.klass == KC_GEMM;
@@ -621,37 +627,43 @@ bool gemm_taken(const Plan& plan, int64_t sym_value) {
     return gemm_f32_worth(c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K);
 }
 
-int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream) {
+int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream, int64_t m_begin, int64_t m_end) {
     const GemmPlan& gp = *plan.gemm;
     const Contraction& c = gp.c;
+    // an optional row window [m_begin, m_end) of the output: the caller splits a contraction so that
+    // a collective on the first rows can start while the remaining rows are still being computed
+    const bool window = m_end >= 0;
+    if (window && (gp.f32 || c.m_sym || m_begin < 0 || m_end > c.M || m_begin >= m_end || (m_begin % 8)))
+        return dev->fail(ANL_ERR_INVALID, "gemm: bad row window");
+    const int64_t M = window ? m_end - m_begin : c.M;
     if (gp.f32)
         return launch_gemm_f32(dev, (const float*)bufs[c.a_param] + c.a_off, (const float*)bufs[c.b_param] + c.b_off, (float*)bufs[0],
                                c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K, c.a_sm, c.a_sk, c.b_sn, c.b_sk, stream);
     if (*gp.status_host != 0) return dev->fail(ANL_ERR_CUDA, "gemm: an earlier launch timed out on a barrier (code " + std::to_string(*gp.status_host) + ")");
-    const __half* a = (const __half*)bufs[c.a_param] + c.a_off;
+    const __half* a = (const __half*)bufs[c.a_param] + c.a_off + (window ? m_begin * c.a_sm : 0);
     const __half* b = (const __half*)bufs[c.b_param] + c.b_off;
     CUtensorMap ma, mb;
     int rc;
-    if (gp.a_mn) rc = encode_map(dev, &ma, a, (uint64_t)c.M, (uint64_t)c.K, (uint64_t)gp.lda, 64, BK);
-    else rc = encode_map(dev, &ma, a, (uint64_t)c.K, (uint64_t)c.M, (uint64_t)gp.lda, BK, BM);
+    if (gp.a_mn) rc = encode_map(dev, &ma, a, (uint64_t)M, (uint64_t)c.K, (uint64_t)gp.lda, 64, BK);
+    else rc = encode_map(dev, &ma, a, (uint64_t)c.K, (uint64_t)M, (uint64_t)gp.lda, BK, BM);
     if (rc) return rc;
     if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
     else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, BN);
     if (rc) return rc;
     GemmArgs g;
-    g.d = (__half*)bufs[0];
-    g.M = (int)c.M; g.N = (int)c.N; g.K = (int)c.K; g.ldd = (int)c.N;
-    g.tiles_m = (int)((c.M + BM - 1) / BM); g.tiles_n = (int)((c.N + BN - 1) / BN);
+    g.d = (__half*)bufs[0] + (window ? m_begin * c.N : 0);
+    g.M = (int)M; g.N = (int)c.N; g.K = (int)c.K; g.ldd = (int)c.N;
+    g.tiles_m = (int)((M + BM - 1) / BM); g.tiles_n = (int)((c.N + BN - 1) / BN);
     g.status = gp.status_dev;
     g.tile_counter = dev->gemm_tile_counter;
     if (cudaMemsetAsync(g.tile_counter, 0, 4, stream) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot reset the tile counter");
     static const bool pair_ok = std::getenv("ANNEAL_GEMM_PAIR") ? std::atoi(std::getenv("ANNEAL_GEMM_PAIR")) != 0 : true;
-    if (pair_ok && c.M >= 2 * BM && c.N >= BN / 2) {
+    if (pair_ok && M >= 2 * BM && c.N >= BN / 2) {
         // two-CTA tiles, 256 rows by 256 or 128 columns.  The narrow tile fills the last wave of tiles
         // better but stages 1.5x the bytes per flop and measured 25% slower on 4096x4096x8192 (it
         // becomes L2-bound), so it is only taken when the wide tile would leave most pairs idle.
         const int npairs = gemm_sm_budget(dev) / 2;
-        const int tm2 = (int)((c.M + 2 * BM - 1) / (2 * BM));
+        const int tm2 = (int)((M + 2 * BM - 1) / (2 * BM));
         auto fill = [&](int bnt) { long long t = (long long)tm2 * ((c.N + bnt - 1) / bnt); long long w = (t + npairs - 1) / npairs; return (double)t / (double)(w * npairs); };
         const int bnt = (fill(128) * 0.7 > fill(256)) ? 128 : 256;
         // B is loaded in halves of bnt/2 columns, so its tensor map gets a box of that many rows

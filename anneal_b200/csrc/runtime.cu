@@ -499,6 +499,24 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         sgd_at[at].push_back(kv.first);
     }
     const bool chains_on = !(dev->flags & ANL_OPEN_NO_ROW_CHAIN) && !(dev->flags & ANL_OPEN_BEAM);
+    // the last all-reduced output of the schedule, when it is a large contraction whose update is
+    // not deferred past it: candidate for the split described at its launch below
+    size_t tail_split = (size_t)-1;
+    if ((dev->nranks > 1 || (dev->flags & ANL_OPEN_TAIL_SPLIT)) && !dev->profiling && !(dev->flags & ANL_OPEN_BEAM)) {
+        for (size_t i = items.size(); i-- > 0;) {
+            auto ra = t.after.find(items[i].bufs[0].id);
+            if (ra == t.after.end() || !ra->second.allreduce) continue;
+            const anl_output& a = ra->second;
+            auto sg = sgd_at.find(i);
+            bool own_update = a.sgd_master && a.resident && sg != sgd_at.end() && sg->second.size() == 1 && sg->second[0] == items[i].bufs[0].id;
+            std::shared_ptr<Plan> p;
+            if (own_update && items[i].source.empty() && get_plan(dev, items[i], opts, p) == ANL_OK) {
+                int64_t row_elems = 0, rows = gemm_window_rows(*p, &row_elems);
+                if (rows >= 1024 && rows * row_elems >= (4ll << 20) && a.resident->elems == rows * row_elems) tail_split = i;
+            }
+            break;      // only the very last collective is exposed
+        }
+    }
     for (size_t i = 0; i < items.size(); i++) {
         const Item& it = items[i];
         if (chains_on) {
@@ -527,9 +545,31 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         if (int rc = get_plan(dev, it, use, plan)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
         std::vector<void*> ptrs;
         for (auto& b : it.bufs) ptrs.push_back(t.bufs[b.id].ptr);
+        auto ra = t.after.find(it.bufs[0].id);
+        if (i == tail_split && ra != t.after.end()) {
+            // The last all-reduced gradient has nothing left to hide behind.  Its contraction is
+            // launched as two row windows; the first half is reduced across ranks and applied while
+            // the second half is still being computed, so only half of it stays exposed.
+            const anl_output& a = ra->second;
+            int64_t row_elems = 0, rows = gemm_window_rows(*plan, &row_elems);
+            const int64_t cut = (rows / 2 + 255) / 256 * 256;
+            const int es = dt_storage_bytes(a.resident->dtype);
+            for (int h = 0; h < 2; h++) {
+                const int64_t m0 = h ? cut : 0, m1 = h ? rows : cut;
+                if (int rc = launch_gemm(dev, *plan, ptrs.data(), item_sym(it, binds), stream, m0, m1)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
+                const int64_t off = m0 * row_elems, cnt = (m1 - m0) * row_elems;
+                if (int rc = comm_allreduce_async(dev, (char*)a.resident->ptr + off * es, cnt, a.resident->dtype, stream)) return rc;
+                anl_buffer gv = *a.resident, mv = *a.sgd_master, pv = a.sgd_param ? *a.sgd_param : *a.sgd_master;
+                gv.ptr = (char*)gv.ptr + off * es; gv.elems = cnt;
+                mv.ptr = (char*)mv.ptr + off * dt_storage_bytes(mv.dtype); mv.elems = cnt;
+                pv.ptr = (char*)pv.ptr + off * dt_storage_bytes(pv.dtype); pv.elems = cnt;
+                comm_fork(dev, stream);
+                if (int rc = launch_sgd(dev, &mv, &pv, &gv, a.sgd_lr, a.sgd_scale, dev->comm_stream)) return rc;
+            }
+            continue;
+        }
         if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
         // side stream: [all-reduce this gradient] behind the producing kernel ...
-        auto ra = t.after.find(it.bufs[0].id);
         if (ra != t.after.end() && ra->second.allreduce)
             if (int rc = comm_allreduce_async(dev, ra->second.resident->ptr, ra->second.resident->elems, ra->second.resident->dtype, stream)) return rc;
         // ... [update the parameter] once its last reader has been queued as well

@@ -119,7 +119,10 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 // hand-written contraction kernels (gemm.cu); returns ANL_OK and fills plan.gemm if the item is a
 // dense SUM-of-products over buffers that they cover, ANL_ERR_UNSUPPORTED otherwise
 int plan_gemm(anl_device* dev, const Item& item, Plan& plan);
-int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream);
+int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream,
+                int64_t m_begin = 0, int64_t m_end = -1);
+// rows of a static f16 contraction's output, or 0 when the plan is not one (no row windows then)
+int64_t gemm_window_rows(const Plan& plan, int64_t* row_elems);
 double gemm_flops(const Plan& plan, int64_t sym_value);
 // true when this launch (with the symbolic extent bound to sym_value) goes to the contraction kernel
 bool gemm_taken(const Plan& plan, int64_t sym_value);

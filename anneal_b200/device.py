@@ -252,6 +252,7 @@ class Device:
     NO_GEMM = 2
     BEAM = 4
     NO_ROW_CHAIN = 8
+    TAIL_SPLIT = 16
 
     def __init__(self, ordinal: Optional[int] = None, flags: int = 0):
         self.L = load_library()

@@ -490,7 +490,11 @@ def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
                 users[w].append(i)
                 indeg[i] += 1
     wanted = {out_buf[placeholders[o.idx].idx].idx for o in outputs}
-    prio = (lambda i: (0 if items[i].bufs[0].uop_idx in wanted else 1, i)) if outputs_first else (lambda i: (0, i))
+    # among ready producers of requested outputs the smallest goes first: a bias gradient's tiny
+    # all-reduce then hides under the weight-gradient contraction instead of queueing behind its
+    # 33 MB all-reduce at the very end of the step
+    prio = ((lambda i: (0, items[i].bufs[0].size, i) if items[i].bufs[0].uop_idx in wanted else (1, 0, i))
+            if outputs_first else (lambda i: (0, 0, i)))
     ready = sorted((i for i in range(n) if indeg[i] == 0), key=prio)
     ordered = []
     while ready:

@@ -26,7 +26,8 @@ def _round_up(n: int, m: int = 128) -> int:
 
 class ResidentTrainer:
     def __init__(self, dev: Device, model, lr: float, world: int = 1, use_graph: bool = True,
-                 materialize: bool = True, resident_inputs: bool = False, overlap: bool = True):
+                 materialize: bool = True, resident_inputs: bool = False, overlap: bool = True,
+                 force_allreduce: bool = False):
         self.dev, self.model, self.lr, self.world, self.use_graph = dev, model, float(lr), world, use_graph
         self.overlap = overlap
         prev = R.MATERIALIZE_CONTRACTION_OPERANDS
@@ -72,7 +73,7 @@ class ResidentTrainer:
             self.inputs[p.t.node.idx] = pv
             self.placed[gid] = gv
             # overlapped mode: each gradient is all-reduced and applied right behind its kernel
-            self.fused[gid] = GradientTarget(gv, mv, pv, self.lr, self.grad_scale / world, allreduce=world > 1)
+            self.fused[gid] = GradientTarget(gv, mv, pv, self.lr, self.grad_scale / world, allreduce=world > 1 or force_allreduce)
         self.loss_host = pinned_array(1)
         self.placed[self.loss_id] = self.loss_host
         self.resident_inputs = resident_inputs

@@ -105,6 +105,8 @@ int anl_get_stats(anl_device* dev, anl_stats* out);
 #define ANL_OPEN_NO_GEMM 2u        /* never route contractions to the tensor-core kernels */
 #define ANL_OPEN_NO_ROW_CHAIN 8u    /* launch every item on its own instead of fusing per-row kernel chains */
 #define ANL_OPEN_BEAM 4u           /* apply / search autotuned transforms (the reference's ANNEAL_BEAM=1) */
+#define ANL_OPEN_TAIL_SPLIT 16u    /* split the last all-reduced contraction into two row windows even on one rank
+                                      (done by itself when ranks > 1; the flag exists to test the path on one GPU) */
 
 /* ── Executor.Run / SymbolicExecutor.RunSymbolic (backend/device.go:10-28; backend/webgpu/executor.go:26-240, 576-810) ──
  * Runs the items of `blob` in order.  `outs` has room for `*n_outs` entries on entry; on return

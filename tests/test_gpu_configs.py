@@ -245,3 +245,29 @@ def test_prefetched_batches_train_like_loaded_batches(cuda):
     assert res[0][0] == res[1][0]
     for a, b in zip(res[0][1], res[1][1]):
         assert np.array_equal(a, b)
+
+
+def test_tail_split_contraction_leaves_the_same_parameters():
+    """The last all-reduced weight gradient is computed as two row windows, each reduced and applied
+    on its own; on one rank (the collective is then a no-op) the parameters must come out exactly
+    as from the unsplit step."""
+    from anneal_b200.device import Device
+    res = []
+    for flags in (Device.TAIL_SPLIT, 0):
+        dev = Device(0, flags)
+        try:
+            R.reset()
+            m = W.WideMLP(batch=512, width=2048, classes=72, depth=2)
+            x, y = m.make_inputs()
+            tr = ResidentTrainer(dev, m, 0.05, use_graph=True, resident_inputs=True, force_allreduce=True)
+            tr.load_batch(x, y)
+            g0 = dev.stats()["gemm_launched"]
+            for _ in range(3):
+                tr.step()
+            res.append((tr.parameters(), tr.loss(), dev.stats()["gemm_launched"] - g0))
+        finally:
+            dev.close()
+    for a, b in zip(res[0][0], res[1][0]):
+        assert np.array_equal(a, b)
+    assert res[0][1] == res[1][1]
+    assert res[0][2] == res[1][2] + 3          # one extra contraction launch per step
