@@ -109,12 +109,25 @@ __device__ __forceinline__ void tmem_ld32(uint32_t taddr, uint32_t* v) {
         : "r"(taddr) : "memory");
 }
 
+// The tile counter must read zero when a launch starts.  Instead of a memset in front of every
+// launch, the launch cleans up after itself: a CTA (or CTA pair) that has drawn its last number,
+// one that is past the end, signs off on the second word, and the last to sign off zeroes both.
+// Nobody draws after its own sign-off, so the reset cannot race with a draw.
+__device__ __forceinline__ void retire_tile_counter(int* counter, int drawers) {
+    __threadfence();
+    if (atomicAdd(counter + 1, 1) == drawers - 1) {
+        counter[0] = 0;
+        counter[1] = 0;
+        __threadfence();
+    }
+}
+
 struct GemmArgs {
     __half* d;
     int M, N, K, ldd;
     int tiles_m, tiles_n;
     int* status;
-    int* tile_counter;      // zeroed before the launch; CTAs draw tile numbers from it
+    int* tile_counter;      // [0] next tile number, [1] drawers that have signed off; both zero between launches
 };
 
 template <bool A_MN, bool B_MN>
@@ -167,7 +180,7 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 tile_ring[qs] = t;
                 mbar_arrive(smem_u32(&tq_full[qs]));
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
-                if (t < 0) break;
+                if (t < 0) { retire_tile_counter(g.tile_counter, (int)gridDim.x); break; }
                 const int m0 = (t % g.tiles_m) * BM, n0 = (t / g.tiles_m) * BN;
                 for (int kb = 0; kb < kblocks; kb++) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 1; break; }
@@ -405,7 +418,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_co
                     mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
                 }
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
-                if (t < 0) break;
+                if (t < 0) { if (rank == 0) retire_tile_counter(g.tile_counter, (int)gridDim.x / 2); break; }
                 const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;          // this CTA's rows of A
                 const int n0 = (t / tiles_m) * BNT + (int)rank * (BNT / 2);          // this CTA's half of B
                 for (int kb = 0; kb < kblocks; kb++) {
@@ -578,7 +591,10 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
         if (cudaHostGetDevicePointer((void**)&status_dev, status_host, 0) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
     }
     gp->status_host = status_host; gp->status_dev = status_dev;
-    if (!dev->gemm_tile_counter && cudaMalloc((void**)&dev->gemm_tile_counter, 256) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
+    if (!dev->gemm_tile_counter) {
+        if (cudaMalloc((void**)&dev->gemm_tile_counter, 256) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
+        if (cudaMemset(dev->gemm_tile_counter, 0, 256) != cudaSuccess) return ANL_ERR_UNSUPPORTED;   // launches leave it zeroed again
+    }
     static bool attr_set = false;
     if (!attr_set) {
         cudaFuncSetAttribute(gemm_f16_tcgen05<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
@@ -656,7 +672,6 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
     g.tiles_m = (int)((M + BM - 1) / BM); g.tiles_n = (int)((c.N + BN - 1) / BN);
     g.status = gp.status_dev;
     g.tile_counter = dev->gemm_tile_counter;
-    if (cudaMemsetAsync(g.tile_counter, 0, 4, stream) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot reset the tile counter");
     static const bool pair_ok = std::getenv("ANNEAL_GEMM_PAIR") ? std::atoi(std::getenv("ANNEAL_GEMM_PAIR")) != 0 : true;
     if (pair_ok && M >= 2 * BM && c.N >= BN / 2) {
         // two-CTA tiles, 256 rows by 256 or 128 columns.  The narrow tile fills the last wave of tiles
