@@ -35,40 +35,81 @@ def flops_per_step(batch, width, classes, depth):
 
 
 class ClockSampler(threading.Thread):
-    """Samples SM clocks and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock, power and clock-event reasons while the timed region runs: NVML polled every
+    few milliseconds (read-only queries), nvidia-smi at its 200 ms minimum when NVML cannot be loaded."""
     Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
          "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    BITS = {"hw_slowdown": 0x8, "hw_thermal_slowdown": 0x40, "sw_thermal_slowdown": 0x20, "sw_power_cap": 0x4}
 
     def __init__(self, index: int):
         super().__init__(daemon=True)
         self.index, self.rows, self.proc = index, [], None
+        self.sm, self.mx, self.power, self.reasons = [], [], [], set()
+        self._stop_flag = threading.Event()
+        self.source = None
+
+    def _nvml(self):
+        import pynvml as nv
+        nv.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        idx = self.index
+        if vis:
+            ids = [v for v in vis.split(",") if v.strip()]
+            if idx < len(ids) and ids[idx].strip().isdigit():
+                idx = int(ids[idx])
+        h = nv.nvmlDeviceGetHandleByIndex(idx)
+        mx = nv.nvmlDeviceGetMaxClockInfo(h, nv.NVML_CLOCK_SM)
+        self.source = "nvml"
+        while not self._stop_flag.is_set():
+            self.sm.append(float(nv.nvmlDeviceGetClockInfo(h, nv.NVML_CLOCK_SM)))
+            self.mx.append(float(mx))
+            try:
+                self.power.append(nv.nvmlDeviceGetPowerUsage(h) / 1000.0)
+                r = nv.nvmlDeviceGetCurrentClocksThrottleReasons(h)
+                for n, bit in self.BITS.items():
+                    if r & bit:
+                        self.reasons.add(n)
+            except Exception:
+                pass
+            time.sleep(0.004)
+        nv.nvmlShutdown()
 
     def run(self):
         try:
+            self._nvml()
+            return
+        except Exception:
+            pass
+        try:
+            self.source = "nvidia-smi"
             self.proc = subprocess.Popen(["nvidia-smi", f"--id={self.index}", f"--query-gpu={self.Q}",
                                           "--format=csv,noheader,nounits", "-lms", "200"],
                                          stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
             for line in self.proc.stdout:
-                self.rows.append([c.strip() for c in line.split(",")])
+                r = [c.strip() for c in line.split(",")]
+                if len(r) > 8 and r[1].replace(".", "").isdigit():
+                    self.sm.append(float(r[1]))
+                    self.mx.append(float(r[2]))
+                    for n, v in zip(names, r[5:9]):
+                        if v.lower().startswith("active"):
+                            self.reasons.add(n)
         except Exception:
             pass
 
+    def reset(self):
+        if self.source == "nvml":
+            self.sm, self.mx, self.power, self.reasons = [], [], [], set()
+
     def stop(self):
+        self._stop_flag.set()
         if self.proc:
             self.proc.terminate()
         self.join(timeout=2)
-        sm = [float(r[1]) for r in self.rows if len(r) > 8 and r[1].replace(".", "").isdigit()]
-        mx = [float(r[2]) for r in self.rows if len(r) > 8 and r[2].replace(".", "").isdigit()]
-        reasons = set()
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        for r in self.rows:
-            if len(r) > 8:
-                for n, v in zip(names, r[5:9]):
-                    if v.lower().startswith("active"):
-                        reasons.add(n)
-        busy = sorted(sm)[len(sm) // 2:] if sm else []
-        return {"sm_mhz": float(np.median(busy)) if busy else None, "sm_max_mhz": max(mx) if mx else None,
-                "reasons": sorted(reasons), "samples": len(sm)}
+        return {"sm_mhz": float(np.median(self.sm)) if self.sm else None, "sm_min_mhz": min(self.sm) if self.sm else None,
+                "sm_max_mhz": max(self.mx) if self.mx else None,
+                "power_w": float(np.median(self.power)) if self.power else None,
+                "reasons": sorted(self.reasons), "samples": len(self.sm), "source": self.source}
 
 
 def peaks():
@@ -165,6 +206,7 @@ def run_ours(args):
     sampler = ClockSampler(local)
     sampler.start()
     time.sleep(0.25)
+    sampler.reset()                      # keep only samples taken while the timed steps run
     launches0 = dev.stats()["kernels_launched"]
     dev.timer_start()
     for _ in range(args.steps):
@@ -197,8 +239,12 @@ def run_ours(args):
         gp = prof["gemm"]
         ach = gp["flops"] / (gp["total_ms"] / 1e3) / 1e12
         peak = pk["bf16_tflops"]
-        roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": None,
-                "peak_kind": f"{pk_kind} burst dense 16-bit", "kernel": "gemm_f16_tcgen05", "launches": gp["launches"],
+        # DRAM bytes of one weight-gradient launch (4096x4096x8192, 160 MB algorithmic) from the ncu
+        # capture summarised in profiles/gemm_f16_tcgen05_pair_wide_mlp.md; not measured in this run
+        roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": 351.7e6,
+                "traffic_of": "one 4096x4096x8192 launch under ncu (algorithmic 160 MB)",
+                "peak_kind": f"{pk_kind} burst dense 16-bit", "kernel": "gemm_f16_tcgen05_pair", "launches": gp["launches"],
+                "frac_of_sustained_peak": ach / pk.get("bf16_tflops_sustained", peak),
                 "avg_launch_ms": gp["total_ms"] / gp["launches"],
                 "share_of_kernel_time": gp["total_ms"] / sum(v["total_ms"] for v in prof.values()),
                 "how": "instrumented eager re-run of the same steps, CUDA event pair around every launch"}
@@ -328,7 +374,8 @@ def run_other(args):
         res = {}
         R.DEFAULT_EXECUTOR = dev
         R.MATERIALIZE_CONTRACTION_OPERANDS = True
-        for b in (1, 17, 256, 4096, 65536):
+        batches = [int(v) for v in args.dyn_batches.split(",")]
+        for b in batches:
             R.reset()
             x, y = m.inputs(b)
             outt, loss, grads, ins = m.graph(b)
@@ -355,7 +402,7 @@ def run_other(args):
                 v.release()
         R.DEFAULT_EXECUTOR = None
         R.MATERIALIZE_CONTRACTION_OPERANDS = False
-        out.update(metric=METRIC, unit=UNIT, value=res["65536"]["samples_per_s"], ms_per_step=res["65536"]["us_per_replay"] / 1e3, dtype="f32",
+        out.update(metric=METRIC, unit=UNIT, value=res[str(batches[-1])]["samples_per_s"], ms_per_step=res[str(batches[-1])]["us_per_replay"] / 1e3, dtype="f32",
                    config={"workload": "dynmlp_symbolic_batch", "per_batch": res, "nvrtc_compiles": dev.stats()["nvrtc_compiles"]})
     out["gpu_launches"] = int(dev.stats()["kernels_launched"])
     print(json.dumps(out))
@@ -370,6 +417,7 @@ def main():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default="wide_mlp", choices=["wide_mlp", "mlp", "cnn", "softmax", "dynmlp"],
                     help="wide_mlp is the headline configuration; the others print a one-GPU line for the remaining configurations")
+    ap.add_argument("--dyn-batches", default="1,17,256,4096,65536", help="dynmlp: batch sizes bound in turn; the last one is reported")
     ap.add_argument("--materialize", type=int, default=-1, help="mlp/cnn: 1/0 forces contraction operands to be buffers or expressions")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
