@@ -440,6 +440,14 @@ struct Gen {
         char b[64]; std::snprintf(b, sizeof b, "%af", (double)f);
         return std::string(b);
     }
+    // x * 1.0 is x bit for bit in IEEE arithmetic (the gradient of a sum multiplies by ones)
+    bool is_float_one(int i) const {
+        const Node& nd = N(i);
+        if (nd.op != OP_CONST || !dt_is_float(nd.dtype)) return false;
+        double d; std::memcpy(&d, &nd.arg, 8);
+        return d == 1.0;
+    }
+
     std::string const_lit(int i) {
         const Node& nd = N(i);
         if (dt_is_float(nd.dtype)) {
@@ -514,6 +522,50 @@ struct Gen {
     int chain_vec = 1;
     std::string dp = "data";                         // name prefix of the buffer pointers
     std::map<int, std::string> chain_subst;          // row chain: parameter → register holding this row's value
+    // row chain: buffers whose whole row is fetched into registers once, before the first stage
+    // (buffer id → row width); a load `buf[row * W + x]` with x the unrolled sweep of a stage then
+    // reads the register copy.  Shared by all stages of one chain.
+    struct RowCached { int64_t width; int dtype; };
+    std::map<uint32_t, RowCached>* row_cache = nullptr;
+    int row_cache_budget = 64;                       // values per thread over all cached buffers
+
+    // the unrolled loop over range `sw` carries an iteration counter j<aux> when it is swept by all
+    // lanes in equal shares: the single range of a short reduce, or the only inner output range
+    bool counted_sweep(int sw) const {
+        if (!row_cache || N(sw).symbolic()) return false;
+        const int64_t w = N(sw).arg;
+        return w % lanes == 0 && w / lanes <= 32;
+    }
+    std::string sweep_counter(int sw) const { return "j" + std::to_string(N(sw).aux); }
+    // the cached form of INDEX node i, or "" when the load does not sweep one cached row
+    std::string row_cached_load(int i, int p, const Lin& f, int ctx) {
+        if (!row_cache || loop_ranges.empty() || f.c != 0 || f.t.size() != 2 || !in_bounds(f, p)) return "";
+        int sw = -1; int64_t row_coef = 0;
+        for (auto& t : f.t) {
+            const Atom& a = atoms[t.first];
+            if (a.kind != Atom::RANGE) return "";
+            if (a.node == loop_ranges[0]) row_coef = t.second;
+            else if (t.second == 1) sw = a.node;
+            else return "";
+        }
+        if (sw < 0 || row_coef != N(sw).arg || !counted_sweep(sw)) return "";
+        // the sweep must be the loop this load sits in
+        if (ctx >= 0) {
+            int cnt = 0, only = -1;
+            for (size_t k = 1; k < N(ctx).src.size(); k++) if (N(N(ctx).src[k]).op == OP_RANGE) { cnt++; only = N(ctx).src[k]; }
+            if (cnt != 1 || only != sw) return "";
+        } else if (!(loop_ranges.size() == 2 && loop_ranges[1] == sw)) return "";
+        const uint32_t id = it.bufs[p].id;
+        auto f0 = row_cache->find(id);
+        if (f0 == row_cache->end()) {
+            int used = 0;
+            for (auto& kv : *row_cache) used += (int)(kv.second.width / lanes);
+            if (used + N(sw).arg / lanes > row_cache_budget) return "";
+            (*row_cache)[id] = RowCached{N(sw).arg, it.bufs[p].dtype};
+        } else if (f0->second.width != N(sw).arg) return "";
+        (void)i;
+        return "rc_" + std::to_string(id) + "[" + sweep_counter(sw) + "]";
+    }
 
     std::string load_expr(int i, int ctx) {
         if (vec_load.count(i)) return vec_load[i] + "[u]";
@@ -544,6 +596,7 @@ struct Gen {
             idx = "clampi_(" + idx + ", " + hi + ")";
         }
         std::string e = dp + std::to_string(p) + "[" + idx + "]";
+        if (!opts.debug_bounds) { std::string rc = row_cached_load(i, p, f, ctx); if (!rc.empty()) e = rc; }
         Cls bc = dtype_cls(it.bufs[p].dtype);
         Cls want = cls(i);
         if (dtype_cls(nd.dtype) == CBOOL) return "(" + e + " != 0u)";
@@ -600,7 +653,11 @@ struct Gen {
                 hdr = "for (int " + rn + " = RED_BEGIN(" + range_bound(rr[0]) + "); " + rn + " < RED_END(" + range_bound(rr[0]) + "); " + rn + " += RED_STEP) {";
                 // short trip counts are unrolled: the loads of one stage of a row chain can then stay in
                 // registers for the next stage instead of being fetched from L1 again
-                if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) {
+                if (unroll_short_loops && counted_sweep(rr[0])) {
+                    // equal shares: an explicit trip counter, so that register copies of the row can be indexed
+                    const std::string j = sweep_counter(rr[0]);
+                    hdr = "_Pragma(\"unroll\") for (int " + j + " = 0; " + j + " < " + std::to_string(N(rr[0]).arg / lanes) + "; " + j + "++) { const int " + rn + " = lane + " + j + " * LANES;";
+                } else if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) {
                     if (chain_vec > 1 && N(rr[0]).arg % chain_vec == 0) {
                         // each lane takes chain_vec consecutive elements per trip: with 16-byte aligned bases the
                         // compiler turns the unrolled scalar loads into one 128-bit access
@@ -696,7 +753,9 @@ struct Gen {
                 case OP_REDUCE: if (ctx >= 0) { fail("codegen: nested REDUCE"); return "0.0f"; } e = reduce_expr(i); break;
                 case OP_CAST: case OP_BITCAST: e = cast_expr(i, ctx); break;
                 case OP_WHERE: { std::string cnd = a(0); if (cnd == "true") return ac(1); if (cnd == "false") return ac(2); e = "(" + cnd + " ? " + ac(1) + " : " + ac(2) + ")"; break; }
-                case OP_EXP2: e = h ? "__float2half_rn(ex2_h_(" + af(0) + "))" : "exp2f(" + af(0) + ")"; break;
+                // one MUFU: results below 2^-126 flush to zero instead of going through exp2f's rescaling
+                // for subnormals (absolute difference < 1.2e-38)
+                case OP_EXP2: e = h ? "__float2half_rn(ex2_h_(" + af(0) + "))" : "ex2_h_(" + af(0) + ")"; break;
                 case OP_LOG2: e = wrap("log2f(" + af(0) + ")"); break;
                 case OP_SIN: e = wrap("sinf(" + af(0) + ")"); break;
                 case OP_SQRT: e = wrap("sqrtf(" + af(0) + ")"); break;
@@ -705,7 +764,10 @@ struct Gen {
                 case OP_NEG: e = h ? "__hneg(" + ac(0) + ")" : "(-" + ac(0) + ")"; break;
                 case OP_ADD: e = h ? "__hadd(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " + " + ac(1) + ")"; break;
                 case OP_SUB: e = h ? "__hsub(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " - " + ac(1) + ")"; break;
-                case OP_MUL: e = h ? "__hmul(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " * " + ac(1) + ")"; break;
+                case OP_MUL:
+                    if (is_float_one(nd.src[0]) && cls(nd.src[1]) == c) return ac(1);
+                    if (is_float_one(nd.src[1]) && cls(nd.src[0]) == c) return ac(0);
+                    e = h ? "__hmul(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " * " + ac(1) + ")"; break;
                 case OP_FDIV: e = wrap("(" + af(0) + " / " + af(1) + ")"); break;
                 case OP_MAX: e = h ? "__hmax(" + ac(0) + ", " + ac(1) + ")" : "fmaxf(" + ac(0) + ", " + ac(1) + ")"; break;
                 case OP_POW: e = wrap("powf(" + af(0) + ", " + af(1) + ")"); break;
@@ -784,7 +846,10 @@ struct Gen {
             case OP_NEG: e = "__hneg2(" + a(0) + ")"; break;
             case OP_ADD: e = "__hadd2(" + a(0) + ", " + a(1) + ")"; break;
             case OP_SUB: e = "__hsub2(" + a(0) + ", " + a(1) + ")"; break;
-            case OP_MUL: e = "__hmul2(" + a(0) + ", " + a(1) + ")"; break;
+            case OP_MUL:
+                if (is_float_one(nd.src[0])) return a(1);
+                if (is_float_one(nd.src[1])) return a(0);
+                e = "__hmul2(" + a(0) + ", " + a(1) + ")"; break;
             case OP_MAX: e = "__hmax2(" + a(0) + ", " + a(1) + ")"; break;
             case OP_MULACC: e = "__hadd2(" + a(0) + ", __hmul2(" + a(1) + ", " + a(2) + "))"; break;
             case OP_EXP2: e = "h2_ex2_(" + a(0) + ")"; break;
@@ -1182,6 +1247,9 @@ struct Gen {
             if (inner <= (int64_t)threads * 32 && inner % chain_vec == 0 && chain_vec > 1) {
                 c << "  _Pragma(\"unroll\") for (int gb = threadIdx.x * " << chain_vec << "; gb < " << inner << "; gb += " << threads * chain_vec << ")\n";
                 c << "  _Pragma(\"unroll\") for (int gv = 0; gv < " << chain_vec << "; gv++) { const int gi = gb + gv;\n";
+            } else if (loop_ranges.size() == 2 && counted_sweep(loop_ranges[1])) {
+                const std::string j = sweep_counter(loop_ranges[1]);
+                c << "  _Pragma(\"unroll\") for (int " << j << " = 0; " << j << " < " << inner / threads << "; " << j << "++) { const int gi = threadIdx.x + " << j << " * " << threads << ";\n";
             } else {
                 c << (inner <= (int64_t)threads * 32 ? "  _Pragma(\"unroll\")\n" : "");
                 c << "  for (int gi = threadIdx.x; gi < " << inner << "; gi += " << threads << ") {\n";
@@ -1445,12 +1513,19 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
     std::ostringstream k, sig, body, aligned;
     std::vector<std::string> result(items.size());
     std::vector<bool> inner(items.size(), false);
+    std::map<uint32_t, std::string> shared_input;      // buffer id -> pointer of the first stage that reads it
+    std::map<uint32_t, Gen::RowCached> row_cache;
+    // Register copies of the rows are off unless asked for: they remove the repeated loads but need 64
+    // registers per thread, two resident blocks per SM instead of four, and the chain is bound by
+    // latency hiding across its barrier phases (measured 0.245 ms against 0.187 ms on 8192x8192).
+    static const bool cache_rows = std::getenv("ANNEAL_CHAIN_ROW_CACHE") && std::atoi(std::getenv("ANNEAL_CHAIN_ROW_CACHE")) != 0;
     int64_t rows = -1;
     sig << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") row_chain(";
     bool first_arg = true;
     std::string decls;
     for (size_t s = 0; s < items.size(); s++) {
         Gen g(*items[s], opts);
+        if (cache_rows) g.row_cache = &row_cache;
         for (auto& pr : chain_reads[s]) {
             if (pr.second < 0 || pr.second >= (int)s || inner[pr.second]) { err = "chain: stage input is not a per-row result of an earlier stage"; return false; }
             g.chain_subst[pr.first] = result[pr.second];
@@ -1468,7 +1543,20 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
             std::string ty = std::string(is_chain_out ? "" : "const ") + buf_ctype(items[s]->bufs[b].dtype) + "*";
             sig << (first_arg ? "" : ", ") << ty << " __restrict__ s" << s << "_data" << b << "_";
             // device blocks are 256-byte aligned (pool granularity, 128-element view offsets)
-            aligned << "  " << ty << " __restrict__ s" << s << "_data" << b << " = (" << ty << ")__builtin_assume_aligned(s" << s << "_data" << b << "_, 16);\n";
+            // a buffer that several stages read arrives once per stage; all stages use the first
+            // pointer, so the compiler sees one load per element and keeps the row in registers
+            // across stages instead of fetching it again through each stage's own parameter
+            const std::string local = "s" + std::to_string(s) + "_data" + std::to_string(b);
+            // Off unless asked for: on the 8192x8192 softmax chain it raised registers from 32 to 40 per
+            // thread, which costs one of the four resident blocks per SM (0.187 -> 0.205 ms).
+            static const bool alias_on = std::getenv("ANNEAL_CHAIN_ALIAS") && std::atoi(std::getenv("ANNEAL_CHAIN_ALIAS")) != 0;
+            auto seen = (b == 0 || !alias_on) ? shared_input.end() : shared_input.find(items[s]->bufs[b].id);
+            if (seen != shared_input.end()) {
+                aligned << "  " << ty << " __restrict__ " << local << " = " << seen->second << ";\n";
+            } else {
+                aligned << "  " << ty << " __restrict__ " << local << " = (" << ty << ")__builtin_assume_aligned(" << local << "_, 16);\n";
+                if (b > 0) shared_input[items[s]->bufs[b].id] = local;
+            }
             first_arg = false;
         }
     }
@@ -1481,6 +1569,13 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
     k << "  const int lane = threadIdx.x, grp = 0;\n  (void)grp;\n";
     k << "  const int row = blockIdx.x;\n";
     k << aligned.str();
+    for (auto& kv : row_cache) {
+        // the whole row, once, with every load of the thread in flight together
+        const std::string id = std::to_string(kv.first), per = std::to_string(kv.second.width / threads);
+        k << "  " << buf_ctype(kv.second.dtype) << " rc_" << id << "[" << per << "];\n";
+        k << "  _Pragma(\"unroll\") for (int j = 0; j < " << per << "; j++) rc_" << id << "[j] = " << shared_input[kv.first]
+          << "[(long long)row * " << kv.second.width << "LL + lane + j * LANES];\n";
+    }
     k << decls << body.str() << "}\n";
     out.source = k.str();
     out.block = (unsigned)threads;

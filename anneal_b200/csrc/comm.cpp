@@ -4,9 +4,12 @@
 // dlopen so that the library loads on machines without it and shares the copy a host process
 // (for example PyTorch) may already have loaded.
 #include <dlfcn.h>
+#include <unistd.h>
 
+#include <chrono>
 #include <cstring>
 #include <string>
+#include <thread>
 
 #include "runtime.hpp"
 
@@ -19,6 +22,7 @@ struct Nccl {
     int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
     int (*CommDestroy)(void*) = nullptr;
     int (*CommAbort)(void*) = nullptr;
+    int (*CommGetAsyncError)(void*, int*) = nullptr;
     const char* (*GetErrorString)(int) = nullptr;
     bool ok = false;
 };
@@ -33,6 +37,7 @@ Nccl& nccl() {
     n.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(n.h, "ncclAllReduce");
     n.CommDestroy = (int (*)(void*))dlsym(n.h, "ncclCommDestroy");
     n.CommAbort = (int (*)(void*))dlsym(n.h, "ncclCommAbort");
+    n.CommGetAsyncError = (int (*)(void*, int*))dlsym(n.h, "ncclCommGetAsyncError");
     n.GetErrorString = (const char* (*)(int))dlsym(n.h, "ncclGetErrorString");
     n.ok = n.GetUniqueId && n.CommInitRank && n.AllReduce && n.CommDestroy;
     return n;
@@ -61,7 +66,7 @@ int anl_comm_init(anl_device* dev, int rank, int nranks, const uint8_t id[128]) 
     std::memcpy(u.internal, id, 128);
     int r = n.CommInitRank(&dev->nccl_comm, nranks, u, rank);
     if (r != 0) return dev->fail(ANL_ERR_COMM, std::string("nccl: ncclCommInitRank: ") + (n.GetErrorString ? n.GetErrorString(r) : "?"));
-    dev->rank = rank; dev->nranks = nranks;
+    dev->rank = rank; dev->nranks = nranks; dev->comm_aborted = false;
     return ANL_OK;
 }
 
@@ -70,6 +75,7 @@ int anl_comm_init(anl_device* dev, int rank, int nranks, const uint8_t id[128]) 
 // it, so later kernels see the reduced values while kernels queued before the call overlap with it.
 int anl_allreduce_sum(anl_device* dev, anl_buffer* buf) {
     if (!dev || !buf) return ANL_ERR_INVALID;
+    if (dev->comm_aborted) return dev->fail(ANL_ERR_COMM, "nccl: the communicator was aborted; create a new one with anl_comm_init");
     if (dev->nranks == 1 || !dev->nccl_comm) return ANL_OK;
     Nccl& n = nccl();
     int dt = buf->dtype == ANL_F16 ? NCCL_FLOAT16 : NCCL_FLOAT32;
@@ -93,6 +99,7 @@ int comm_fork(anl_device* dev, cudaStream_t stream) {
     return ANL_OK;
 }
 int comm_allreduce_async(anl_device* dev, void* ptr, int64_t elems, int dtype, cudaStream_t stream) {
+    if (dev->comm_aborted) return dev->fail(ANL_ERR_COMM, "nccl: the communicator was aborted; create a new one with anl_comm_init");
     if (dev->nranks == 1 || !dev->nccl_comm) return ANL_OK;
     Nccl& n = nccl();
     comm_fork(dev, stream);
@@ -113,10 +120,76 @@ int comm_join(anl_device* dev, cudaStream_t stream) {
 extern "C" {
 
 int anl_comm_destroy(anl_device* dev) {
-    if (!dev || !dev->nccl_comm) return ANL_OK;
+    if (!dev) return ANL_OK;
+    dev->comm_aborted = false;
+    if (!dev->nccl_comm) return ANL_OK;
     Nccl& n = nccl();
     if (n.ok) n.CommDestroy(dev->nccl_comm);
     dev->nccl_comm = nullptr; dev->nranks = 1; dev->rank = 0;
+    return ANL_OK;
+}
+
+// ── watchdog ────────────────────────────────────────────────────────────────────────────────
+// A rank that has died or never joined leaves the others inside a collective for ever.  The host
+// side therefore never blocks on the communication stream without a limit once a timeout is set:
+// it polls the stream, asks NCCL for asynchronous errors, and on either an error or the deadline
+// aborts the communicator (ncclCommAbort ends the kernels that are waiting for the missing peer),
+// reports ANL_ERR_COMM and refuses further collectives until anl_comm_init is called again.
+static void abort_comm(anl_device* dev) {
+    Nccl& n = nccl();
+    if (dev->nccl_comm && n.CommAbort) n.CommAbort(dev->nccl_comm);
+    dev->nccl_comm = nullptr;
+    dev->comm_aborted = true;
+}
+
+int anl_comm_set_timeout(anl_device* dev, int milliseconds) {
+    if (!dev || milliseconds < 0) return ANL_ERR_INVALID;
+    dev->comm_timeout_ms = milliseconds;
+    return ANL_OK;
+}
+
+int anl_comm_abort(anl_device* dev) {
+    if (!dev) return ANL_ERR_INVALID;
+    abort_comm(dev);
+    return ANL_OK;
+}
+
+int anl_comm_wait(anl_device* dev) {
+    if (!dev) return ANL_ERR_INVALID;
+    if (!dev->comm_stream) return ANL_OK;
+    cudaSetDevice(dev->ordinal);
+    Nccl& n = nccl();
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t q = cudaStreamQuery(dev->comm_stream);
+        if (q == cudaSuccess) return ANL_OK;
+        if (q != cudaErrorNotReady) return dev->fail(ANL_ERR_CUDA, std::string("cuda: communication stream: ") + cudaGetErrorString(q));
+        if (dev->nccl_comm && n.CommGetAsyncError) {
+            int ae = 0;
+            if (n.CommGetAsyncError(dev->nccl_comm, &ae) == 0 && ae != 0) {
+                abort_comm(dev);
+                return dev->fail(ANL_ERR_COMM, std::string("nccl: asynchronous error: ") + (n.GetErrorString ? n.GetErrorString(ae) : "?") + "; communicator aborted");
+            }
+        }
+        if (dev->comm_timeout_ms > 0) {
+            auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+            if (ms >= dev->comm_timeout_ms) {
+                abort_comm(dev);
+                return dev->fail(ANL_ERR_COMM, "nccl: collective did not finish within " + std::to_string(dev->comm_timeout_ms) + " ms (a peer is missing or stalled); communicator aborted");
+            }
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+
+// Host-side failure injection for tests: holds the communication stream back by `milliseconds`
+// with a host callback (the GPU is idle meanwhile; nothing on the device faults or spins).
+static void CUDART_CB comm_host_sleep(void* p) { usleep((useconds_t)(intptr_t)p * 1000); }
+int anl_comm_inject_delay(anl_device* dev, int milliseconds) {
+    if (!dev || !dev->comm_stream || milliseconds < 0) return ANL_ERR_INVALID;
+    cudaSetDevice(dev->ordinal);
+    if (cudaLaunchHostFunc(dev->comm_stream, comm_host_sleep, (void*)(intptr_t)milliseconds) != cudaSuccess)
+        return dev->fail(ANL_ERR_CUDA, "cuda: cannot queue the host callback");
     return ANL_OK;
 }
 

@@ -712,6 +712,9 @@ int anl_get_stats(anl_device* dev, anl_stats* out) { if (!dev || !out) return AN
 
 int anl_synchronize(anl_device* dev) {
     if (!dev) return ANL_ERR_INVALID;
+    // with a communication timeout set, the collective stream is waited for under the watchdog first:
+    // the compute stream may itself be waiting for a collective that will never finish
+    if (dev->comm_stream && dev->comm_timeout_ms > 0) if (int rc = anl_comm_wait(dev)) return rc;
     CK(dev, cudaStreamSynchronize(dev->stream));
     if (dev->comm_stream) CK(dev, cudaStreamSynchronize(dev->comm_stream));
     if (dev->copy_stream) CK(dev, cudaStreamSynchronize(dev->copy_stream));

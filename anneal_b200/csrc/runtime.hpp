@@ -94,6 +94,8 @@ struct anl_device {
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
     bool comm_pending = false;
+    bool comm_aborted = false;            // set by the watchdog: collectives refuse until a new anl_comm_init
+    int comm_timeout_ms = 0;              // 0: wait without limit
     int comm_reserved_sms = 0;            // SMs the persistent GEMM leaves to collectives when nranks > 1
 
     int fail(int code, const std::string& m) { err = m; return code; }

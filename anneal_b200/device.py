@@ -115,6 +115,10 @@ def load_library():
     L.anl_comm_init.argtypes = [vp, i, i, C.c_char_p]
     L.anl_allreduce_sum.argtypes = [vp, vp]
     L.anl_comm_destroy.argtypes = [vp]
+    L.anl_comm_set_timeout.argtypes = [vp, i]
+    L.anl_comm_wait.argtypes = [vp]
+    L.anl_comm_abort.argtypes = [vp]
+    L.anl_comm_inject_delay.argtypes = [vp, i]
     L.anl_timer_start.argtypes = [vp]
     L.anl_timer_stop.argtypes = [vp, C.POINTER(C.c_float)]
     L.anl_profile_enable.argtypes = [vp, i]
@@ -134,7 +138,7 @@ ABI_SYMBOLS = [
     "anl_lower", "anl_lower_chain", "anl_compile_check", "anl_benchmark", "anl_graph_create", "anl_graph_replay", "anl_graph_release",
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
-    "anl_comm_destroy", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
+    "anl_comm_destroy", "anl_comm_set_timeout", "anl_comm_wait", "anl_comm_abort", "anl_comm_inject_delay", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
     "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search",
 ]
 
@@ -410,6 +414,20 @@ class Device:
 
     def allreduce_sum(self, buf: ResidentBuffer):
         self._check(self.L.anl_allreduce_sum(self.h, buf.h))
+
+    def comm_set_timeout(self, milliseconds: int):
+        """Longest a collective may stay unfinished before the watchdog aborts the communicator."""
+        self._check(self.L.anl_comm_set_timeout(self.h, int(milliseconds)))
+
+    def comm_wait(self):
+        self._check(self.L.anl_comm_wait(self.h))
+
+    def comm_abort(self):
+        self._check(self.L.anl_comm_abort(self.h))
+
+    def comm_inject_delay(self, milliseconds: int):
+        """Test aid: a host callback holds the communication stream back (no GPU work involved)."""
+        self._check(self.L.anl_comm_inject_delay(self.h, int(milliseconds)))
 
     def timer_start(self):
         self._check(self.L.anl_timer_start(self.h))

@@ -201,6 +201,17 @@ int anl_comm_unique_id(uint8_t id[128]);
 int anl_comm_init(anl_device* dev, int rank, int nranks, const uint8_t id[128]);
 int anl_allreduce_sum(anl_device* dev, anl_buffer* buf);     /* in place, on the comm stream, ordered after prior work */
 int anl_comm_destroy(anl_device* dev);
+/* Watchdog.  With a timeout set (milliseconds, 0 = none), anl_comm_wait — and anl_synchronize,
+ * which calls it first — polls the communication stream instead of blocking on it, asks NCCL for
+ * asynchronous errors, and on an error or when the time is up aborts the communicator
+ * (ncclCommAbort), returns ANL_ERR_COMM and makes every later collective fail until anl_comm_init
+ * is called again.  anl_comm_abort does the same on request (another rank was reported dead by the
+ * launcher).  anl_comm_inject_delay is host-side failure injection for tests: a host callback
+ * holds the communication stream back; nothing on the GPU faults or spins. */
+int anl_comm_set_timeout(anl_device* dev, int milliseconds);
+int anl_comm_wait(anl_device* dev);
+int anl_comm_abort(anl_device* dev);
+int anl_comm_inject_delay(anl_device* dev, int milliseconds);
 
 /* host staging memory that the GPU can copy from directly */
 int anl_host_alloc(size_t bytes, void** out);
