@@ -22,21 +22,22 @@ def test_wait_without_pending_work_returns_at_once():
 
 
 def test_stalled_collective_stream_times_out_and_poisons_the_communicator():
+    """No NCCL communicator is attached while the stream is stalled: ncclCommAbort drains the
+    device before it returns, and a host callback cannot be cut short the way a kernel waiting for
+    a peer is, so with a real communicator the call would last as long as the injected stall."""
     dev = Device(0)
     try:
-        dev.comm_init(0, 1, dev.comm_unique_id())        # a real one-rank communicator
         buf = dev.buffer(dtypes.float32, 1024).upload(np.ones(1024, np.float32))
-        dev.allreduce_sum(buf)                           # one rank: nothing to exchange, no error
         dev.comm_set_timeout(40)
-        dev.comm_inject_delay(4000)
+        dev.comm_inject_delay(1500)
         t0 = time.perf_counter()
         with pytest.raises(DeviceError, match="did not finish within 40 ms"):
             dev.synchronize()
         waited = time.perf_counter() - t0
-        assert 0.03 <= waited < 3.0                      # gave up at the deadline (plus NCCL's own teardown), not after the 4 s stall
+        assert 0.03 <= waited < 1.0                      # gave up at the deadline, not after the stall
         with pytest.raises(DeviceError, match="aborted"):
             dev.allreduce_sum(buf)
-        time.sleep(max(0.0, 4.2 - (time.perf_counter() - t0)))   # let the callback return
+        time.sleep(max(0.0, 1.7 - (time.perf_counter() - t0)))   # let the callback return
         dev.comm_set_timeout(0)
         dev.synchronize()
         assert np.array_equal(buf.download(), np.ones(1024, np.float32))
