@@ -45,17 +45,59 @@ __global__ void cvt_f16_to_f32(const __half* __restrict__ in, float* __restrict_
 
 // Parameter.SGDStep (tensor/nn/nn.go:69-76) with the re-quantisation of Parameter.Load
 // (tensor/nn/nn.go:56-61) fused: one pass over master, grad and param.
+// Streaming accesses (evict-first): the 12 bytes per parameter this pass moves are not needed again
+// before the next step, while the contractions running beside it live on the operand tiles they
+// keep in L2.  Four parameters per thread and trip when the views are 16-byte aligned.
+template <class T> __device__ __forceinline__ float sgd_ld(const T* p) { return (float)__ldcs(p); }
+template <> __device__ __forceinline__ float sgd_ld<__half>(const __half* p) { return __half2float(__ldcs(p)); }
+
 template <class G, class P>
 __global__ void sgd_kernel(float* __restrict__ master, P* __restrict__ param, const G* __restrict__ grad,
-                           float lr, float scale, long long n, int bf16) {
-    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+                           float lr, float scale, long long n, int bf16, int vec) {
+    const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
-    for (; i < n; i += stride) {
-        float g = (float)grad[i] * scale;
+    const bool separate = (void*)param != (void*)master;
+    long long done = 0;
+    if (vec) {
+        const long long n4 = n >> 2;
+        for (long long q = tid; q < n4; q += stride) {
+            float4 m = __ldcs(reinterpret_cast<const float4*>(master) + q);
+            float g[4];
+            if (sizeof(G) == 2) {
+                uint2 raw = __ldcs(reinterpret_cast<const uint2*>(grad) + q);
+                const __half2 lo = *reinterpret_cast<const __half2*>(&raw.x), hi = *reinterpret_cast<const __half2*>(&raw.y);
+                g[0] = __low2float(lo); g[1] = __high2float(lo); g[2] = __low2float(hi); g[3] = __high2float(hi);
+            } else {
+                float4 raw = __ldcs(reinterpret_cast<const float4*>(grad) + q);
+                g[0] = raw.x; g[1] = raw.y; g[2] = raw.z; g[3] = raw.w;
+            }
+            float r[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+            for (int j = 0; j < 4; j++) {
+                const float gs = g[j] * scale;
+                r[j] = r[j] - lr * gs;
+            }
+            __stcs(reinterpret_cast<float4*>(master) + q, make_float4(r[0], r[1], r[2], r[3]));
+            if (separate) {
+                if (sizeof(P) == 2) {
+                    const __half2 lo = __floats2half2_rn(r[0], r[1]), hi = __floats2half2_rn(r[2], r[3]);
+                    uint2 o; o.x = *reinterpret_cast<const unsigned*>(&lo); o.y = *reinterpret_cast<const unsigned*>(&hi);
+                    __stcs(reinterpret_cast<uint2*>(param) + q, o);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 4; j++) if (bf16) r[j] = __int_as_float(__float_as_int(r[j]) & 0xFFFF0000);
+                    __stcs(reinterpret_cast<float4*>(param) + q, make_float4(r[0], r[1], r[2], r[3]));
+                }
+            }
+        }
+        done = n4 << 2;
+    }
+    for (long long i = done + tid; i < n; i += stride) {
+        float g = sgd_ld(grad + i) * scale;
         float m = master[i] - lr * g;
         master[i] = m;
         if (bf16) m = __int_as_float(__float_as_int(m) & 0xFFFF0000);
-        if ((void*)param != (void*)master) param[i] = (P)m;
+        if (separate) param[i] = (P)m;
     }
 }
 
@@ -253,19 +295,27 @@ static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item
     return rc;
 }
 
-int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream) {
+int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream,
+               bool background) {
     if (master->dtype != ANL_F32) return dev->fail(ANL_ERR_INVALID, "sgd: master weights must be f32");
     if (grad->elems < master->elems || param->elems < master->elems) return dev->fail(ANL_ERR_INVALID, "sgd: gradient length != parameter length");
     long long n = master->elems;
     if (n == 0) return ANL_OK;
-    unsigned g = grid_for(n, 256, dev->prop.multiProcessorCount);
+    auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+    const int vec = n >= 4 && al16(master->ptr) && al16(param->ptr) && al16(grad->ptr);
+    // An update that runs beside the backward pass has until the end of the step: one block per SM
+    // leaves the issue slots and most of the memory system to the contractions.  The last update
+    // of a step, and the stand-alone call, take the whole machine.
+    const int sms = dev->prop.multiProcessorCount;
+    unsigned g = background ? (unsigned)std::max<long long>(1, std::min<long long>((n / 4 + 255) / 256, sms))
+                            : grid_for(vec ? (n + 3) / 4 : n, 256, sms);
     float* m = (float*)master->ptr;
     bool gh = grad->dtype == ANL_F16, ph = param->dtype == ANL_F16;
     int bf = param->dtype == ANL_BF16;
-    if (gh && ph) sgd_kernel<__half, __half><<<g, 256, 0, stream>>>(m, (__half*)param->ptr, (const __half*)grad->ptr, lr, scale, n, 0);
-    else if (gh) sgd_kernel<__half, float><<<g, 256, 0, stream>>>(m, (float*)param->ptr, (const __half*)grad->ptr, lr, scale, n, bf);
-    else if (ph) sgd_kernel<float, __half><<<g, 256, 0, stream>>>(m, (__half*)param->ptr, (const float*)grad->ptr, lr, scale, n, 0);
-    else sgd_kernel<float, float><<<g, 256, 0, stream>>>(m, (float*)param->ptr, (const float*)grad->ptr, lr, scale, n, bf);
+    if (gh && ph) sgd_kernel<__half, __half><<<g, 256, 0, stream>>>(m, (__half*)param->ptr, (const __half*)grad->ptr, lr, scale, n, 0, vec);
+    else if (gh) sgd_kernel<__half, float><<<g, 256, 0, stream>>>(m, (float*)param->ptr, (const __half*)grad->ptr, lr, scale, n, bf, vec);
+    else if (ph) sgd_kernel<float, __half><<<g, 256, 0, stream>>>(m, (__half*)param->ptr, (const float*)grad->ptr, lr, scale, n, 0, vec);
+    else sgd_kernel<float, float><<<g, 256, 0, stream>>>(m, (float*)param->ptr, (const float*)grad->ptr, lr, scale, n, bf, vec);
     dev->stats.kernels_launched++;
     CK(dev, cudaGetLastError());
     return ANL_OK;
@@ -499,6 +549,7 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         sgd_at[at].push_back(kv.first);
     }
     const bool chains_on = !(dev->flags & ANL_OPEN_NO_ROW_CHAIN) && !(dev->flags & ANL_OPEN_BEAM);
+    static const bool sgd_foreground = std::getenv("ANNEAL_SGD_FOREGROUND") && std::atoi(std::getenv("ANNEAL_SGD_FOREGROUND")) != 0;
     // the last all-reduced output of the schedule, when it is a large contraction whose update is
     // not deferred past it: candidate for the split described at its launch below
     size_t tail_split = (size_t)-1;
@@ -564,7 +615,7 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
                 mv.ptr = (char*)mv.ptr + off * dt_storage_bytes(mv.dtype); mv.elems = cnt;
                 pv.ptr = (char*)pv.ptr + off * dt_storage_bytes(pv.dtype); pv.elems = cnt;
                 comm_fork(dev, stream);
-                if (int rc = launch_sgd(dev, &mv, &pv, &gv, a.sgd_lr, a.sgd_scale, dev->comm_stream)) return rc;
+                if (int rc = launch_sgd(dev, &mv, &pv, &gv, a.sgd_lr, a.sgd_scale, dev->comm_stream, h == 0 && !sgd_foreground)) return rc;
             }
             continue;
         }
@@ -578,7 +629,8 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             comm_fork(dev, stream);
             for (uint32_t id : sg->second) {
                 const anl_output& a = t.after[id];
-                if (int rc = launch_sgd(dev, a.sgd_master, a.sgd_param ? a.sgd_param : a.sgd_master, a.resident, a.sgd_lr, a.sgd_scale, dev->comm_stream)) return rc;
+                const bool background = i + 1 < items.size() && !sgd_foreground;
+                if (int rc = launch_sgd(dev, a.sgd_master, a.sgd_param ? a.sgd_param : a.sgd_master, a.resident, a.sgd_lr, a.sgd_scale, dev->comm_stream, background)) return rc;
             }
         }
     }
