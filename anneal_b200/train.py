@@ -124,6 +124,31 @@ class ResidentTrainer:
             return float(self.loss_res.download()[0])
         return float(self.loss_host[0])
 
+    def _named(self, names=None) -> Dict[str, object]:
+        names = list(names) if names is not None else [f"param.{i}" for i in range(len(self.params))]
+        if len(names) != len(self.params):
+            raise ValueError(f"checkpoint: {len(names)} names for {len(self.params)} parameters")
+        return dict(zip(names, self.params))
+
+    def save_checkpoint(self, path: str, names=None) -> None:
+        """Master weights → host ``Parameter.value`` → safetensors file (tensor/safetensors/safetensors.go:75).
+        SGD keeps no optimiser state, so this is all a resume needs."""
+        from . import safetensors
+        for p, v in zip(self.params, self.parameters()):
+            p.value[:] = v
+        safetensors.save(path, self._named(names))
+
+    def load_checkpoint(self, path: str, names=None) -> None:
+        """safetensors file → host values → master and storage-dtype buckets on the device."""
+        from . import safetensors
+        safetensors.load(path, self._named(names))
+        flat = np.zeros(self.total, dtype=np.float32)
+        for p, o in zip(self.params, self.offsets):
+            flat[o:o + p.value.size] = p.value
+        self.master.upload(flat)
+        if self.store is not self.master:
+            self.store.upload(flat)
+
     def parameters(self) -> List[np.ndarray]:
         """Master weights back on the host, one array per parameter (for checkpoints and tests)."""
         flat = self.master.download()

@@ -271,3 +271,29 @@ def test_tail_split_contraction_leaves_the_same_parameters():
         assert np.array_equal(a, b)
     assert res[0][1] == res[1][1]
     assert res[0][2] == res[1][2] + 3          # one extra contraction launch per step
+
+
+def test_checkpoint_resume_continues_the_same_trajectory(cuda, tmp_path):
+    """Three steps, save, load into a fresh trainer, three more steps: the same parameters, bit for
+    bit, as six uninterrupted steps (SGD carries no optimiser state; the f32 masters are the state)."""
+    def fresh():
+        R.reset()
+        m = W.WideMLP(batch=256, width=256, classes=72, depth=2)
+        tr = ResidentTrainer(cuda, m, 0.05, use_graph=True, resident_inputs=True)
+        tr.load_batch(*m.make_inputs())
+        return tr
+    a = fresh()
+    for _ in range(6):
+        a.step()
+    b = fresh()
+    for _ in range(3):
+        b.step()
+    path = str(tmp_path / "resume.safetensors")
+    b.save_checkpoint(path)
+    c = fresh()
+    c.load_checkpoint(path)
+    for _ in range(3):
+        c.step()
+    for x, y in zip(a.parameters(), c.parameters()):
+        assert np.array_equal(x, y)
+    assert a.loss() == c.loss()
