@@ -549,7 +549,11 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         sgd_at[at].push_back(kv.first);
     }
     const bool chains_on = !(dev->flags & ANL_OPEN_NO_ROW_CHAIN) && !(dev->flags & ANL_OPEN_BEAM);
-    static const bool sgd_foreground = std::getenv("ANNEAL_SGD_FOREGROUND") && std::atoi(std::getenv("ANNEAL_SGD_FOREGROUND")) != 0;
+    // Updates beside the backward pass take the whole machine unless ANNEAL_SGD_BACKGROUND=1 asks for
+    // one block per SM: the narrow form disturbs the contractions less when they are timed one by
+    // one, but on two GPUs it stretches the serial communication stream and the step got 0.06 ms
+    // longer (3.59-3.61 against 3.52-3.56 ms), and on one GPU the step time did not change.
+    static const bool sgd_foreground = !(std::getenv("ANNEAL_SGD_BACKGROUND") && std::atoi(std::getenv("ANNEAL_SGD_BACKGROUND")) != 0);
     // the last all-reduced output of the schedule, when it is a large contraction whose update is
     // not deferred past it: candidate for the split described at its launch below
     size_t tail_split = (size_t)-1;

@@ -112,6 +112,34 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.sm), "source": self.source}
 
 
+def bind_to_gpu_numa_node(index: int):
+    """Restrict this process to the CPUs NVML lists as local to GPU `index`, before any pinned memory is
+    allocated, so that the staged batches sit on the GPU's own NUMA node (with one process per GPU all
+    ranks otherwise tend to allocate on one socket and share its memory controllers and PCIe root).
+    Changes only this process's scheduling mask; returns the CPU list or None."""
+    try:
+        import pynvml as nv
+        nv.nvmlInit()
+        vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+        if vis:
+            ids = [v.strip() for v in vis.split(",") if v.strip()]
+            if index < len(ids) and ids[index].isdigit():
+                index = int(ids[index])
+        h = nv.nvmlDeviceGetHandleByIndex(index)
+        words = (os.cpu_count() + 63) // 64
+        mask = nv.nvmlDeviceGetCpuAffinity(h, words)
+        cpus = [w * 64 + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1]
+        allowed = os.sched_getaffinity(0)
+        cpus = [c for c in cpus if c in allowed]
+        nv.nvmlShutdown()
+        if cpus and len(cpus) < len(allowed):
+            os.sched_setaffinity(0, cpus)
+            return cpus
+    except Exception:
+        pass
+    return None
+
+
 def peaks():
     try:
         with open(os.path.join(ROOT, "MEASURED_PEAKS.json")) as f:
@@ -181,6 +209,7 @@ def run_ours(args):
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    numa_cpus = bind_to_gpu_numa_node(local) if world > 1 else None
     if world > 1:
         dist.init_process_group("gloo", rank=rank, world_size=world)
     dev = Device(local)
@@ -290,6 +319,7 @@ def run_ours(args):
     e2e = {"value": CFG["batch"] * world * args.steps / (ms2 / 1e3), "unit": UNIT,
            "h2d_bytes_per_step": int((x.size + y.size) * 4), "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps,
            "how": "batch i+1 copied from pinned host memory on a copy stream while step i runs; loss read back every step",
+           "host_cpus_bound": len(numa_cpus) if numa_cpus else None,
            "loss": e2e_loss}
 
     cpu = None

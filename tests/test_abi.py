@@ -129,3 +129,49 @@ def test_opts_change_the_launch_shape():
     assert forced["block"] == 128 and "lanes=4" in forced["note"] and base["note"] != forced["note"]
     split = device.lower(R.build_schedule([Tensor.new_leaf((1 << 20,)).sum()])[0], 0)
     assert split["class"] == "reduce_split"
+
+
+def test_f16_elementwise_kernels_pair_their_arithmetic():
+    """All-f16 elementwise kernels are rendered in __half2 (two outputs per instruction); a kernel
+    with an f32 value in it keeps the one-element form. Both must compile for sm_100a."""
+    from anneal_b200 import nn
+    R.reset()
+    x = Tensor.new_leaf((64, 256), dtypes.float16)
+    b = Tensor.new_leaf((256,), dtypes.float16)
+    from anneal_b200.tensor import broadcast_to
+    items, _ = R.build_schedule([nn.gelu_tanh(x.add(broadcast_to(b, (64, 256))))])
+    low = device.lower(items, 0)
+    assert "paired f16" in low["note"] and "__hmul2" in low["source"] and "h2_ex2_" in low["source"]
+    assert "* 0x1p+0f" not in low["source"]                   # multiplications by one are folded
+    device.compile_check(low["source"])
+    # a comparison and a select stay paired: masks and a bitwise select
+    R.reset()
+    y = Tensor.new_leaf((64, 256), dtypes.float16)
+    z = Tensor.new_leaf((64, 256), dtypes.float16)
+    items, _ = R.build_schedule([y.maximum(z).mul(y)])
+    low = device.lower(items, 0)
+    assert "paired f16" in low["note"]
+    device.compile_check(low["source"])
+    # mixed precision: not paired
+    R.reset()
+    w = Tensor.new_leaf((64, 256), dtypes.float32)
+    items, _ = R.build_schedule([w.mul(w).exp()])
+    low = device.lower(items, 0)
+    assert "paired" not in low["note"]
+    device.compile_check(low["source"])
+
+
+def test_contraction_is_reported_with_symbolic_extents():
+    """`lower` says when the device would route an item to a contraction kernel: f32 with the bound
+    batch as M (forward) or as K (weight gradient)."""
+    R.reset()
+    R.MATERIALIZE_CONTRACTION_OPERANDS = True
+    try:
+        m = W.DynMLP(din=64, hidden=128, dout=32, max_batch=4096)
+        out, loss, grads, _ = m.graph(8)
+        items, _ = R.build_schedule([out] + grads)
+        notes = [device.lower(items, i)["note"] for i in range(len(items))]
+    finally:
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+    assert any("contraction f32 M=n N=128 K=64" in n for n in notes)
+    assert any("contraction f32 M=128 N=64 K=n" in n for n in notes)
