@@ -1149,6 +1149,7 @@ struct Gen {
         // votes: bytes of loads that are unit-stride along the innermost reduce range (RC) against
         // loads unit-stride along the innermost output range (OC)
         int64_t rc = 0, oc = 0;
+        int oc_min_bytes = 4;
         int out_inner = loop_ranges.empty() ? -1 : loop_ranges.back();
         for (int r : reduces) {
             int red_inner = -1;
@@ -1162,7 +1163,7 @@ struct Gen {
                 int64_t c2 = out_inner >= 0 ? lin_coef(f, out_inner, ok2) : 0;
                 int bytes = dt_storage_bytes(it.bufs[(int)N(N(i).src[0]).arg].dtype);
                 if (ok1 && std::llabs(c1) == 1) rc += bytes;
-                else if (ok2 && std::llabs(c2) == 1) oc += bytes;
+                else if (ok2 && std::llabs(c2) == 1) { oc += bytes; oc_min_bytes = std::min(oc_min_bytes, bytes); }
             }
         }
         threads = opts.block_threads > 0 ? opts.block_threads : 256;
@@ -1171,7 +1172,13 @@ struct Gen {
             rc_layout = false;
             int L = 1;
             if (opts.reduce_lanes > 0) L = opts.reduce_lanes;
-            else while (L < 32 && total * L < want_threads && rtot_max / (L * 2) >= 16) L *= 2;
+            else {
+                while (L < 32 && total * L < want_threads && rtot_max / (L * 2) >= 16) L *= 2;
+                // the threads that share a row cover TOUTS adjacent outputs: keep that run at least one
+                // 32-byte sector wide, or every sector fetched is only partly used (f16: 16 outputs)
+                const int min_touts = std::max(1, 32 / std::max(1, oc_min_bytes));
+                while (L > 1 && threads / L < min_touts) L /= 2;
+            }
             lanes = L;
         } else {
             rc_layout = true;

@@ -20,6 +20,8 @@ struct Nccl {
     int (*GetUniqueId)(nccl_uid*) = nullptr;
     int (*CommInitRank)(void**, int, nccl_uid, int) = nullptr;
     int (*AllReduce)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*ReduceScatter)(const void*, void*, size_t, int, int, void*, cudaStream_t) = nullptr;
+    int (*AllGather)(const void*, void*, size_t, int, void*, cudaStream_t) = nullptr;
     int (*CommDestroy)(void*) = nullptr;
     int (*CommAbort)(void*) = nullptr;
     int (*CommGetAsyncError)(void*, int*) = nullptr;
@@ -35,6 +37,8 @@ Nccl& nccl() {
     n.GetUniqueId = (int (*)(nccl_uid*))dlsym(n.h, "ncclGetUniqueId");
     n.CommInitRank = (int (*)(void**, int, nccl_uid, int))dlsym(n.h, "ncclCommInitRank");
     n.AllReduce = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(n.h, "ncclAllReduce");
+    n.ReduceScatter = (int (*)(const void*, void*, size_t, int, int, void*, cudaStream_t))dlsym(n.h, "ncclReduceScatter");
+    n.AllGather = (int (*)(const void*, void*, size_t, int, void*, cudaStream_t))dlsym(n.h, "ncclAllGather");
     n.CommDestroy = (int (*)(void*))dlsym(n.h, "ncclCommDestroy");
     n.CommAbort = (int (*)(void*))dlsym(n.h, "ncclCommAbort");
     n.CommGetAsyncError = (int (*)(void*, int*))dlsym(n.h, "ncclCommGetAsyncError");
@@ -108,6 +112,35 @@ int comm_allreduce_async(anl_device* dev, void* ptr, int64_t elems, int dtype, c
     dev->comm_pending = true;
     return ANL_OK;
 }
+static size_t nccl_elem_bytes(int dtype) { return dtype == ANL_F16 ? 2 : 4; }
+bool comm_can_shard(anl_device* dev) { Nccl& n = nccl(); return dev->nranks > 1 && dev->nccl_comm && n.ReduceScatter && n.AllGather; }
+// In-place reduce-scatter: afterwards rank r holds the sum of elements [r*elems/nranks, (r+1)*elems/nranks)
+// at their own position; the other positions hold partial garbage.  elems must divide by nranks.
+int comm_reduce_scatter_async(anl_device* dev, void* ptr, int64_t elems, int dtype, cudaStream_t stream) {
+    if (dev->comm_aborted) return dev->fail(ANL_ERR_COMM, "nccl: the communicator was aborted; create a new one with anl_comm_init");
+    Nccl& n = nccl();
+    const int64_t cnt = elems / dev->nranks;
+    comm_fork(dev, stream);
+    char* base = (char*)ptr;
+    int r = n.ReduceScatter(base, base + (size_t)dev->rank * cnt * nccl_elem_bytes(dtype), (size_t)cnt,
+                            dtype == ANL_F16 ? NCCL_FLOAT16 : NCCL_FLOAT32, NCCL_SUM, dev->nccl_comm, dev->comm_stream);
+    if (r != 0) return dev->fail(ANL_ERR_COMM, std::string("nccl: ncclReduceScatter: ") + (n.GetErrorString ? n.GetErrorString(r) : "?"));
+    dev->comm_pending = true;
+    return ANL_OK;
+}
+// In-place all-gather on the communication stream (behind whatever was queued there): every rank
+// contributes its own shard of `ptr` and receives the others'.
+int comm_allgather_async(anl_device* dev, void* ptr, int64_t elems, int dtype) {
+    if (dev->comm_aborted) return dev->fail(ANL_ERR_COMM, "nccl: the communicator was aborted; create a new one with anl_comm_init");
+    Nccl& n = nccl();
+    const int64_t cnt = elems / dev->nranks;
+    char* base = (char*)ptr;
+    int r = n.AllGather(base + (size_t)dev->rank * cnt * nccl_elem_bytes(dtype), base, (size_t)cnt,
+                        dtype == ANL_F16 ? NCCL_FLOAT16 : NCCL_FLOAT32, dev->nccl_comm, dev->comm_stream);
+    if (r != 0) return dev->fail(ANL_ERR_COMM, std::string("nccl: ncclAllGather: ") + (n.GetErrorString ? n.GetErrorString(r) : "?"));
+    dev->comm_pending = true;
+    return ANL_OK;
+}
 int comm_join(anl_device* dev, cudaStream_t stream) {
     if (!dev->comm_pending) return ANL_OK;
     cudaEventRecord(dev->comm_done, dev->comm_stream);
@@ -127,6 +160,21 @@ int anl_comm_destroy(anl_device* dev) {
     if (n.ok) n.CommDestroy(dev->nccl_comm);
     dev->nccl_comm = nullptr; dev->nranks = 1; dev->rank = 0;
     return ANL_OK;
+}
+
+// Every rank's shard of `buf` (elems / nranks each, in rank order) gathered into all ranks' copies,
+// in place; ordered after prior work on the compute stream, which then waits for it.  Used to
+// assemble the f32 master weights when the update is sharded across ranks.
+int anl_allgather(anl_device* dev, anl_buffer* buf) {
+    if (!dev || !buf) return ANL_ERR_INVALID;
+    if (dev->comm_aborted) return dev->fail(ANL_ERR_COMM, "nccl: the communicator was aborted; create a new one with anl_comm_init");
+    if (dev->nranks == 1 || !dev->nccl_comm) return ANL_OK;
+    if (!anl::comm_can_shard(dev)) return dev->fail(ANL_ERR_COMM, "nccl: ncclAllGather not available");
+    if (buf->elems % dev->nranks) return dev->fail(ANL_ERR_INVALID, "allgather: buffer length is not a multiple of the rank count");
+    cudaSetDevice(dev->ordinal);
+    anl::comm_fork(dev, dev->stream);
+    if (int rc = anl::comm_allgather_async(dev, buf->ptr, buf->elems, buf->dtype)) return rc;
+    return anl::comm_join(dev, dev->stream);
 }
 
 // ── watchdog ────────────────────────────────────────────────────────────────────────────────

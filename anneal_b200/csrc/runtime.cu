@@ -572,6 +572,35 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             break;      // only the very last collective is exposed
         }
     }
+    // A gradient flagged `allreduce == 2` with an update attached is handled the sharded way when its
+    // length divides by the rank count: reduce-scatter, every rank updates only its own 1/nranks of
+    // the parameter (the update is pure memory traffic, 12 bytes per parameter, and costs as much
+    // step time beside the backward pass as after it), then the new parameter values are
+    // all-gathered.  The bytes on the wire equal an all-reduce's.  Otherwise: plain all-reduce and a
+    // full update on every rank.
+    auto sharded = [&](const anl_output& a, int64_t cnt) {
+        return a.allreduce == 2 && a.sgd_master && a.resident && comm_can_shard(dev) && cnt > 0 && cnt % dev->nranks == 0;
+    };
+    auto reduce_part = [&](const anl_output& a, int64_t off, int64_t cnt) -> int {
+        char* g = (char*)a.resident->ptr + off * dt_storage_bytes(a.resident->dtype);
+        if (sharded(a, cnt)) return comm_reduce_scatter_async(dev, g, cnt, a.resident->dtype, stream);
+        return comm_allreduce_async(dev, g, cnt, a.resident->dtype, stream);
+    };
+    auto update_part = [&](const anl_output& a, int64_t off, int64_t cnt, bool background) -> int {
+        const bool sh = sharded(a, cnt);
+        const int64_t sc = sh ? cnt / dev->nranks : cnt, so = sh ? off + dev->rank * sc : off;
+        anl_buffer gv = *a.resident, mv = *a.sgd_master, pv = a.sgd_param ? *a.sgd_param : *a.sgd_master;
+        gv.ptr = (char*)gv.ptr + so * dt_storage_bytes(gv.dtype); gv.elems = sc;
+        mv.ptr = (char*)mv.ptr + so * dt_storage_bytes(mv.dtype); mv.elems = sc;
+        pv.ptr = (char*)pv.ptr + so * dt_storage_bytes(pv.dtype); pv.elems = sc;
+        comm_fork(dev, stream);
+        if (int rc = launch_sgd(dev, &mv, &pv, &gv, a.sgd_lr, a.sgd_scale, dev->comm_stream, background)) return rc;
+        if (sh) {
+            const anl_buffer* pb = a.sgd_param ? a.sgd_param : a.sgd_master;
+            if (int rc = comm_allgather_async(dev, (char*)pb->ptr + off * dt_storage_bytes(pb->dtype), cnt, pb->dtype)) return rc;
+        }
+        return ANL_OK;
+    };
     for (size_t i = 0; i < items.size(); i++) {
         const Item& it = items[i];
         if (chains_on) {
@@ -608,33 +637,26 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             const anl_output& a = ra->second;
             int64_t row_elems = 0, rows = gemm_window_rows(*plan, &row_elems);
             const int64_t cut = (rows / 2 + 255) / 256 * 256;
-            const int es = dt_storage_bytes(a.resident->dtype);
-            for (int h = 0; h < 2; h++) {
+                        for (int h = 0; h < 2; h++) {
                 const int64_t m0 = h ? cut : 0, m1 = h ? rows : cut;
                 if (int rc = launch_gemm(dev, *plan, ptrs.data(), item_sym(it, binds), stream, m0, m1)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
                 const int64_t off = m0 * row_elems, cnt = (m1 - m0) * row_elems;
-                if (int rc = comm_allreduce_async(dev, (char*)a.resident->ptr + off * es, cnt, a.resident->dtype, stream)) return rc;
-                anl_buffer gv = *a.resident, mv = *a.sgd_master, pv = a.sgd_param ? *a.sgd_param : *a.sgd_master;
-                gv.ptr = (char*)gv.ptr + off * es; gv.elems = cnt;
-                mv.ptr = (char*)mv.ptr + off * dt_storage_bytes(mv.dtype); mv.elems = cnt;
-                pv.ptr = (char*)pv.ptr + off * dt_storage_bytes(pv.dtype); pv.elems = cnt;
-                comm_fork(dev, stream);
-                if (int rc = launch_sgd(dev, &mv, &pv, &gv, a.sgd_lr, a.sgd_scale, dev->comm_stream, h == 0 && !sgd_foreground)) return rc;
+                if (int rc = reduce_part(a, off, cnt)) return rc;
+                if (int rc = update_part(a, off, cnt, h == 0 && !sgd_foreground)) return rc;
             }
             continue;
         }
         if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
         // side stream: [all-reduce this gradient] behind the producing kernel ...
         if (ra != t.after.end() && ra->second.allreduce)
-            if (int rc = comm_allreduce_async(dev, ra->second.resident->ptr, ra->second.resident->elems, ra->second.resident->dtype, stream)) return rc;
+            if (int rc = reduce_part(ra->second, 0, ra->second.resident->elems)) return rc;
         // ... [update the parameter] once its last reader has been queued as well
         auto sg = sgd_at.find(i);
         if (sg != sgd_at.end()) {
-            comm_fork(dev, stream);
             for (uint32_t id : sg->second) {
                 const anl_output& a = t.after[id];
                 const bool background = i + 1 < items.size() && !sgd_foreground;
-                if (int rc = launch_sgd(dev, a.sgd_master, a.sgd_param ? a.sgd_param : a.sgd_master, a.resident, a.sgd_lr, a.sgd_scale, dev->comm_stream, background)) return rc;
+                if (int rc = update_part(a, 0, a.sgd_master->elems, background)) return rc;
             }
         }
     }

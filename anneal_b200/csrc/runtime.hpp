@@ -136,6 +136,9 @@ int launch_gemm_f32(anl_device* dev, const float* a, const float* b, float* d, i
 // everything queued so far on `stream`; comm_join makes `stream` wait for all of them
 int comm_fork(anl_device* dev, cudaStream_t stream);     // side stream waits for everything queued on `stream`
 int comm_allreduce_async(anl_device* dev, void* ptr, int64_t elems, int dtype, cudaStream_t stream);
+bool comm_can_shard(anl_device* dev);
+int comm_reduce_scatter_async(anl_device* dev, void* ptr, int64_t elems, int dtype, cudaStream_t stream);
+int comm_allgather_async(anl_device* dev, void* ptr, int64_t elems, int dtype);
 int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream,
                bool background = false);
 int comm_join(anl_device* dev, cudaStream_t stream);

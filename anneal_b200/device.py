@@ -114,6 +114,7 @@ def load_library():
     L.anl_comm_unique_id.argtypes = [C.c_char_p]
     L.anl_comm_init.argtypes = [vp, i, i, C.c_char_p]
     L.anl_allreduce_sum.argtypes = [vp, vp]
+    L.anl_allgather.argtypes = [vp, vp]
     L.anl_comm_destroy.argtypes = [vp]
     L.anl_comm_set_timeout.argtypes = [vp, i]
     L.anl_comm_wait.argtypes = [vp]
@@ -137,7 +138,7 @@ ABI_SYMBOLS = [
     "anl_open", "anl_close", "anl_device_info", "anl_last_error", "anl_get_stats", "anl_run", "anl_outputs_free",
     "anl_lower", "anl_lower_chain", "anl_compile_check", "anl_benchmark", "anl_graph_create", "anl_graph_replay", "anl_graph_release",
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
-    "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum",
+    "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum", "anl_allgather",
     "anl_comm_destroy", "anl_comm_set_timeout", "anl_comm_wait", "anl_comm_abort", "anl_comm_inject_delay", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
     "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search",
 ]
@@ -196,8 +197,10 @@ class GradientTarget:
     """Where a gradient output goes and what happens right behind it: optional all-reduce across
     ranks, optional SGD update of its parameter (master f32 + storage copy)."""
 
-    def __init__(self, grad, master=None, param=None, lr: float = 0.0, scale: float = 1.0, allreduce: bool = False):
-        self.grad, self.master, self.param, self.lr, self.scale, self.allreduce = grad, master, param, lr, scale, allreduce
+    def __init__(self, grad, master=None, param=None, lr: float = 0.0, scale: float = 1.0, allreduce=False):
+        # allreduce: False/0 none, True/1 all-reduce then update everywhere, 2 reduce-scatter, update the
+        # rank's own shard, all-gather the new parameter values
+        self.grad, self.master, self.param, self.lr, self.scale, self.allreduce = grad, master, param, lr, scale, int(allreduce)
 
 
 class ResidentBuffer:
@@ -316,7 +319,7 @@ class Device:
         arr = (_Output * max(len(placed), 1))()
         for k, (idx, v) in enumerate(placed.items()):
             if isinstance(v, GradientTarget):
-                arr[k] = _Output(idx, None, v.grad.elems, v.grad.h, 1 if v.allreduce else 0,
+                arr[k] = _Output(idx, None, v.grad.elems, v.grad.h, int(v.allreduce),
                                  v.master.h if v.master is not None else None, v.param.h if v.param is not None else None,
                                  v.lr, v.scale)
             elif isinstance(v, ResidentBuffer):
@@ -414,6 +417,10 @@ class Device:
 
     def allreduce_sum(self, buf: ResidentBuffer):
         self._check(self.L.anl_allreduce_sum(self.h, buf.h))
+
+    def allgather(self, buf: ResidentBuffer):
+        """In place: every rank's 1/nranks shard of ``buf`` gathered into all ranks' copies."""
+        self._check(self.L.anl_allgather(self.h, buf.h))
 
     def comm_set_timeout(self, milliseconds: int):
         """Longest a collective may stay unfinished before the watchdog aborts the communicator."""

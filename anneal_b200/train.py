@@ -27,9 +27,10 @@ def _round_up(n: int, m: int = 128) -> int:
 class ResidentTrainer:
     def __init__(self, dev: Device, model, lr: float, world: int = 1, use_graph: bool = True,
                  materialize: bool = True, resident_inputs: bool = False, overlap: bool = True,
-                 force_allreduce: bool = False):
+                 force_allreduce: bool = False, shard_update: bool = True):
         self.dev, self.model, self.lr, self.world, self.use_graph = dev, model, float(lr), world, use_graph
         self.overlap = overlap
+        self.shard_update = shard_update
         prev = R.MATERIALIZE_CONTRACTION_OPERANDS
         R.MATERIALIZE_CONTRACTION_OPERANDS = materialize
         try:
@@ -73,7 +74,10 @@ class ResidentTrainer:
             self.inputs[p.t.node.idx] = pv
             self.placed[gid] = gv
             # overlapped mode: each gradient is all-reduced and applied right behind its kernel
-            self.fused[gid] = GradientTarget(gv, mv, pv, self.lr, self.grad_scale / world, allreduce=world > 1 or force_allreduce)
+            # across ranks: reduce-scatter the gradient, update this rank's shard of the parameter,
+            # all-gather the new values (shard_update), or all-reduce and update everything everywhere
+            mode = (2 if shard_update else 1) if (world > 1 or force_allreduce) else 0
+            self.fused[gid] = GradientTarget(gv, mv, pv, self.lr, self.grad_scale / world, allreduce=mode)
         self.loss_host = pinned_array(1)
         self.placed[self.loss_id] = self.loss_host
         self.resident_inputs = resident_inputs
@@ -150,7 +154,17 @@ class ResidentTrainer:
             self.store.upload(flat)
 
     def parameters(self) -> List[np.ndarray]:
-        """Master weights back on the host, one array per parameter (for checkpoints and tests)."""
+        """Master weights back on the host, one array per parameter (for checkpoints and tests).
+        With the update sharded across ranks each rank's f32 masters are current only in its own
+        shard of every parameter (the storage-dtype copies are complete): the shards are gathered
+        first. Every rank must make this call."""
+        if self.world > 1 and self.overlap and self.shard_update and self.store is not self.master:
+            for p, o in zip(self.params, self.offsets):
+                if p.value.size % self.world == 0:
+                    mv = self.master.view(o, p.value.size)
+                    self.dev.allgather(mv)
+                    self.dev.synchronize()
+                    mv.release()
         flat = self.master.download()
         return [flat[o:o + p.value.size].copy() for p, o in zip(self.params, self.offsets)]
 

@@ -73,9 +73,16 @@ typedef struct {
     float* data;
     int64_t elems;
     anl_buffer* resident;
-    int allreduce;   /* placed + resident only: sum this output over all ranks as soon as its kernel
+    int allreduce;   /* placed + resident only: 1 = sum this output over all ranks as soon as its kernel
                         has been queued, on the communication stream, overlapping the rest of the
-                        schedule; the run (or graph replay) completes after the reduction */
+                        schedule; the run (or graph replay) completes after the reduction.
+                        2 = with an update attached (sgd_master) and a length that divides by the rank
+                        count: reduce-scatter instead, each rank updates only its own 1/nranks of
+                        the parameter and the new parameter values are all-gathered — same bytes on
+                        the wire, 1/nranks of the update's memory traffic per GPU.  The f32 masters
+                        are then current only in each rank's shard (anl_allgather assembles them) and
+                        the gradient buffer holds the reduced sum only there.  Falls back to 1 when
+                        the length does not divide. */
     /* placed + resident only, optional: treat this output as the gradient of a parameter and apply
      * anl_sgd_step(sgd_master, sgd_param, this output, sgd_lr, sgd_scale) right behind it (after the
      * all-reduce when one is requested) on the same side stream, so the update of early-finished
@@ -200,6 +207,7 @@ int anl_sgd_step(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buf
 int anl_comm_unique_id(uint8_t id[128]);
 int anl_comm_init(anl_device* dev, int rank, int nranks, const uint8_t id[128]);
 int anl_allreduce_sum(anl_device* dev, anl_buffer* buf);     /* in place, on the comm stream, ordered after prior work */
+int anl_allgather(anl_device* dev, anl_buffer* buf);         /* in place: rank r contributes elements [r*n/R, (r+1)*n/R) */
 int anl_comm_destroy(anl_device* dev);
 /* Watchdog.  With a timeout set (milliseconds, 0 = none), anl_comm_wait — and anl_synchronize,
  * which calls it first — polls the communication stream instead of blocking on it, asks NCCL for
