@@ -578,8 +578,9 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
     // step time beside the backward pass as after it), then the new parameter values are
     // all-gathered.  The bytes on the wire equal an all-reduce's.  Otherwise: plain all-reduce and a
     // full update on every rank.
+    bool allow_shard = true;      // cleared around the tail split: its halves would shard at other boundaries
     auto sharded = [&](const anl_output& a, int64_t cnt) {
-        return a.allreduce == 2 && a.sgd_master && a.resident && comm_can_shard(dev) && cnt > 0 && cnt % dev->nranks == 0;
+        return allow_shard && a.allreduce == 2 && a.sgd_master && a.resident && comm_can_shard(dev) && cnt > 0 && cnt % dev->nranks == 0;
     };
     auto reduce_part = [&](const anl_output& a, int64_t off, int64_t cnt) -> int {
         char* g = (char*)a.resident->ptr + off * dt_storage_bytes(a.resident->dtype);
@@ -637,13 +638,17 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             const anl_output& a = ra->second;
             int64_t row_elems = 0, rows = gemm_window_rows(*plan, &row_elems);
             const int64_t cut = (rows / 2 + 255) / 256 * 256;
-                        for (int h = 0; h < 2; h++) {
+                        // both halves are all-reduced and updated in full on every rank: sharding each half would put
+            // a rank's shards at other offsets than anl_allgather assumes for the whole parameter
+            allow_shard = false;
+            for (int h = 0; h < 2; h++) {
                 const int64_t m0 = h ? cut : 0, m1 = h ? rows : cut;
                 if (int rc = launch_gemm(dev, *plan, ptrs.data(), item_sym(it, binds), stream, m0, m1)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
                 const int64_t off = m0 * row_elems, cnt = (m1 - m0) * row_elems;
                 if (int rc = reduce_part(a, off, cnt)) return rc;
                 if (int rc = update_part(a, off, cnt, h == 0 && !sgd_foreground)) return rc;
             }
+            allow_shard = true;
             continue;
         }
         if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
