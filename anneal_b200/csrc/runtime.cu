@@ -47,12 +47,49 @@ __global__ void cvt_f16_to_f32(const __half* __restrict__ in, float* __restrict_
 // (tensor/nn/nn.go:56-61) fused: one pass over master, grad and param.
 // Streaming accesses (evict-first): the 12 bytes per parameter this pass moves are not needed again
 // before the next step, while the contractions running beside it live on the operand tiles they
-// keep in L2.  Four parameters per thread and trip when the views are 16-byte aligned.
+// keep in L2.  Two groups of four parameters per thread and trip when the views are 16-byte aligned.
 template <class T> __device__ __forceinline__ float sgd_ld(const T* p) { return (float)__ldcs(p); }
 template <> __device__ __forceinline__ float sgd_ld<__half>(const __half* p) { return __half2float(__ldcs(p)); }
 
+// four gradients as f32 from one 8- or 16-byte streaming load
+template <class G> __device__ __forceinline__ void sgd_ld4(const G* grad, long long q, float g[4]);
+template <> __device__ __forceinline__ void sgd_ld4<__half>(const __half* grad, long long q, float g[4]) {
+    uint2 raw = __ldcs(reinterpret_cast<const uint2*>(grad) + q);
+    const __half2 lo = *reinterpret_cast<const __half2*>(&raw.x), hi = *reinterpret_cast<const __half2*>(&raw.y);
+    g[0] = __low2float(lo); g[1] = __high2float(lo); g[2] = __low2float(hi); g[3] = __high2float(hi);
+}
+template <> __device__ __forceinline__ void sgd_ld4<float>(const float* grad, long long q, float g[4]) {
+    float4 raw = __ldcs(reinterpret_cast<const float4*>(grad) + q);
+    g[0] = raw.x; g[1] = raw.y; g[2] = raw.z; g[3] = raw.w;
+}
+
+template <class P>
+__device__ __forceinline__ void sgd_apply4(float* master, P* param, long long q, float4 m, const float g[4],
+                                           float lr, float scale, bool separate, int bf16) {
+    float r[4] = {m.x, m.y, m.z, m.w};
+#pragma unroll
+    for (int j = 0; j < 4; j++) {
+        const float gs = g[j] * scale;
+        r[j] = r[j] - lr * gs;
+    }
+    __stcs(reinterpret_cast<float4*>(master) + q, make_float4(r[0], r[1], r[2], r[3]));
+    if (separate) {
+        if (sizeof(P) == 2) {
+            const __half2 lo = __floats2half2_rn(r[0], r[1]), hi = __floats2half2_rn(r[2], r[3]);
+            uint2 o; o.x = *reinterpret_cast<const unsigned*>(&lo); o.y = *reinterpret_cast<const unsigned*>(&hi);
+            __stcs(reinterpret_cast<uint2*>(param) + q, o);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) if (bf16) r[j] = __int_as_float(__float_as_int(r[j]) & 0xFFFF0000);
+            __stcs(reinterpret_cast<float4*>(param) + q, make_float4(r[0], r[1], r[2], r[3]));
+        }
+    }
+}
+
+// Two 4-element groups per thread and iteration, both groups' loads issued before either is used:
+// 48 bytes in flight per thread keep enough of HBM's latency covered at 2048 threads per SM.
 template <class G, class P>
-__global__ void sgd_kernel(float* __restrict__ master, P* __restrict__ param, const G* __restrict__ grad,
+__global__ void __launch_bounds__(256, 6) sgd_kernel(float* __restrict__ master, P* __restrict__ param, const G* __restrict__ grad,
                            float lr, float scale, long long n, int bf16, int vec) {
     const long long tid = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long stride = (long long)gridDim.x * blockDim.x;
@@ -60,35 +97,17 @@ __global__ void sgd_kernel(float* __restrict__ master, P* __restrict__ param, co
     long long done = 0;
     if (vec) {
         const long long n4 = n >> 2;
-        for (long long q = tid; q < n4; q += stride) {
-            float4 m = __ldcs(reinterpret_cast<const float4*>(master) + q);
-            float g[4];
-            if (sizeof(G) == 2) {
-                uint2 raw = __ldcs(reinterpret_cast<const uint2*>(grad) + q);
-                const __half2 lo = *reinterpret_cast<const __half2*>(&raw.x), hi = *reinterpret_cast<const __half2*>(&raw.y);
-                g[0] = __low2float(lo); g[1] = __high2float(lo); g[2] = __low2float(hi); g[3] = __high2float(hi);
-            } else {
-                float4 raw = __ldcs(reinterpret_cast<const float4*>(grad) + q);
-                g[0] = raw.x; g[1] = raw.y; g[2] = raw.z; g[3] = raw.w;
-            }
-            float r[4] = {m.x, m.y, m.z, m.w};
-#pragma unroll
-            for (int j = 0; j < 4; j++) {
-                const float gs = g[j] * scale;
-                r[j] = r[j] - lr * gs;
-            }
-            __stcs(reinterpret_cast<float4*>(master) + q, make_float4(r[0], r[1], r[2], r[3]));
-            if (separate) {
-                if (sizeof(P) == 2) {
-                    const __half2 lo = __floats2half2_rn(r[0], r[1]), hi = __floats2half2_rn(r[2], r[3]);
-                    uint2 o; o.x = *reinterpret_cast<const unsigned*>(&lo); o.y = *reinterpret_cast<const unsigned*>(&hi);
-                    __stcs(reinterpret_cast<uint2*>(param) + q, o);
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 4; j++) if (bf16) r[j] = __int_as_float(__float_as_int(r[j]) & 0xFFFF0000);
-                    __stcs(reinterpret_cast<float4*>(param) + q, make_float4(r[0], r[1], r[2], r[3]));
-                }
-            }
+#pragma unroll 1
+        for (long long q = tid; q < n4; q += 2 * stride) {
+            const long long q1 = q + stride;
+            const bool two = q1 < n4;
+            float g0[4], g1[4];
+            float4 m0 = __ldcs(reinterpret_cast<const float4*>(master) + q), m1 = m0;
+            if (two) m1 = __ldcs(reinterpret_cast<const float4*>(master) + q1);
+            sgd_ld4<G>(grad, q, g0);
+            if (two) sgd_ld4<G>(grad, q1, g1);
+            sgd_apply4<P>(master, param, q, m0, g0, lr, scale, separate, bf16);
+            if (two) sgd_apply4<P>(master, param, q1, m1, g1, lr, scale, separate, bf16);
         }
         done = n4 << 2;
     }

@@ -27,7 +27,7 @@ def _round_up(n: int, m: int = 128) -> int:
 class ResidentTrainer:
     def __init__(self, dev: Device, model, lr: float, world: int = 1, use_graph: bool = True,
                  materialize: bool = True, resident_inputs: bool = False, overlap: bool = True,
-                 force_allreduce: bool = False, shard_update: bool = True):
+                 force_allreduce: bool = False, shard_update: bool = False):
         self.dev, self.model, self.lr, self.world, self.use_graph = dev, model, float(lr), world, use_graph
         self.overlap = overlap
         self.shard_update = shard_update

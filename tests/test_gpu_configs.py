@@ -297,3 +297,52 @@ def test_checkpoint_resume_continues_the_same_trajectory(cuda, tmp_path):
     for x, y in zip(a.parameters(), c.parameters()):
         assert np.array_equal(x, y)
     assert a.loss() == c.loss()
+
+
+def test_c4_wide_mlp_full_size_step(cuda):
+    """The headline configuration at full size (batch 8192, 4 x 4096 wide, 1000 classes, f16
+    storage): one forward + backward through the tcgen05 contractions and the generated f16
+    kernels. The CPU oracle needs hours for 3.2 TFLOP of serial sums, so the check is against
+    float32 PyTorch on the same GPU, started from the same f16-rounded inputs and parameters.
+
+    PyTorch keeps every activation in f32 where this path stores them in f16 (about 5e-4 relative
+    per stored value, through five layers and back), so the bound is twice the 2e-3 that the
+    f16-storage comparisons against the oracle use; what it would miss at that size — a wrong tile,
+    a dropped k-block, an operand read with the wrong major-ness — shows as an error of order one.
+    Errors are relative to the largest magnitude of each gradient, as everywhere in these tests."""
+    import torch
+    from anneal_b200.realize import leaf_inputs
+    R.MATERIALIZE_CONTRACTION_OPERANDS = True
+    try:
+        m = W.WideMLP()
+        B, D, C = m.batch, m.width, m.classes
+        x, y = m.make_inputs()
+        g = m.graph(x, y)
+        items, out_ids = R.build_schedule(g.targets())
+        before = cuda.stats()["gemm_launched"]
+        got = cuda.run(items, leaf_inputs(g.targets()))
+        gemms = cuda.stats()["gemm_launched"] - before
+    finally:
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+    # 5 forward + 5 weight-gradient + 4 input-gradient contractions, all on the hand-written kernel
+    assert gemms == 14, gemms
+
+    t = lambda a, shape: torch.tensor(np.asarray(a, np.float32).reshape(shape)).half().float().cuda()
+    ps = [t(p.value, p.shape).requires_grad_() for p in m.params]
+    h = t(x, (B, D))
+    for l in range(m.depth):
+        h = torch.nn.functional.gelu(h @ ps[2 * l].T + ps[2 * l + 1], approximate="tanh")
+    logits = h @ ps[-2].T + ps[-1]
+    loss = -(t(y, (B, C)) * torch.log_softmax(logits, 1)).sum()
+    loss.backward()
+
+    mean_loss = float(got[out_ids[0]][0])
+    assert abs(mean_loss - loss.item() / B) <= 2e-3 * abs(loss.item() / B), (mean_loss, loss.item() / B)
+    for k, p in zip(out_ids[1:], ps):
+        v = got[k]
+        assert np.isfinite(v).all()
+        assert rel_err(v, p.grad.cpu().numpy().reshape(-1)) <= 4e-3, (tuple(p.shape), rel_err(v, p.grad.cpu().numpy().reshape(-1)))
+    # a size-independent property: the bias gradient of the head is the column sum of
+    # softmax - onehot, whose entries sum to zero over the classes (each row of both sums to one)
+    db_head = got[out_ids[-1]].astype(np.float64)
+    assert abs(db_head.sum()) <= 2e-3 * np.abs(db_head).sum()
