@@ -567,6 +567,52 @@ struct Gen {
         return "rc_" + std::to_string(id) + "[" + sweep_counter(sw) + "]";
     }
 
+
+    // Row-chain stages with chain_vec > 1: INDEX nodes below `root` (nested reductions excluded) that
+    // sweep `sweep` with unit stride and whose address is provably a multiple of chain_vec elements
+    // when the sweep variable is (16-byte aligned bases, every other term a multiple of chain_vec).
+    // Each gets one wide load per chunk into a small array; load_expr then hands out array[u].
+    // Returns the declarations + loads, written for a scope in which the sweep variable holds the
+    // chunk's first index.
+    std::string chain_wide_loads(int root, int sweep, int ctx) {
+        std::string code;
+        if (chain_vec <= 1 || row_cache || opts.debug_bounds) return code;
+        std::vector<int> stack{root}, seen_nodes;
+        std::set<int> seen;
+        while (!stack.empty()) {
+            int j = stack.back(); stack.pop_back();
+            if (!seen.insert(j).second) continue;
+            const Node& nd = N(j);
+            if (nd.op == OP_REDUCE && j != root) continue;
+            if (nd.op == OP_INDEX) { seen_nodes.push_back(j); continue; }
+            for (int c : nd.src) stack.push_back(c);
+        }
+        std::sort(seen_nodes.begin(), seen_nodes.end());
+        const std::string V = std::to_string(chain_vec);
+        for (int j : seen_nodes) {
+            const Node& nd = N(j);
+            if (N(nd.src[0]).op != OP_PARAM || !dep[j][range_slot[sweep]]) continue;
+            int p = (int)N(nd.src[0]).arg;
+            if (p <= 0 || p >= (int)it.bufs.size() || chain_subst.count(p)) continue;
+            Cls bc = dtype_cls(it.bufs[p].dtype);
+            if (bc != cls(j) || (bc != CF32 && bc != CF16) || dtype_cls(nd.dtype) == CBOOL) continue;
+            Lin f = flat_index(j);
+            if (!in_bounds(f, p) || f.c % chain_vec != 0) continue;
+            bool ok = true;
+            for (auto& t : f.t) {
+                const Atom& a = atoms[t.first];
+                if (a.kind != Atom::RANGE) { ok = false; break; }
+                if (a.node == sweep ? t.second != 1 : t.second % chain_vec != 0) { ok = false; break; }
+            }
+            bool cok; if (!ok || lin_coef(f, sweep, cok) != 1 || !cok) continue;
+            const std::string arr = "vl" + std::to_string(j) + "_" + std::to_string(ctx < 0 ? 0 : ctx), bt = buf_ctype(it.bufs[p].dtype);
+            code += "    " + bt + " " + arr + "[" + V + "];\n";
+            code += "    ldv_<" + bt + ", " + V + ">(" + dp + std::to_string(p) + " + " + render(f, ctx) + ", " + arr + ");\n";
+            vec_load[j] = arr;
+        }
+        return code;
+    }
+
     std::string load_expr(int i, int ctx) {
         if (vec_load.count(i)) return vec_load[i] + "[u]";
         const Node& nd = N(i);
@@ -642,7 +688,19 @@ struct Gen {
             if (!isf) pe = std::string("(") + at + ")__float_as_int(" + pe + ")";
             stmt(-1, "for (int p = 0; p < SPLIT; p++) " + acc + " = " + combine(rop, acc_c, acc, pe) + ";");
         } else {
+            // row-chain stage sweeping the row in chunks: the wide loads must be known before the body is rendered
+            bool chunked = false;
+            std::string wide;
+            std::vector<int> wide_nodes;
+            if (rr.size() == 1 && unroll_short_loops && chain_vec > 1 && !counted_sweep(rr[0]) && !N(rr[0]).symbolic() &&
+                N(rr[0]).arg <= (int64_t)lanes * 32 && N(rr[0]).arg % ((int64_t)lanes * chain_vec) == 0) {
+                chunked = true;
+                std::map<int, std::string> before = vec_load;
+                wide = chain_wide_loads(nd.src[0], rr[0], i);
+                for (auto& kv : vec_load) if (!before.count(kv.first)) wide_nodes.push_back(kv.first);
+            }
             std::string e = val(nd.src[0], i);
+            for (int j : wide_nodes) vec_load.erase(j);
             std::string ef = (isf && cls(nd.src[0]) == CF16) ? "__half2float(" + e + ")" : e;
             // emit: loop header, hoisted code is already in `top`, then the loop body
             std::string hdr;
@@ -658,12 +716,14 @@ struct Gen {
                     const std::string j = sweep_counter(rr[0]);
                     hdr = "_Pragma(\"unroll\") for (int " + j + " = 0; " + j + " < " + std::to_string(N(rr[0]).arg / lanes) + "; " + j + "++) { const int " + rn + " = lane + " + j + " * LANES;";
                 } else if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) {
-                    if (chain_vec > 1 && N(rr[0]).arg % chain_vec == 0) {
-                        // each lane takes chain_vec consecutive elements per trip: with 16-byte aligned bases the
-                        // compiler turns the unrolled scalar loads into one 128-bit access
+                    if (chunked) {
+                        // each lane takes chain_vec consecutive elements per trip; unit-stride operands
+                        // arrive by one explicit 128-bit load per chunk (the inner declaration of the
+                        // sweep variable shadows the chunk's first index the loads are written with)
                         std::string V = std::to_string(chain_vec), nb = range_bound(rr[0]);
-                        hdr = "_Pragma(\"unroll\") for (int " + rn + "b = lane * " + V + "; " + rn + "b < " + nb + "; " + rn + "b += LANES * " + V + ") "
-                              "_Pragma(\"unroll\") for (int " + rn + "v = 0; " + rn + "v < " + V + "; " + rn + "v++) { const int " + rn + " = " + rn + "b + " + rn + "v;";
+                        hdr = "_Pragma(\"unroll\") for (int " + rn + "b = lane * " + V + "; " + rn + "b < " + nb + "; " + rn + "b += LANES * " + V + ") {\n"
+                              "    const int " + rn + " = " + rn + "b; (void)" + rn + ";\n" + wide +
+                              "  _Pragma(\"unroll\") for (int u = 0; u < " + V + "; u++) { const int " + rn + " = " + rn + "b + u;";
                     } else hdr = "_Pragma(\"unroll\") " + hdr;
                 }
             } else {
@@ -685,7 +745,7 @@ struct Gen {
             }
             T().code += loop[i].code;
             T().code += "    " + acc + " = " + combine(rop, acc_c, acc, ef) + ";\n";
-            T().code += "  }\n";
+            T().code += chunked ? "  } }\n" : "  }\n";
             if (reduce_combine_mode == "group")
                 stmt(-1, acc + " = group_" + rop_tag(rop) + "_" + (isf ? "f" : "i") + "(" + acc + ", lane, grp, red_smem);");
             else if (reduce_combine_mode == "partial")
@@ -1236,7 +1296,10 @@ struct Gen {
         reset_emit();
         reduce_combine_mode = "group";
         unroll_short_loops = true;
-        chain_vec = 1;      // 4-element chunks per lane measured slower: nvcc keeps the loads scalar, and they lose coalescing
+        // 4-element chunks per lane with explicit 128-bit loads and stores; ANNEAL_CHAIN_VEC=1 keeps one
+        // element per lane and trip (scalar, lane-interleaved accesses)
+        static const int chain_vec_env = std::getenv("ANNEAL_CHAIN_VEC") ? std::atoi(std::getenv("ANNEAL_CHAIN_VEC")) : 4;
+        chain_vec = (chain_vec_env == 2 || chain_vec_env == 4) ? chain_vec_env : 1;
         dp = "s" + std::to_string(k) + "_data";
         std::ostringstream c;
         std::string bt = buf_ctype(it.bufs[0].dtype);
@@ -1247,13 +1310,23 @@ struct Gen {
         cur_top = &prelude;
         for (int r : reduces) { val(r, -1); if (!err.empty()) return false; }
         cur_top = nullptr;
+        // the last stage writes the row in chunks of chain_vec outputs per lane: wide loads of its
+        // unit-stride operands, one wide store
+        const Cls oc = dtype_cls(it.bufs[0].dtype);
+        const bool chunk_sweep = has_inner && chain_vec > 1 && inner <= (int64_t)threads * 32 && inner % ((int64_t)threads * chain_vec) == 0 &&
+                                 N(loop_ranges.back()).arg % chain_vec == 0 && (oc == CF32 || oc == CF16) && it.bufs[0].dtype != DT_BF16;
+        std::string wide;
+        if (chunk_sweep) wide = chain_wide_loads(body, loop_ranges.back(), -1);
         std::string v = val(body, -1);
         if (!err.empty()) return false;
         c << prelude.code;
         if (has_inner) {
-            if (inner <= (int64_t)threads * 32 && inner % chain_vec == 0 && chain_vec > 1) {
-                c << "  _Pragma(\"unroll\") for (int gb = threadIdx.x * " << chain_vec << "; gb < " << inner << "; gb += " << threads * chain_vec << ")\n";
-                c << "  _Pragma(\"unroll\") for (int gv = 0; gv < " << chain_vec << "; gv++) { const int gi = gb + gv;\n";
+            if (chunk_sweep) {
+                c << "  _Pragma(\"unroll\") for (int gb = threadIdx.x * " << chain_vec << "; gb < " << inner << "; gb += " << threads * chain_vec << ") {\n";
+                c << "    " << bt << " outv[" << chain_vec << "];\n";
+                // the loads are written with the chunk's first index; the per-element scope below shadows it
+                c << "    const int gi = gb; (void)gi;\n" << decompose("gi", 1, loop_ranges.size(), "    ") << wide;
+                c << "  _Pragma(\"unroll\") for (int u = 0; u < " << chain_vec << "; u++) { const int gi = gb + u;\n";
             } else if (loop_ranges.size() == 2 && counted_sweep(loop_ranges[1])) {
                 const std::string j = sweep_counter(loop_ranges[1]);
                 c << "  _Pragma(\"unroll\") for (int " << j << " = 0; " << j << " < " << inner / threads << "; " << j << "++) { const int gi = threadIdx.x + " << j << " * " << threads << ";\n";
@@ -1263,7 +1336,10 @@ struct Gen {
             }
             c << decompose("gi", 1, loop_ranges.size(), "    ");
             c << top.code;
-            c << "    " << dp << "0[(long long)row * " << inner << "LL + gi] = " << store_value(v, body) << ";\n";
+            if (chunk_sweep) {
+                c << "    outv[u] = " << store_value(v, body) << ";\n  }\n";
+                c << "    stv_<" << bt << ", " << chain_vec << ">(" << dp << "0 + ((long long)row * " << inner << "LL + gb), outv);\n";
+            } else c << "    " << dp << "0[(long long)row * " << inner << "LL + gi] = " << store_value(v, body) << ";\n";
             c << "  }\n";
         } else {
             c << top.code;

@@ -982,7 +982,7 @@ int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems) {
 // Pipelined upload, first half: the copy stream moves `elems` floats from (pinned) host memory
 // into the buffer's staging block and returns at once.  The buffer's contents are untouched, so
 // kernels already queued on the compute stream keep reading the previous batch meanwhile.
-int anl_buffer_upload_begin(anl_buffer* buf, const float* data, int64_t elems) {
+static int upload_begin_impl(anl_buffer* buf, const void* data, int64_t elems, bool stored) {
     if (!buf || !data || elems <= 0 || elems > buf->elems) return ANL_ERR_INVALID;
     anl_device* dev = buf->dev;
     cudaSetDevice(dev->ordinal);
@@ -995,13 +995,18 @@ int anl_buffer_upload_begin(anl_buffer* buf, const float* data, int64_t elems) {
         CK(dev, cudaEventRecord(buf->stage_free, dev->stream));
         buf->stage_free_recorded = true;
     }
+    // host elements are f32, or already in the buffer's storage format (2 bytes for f16, else 4)
+    const size_t esz = (stored && buf->dtype == DT_F16) ? 2 : 4;
     if (buf->stage_free_recorded) CK(dev, cudaStreamWaitEvent(dev->copy_stream, buf->stage_free, 0));
-    CK(dev, cudaMemcpyAsync(buf->stage, data, (size_t)elems * 4, cudaMemcpyHostToDevice, dev->copy_stream));
+    CK(dev, cudaMemcpyAsync(buf->stage, data, (size_t)elems * esz, cudaMemcpyHostToDevice, dev->copy_stream));
     CK(dev, cudaEventRecord(buf->stage_ready, dev->copy_stream));
     buf->staged_elems = elems;
-    dev->stats.h2d_bytes += (uint64_t)elems * 4;
+    buf->staged_stored = stored;
+    dev->stats.h2d_bytes += (uint64_t)elems * esz;
     return ANL_OK;
 }
+int anl_buffer_upload_begin(anl_buffer* buf, const float* data, int64_t elems) { return upload_begin_impl(buf, data, elems, false); }
+int anl_buffer_upload_begin_stored(anl_buffer* buf, const void* data, int64_t elems) { return upload_begin_impl(buf, data, elems, true); }
 // Second half: the compute stream waits for the staged copy and converts it into the buffer's
 // storage dtype, in stream order with the kernels around it.
 int anl_buffer_upload_commit(anl_buffer* buf) {
@@ -1011,7 +1016,10 @@ int anl_buffer_upload_commit(anl_buffer* buf) {
     cudaSetDevice(dev->ordinal);
     const int64_t n = buf->staged_elems;
     CK(dev, cudaStreamWaitEvent(dev->stream, buf->stage_ready, 0));
-    if (buf->dtype == DT_F16 || buf->dtype == DT_BF16) {
+    if (buf->staged_stored) {
+        // already in storage format: bytes move as they are (a bf16 slot must arrive with its low half clear)
+        CK(dev, cudaMemcpyAsync(buf->ptr, buf->stage, (size_t)n * (buf->dtype == DT_F16 ? 2 : 4), cudaMemcpyDeviceToDevice, dev->stream));
+    } else if (buf->dtype == DT_F16 || buf->dtype == DT_BF16) {
         unsigned g = grid_for(n, 256, dev->prop.multiProcessorCount);
         if (buf->dtype == DT_F16) cvt_f32_to_f16<<<g, 256, 0, dev->stream>>>((const float*)buf->stage, (__half*)buf->ptr, n);
         else cvt_f32_to_bf16slot<<<g, 256, 0, dev->stream>>>((const float*)buf->stage, (float*)buf->ptr, n);

@@ -62,6 +62,7 @@ struct anl_buffer {
     // the buffer's current contents
     void* stage = nullptr;
     int64_t staged_elems = 0;
+    bool staged_stored = false;   // the staged bytes are already in the buffer's storage format
     cudaEvent_t stage_ready = nullptr, stage_free = nullptr;
     bool stage_free_recorded = false;
 };

@@ -101,6 +101,7 @@ def load_library():
     L.anl_buffer_create.argtypes = [vp, i, C.c_int64, C.POINTER(vp)]
     L.anl_buffer_upload.argtypes = [vp, vp, C.c_int64]
     L.anl_buffer_upload_begin.argtypes = [vp, vp, C.c_int64]
+    L.anl_buffer_upload_begin_stored.argtypes = [vp, vp, C.c_int64]
     L.anl_buffer_upload_commit.argtypes = [vp]
     L.anl_buffer_download.argtypes = [vp, vp, C.c_int64]
     L.anl_buffer_release.argtypes = [vp]
@@ -137,7 +138,7 @@ def load_library():
 ABI_SYMBOLS = [
     "anl_open", "anl_close", "anl_device_info", "anl_last_error", "anl_get_stats", "anl_run", "anl_outputs_free",
     "anl_lower", "anl_lower_chain", "anl_compile_check", "anl_benchmark", "anl_graph_create", "anl_graph_replay", "anl_graph_release",
-    "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
+    "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_begin_stored", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum", "anl_allgather",
     "anl_comm_destroy", "anl_comm_set_timeout", "anl_comm_wait", "anl_comm_abort", "anl_comm_inject_delay", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
     "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search",
@@ -225,10 +226,18 @@ class ResidentBuffer:
         return self
 
     def upload_begin(self, data: np.ndarray):
-        """Start copying `data` (contiguous float32, ideally pinned) on the copy stream; the buffer keeps
-        its contents until `upload_commit`.  The array is held until then."""
-        if data.dtype != np.float32 or not data.flags["C_CONTIGUOUS"]:
-            raise ValueError("upload_begin: a contiguous float32 array is required (no hidden copy may outlive the call)")
+        """Start copying `data` (contiguous, ideally pinned) on the copy stream; the buffer keeps
+        its contents until `upload_commit`.  The array is held until then.  float32 data is
+        converted to the storage dtype at the commit; a float16 array is accepted for an f16 buffer
+        and moves as it is (half the bytes, no conversion pass)."""
+        if not data.flags["C_CONTIGUOUS"]:
+            raise ValueError("upload_begin: a contiguous array is required (no hidden copy may outlive the call)")
+        if data.dtype == np.float16 and self.dtype.code == 10:      # ANL_F16
+            self._staged = data
+            self.dev._check(self.dev.L.anl_buffer_upload_begin_stored(self.h, data.ctypes.data, data.size))
+            return self
+        if data.dtype != np.float32:
+            raise ValueError("upload_begin: float32 data, or float16 data for an f16 buffer, is required")
         self._staged = data
         self.dev._check(self.dev.L.anl_buffer_upload_begin(self.h, data.ctypes.data, data.size))
         return self
@@ -484,10 +493,14 @@ class Device:
             pass
 
 
-def pinned_array(n: int) -> np.ndarray:
-    """float32 array in page-locked host memory (lives until process exit)."""
+def pinned_array(n: int, dtype=np.float32) -> np.ndarray:
+    """float32 (or float16) array in page-locked host memory (lives until process exit)."""
     L = load_library()
     p = C.c_void_p()
-    if L.anl_host_alloc(n * 4, C.byref(p)):
+    dt = np.dtype(dtype)
+    if dt not in (np.dtype(np.float32), np.dtype(np.float16)):
+        raise ValueError("pinned_array: float32 or float16")
+    if L.anl_host_alloc(n * dt.itemsize, C.byref(p)):
         raise DeviceError("cuda: pinned host allocation failed")
-    return np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_float)), shape=(n,))
+    raw = np.ctypeslib.as_array(C.cast(p, C.POINTER(C.c_uint8)), shape=(n * dt.itemsize,))
+    return raw.view(dt)

@@ -95,8 +95,10 @@ class ResidentTrainer:
     def prefetch(self, x: np.ndarray, y: np.ndarray) -> None:
         """Resident-input mode: start moving the NEXT batch to the device on the copy stream while
         the steps already queued run; the following ``step`` picks it up. ``x`` and ``y`` are
-        contiguous float32 host arrays (pinned for a truly asynchronous copy) that stay untouched
-        until that step has been issued."""
+        contiguous host arrays (pinned for a truly asynchronous copy) that stay untouched until
+        that step has been issued: float32, or float16 when the inputs are stored as f16 (half the
+        bytes over PCIe and no conversion pass; rounding to f16 on the host is what the reference
+        does when a leaf is set, tensor/tensor.go:58-68)."""
         self.x_res.upload_begin(x)
         self.y_res.upload_begin(y)
         self._staged = True

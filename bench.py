@@ -286,8 +286,12 @@ def run_ours(args):
     tr2 = ResidentTrainer(dev, model, model.lr, world=world, use_graph=not args.no_graph, resident_inputs=True,
                           overlap=not args.no_overlap, shard_update=args.shard_update)
     host = []
+    # batches wait in the loader in the stored format: f16 rows (rounded on the host once, as the
+    # reference rounds a leaf when it is set) unless --e2e-f32-host asks for float32 rows, which the
+    # device then converts
+    hdt = np.float32 if args.e2e_f32_host else np.float16
     for _ in range(2):
-        xh, yh = pinned_array(x.size), pinned_array(y.size)
+        xh, yh = pinned_array(x.size, hdt), pinned_array(y.size, hdt)
         xh[:] = x
         yh[:] = y
         host.append((xh, yh))
@@ -317,7 +321,7 @@ def run_ours(args):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms2 = float(t[0])
     e2e = {"value": CFG["batch"] * world * args.steps / (ms2 / 1e3), "unit": UNIT,
-           "h2d_bytes_per_step": int((x.size + y.size) * 4), "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps,
+           "h2d_bytes_per_step": int((x.size + y.size) * np.dtype(hdt).itemsize), "host_batch_dtype": np.dtype(hdt).name, "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps,
            "how": "batch i+1 copied from pinned host memory on a copy stream while step i runs; loss read back every step",
            "host_cpus_bound": len(numa_cpus) if numa_cpus else None,
            "loss": e2e_loss}
@@ -450,6 +454,7 @@ def main():
     ap.add_argument("--shard-update", action="store_true", help="N>1: reduce-scatter, update this rank's shard, all-gather, instead of all-reducing and updating everything on every rank (measured slower on 8 GPUs: 3.82 against 3.64 ms per step)")
     ap.add_argument("--dyn-batches", default="1,17,256,4096,65536", help="dynmlp: batch sizes bound in turn; the last one is reported")
     ap.add_argument("--materialize", type=int, default=-1, help="mlp/cnn: 1/0 forces contraction operands to be buffers or expressions")
+    ap.add_argument("--e2e-f32-host", action="store_true", help="e2e: host batches as float32 rows (converted on the device) instead of rows already rounded to the f16 storage format")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="all-reduce the whole gradient bucket after the backward pass")

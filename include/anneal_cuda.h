@@ -188,6 +188,12 @@ int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems);
  * should be pinned (anl_host_alloc) and must stay unchanged until the commit has executed. */
 int anl_buffer_upload_begin(anl_buffer* buf, const float* data, int64_t elems);
 int anl_buffer_upload_commit(anl_buffer* buf);
+/* The same first half for host data that is already in the buffer's storage format: IEEE half
+ * bit patterns (2 bytes each) for an f16 buffer, 4-byte slots otherwise (a bf16 slot with its low
+ * 16 bits clear).  The reference quantises a leaf on the host when it is set (tensor/tensor.go:58-68)
+ * and again on upload (backend/webgpu/executor.go:166-175); a loader that keeps its batches in the
+ * stored format moves half the bytes for f16 and needs no conversion pass on the device. */
+int anl_buffer_upload_begin_stored(anl_buffer* buf, const void* data, int64_t elems);
 void anl_buffer_release(anl_buffer* buf);
 /* A window [offset, offset+elems) of `parent` as a buffer of its own (same dtype, no copy).  Used
  * to lay all parameters, or all gradients, out in one contiguous bucket so that one all-reduce and

@@ -175,3 +175,23 @@ def test_contraction_is_reported_with_symbolic_extents():
         R.MATERIALIZE_CONTRACTION_OPERANDS = False
     assert any("contraction f32 M=n N=128 K=64" in n for n in notes)
     assert any("contraction f32 M=128 N=64 K=n" in n for n in notes)
+
+
+def test_row_chain_sweeps_wide_rows_in_chunks():
+    """A softmax forward+backward whose rows are a multiple of 4 x 512 elements is rendered with one
+    128-bit load per operand and chunk and a 128-bit store; narrower rows keep the one-element
+    form. Both compile for sm_100a."""
+    R.reset()
+    s = W.SoftmaxFwdBwd(8, 4096)
+    ts, _ = s.graph()
+    items, _ = R.build_schedule(ts)
+    wide = device.lower_chain(items, 0, len(items))["source"]
+    assert wide.count("ldv_<float, 4>") >= 7 and "stv_<float, 4>" in wide
+    device.compile_check(wide)
+    R.reset()
+    s = W.SoftmaxFwdBwd(8, 320)
+    ts, _ = s.graph()
+    items, _ = R.build_schedule(ts)
+    narrow = device.lower_chain(items, 0, len(items))["source"]
+    assert "ldv_<float, 4>(" not in narrow.split("row_chain(")[1]
+    device.compile_check(narrow)

@@ -185,6 +185,24 @@ def test_row_chain_fuses_softmax_fwd_bwd_into_one_kernel(cuda, oracle):
     assert rel_err(got, ref) < 1e-5
 
 
+@pytest.mark.parametrize("rows,cols", [(160, 2048), (128, 4096)])
+def test_row_chain_chunked_rows_match_oracle(cuda, oracle, rows, cols):
+    """Rows that are a multiple of 4 x 512 elements are swept in 4-element chunks per lane with
+    128-bit loads and stores (the form the 8192-wide configuration runs in); the result must stay
+    within the reduction tolerance of the oracle's serial sums."""
+    s = W.SoftmaxFwdBwd(rows, cols)
+    ts, _ = s.graph()
+    items, out_ids, inputs = schedule(ts)
+    from anneal_b200 import device
+    assert "ldv_<float, 4>" in device.lower_chain(items, 0, len(items))["source"]
+    before = cuda.stats()["kernels_launched"]
+    got = cuda.run(items, inputs)[out_ids[0]]
+    assert cuda.stats()["kernels_launched"] - before == 1
+    want = oracle.run(items, inputs)[out_ids[0]]
+    assert rel_err(got, want) < 1e-4
+    assert rel_err(got, s.reference_dx().reshape(-1)) < 1e-4
+
+
 def test_pipelined_upload_begin_commit(cuda):
     """upload_begin leaves the buffer untouched; upload_commit installs the staged batch in the
     buffer's storage dtype; a second round reuses the staging block."""
@@ -207,6 +225,36 @@ def test_pipelined_upload_begin_commit(cuda):
         with pytest.raises(Exception):
             buf.upload_commit()          # nothing staged
         buf.release()
+
+
+def test_pipelined_upload_of_rows_already_in_f16(cuda):
+    """A float16 host array staged into an f16 buffer arrives bit for bit (no conversion pass, half
+    the bytes); staging float32 rows afterwards through the same block still converts them; a
+    float16 array offered to an f32 buffer is refused on the host."""
+    from anneal_b200.device import pinned_array
+    rng = np.random.default_rng(6)
+    buf = cuda.buffer(dtypes.float16, 4096)
+    buf.upload(np.zeros(4096, np.float32))
+    h16 = pinned_array(4096, np.float16)
+    h16[:] = rng.standard_normal(4096).astype(np.float16)
+    h16[:4] = [np.float16(6.1e-5), np.float16(-5.96e-8), np.float16(65504.0), np.float16(-0.0)]   # subnormal, smallest, largest, -0
+    moved = cuda.stats()["h2d_bytes"]
+    buf.upload_begin(h16)
+    cuda.synchronize()
+    assert not buf.download().any()                      # still the old contents
+    buf.upload_commit()
+    assert cuda.stats()["h2d_bytes"] - moved == 4096 * 2
+    got = buf.download()
+    assert np.array_equal(got.view(np.uint32), h16.astype(np.float32).view(np.uint32))
+    h32 = pinned_array(4096)
+    h32[:] = rng.standard_normal(4096).astype(np.float32)
+    buf.upload_begin(h32).upload_commit()
+    assert np.array_equal(buf.download(), h32.astype(np.float16).astype(np.float32))
+    buf.release()
+    f32 = cuda.buffer(dtypes.float32, 16)
+    with pytest.raises(ValueError):
+        f32.upload_begin(np.zeros(16, np.float16))
+    f32.release()
 
 
 def test_prefetched_batches_train_like_loaded_batches(cuda):
