@@ -402,7 +402,11 @@ def run_other(args):
         out.update(metric="softmax_fwd_bwd_hbm_gbs", unit="GB/s", value=gbs, ms_per_step=ms / args.steps, dtype="f32",
                    config={"workload": "softmax_fwd_bwd_8192x8192", "kernels_per_step": len(items), "algorithmic_bytes": algo},
                    roofline={"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
-                             "traffic": None, "peak_kind": kind + " copy", "note": "whole schedule, not one kernel"})
+                             # DRAM bytes of one launch from the ncu capture summarised in
+                             # profiles/row_chain_softmax_8192.md (rate x duration); not measured in this run
+                             "traffic": 775.7e6, "traffic_of": "one row_chain launch under ncu (algorithmic 805.3 MB)",
+                             "peak_kind": kind + " copy", "kernel": "row_chain",
+                             "note": "the whole schedule is this one launch; timed over graph replays"})
     elif args.workload == "dynmlp":
         m = W.DynMLP()
         res = {}
