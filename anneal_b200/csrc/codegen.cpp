@@ -1603,7 +1603,13 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
     // latency hiding across its barrier phases (measured 0.245 ms against 0.187 ms on 8192x8192).
     static const bool cache_rows = std::getenv("ANNEAL_CHAIN_ROW_CACHE") && std::atoi(std::getenv("ANNEAL_CHAIN_ROW_CACHE")) != 0;
     int64_t rows = -1;
-    sig << "extern \"C\" __global__ void __launch_bounds__(" << threads << ") row_chain(";
+    // ask for full occupancy (2048 threads per SM): without the second bound the run-time compiler took 36
+    // registers for the 8192-wide softmax chain and one of four resident blocks was lost (0.1665 ms
+    // against 0.1604 with the bound); ANNEAL_CHAIN_FULL_OCCUPANCY=0 drops the bound
+    static const int full_occ = std::getenv("ANNEAL_CHAIN_FULL_OCCUPANCY") ? std::atoi(std::getenv("ANNEAL_CHAIN_FULL_OCCUPANCY")) : 1;
+    sig << "extern \"C\" __global__ void __launch_bounds__(" << threads;
+    if (full_occ && threads <= 1024 && 2048 % threads == 0) sig << ", " << 2048 / threads;
+    sig << ") row_chain(";
     bool first_arg = true;
     std::string decls;
     for (size_t s = 0; s < items.size(); s++) {

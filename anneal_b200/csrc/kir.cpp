@@ -21,6 +21,60 @@ struct Reader {
     }
     bool skip(size_t n) { if (p + n > end) { ok = false; return false; } p += n; return true; }
 };
+
+// Structural checks on one parsed item, so that the code generator and the runtime can index
+// `bufs`, `src` and shapes without re-checking: known opcodes with at least the sources they
+// need, PARAM numbers inside the buffer table, INDEX rooted at a PARAM, extents and shapes that are
+// non-negative and small enough that no product of them overflows 63 bits.
+bool validate_item(const Item& it, std::string& err) {
+    const int64_t kMaxExtent = (int64_t)1 << 40;
+    for (const BufDesc& b : it.bufs) {
+        if (b.dtype < DT_BOOL || b.dtype > DT_INDEX) { err = "kir: unknown buffer dtype"; return false; }
+        if (b.size < 0 || b.size > kMaxExtent) { err = "kir: buffer size out of range"; return false; }
+        int64_t prod = 1; int zeros = 0;
+        for (int64_t d : b.shape) {
+            if (d < 0 || d > kMaxExtent) { err = "kir: buffer shape out of range"; return false; }
+            if (d == 0) { zeros++; continue; }
+            if (prod > kMaxExtent / d) { err = "kir: buffer has more than 2^40 elements"; return false; }
+            prod *= d;
+        }
+        if (zeros > 1) { err = "kir: more than one symbolic dimension in a buffer"; return false; }
+    }
+    for (size_t i = 0; i < it.nodes.size(); i++) {
+        const Node& nd = it.nodes[i];
+        size_t need = 0;
+        switch (nd.op) {
+            case OP_PARAM:
+                if (nd.arg < 0 || nd.arg >= (int64_t)it.bufs.size()) { err = "kir: PARAM number outside the buffer table"; return false; }
+                break;
+            case OP_CONST: break;
+            case OP_RANGE:
+                if (nd.arg < 0 || nd.arg > kMaxExtent) { err = "kir: RANGE extent out of range"; return false; }
+                if (!nd.symbolic() && nd.arg == 0) { err = "kir: empty RANGE"; return false; }
+                break;
+            case OP_INDEX:
+                need = 1;
+                if (!nd.src.empty() && it.nodes[nd.src[0]].op != OP_PARAM) { err = "kir: INDEX of a non-parameter"; return false; }
+                if (nd.src.size() > 9) { err = "kir: INDEX with more than 8 coordinates"; return false; }
+                break;
+            case OP_CAST: case OP_BITCAST: case OP_EXP2: case OP_LOG2: case OP_SIN: case OP_SQRT: case OP_RECIP:
+            case OP_NEG: case OP_TRUNC: case OP_SINK: case OP_END: case OP_REDUCE:
+                need = 1; break;
+            case OP_ADD: case OP_MUL: case OP_SHL: case OP_SHR: case OP_IDIV: case OP_MAX: case OP_MOD: case OP_CMPLT:
+            case OP_CMPNE: case OP_CMPEQ: case OP_XOR: case OP_OR: case OP_AND: case OP_SUB: case OP_FDIV: case OP_POW:
+            case OP_STORE:
+                need = 2; break;
+            case OP_WHERE: case OP_MULACC:
+                need = 3; break;
+            default:
+                err = "kir: unknown opcode " + std::to_string(nd.op); return false;
+        }
+        if (nd.src.size() < need) { err = "kir: node with too few sources"; return false; }
+        if (nd.dtype < DT_VOID || nd.dtype > DT_INDEX) { err = "kir: unknown node dtype"; return false; }
+    }
+    if (!it.nodes.empty() && it.nodes.back().op != OP_SINK) { err = "kir: last node is not the SINK"; return false; }
+    return true;
+}
 }  // namespace
 
 bool parse_kir(const uint8_t* blob, size_t len, std::vector<Item>& out, std::string& err) {
@@ -57,6 +111,8 @@ bool parse_kir(const uint8_t* blob, size_t len, std::vector<Item>& out, std::str
                 nd.src[s] = (int)v;
             }
         }
+        // every buffer record takes at least 20 bytes, every name at least 2
+        if ((size_t)(r.end - r.p) / 20 < n_bufs || (size_t)(r.end - r.p) / 2 < n_sym) { r.ok = false; break; }
         it.bufs.resize(n_bufs);
         for (uint32_t b = 0; b < n_bufs && r.ok; b++) {
             BufDesc& bd = it.bufs[b];
@@ -80,6 +136,7 @@ bool parse_kir(const uint8_t* blob, size_t len, std::vector<Item>& out, std::str
             r.ok = false;
         }
         if (!r.ok) break;
+        if (!validate_item(it, err)) { out.clear(); return false; }
         it.hash = fnv1a(item_begin, (size_t)(r.p - item_begin));
         out.push_back(std::move(it));
     }

@@ -12,6 +12,7 @@
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
+#include <new>
 #include <set>
 #include <unordered_set>
 
@@ -755,6 +756,19 @@ struct anl_graph {
     std::vector<std::pair<uint32_t, anl_buffer*>> resident_in, resident_out;
 };
 
+// ── exception fence ──────────────────────────────────────────────────────────────────────────
+// The entry points that parse, generate code or build tables use the C++ library freely; nothing it
+// throws (bad_alloc above all) may cross the C boundary, where the caller is Go or ctypes.
+namespace {
+template <class F> int fenced(anl_device* dev, const char* what, F&& f) noexcept {
+    try { return f(); }
+    catch (const std::bad_alloc&) { std::string m = std::string("cuda: ") + what + ": out of host memory"; return dev ? dev->fail(ANL_ERR_LIMIT, m) : ANL_ERR_LIMIT; }
+    catch (const std::exception& e) { std::string m = std::string("cuda: ") + what + ": " + e.what(); return dev ? dev->fail(ANL_ERR_INVALID, m) : ANL_ERR_INVALID; }
+    catch (...) { return dev ? dev->fail(ANL_ERR_INVALID, std::string("cuda: ") + what + ": unknown failure") : ANL_ERR_INVALID; }
+}
+}  // namespace
+
+
 extern "C" {
 
 int anl_open(int ordinal, unsigned flags, anl_device** out) {
@@ -823,7 +837,7 @@ int anl_synchronize(anl_device* dev) {
     return ANL_OK;
 }
 
-int anl_run(anl_device* dev, const uint8_t* blob, size_t blob_len, const anl_input* inputs, int n_inputs,
+static int run_impl(anl_device* dev, const uint8_t* blob, size_t blob_len, const anl_input* inputs, int n_inputs,
             const anl_binding* binds, int n_binds, const anl_output* placed, int n_placed, anl_output* outs, int* n_outs) {
     if (!dev || !n_outs) return ANL_ERR_INVALID;
     cudaSetDevice(dev->ordinal);
@@ -851,7 +865,7 @@ void anl_outputs_free(anl_output* outs, int n_outs) {
     }
 }
 
-int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o,
+static int lower_impl(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o,
               char* src, size_t src_cap, size_t* src_len, int* klass, int* block, int64_t* opb, char* note, size_t note_cap) {
     std::vector<Item> items; std::string err;
     if (!parse_kir(blob, blob_len, items, err)) { if (dev) dev->err = err; return ANL_ERR_INVALID; }
@@ -879,7 +893,7 @@ int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, 
     return ANL_OK;
 }
 
-int anl_lower_chain(const uint8_t* blob, size_t blob_len, int first, int count, char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap) {
+static int lower_chain_impl(const uint8_t* blob, size_t blob_len, int first, int count, char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap) {
     std::vector<Item> items; std::string err;
     if (!parse_kir(blob, blob_len, items, err) || first < 0 || count < 2 || first + count > (int)items.size()) {
         if (note && note_cap) std::snprintf(note, note_cap, "%s", err.empty() ? "chain: bad item range" : err.c_str());
@@ -913,7 +927,7 @@ int anl_compile_check(const char* src, char* log, size_t log_cap) {
 // Benchmarker.Benchmark (backend/webgpu/benchmark.go:18-208): the reference times submit+wait with
 // the host clock and reports min/median/max/mean/stddev/CV; here each iteration is bracketed by CUDA
 // events on the launching stream.  Inputs are zero-filled device buffers, as the reference's are.
-int anl_benchmark(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o, int warmup, int iterations, anl_bench_result* out) {
+static int benchmark_impl(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o, int warmup, int iterations, anl_bench_result* out) {
     if (!dev || !out || iterations <= 0) return ANL_ERR_INVALID;
     cudaSetDevice(dev->ordinal);
     std::vector<Item> items; std::string perr;
@@ -1104,7 +1118,7 @@ int anl_host_alloc(size_t bytes, void** out) { return cudaMallocHost(out, bytes 
 void anl_host_free(void* p) { if (p) cudaFreeHost(p); }
 
 // ── JIT replay through a CUDA graph ──────────────────────────────────────────────────────────
-int anl_graph_create(anl_device* dev, const uint8_t* blob, size_t blob_len, anl_graph** out) {
+static int graph_create_impl(anl_device* dev, const uint8_t* blob, size_t blob_len, anl_graph** out) {
     if (!dev || !out) return ANL_ERR_INVALID;
     auto* g = new anl_graph();
     g->dev = dev;
@@ -1122,7 +1136,7 @@ static void graph_drop(anl_graph* g) {
     g->built = false;
 }
 
-int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs, const anl_binding* binds, int n_binds,
+static int graph_replay_impl(anl_graph* g, const anl_input* inputs, int n_inputs, const anl_binding* binds, int n_binds,
                      const anl_output* placed, int n_placed, anl_output* outs, int* n_outs) {
     if (!g || !n_outs) return ANL_ERR_INVALID;
     anl_device* dev = g->dev;
@@ -1191,6 +1205,28 @@ void anl_graph_release(anl_graph* g) {
     cudaStreamSynchronize(g->dev->stream);
     graph_drop(g);
     delete g;
+}
+
+int anl_run(anl_device* dev, const uint8_t* blob, size_t blob_len, const anl_input* inputs, int n_inputs,
+            const anl_binding* binds, int n_binds, const anl_output* placed, int n_placed, anl_output* outs, int* n_outs) {
+    return fenced(dev, "run", [&] { return run_impl(dev, blob, blob_len, inputs, n_inputs, binds, n_binds, placed, n_placed, outs, n_outs); });
+}
+int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o,
+              char* src, size_t src_cap, size_t* src_len, int* klass, int* block, int64_t* opb, char* note, size_t note_cap) {
+    return fenced(dev, "lower", [&] { return lower_impl(dev, blob, blob_len, index, o, src, src_cap, src_len, klass, block, opb, note, note_cap); });
+}
+int anl_lower_chain(const uint8_t* blob, size_t blob_len, int first, int count, char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap) {
+    return fenced(nullptr, "lower_chain", [&] { return lower_chain_impl(blob, blob_len, first, count, src, src_cap, src_len, note, note_cap); });
+}
+int anl_benchmark(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o, int warmup, int iterations, anl_bench_result* out) {
+    return fenced(dev, "benchmark", [&] { return benchmark_impl(dev, blob, blob_len, index, o, warmup, iterations, out); });
+}
+int anl_graph_create(anl_device* dev, const uint8_t* blob, size_t blob_len, anl_graph** out) {
+    return fenced(dev, "graph_create", [&] { return graph_create_impl(dev, blob, blob_len, out); });
+}
+int anl_graph_replay(anl_graph* g, const anl_input* inputs, int n_inputs, const anl_binding* binds, int n_binds,
+                     const anl_output* placed, int n_placed, anl_output* outs, int* n_outs) {
+    return fenced(nullptr, "graph_replay", [&] { return graph_replay_impl(g, inputs, n_inputs, binds, n_binds, placed, n_placed, outs, n_outs); });
 }
 
 }  // extern "C"

@@ -195,3 +195,17 @@ def test_row_chain_sweeps_wide_rows_in_chunks():
     narrow = device.lower_chain(items, 0, len(items))["source"]
     assert "ldv_<float, 4>(" not in narrow.split("row_chain(")[1]
     device.compile_check(narrow)
+
+
+def test_damaged_blobs_never_crash_the_library():
+    """Truncated and bit-damaged schedules must come back as a status from `anl_lower` and
+    `anl_lower_chain` (parser + code generator), never as a crash: the helper runs in a child
+    process so that a segmentation fault shows up as its exit code."""
+    import os
+    import subprocess
+    import sys
+    helper = os.path.join(os.path.dirname(os.path.abspath(__file__)), "kir_fuzz.py")
+    for seed in (1, 2):
+        r = subprocess.run([sys.executable, helper, str(seed), "4000"], capture_output=True, text=True, timeout=300)
+        assert r.returncode == 0, (seed, r.returncode, r.stderr[-400:])
+        assert "rejected=" in r.stdout
