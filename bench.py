@@ -407,6 +407,28 @@ def run_other(args):
                              "traffic": 775.7e6, "traffic_of": "one row_chain launch under ncu (algorithmic 805.3 MB)",
                              "peak_kind": kind + " copy", "kernel": "row_chain",
                              "note": "the whole schedule is this one launch; timed over graph replays"})
+    elif args.workload == "sgd":
+        # the fused SGD + re-quantise pass alone, over the wide MLP's parameter count: f32 masters and
+        # f16 gradients read, f32 masters and f16 parameters written (12 bytes per parameter)
+        n = 71_200_000 // 128 * 128
+        mb, pb, gb = dev.buffer(dtypes.float32, n), dev.buffer(dtypes.float16, n), dev.buffer(dtypes.float16, n)
+        zeros = np.zeros(n, np.float32)
+        for b in (mb, pb, gb):
+            b.upload(zeros)
+        for _ in range(args.warmup):
+            dev.sgd_step(mb, pb, gb, 1e-3, 1.0)
+        dev.synchronize()
+        dev.timer_start()
+        for _ in range(args.steps):
+            dev.sgd_step(mb, pb, gb, 1e-3, 1.0)
+        ms = dev.timer_stop()
+        algo = n * 12
+        pk, kind = peaks()
+        gbs = algo * args.steps / (ms / 1e3) / 1e9
+        out.update(metric="sgd_update_hbm_gbs", unit="GB/s", value=gbs, ms_per_step=ms / args.steps, dtype="f32",
+                   config={"workload": "sgd_update_71.2M_params", "algorithmic_bytes": algo, "l2": "854 MB per pass exceeds the 126 MB L2"},
+                   roofline={"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
+                             "traffic": None, "peak_kind": kind + " copy", "kernel": "sgd_kernel"})
     elif args.workload == "dynmlp":
         m = W.DynMLP()
         res = {}
@@ -453,7 +475,7 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="wide_mlp", choices=["wide_mlp", "mlp", "cnn", "softmax", "dynmlp"],
+    ap.add_argument("--workload", default="wide_mlp", choices=["wide_mlp", "mlp", "cnn", "softmax", "dynmlp", "sgd"],
                     help="wide_mlp is the headline configuration; the others print a one-GPU line for the remaining configurations")
     ap.add_argument("--shard-update", action="store_true", help="N>1: reduce-scatter, update this rank's shard, all-gather, instead of all-reducing and updating everything on every rank (measured slower on 8 GPUs: 3.82 against 3.64 ms per step)")
     ap.add_argument("--dyn-batches", default="1,17,256,4096,65536", help="dynmlp: batch sizes bound in turn; the last one is reported")
