@@ -49,6 +49,18 @@ cases = {
     "f16_to_f32_bits": {"ref": "uop/dtype_conversion_test.go:65-99", "cases": [
         [0x0000, 0x00000000], [0x8000, 0x80000000], [0x3C00, 0x3F800000], [0xBC00, 0xBF800000], [0x7BFF, 0x477FE000],
         [0x0400, 0x38800000], [0x0001, 0x33800000], [0x7C00, 0x7F800000], [0xFC00, 0xFF800000]]},
+    # the backend's own copy of the conversion (backend/webgpu/executor.go), tested with its own table
+    "backend_f32_to_f16_bits": {"ref": "backend/webgpu/conversion_test.go:8-51", "cases": [
+        [0x00000000, 0x0000], [0x80000000, 0x8000], [0x3F800000, 0x3C00], [0xBF800000, 0xBC00], [0x477FE000, 0x7BFF],
+        [0x38800000, 0x0400], [0x3F801000, 0x3C00], [0x3F802000, 0x3C01], [0x3F803000, 0x3C02], [0x3F805000, 0x3C02],
+        [0x33800000, 0x0001], [0x33000000, 0x0000], [0x477FF000, 0x7C00], [0x501502F9, 0x7C00],
+        [0x7F800000, 0x7C00], [0x7FC00000, 0x7E00], [0x7F800001, 0x7C01]]},
+    "backend_f16_to_f32_bits": {"ref": "backend/webgpu/conversion_test.go:53-77", "cases": [[0x3C00, 0x3F800000], [0x0001, 0x33800000]]},
+    "backend_bulk_f16": {"ref": "backend/webgpu/conversion_test.go:79-99", "x": [0.0, 1.0, 2.0, 65504.0],
+                         "bytes": [0x00, 0x00, 0x00, 0x3C, 0x00, 0x40, 0xFF, 0x7B]},
+    # one compiled symbolic kernel out[i] = a[i] + b[i] dispatched at n = 8 and n = 128
+    "symbolic_add": {"ref": "backend/webgpu/symbolic_test.go:27-152", "tol": 1e-5,
+                     "runs": [{"n": 8, "a_scale": 1.0, "b_scale": 2.0}, {"n": 128, "a_scale": 0.5, "b_scale": 1.5}]},
     "beam_test_inputs": {"ref": "codegen/beam.go:410-420", "formula": "((j + i*17) % 13 + 1) * 0.01"},
 }
 

@@ -55,11 +55,11 @@ def test_bf16_add_matches_truncation_model():
 
 
 def test_f32_to_f16_known_answers_on_upload():
-    """The 36 f32 -> f16 bit patterns of the reference's conversion test (uop/dtype.go:392-441),
-    through the device's own conversion: values travel as f32, are rounded to f16 storage on
+    """The f32 -> f16 bit patterns of the reference's two conversion tests (the uop package's and the
+    backend's own copy, backend/webgpu/conversion_test.go:8-51), through the device's own conversion: values travel as f32, are rounded to f16 storage on
     upload, and come back widened. NaN inputs must stay NaN; everything else is compared bit for
     bit against the expected f16 pattern widened to f32."""
-    cases = GOLD["f32_to_f16_bits"]["cases"]
+    cases = GOLD["f32_to_f16_bits"]["cases"] + GOLD["backend_f32_to_f16_bits"]["cases"]
     src = np.array([c[0] for c in cases], dtype=np.uint32).view(np.float32)
     want = np.array([c[1] for c in cases], dtype=np.uint16).view(np.float16).astype(np.float32)
     # set_data would quantise on the host first; hand the raw f32 values to the device instead
@@ -71,6 +71,27 @@ def test_f32_to_f16_known_answers_on_upload():
     nan = np.isnan(want)
     assert np.isnan(y.data[nan]).all()
     assert np.array_equal(y.data[~nan].view(np.uint32), want[~nan].view(np.uint32))
+
+
+def test_bulk_f16_values_survive_the_round_trip(cuda):
+    """backend/webgpu/conversion_test.go:79-99: 0, 1, 2 and 65504 are exact in f16; stored in an
+    f16 buffer and read back they are unchanged."""
+    x = np.asarray(GOLD["backend_bulk_f16"]["x"], np.float32)
+    buf = cuda.buffer(dtypes.float16, x.size)
+    buf.upload(x)
+    assert np.array_equal(buf.download(), x)
+    buf.release()
+
+
+def test_symbolic_add_compiles_once_for_both_extents(cuda):
+    """backend/webgpu/symbolic_test.go:27-152: one symbolic kernel, dispatched at n = 8 and at
+    n = 128 with the reference's inputs; exact results, and the second extent compiles nothing."""
+    runs = GOLD["symbolic_add"]["runs"]
+    G.symbolic_add_run(runs[0])
+    compiles = cuda.stats()["nvrtc_compiles"]
+    R.reset()
+    G.symbolic_add_run(runs[1])
+    assert cuda.stats()["nvrtc_compiles"] == compiles
 
 
 def test_f16_arithmetic_is_rounded_per_op():

@@ -130,7 +130,7 @@ def test_bf16_add_matches_truncation_model():
     assert np.abs(z.data - tr(tr(a) + tr(b))).max() <= 1e-6
 
 
-@pytest.mark.parametrize("bits,want", GOLD["f32_to_f16_bits"]["cases"])
+@pytest.mark.parametrize("bits,want", GOLD["f32_to_f16_bits"]["cases"] + GOLD["backend_f32_to_f16_bits"]["cases"])
 def test_f32_to_f16_known_answers(bits, want):
     f = np.array([bits], dtype=np.uint32).view(np.float32)[0]
     assert binding.lib().orc_f32_to_f16_bits(float(f) if f == f else f) == want or (f != f and bits == 0x7F800001)
@@ -139,7 +139,7 @@ def test_f32_to_f16_known_answers(bits, want):
         assert np.array([q[0]], np.float32).astype(np.float16).view(np.uint16)[0] == want
 
 
-@pytest.mark.parametrize("bits,want", GOLD["f16_to_f32_bits"]["cases"])
+@pytest.mark.parametrize("bits,want", GOLD["f16_to_f32_bits"]["cases"] + GOLD["backend_f16_to_f32_bits"]["cases"])
 def test_f16_to_f32_known_answers(bits, want):
     assert np.array([bits], dtype=np.uint16).view(np.float16).astype(np.float32).view(np.uint32)[0] == want
 
@@ -166,3 +166,33 @@ def test_max_identity_is_minus_flt_max_not_inf():
     y = leaf((1, 2), [1.0, 2.0]).pad(((0, 0), (2, 0))).shrink(((0, 1), (0, 2))).max([1])
     R.realize(y)
     assert y.data[0] == np.float32(-3.4028234663852886e38)
+
+
+def test_bulk_f16_bytes():
+    """float32sToF16Bytes of the backend (backend/webgpu/conversion_test.go:79-99): little-endian
+    half bit patterns, through the oracle's converter and the frontend's quantiser."""
+    c = GOLD["backend_bulk_f16"]
+    x = np.asarray(c["x"], np.float32)
+    assert x.astype(np.float16).tobytes() == bytes(c["bytes"])
+    bits = [binding.lib().orc_f32_to_f16_bits(float(v)) for v in x]
+    assert np.asarray(bits, np.uint16).tobytes() == bytes(c["bytes"])
+
+
+def symbolic_add_run(run):
+    """out[i] = a[i] + b[i] over a symbolic extent (backend/webgpu/symbolic_test.go:27-152), built
+    with the frontend: two [n, 1] inputs whose outermost size is bound per call."""
+    from anneal_b200 import uop as U
+    n = run["n"]
+    var = U.Var("n", 1, 1024)
+    a = Tensor.new_symbolic_batch_input(var, (1,)).set_data(np.arange(n, dtype=np.float32) * run["a_scale"])
+    b = Tensor.new_symbolic_batch_input(var, (1,)).set_data(np.arange(n, dtype=np.float32) * run["b_scale"])
+    out = a.add(b)
+    R.realize_with_binding({"n": n}, out)
+    want = np.arange(n, dtype=np.float32) * run["a_scale"] + np.arange(n, dtype=np.float32) * run["b_scale"]
+    assert out.data.shape == (n,)
+    assert np.abs(out.data - want).max() <= GOLD["symbolic_add"]["tol"]
+
+
+@pytest.mark.parametrize("run", GOLD["symbolic_add"]["runs"], ids=lambda r: f"n={r['n']}")
+def test_symbolic_add_known_answers(run):
+    symbolic_add_run(run)
