@@ -61,6 +61,22 @@ cases = {
     # one compiled symbolic kernel out[i] = a[i] + b[i] dispatched at n = 8 and n = 128
     "symbolic_add": {"ref": "backend/webgpu/symbolic_test.go:27-152", "tol": 1e-5,
                      "runs": [{"n": 8, "a_scale": 1.0, "b_scale": 2.0}, {"n": 128, "a_scale": 0.5, "b_scale": 1.5}]},
+    # gradient of sum(f(x)) for the primitive rules, inputs from the reference's testData helper
+    # (tensor/gradient_test.go:540-551: 0.5 + 0.3 i + offset, wrapped to 0.5 + 0.3 (i % 4) above 2.5);
+    # the reference compares Backward with central differences of its evaluator at these tolerances,
+    # the expectation recorded here is the derivative's closed form
+    "gradient_checks": {"ref": "tensor/gradient_test.go:555-704", "data": "testData(shape, offset), tensor/gradient_test.go:540-551", "cases": [
+        {"f": "neg", "n": 3, "offset": 0.0, "tol": 1e-4, "ref": "tensor/gradient_test.go:555-565"},
+        {"f": "exp2", "n": 3, "offset": 0.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:567-577"},
+        {"f": "log2", "n": 3, "offset": 0.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:579-589"},
+        {"f": "sin", "n": 4, "offset": 0.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:591-601"},
+        {"f": "sqrt", "n": 3, "offset": 0.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:603-613"},
+        {"f": "recip", "n": 3, "offset": 1.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:615-625"},
+        {"f": "exp", "n": 3, "offset": 0.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:631-641"},
+        {"f": "log", "n": 3, "offset": 0.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:645-655"},
+        {"f": "add", "n": 3, "offset": 0.0, "offset_y": 1.0, "tol": 1e-4, "ref": "tensor/gradient_test.go:659-672"},
+        {"f": "mul", "n": 3, "offset": 0.0, "offset_y": 1.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:674-687"},
+        {"f": "diamond", "n": 3, "offset": 0.5, "tol": 1e-3, "ref": "tensor/gradient_test.go:691-702"}]},
     "beam_test_inputs": {"ref": "codegen/beam.go:410-420", "formula": "((j + i*17) % 13 + 1) * 0.01"},
 }
 

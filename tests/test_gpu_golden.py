@@ -94,6 +94,11 @@ def test_symbolic_add_compiles_once_for_both_extents(cuda):
     assert cuda.stats()["nvrtc_compiles"] == compiles
 
 
+@pytest.mark.parametrize("case", GOLD["gradient_checks"]["cases"], ids=lambda c: c["f"])
+def test_gradient_known_answers(case):
+    G.gradient_check(case)
+
+
 def test_f16_arithmetic_is_rounded_per_op():
     G.test_f16_arithmetic_is_rounded_per_op()
 

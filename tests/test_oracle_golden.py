@@ -196,3 +196,47 @@ def symbolic_add_run(run):
 @pytest.mark.parametrize("run", GOLD["symbolic_add"]["runs"], ids=lambda r: f"n={r['n']}")
 def test_symbolic_add_known_answers(run):
     symbolic_add_run(run)
+
+
+def reference_test_data(n, offset):
+    """testData of the reference's gradient tests (tensor/gradient_test.go:540-551), in float32."""
+    d = np.empty(n, np.float32)
+    for i in range(n):
+        v = np.float32(0.5) + np.float32(i) * np.float32(0.3) + np.float32(offset)
+        if v > np.float32(2.5):
+            v = np.float32(0.5) + np.float32(i % 4) * np.float32(0.3)
+        d[i] = v
+    return d
+
+
+def gradient_check(case):
+    """Backward of sum(f(x)) realized on the executor in use, against the closed-form derivative at
+    the reference's inputs and tolerance (absolute, as the reference compares)."""
+    n = case["n"]
+    xd = reference_test_data(n, case["offset"]).astype(np.float64)
+    x = leaf((n,), xd)
+    f = case["f"]
+    ln2 = np.log(2.0)
+    if f in ("add", "mul"):
+        yd = reference_test_data(n, case["offset_y"]).astype(np.float64)
+        y = leaf((n,), yd)
+        loss = (x.add(y) if f == "add" else x.mul(y)).sum()
+        g = backward(loss, [x, y])
+        R.realize(g[x], g[y])
+        want = (np.ones(n), np.ones(n)) if f == "add" else (yd, xd)
+        assert np.abs(g[x].data - want[0]).max() <= case["tol"]
+        assert np.abs(g[y].data - want[1]).max() <= case["tol"]
+        return
+    build_f = {"neg": lambda t: t.neg(), "exp2": lambda t: t.exp2(), "log2": lambda t: t.log2(), "sin": lambda t: t.sin(),
+               "sqrt": lambda t: t.sqrt(), "recip": lambda t: t.recip(), "exp": lambda t: t.exp(), "log": lambda t: t.log(),
+               "diamond": lambda t: t.mul(t).add(t)}[f]
+    want = {"neg": -np.ones(n), "exp2": ln2 * 2.0 ** xd, "log2": 1.0 / (xd * ln2), "sin": np.cos(xd), "sqrt": 0.5 / np.sqrt(xd),
+            "recip": -1.0 / xd ** 2, "exp": np.exp(xd), "log": 1.0 / xd, "diamond": 2.0 * xd + 1.0}[f]
+    g = backward(build_f(x).sum(), [x])[x]
+    R.realize(g)
+    assert np.abs(g.data - want).max() <= case["tol"], (f, g.data, want)
+
+
+@pytest.mark.parametrize("case", GOLD["gradient_checks"]["cases"], ids=lambda c: c["f"])
+def test_gradient_known_answers(case):
+    gradient_check(case)
