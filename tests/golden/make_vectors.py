@@ -77,6 +77,15 @@ cases = {
         {"f": "add", "n": 3, "offset": 0.0, "offset_y": 1.0, "tol": 1e-4, "ref": "tensor/gradient_test.go:659-672"},
         {"f": "mul", "n": 3, "offset": 0.0, "offset_y": 1.0, "tol": 1e-3, "ref": "tensor/gradient_test.go:674-687"},
         {"f": "diamond", "n": 3, "offset": 0.5, "tol": 1e-3, "ref": "tensor/gradient_test.go:691-702"}]},
+    # the same comparison for the structured graphs: tolerances are the reference's, inputs testData with
+    # the listed offsets, expectations the closed forms worked out in float64 by the test
+    "structured_gradients": {"data": "testData(shape, offset), tensor/gradient_test.go:540-551", "cases": [
+        {"graph": "broadcast", "ref": "tensor/gradient_test.go:730-744", "tol": {"w": 1e-3}},
+        {"graph": "matmul", "ref": "tensor/gradient_test.go:748-762", "tol": {"x": 5e-3, "w": 5e-3}},
+        {"graph": "linear", "ref": "tensor/gradient_test.go:766-794", "tol": {"w": 5e-3, "b": 3e-3}},
+        {"graph": "mlp", "ref": "tensor/gradient_test.go:798-829", "tol": {"w1": 5e-3, "w2": 5e-3}},
+        {"graph": "conv2d", "ref": "tensor/gradient_test.go:833-878", "tol": {"weight": 5e-3}},
+        {"graph": "reduce_sum", "ref": "tensor/gradient_test.go:882-893", "tol": {"x": 5e-4}}]},
     "beam_test_inputs": {"ref": "codegen/beam.go:410-420", "formula": "((j + i*17) % 13 + 1) * 0.01"},
 }
 

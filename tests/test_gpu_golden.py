@@ -99,6 +99,11 @@ def test_gradient_known_answers(case):
     G.gradient_check(case)
 
 
+@pytest.mark.parametrize("case", GOLD["structured_gradients"]["cases"], ids=lambda c: c["graph"])
+def test_structured_gradient_known_answers(case):
+    G.structured_gradient_check(case)
+
+
 def test_f16_arithmetic_is_rounded_per_op():
     G.test_f16_arithmetic_is_rounded_per_op()
 
