@@ -86,6 +86,15 @@ cases = {
         {"graph": "mlp", "ref": "tensor/gradient_test.go:798-829", "tol": {"w1": 5e-3, "w2": 5e-3}},
         {"graph": "conv2d", "ref": "tensor/gradient_test.go:833-878", "tol": {"weight": 5e-3}},
         {"graph": "reduce_sum", "ref": "tensor/gradient_test.go:882-893", "tol": {"x": 5e-4}}]},
+    # max-pool backward: data (i+1)*0.1, loss = sum(pool(x)^2); the reference checks the first four
+    # elements against central differences at 1e-3, the tests check every element against the closed form
+    "maxpool_backward": {"ref": "tensor/nn/maxpool_test.go:131-215", "tol": 1e-3,
+                         "cases": [[1, 1, 4, 4, 2, 2, 2, 2], [1, 1, 4, 4, 2, 2, 1, 1], [1, 1, 6, 6, 3, 3, 3, 3], [8, 4, 4, 4, 2, 2, 2, 2]]},
+    # ties split the adjoint equally (literal inputs and expectations)
+    "maxpool_ties": {"ref": "tensor/nn/maxpool_test.go:217-305", "tol": 1e-5, "cases": [
+        {"shape": [1, 1, 2, 2], "k": [2, 2], "s": [2, 2], "x": [3, 3, 1, 2], "want": [0.5, 0.5, 0, 0]},
+        {"shape": [1, 1, 1, 9], "k": [1, 9], "s": [1, 9], "x": [5, 5, 5, 0, 0, 0, 0, 0, 0],
+         "want": [1 / 3, 1 / 3, 1 / 3, 0, 0, 0, 0, 0, 0]}]},
     "beam_test_inputs": {"ref": "codegen/beam.go:410-420", "formula": "((j + i*17) % 13 + 1) * 0.01"},
 }
 

@@ -104,6 +104,16 @@ def test_structured_gradient_known_answers(case):
     G.structured_gradient_check(case)
 
 
+@pytest.mark.parametrize("case", GOLD["maxpool_backward"]["cases"], ids=str)
+def test_maxpool_backward_known_answers(case):
+    G.maxpool_backward_check(case)
+
+
+@pytest.mark.parametrize("case", GOLD["maxpool_ties"]["cases"], ids=lambda c: str(c["shape"]))
+def test_maxpool_ties_split_equally(case):
+    G.maxpool_tie_check(case)
+
+
 def test_f16_arithmetic_is_rounded_per_op():
     G.test_f16_arithmetic_is_rounded_per_op()
 

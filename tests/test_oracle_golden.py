@@ -312,3 +312,44 @@ def structured_gradient_check(case):
 @pytest.mark.parametrize("case", GOLD["structured_gradients"]["cases"], ids=lambda c: c["graph"])
 def test_structured_gradient_known_answers(case):
     structured_gradient_check(case)
+
+
+def maxpool_backward_check(case):
+    """d/dx of sum(MaxPool2D(x)^2) at x = (i+1)*0.1 (tensor/nn/maxpool_test.go:131-215): without ties
+    every window hands 2*max to its arg-max; all elements are compared, not only the first four."""
+    N, C, H, W, kH, kW, sH, sW = case
+    data = (np.arange(1, N * C * H * W + 1, dtype=np.float32) * np.float32(0.1))
+    x = leaf((N, C, H, W), data)
+    out = nn.max_pool2d(x, kH, kW, sH, sW)
+    g = backward(out.mul(out).sum(), [x])[x]
+    R.realize(g)
+    xd = data.astype(np.float64).reshape(N, C, H, W)
+    want = np.zeros_like(xd)
+    for i in range((H - kH) // sH + 1):
+        for j in range((W - kW) // sW + 1):
+            win = xd[:, :, i * sH:i * sH + kH, j * sW:j * sW + kW].reshape(N, C, -1)
+            am = win.argmax(-1)
+            for n in range(N):
+                for c in range(C):
+                    di, dj = divmod(int(am[n, c]), kW)
+                    want[n, c, i * sH + di, j * sW + dj] += 2.0 * win[n, c, am[n, c]]
+    assert np.abs(g.data - want.reshape(-1)).max() <= GOLD["maxpool_backward"]["tol"]
+
+
+@pytest.mark.parametrize("case", GOLD["maxpool_backward"]["cases"], ids=str)
+def test_maxpool_backward_known_answers(case):
+    maxpool_backward_check(case)
+
+
+def maxpool_tie_check(case):
+    """Tied maxima share the adjoint equally (tensor/nn/maxpool_test.go:217-305)."""
+    x = leaf(tuple(case["shape"]), case["x"])
+    out = nn.max_pool2d(x, case["k"][0], case["k"][1], case["s"][0], case["s"][1])
+    g = backward(out.sum(), [x])[x]
+    R.realize(g)
+    assert np.abs(g.data - np.asarray(case["want"], np.float64)).max() <= GOLD["maxpool_ties"]["tol"]
+
+
+@pytest.mark.parametrize("case", GOLD["maxpool_ties"]["cases"], ids=lambda c: str(c["shape"]))
+def test_maxpool_ties_split_equally(case):
+    maxpool_tie_check(case)
