@@ -144,3 +144,32 @@ def test_realize_without_backend_reports_it():
     R.DEFAULT_EXECUTOR = None
     with pytest.raises(R.RealizeError, match="no backend registered"):
         R.realize(Tensor.new_leaf((2,)).exp2())
+
+
+def test_movement_ops_dissolve_into_one_kernel(oracle):
+    """schedule/schedule_test.go:613-807: a movement op followed by an elementwise op (or a
+    reduction) is one kernel — reshape, permute, expand, shrink, pad, flip, a scalar sum, a sum over
+    a permuted tensor; the reference only counts kernels and checks their structure, here the values
+    are checked against numpy as well."""
+    def data(shape):
+        return (np.arange(1, int(np.prod(shape)) + 1, dtype=np.float32) * np.float32(0.25))
+
+    cases = [
+        ((32,), lambda t: t.reshape((4, 8)).neg(), lambda a: -a.reshape(4, 8)),
+        ((3, 4), lambda t: t.permute((1, 0)).sin(), lambda a: np.sin(a.T)),
+        ((1, 4), lambda t: t.expand((3, 4)).sqrt(), lambda a: np.sqrt(np.broadcast_to(a, (3, 4)))),
+        ((4, 8), lambda t: t.shrink(((0, 2), (2, 6))).recip(), lambda a: 1.0 / a[0:2, 2:6]),
+        ((4,), lambda t: t.pad(((2, 2),)).exp2(), lambda a: np.exp2(np.pad(a, (2, 2)))),
+        ((4, 4), lambda t: t.flip((True, False)).log2(), lambda a: np.log2(a[::-1])),
+        ((4, 8), lambda t: t.sum([0, 1]), lambda a: a.sum()),
+        ((3, 4), lambda t: t.permute((1, 0)).sum([0]), lambda a: a.T.sum(0)),
+    ]
+    for shape, build, ref in cases:
+        R.reset()
+        x = Tensor.new_leaf(shape).set_data(data(shape))
+        y = build(x)
+        items, out = S.create_schedule([y.node])
+        assert len(items) == 1, (shape, len(items))
+        got = oracle.run(items, R.leaf_inputs([y]))[out[y.node.idx]]
+        want = np.asarray(ref(data(shape).astype(np.float64).reshape(shape)), np.float64).reshape(-1)
+        assert np.allclose(got, want, rtol=1e-6, atol=1e-6), (shape, got, want)
