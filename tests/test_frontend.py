@@ -173,3 +173,15 @@ def test_movement_ops_dissolve_into_one_kernel(oracle):
         got = oracle.run(items, R.leaf_inputs([y]))[out[y.node.idx]]
         want = np.asarray(ref(data(shape).astype(np.float64).reshape(shape)), np.float64).reshape(-1)
         assert np.allclose(got, want, rtol=1e-6, atol=1e-6), (shape, got, want)
+
+
+def test_row_major_strides_known_answers():
+    """schedule/index_sint_test.go:69-143: strides[i] = product of the dims to the right; a symbolic
+    (outermost) dim takes the product of the concrete tail and contributes nothing itself."""
+    for dims, want in (((4,), [1]), ((2, 3), [3, 1]), ((2, 3, 5), [15, 5, 1]), ((2, 3, 5, 7), [105, 35, 7, 1]),
+                       ((4, 1, 3), [3, 3, 1])):
+        assert S._strides(dims) == want
+    n = U.Var("n", 1, 64)
+    assert S._strides((n, 16)) == [16, 1]
+    assert S._strides((U.Var("m", 1, 32), 4, 8)) == [32, 8, 1]
+    assert S._strides((U.Var("k", 1, 8),)) == [1]
