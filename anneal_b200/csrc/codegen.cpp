@@ -522,51 +522,6 @@ struct Gen {
     int chain_vec = 1;
     std::string dp = "data";                         // name prefix of the buffer pointers
     std::map<int, std::string> chain_subst;          // row chain: parameter → register holding this row's value
-    // row chain: buffers whose whole row is fetched into registers once, before the first stage
-    // (buffer id → row width); a load `buf[row * W + x]` with x the unrolled sweep of a stage then
-    // reads the register copy.  Shared by all stages of one chain.
-    struct RowCached { int64_t width; int dtype; };
-    std::map<uint32_t, RowCached>* row_cache = nullptr;
-    int row_cache_budget = 64;                       // values per thread over all cached buffers
-
-    // the unrolled loop over range `sw` carries an iteration counter j<aux> when it is swept by all
-    // lanes in equal shares: the single range of a short reduce, or the only inner output range
-    bool counted_sweep(int sw) const {
-        if (!row_cache || N(sw).symbolic()) return false;
-        const int64_t w = N(sw).arg;
-        return w % lanes == 0 && w / lanes <= 32;
-    }
-    std::string sweep_counter(int sw) const { return "j" + std::to_string(N(sw).aux); }
-    // the cached form of INDEX node i, or "" when the load does not sweep one cached row
-    std::string row_cached_load(int i, int p, const Lin& f, int ctx) {
-        if (!row_cache || loop_ranges.empty() || f.c != 0 || f.t.size() != 2 || !in_bounds(f, p)) return "";
-        int sw = -1; int64_t row_coef = 0;
-        for (auto& t : f.t) {
-            const Atom& a = atoms[t.first];
-            if (a.kind != Atom::RANGE) return "";
-            if (a.node == loop_ranges[0]) row_coef = t.second;
-            else if (t.second == 1) sw = a.node;
-            else return "";
-        }
-        if (sw < 0 || row_coef != N(sw).arg || !counted_sweep(sw)) return "";
-        // the sweep must be the loop this load sits in
-        if (ctx >= 0) {
-            int cnt = 0, only = -1;
-            for (size_t k = 1; k < N(ctx).src.size(); k++) if (N(N(ctx).src[k]).op == OP_RANGE) { cnt++; only = N(ctx).src[k]; }
-            if (cnt != 1 || only != sw) return "";
-        } else if (!(loop_ranges.size() == 2 && loop_ranges[1] == sw)) return "";
-        const uint32_t id = it.bufs[p].id;
-        auto f0 = row_cache->find(id);
-        if (f0 == row_cache->end()) {
-            int used = 0;
-            for (auto& kv : *row_cache) used += (int)(kv.second.width / lanes);
-            if (used + N(sw).arg / lanes > row_cache_budget) return "";
-            (*row_cache)[id] = RowCached{N(sw).arg, it.bufs[p].dtype};
-        } else if (f0->second.width != N(sw).arg) return "";
-        (void)i;
-        return "rc_" + std::to_string(id) + "[" + sweep_counter(sw) + "]";
-    }
-
 
     // Row-chain stages with chain_vec > 1: INDEX nodes below `root` (nested reductions excluded) that
     // sweep `sweep` with unit stride and whose address is provably a multiple of chain_vec elements
@@ -576,7 +531,7 @@ struct Gen {
     // chunk's first index.
     std::string chain_wide_loads(int root, int sweep, int ctx) {
         std::string code;
-        if (chain_vec <= 1 || row_cache || opts.debug_bounds) return code;
+        if (chain_vec <= 1 || opts.debug_bounds) return code;
         std::vector<int> stack{root}, seen_nodes;
         std::set<int> seen;
         while (!stack.empty()) {
@@ -642,7 +597,6 @@ struct Gen {
             idx = "clampi_(" + idx + ", " + hi + ")";
         }
         std::string e = dp + std::to_string(p) + "[" + idx + "]";
-        if (!opts.debug_bounds) { std::string rc = row_cached_load(i, p, f, ctx); if (!rc.empty()) e = rc; }
         Cls bc = dtype_cls(it.bufs[p].dtype);
         Cls want = cls(i);
         if (dtype_cls(nd.dtype) == CBOOL) return "(" + e + " != 0u)";
@@ -692,7 +646,7 @@ struct Gen {
             bool chunked = false;
             std::string wide;
             std::vector<int> wide_nodes;
-            if (rr.size() == 1 && unroll_short_loops && chain_vec > 1 && !counted_sweep(rr[0]) && !N(rr[0]).symbolic() &&
+            if (rr.size() == 1 && unroll_short_loops && chain_vec > 1 && !N(rr[0]).symbolic() &&
                 N(rr[0]).arg <= (int64_t)lanes * 32 && N(rr[0]).arg % ((int64_t)lanes * chain_vec) == 0) {
                 chunked = true;
                 std::map<int, std::string> before = vec_load;
@@ -711,11 +665,7 @@ struct Gen {
                 hdr = "for (int " + rn + " = RED_BEGIN(" + range_bound(rr[0]) + "); " + rn + " < RED_END(" + range_bound(rr[0]) + "); " + rn + " += RED_STEP) {";
                 // short trip counts are unrolled: the loads of one stage of a row chain can then stay in
                 // registers for the next stage instead of being fetched from L1 again
-                if (unroll_short_loops && counted_sweep(rr[0])) {
-                    // equal shares: an explicit trip counter, so that register copies of the row can be indexed
-                    const std::string j = sweep_counter(rr[0]);
-                    hdr = "_Pragma(\"unroll\") for (int " + j + " = 0; " + j + " < " + std::to_string(N(rr[0]).arg / lanes) + "; " + j + "++) { const int " + rn + " = lane + " + j + " * LANES;";
-                } else if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) {
+                if (unroll_short_loops && !N(rr[0]).symbolic() && N(rr[0]).arg <= (int64_t)lanes * 32) {
                     if (chunked) {
                         // each lane takes chain_vec consecutive elements per trip; unit-stride operands
                         // arrive by one explicit 128-bit load per chunk (the inner declaration of the
@@ -1296,10 +1246,8 @@ struct Gen {
         reset_emit();
         reduce_combine_mode = "group";
         unroll_short_loops = true;
-        // 4-element chunks per lane with explicit 128-bit loads and stores; ANNEAL_CHAIN_VEC=1 keeps one
-        // element per lane and trip (scalar, lane-interleaved accesses)
-        static const int chain_vec_env = std::getenv("ANNEAL_CHAIN_VEC") ? std::atoi(std::getenv("ANNEAL_CHAIN_VEC")) : 4;
-        chain_vec = (chain_vec_env == 2 || chain_vec_env == 4) ? chain_vec_env : 1;
+        // 4-element chunks per lane with explicit 128-bit loads and stores where a row allows it
+        chain_vec = 4;
         dp = "s" + std::to_string(k) + "_data";
         std::ostringstream c;
         std::string bt = buf_ctype(it.bufs[0].dtype);
@@ -1327,9 +1275,6 @@ struct Gen {
                 // the loads are written with the chunk's first index; the per-element scope below shadows it
                 c << "    const int gi = gb; (void)gi;\n" << decompose("gi", 1, loop_ranges.size(), "    ") << wide;
                 c << "  _Pragma(\"unroll\") for (int u = 0; u < " << chain_vec << "; u++) { const int gi = gb + u;\n";
-            } else if (loop_ranges.size() == 2 && counted_sweep(loop_ranges[1])) {
-                const std::string j = sweep_counter(loop_ranges[1]);
-                c << "  _Pragma(\"unroll\") for (int " << j << " = 0; " << j << " < " << inner / threads << "; " << j << "++) { const int gi = threadIdx.x + " << j << " * " << threads << ";\n";
             } else {
                 c << (inner <= (int64_t)threads * 32 ? "  _Pragma(\"unroll\")\n" : "");
                 c << "  for (int gi = threadIdx.x; gi < " << inner << "; gi += " << threads << ") {\n";
@@ -1596,25 +1541,17 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
     std::ostringstream k, sig, body, aligned;
     std::vector<std::string> result(items.size());
     std::vector<bool> inner(items.size(), false);
-    std::map<uint32_t, std::string> shared_input;      // buffer id -> pointer of the first stage that reads it
-    std::map<uint32_t, Gen::RowCached> row_cache;
-    // Register copies of the rows are off unless asked for: they remove the repeated loads but need 64
-    // registers per thread, two resident blocks per SM instead of four, and the chain is bound by
-    // latency hiding across its barrier phases (measured 0.245 ms against 0.187 ms on 8192x8192).
-    static const bool cache_rows = std::getenv("ANNEAL_CHAIN_ROW_CACHE") && std::atoi(std::getenv("ANNEAL_CHAIN_ROW_CACHE")) != 0;
     int64_t rows = -1;
     // ask for full occupancy (2048 threads per SM): without the second bound the run-time compiler took 36
     // registers for the 8192-wide softmax chain and one of four resident blocks was lost (0.1665 ms
-    // against 0.1604 with the bound); ANNEAL_CHAIN_FULL_OCCUPANCY=0 drops the bound
-    static const int full_occ = std::getenv("ANNEAL_CHAIN_FULL_OCCUPANCY") ? std::atoi(std::getenv("ANNEAL_CHAIN_FULL_OCCUPANCY")) : 1;
+    // against 0.1604 with the bound)
     sig << "extern \"C\" __global__ void __launch_bounds__(" << threads;
-    if (full_occ && threads <= 1024 && 2048 % threads == 0) sig << ", " << 2048 / threads;
+    if (threads <= 1024 && 2048 % threads == 0) sig << ", " << 2048 / threads;
     sig << ") row_chain(";
     bool first_arg = true;
     std::string decls;
     for (size_t s = 0; s < items.size(); s++) {
         Gen g(*items[s], opts);
-        if (cache_rows) g.row_cache = &row_cache;
         for (auto& pr : chain_reads[s]) {
             if (pr.second < 0 || pr.second >= (int)s || inner[pr.second]) { err = "chain: stage input is not a per-row result of an earlier stage"; return false; }
             g.chain_subst[pr.first] = result[pr.second];
@@ -1632,20 +1569,8 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
             std::string ty = std::string(is_chain_out ? "" : "const ") + buf_ctype(items[s]->bufs[b].dtype) + "*";
             sig << (first_arg ? "" : ", ") << ty << " __restrict__ s" << s << "_data" << b << "_";
             // device blocks are 256-byte aligned (pool granularity, 128-element view offsets)
-            // a buffer that several stages read arrives once per stage; all stages use the first
-            // pointer, so the compiler sees one load per element and keeps the row in registers
-            // across stages instead of fetching it again through each stage's own parameter
             const std::string local = "s" + std::to_string(s) + "_data" + std::to_string(b);
-            // Off unless asked for: on the 8192x8192 softmax chain it raised registers from 32 to 40 per
-            // thread, which costs one of the four resident blocks per SM (0.187 -> 0.205 ms).
-            static const bool alias_on = std::getenv("ANNEAL_CHAIN_ALIAS") && std::atoi(std::getenv("ANNEAL_CHAIN_ALIAS")) != 0;
-            auto seen = (b == 0 || !alias_on) ? shared_input.end() : shared_input.find(items[s]->bufs[b].id);
-            if (seen != shared_input.end()) {
-                aligned << "  " << ty << " __restrict__ " << local << " = " << seen->second << ";\n";
-            } else {
-                aligned << "  " << ty << " __restrict__ " << local << " = (" << ty << ")__builtin_assume_aligned(" << local << "_, 16);\n";
-                if (b > 0) shared_input[items[s]->bufs[b].id] = local;
-            }
+            aligned << "  " << ty << " __restrict__ " << local << " = (" << ty << ")__builtin_assume_aligned(" << local << "_, 16);\n";
             first_arg = false;
         }
     }
@@ -1658,13 +1583,6 @@ bool render_row_chain(const std::vector<const Item*>& items, const std::vector<s
     k << "  const int lane = threadIdx.x, grp = 0;\n  (void)grp;\n";
     k << "  const int row = blockIdx.x;\n";
     k << aligned.str();
-    for (auto& kv : row_cache) {
-        // the whole row, once, with every load of the thread in flight together
-        const std::string id = std::to_string(kv.first), per = std::to_string(kv.second.width / threads);
-        k << "  " << buf_ctype(kv.second.dtype) << " rc_" << id << "[" << per << "];\n";
-        k << "  _Pragma(\"unroll\") for (int j = 0; j < " << per << "; j++) rc_" << id << "[j] = " << shared_input[kv.first]
-          << "[(long long)row * " << kv.second.width << "LL + lane + j * LANES];\n";
-    }
     k << decls << body.str() << "}\n";
     out.source = k.str();
     out.block = (unsigned)threads;

@@ -30,7 +30,8 @@ struct CodegenOpts {
 
 struct Launch {
     std::string entry;
-    unsigned block = 1;
+    unsigned block = 1, block_y = 1, block_z = 1;   // y and z only for caller-supplied source
+    unsigned grid_y = 1, grid_z = 1;
     // grid.x = ceil(outputs / outputs_per_block) where outputs = static_outputs, or
     // sym_value * sym_trailing for a kernel with a symbolic output range
     int64_t static_outputs = 1;

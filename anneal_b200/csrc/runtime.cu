@@ -242,8 +242,9 @@ int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::sh
         p->r.klass = KC_RAW;
         p->r.source = item.source;
         p->r.main.entry = "main_kernel";
-        p->r.main.block = item.local[0] * item.local[1] * item.local[2];
+        p->r.main.block = item.local[0]; p->r.main.block_y = item.local[1]; p->r.main.block_z = item.local[2];
         p->r.main.static_outputs = (int64_t)item.grid[0];
+        p->r.main.grid_y = item.grid[1]; p->r.main.grid_z = item.grid[2];
         p->r.main.outputs_per_block = 1;
     } else {
         bool routed = false;
@@ -270,7 +271,7 @@ static int launch_one(anl_device* dev, CUfunction fn, const Launch& l, int64_t s
     if (work <= 0) return ANL_OK;
     int64_t grid = (work + l.outputs_per_block - 1) / l.outputs_per_block;
     if (grid > 0x7fffffffLL) return dev->fail(ANL_ERR_LIMIT, "cuda: grid too large");
-    CUresult cr = dev->drv.LaunchKernel(fn, (unsigned)grid, 1, 1, l.block, 1, 1, l.smem_bytes, (CUstream)stream, args.data(), nullptr);
+    CUresult cr = dev->drv.LaunchKernel(fn, (unsigned)grid, l.grid_y, l.grid_z, l.block, l.block_y, l.block_z, l.smem_bytes, (CUstream)stream, args.data(), nullptr);
     if (cr != CUDA_SUCCESS) { const char* s = nullptr; dev->drv.GetErrorString(cr, &s); return dev->fail(ANL_ERR_CUDA, std::string("cuda: cuLaunchKernel(") + l.entry + "): " + (s ? s : "?")); }
     dev->stats.kernels_launched++;
     return ANL_OK;
@@ -315,20 +316,15 @@ static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item
     return rc;
 }
 
-int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream,
-               bool background) {
+int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream) {
     if (master->dtype != ANL_F32) return dev->fail(ANL_ERR_INVALID, "sgd: master weights must be f32");
     if (grad->elems < master->elems || param->elems < master->elems) return dev->fail(ANL_ERR_INVALID, "sgd: gradient length != parameter length");
     long long n = master->elems;
     if (n == 0) return ANL_OK;
     auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
     const int vec = n >= 4 && al16(master->ptr) && al16(param->ptr) && al16(grad->ptr);
-    // An update that runs beside the backward pass has until the end of the step: one block per SM
-    // leaves the issue slots and most of the memory system to the contractions.  The last update
-    // of a step, and the stand-alone call, take the whole machine.
     const int sms = dev->prop.multiProcessorCount;
-    unsigned g = background ? (unsigned)std::max<long long>(1, std::min<long long>((n / 4 + 255) / 256, sms))
-                            : grid_for(vec ? (n + 3) / 4 : n, 256, sms);
+    unsigned g = grid_for(vec ? (n + 3) / 4 : n, 256, sms);
     float* m = (float*)master->ptr;
     bool gh = grad->dtype == ANL_F16, ph = param->dtype == ANL_F16;
     int bf = param->dtype == ANL_BF16;
@@ -518,8 +514,6 @@ int try_row_chain(anl_device* dev, const std::vector<Item>& items, size_t first,
         else {
             cp = std::make_shared<ChainPlan>();
             CodegenOpts o; std::string err;
-            static const int chain_threads = std::getenv("ANNEAL_CHAIN_THREADS") ? std::atoi(std::getenv("ANNEAL_CHAIN_THREADS")) : 0;
-            o.block_threads = chain_threads;
             if (!render_row_chain(members, reads, o, cp->r, err)) cp.reset();
             else {
                 std::shared_ptr<Module> mod;
@@ -569,11 +563,6 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         sgd_at[at].push_back(kv.first);
     }
     const bool chains_on = !(dev->flags & ANL_OPEN_NO_ROW_CHAIN) && !(dev->flags & ANL_OPEN_BEAM);
-    // Updates beside the backward pass take the whole machine unless ANNEAL_SGD_BACKGROUND=1 asks for
-    // one block per SM: the narrow form disturbs the contractions less when they are timed one by
-    // one, but on two GPUs it stretches the serial communication stream and the step got 0.06 ms
-    // longer (3.59-3.61 against 3.52-3.56 ms), and on one GPU the step time did not change.
-    static const bool sgd_foreground = !(std::getenv("ANNEAL_SGD_BACKGROUND") && std::atoi(std::getenv("ANNEAL_SGD_BACKGROUND")) != 0);
     // the last all-reduced output of the schedule, when it is a large contraction whose update is
     // not deferred past it: candidate for the split described at its launch below
     size_t tail_split = (size_t)-1;
@@ -607,7 +596,7 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         if (sharded(a, cnt)) return comm_reduce_scatter_async(dev, g, cnt, a.resident->dtype, stream);
         return comm_allreduce_async(dev, g, cnt, a.resident->dtype, stream);
     };
-    auto update_part = [&](const anl_output& a, int64_t off, int64_t cnt, bool background) -> int {
+    auto update_part = [&](const anl_output& a, int64_t off, int64_t cnt) -> int {
         const bool sh = sharded(a, cnt);
         const int64_t sc = sh ? cnt / dev->nranks : cnt, so = sh ? off + dev->rank * sc : off;
         anl_buffer gv = *a.resident, mv = *a.sgd_master, pv = a.sgd_param ? *a.sgd_param : *a.sgd_master;
@@ -615,10 +604,20 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         mv.ptr = (char*)mv.ptr + so * dt_storage_bytes(mv.dtype); mv.elems = sc;
         pv.ptr = (char*)pv.ptr + so * dt_storage_bytes(pv.dtype); pv.elems = sc;
         comm_fork(dev, stream);
-        if (int rc = launch_sgd(dev, &mv, &pv, &gv, a.sgd_lr, a.sgd_scale, dev->comm_stream, background)) return rc;
+        if (int rc = launch_sgd(dev, &mv, &pv, &gv, a.sgd_lr, a.sgd_scale, dev->comm_stream)) return rc;
         if (sh) {
             const anl_buffer* pb = a.sgd_param ? a.sgd_param : a.sgd_master;
             if (int rc = comm_allgather_async(dev, (char*)pb->ptr + off * dt_storage_bytes(pb->dtype), cnt, pb->dtype)) return rc;
+        }
+        return ANL_OK;
+    };
+    // [update the parameter] hooks that fall due once item `at` has been queued
+    auto updates_due = [&](size_t at) -> int {
+        auto sg = sgd_at.find(at);
+        if (sg == sgd_at.end()) return ANL_OK;
+        for (uint32_t id : sg->second) {
+            const anl_output& a = t.after[id];
+            if (int rc = update_part(a, 0, a.sgd_master->elems)) return rc;
         }
         return ANL_OK;
     };
@@ -628,7 +627,12 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             size_t used = 0;
             int rc = try_row_chain(dev, items, i, t, stream, &used);
             if (rc != ANL_OK) return rc;
-            if (used > 0) { i += used - 1; continue; }
+            if (used > 0) {
+                // a member of the chain may be the last reader of a parameter: its update falls due now
+                for (size_t j = i; j < i + used; j++) if (int rc2 = updates_due(j)) return rc2;
+                i += used - 1;
+                continue;
+            }
         }
         std::shared_ptr<Plan> plan;
         CodegenOpts use = opts;
@@ -666,7 +670,7 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
                 if (int rc = launch_gemm(dev, *plan, ptrs.data(), item_sym(it, binds), stream, m0, m1)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
                 const int64_t off = m0 * row_elems, cnt = (m1 - m0) * row_elems;
                 if (int rc = reduce_part(a, off, cnt)) return rc;
-                if (int rc = update_part(a, off, cnt, h == 0 && !sgd_foreground)) return rc;
+                if (int rc = update_part(a, off, cnt)) return rc;
             }
             allow_shard = true;
             continue;
@@ -676,14 +680,7 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         if (ra != t.after.end() && ra->second.allreduce)
             if (int rc = reduce_part(ra->second, 0, ra->second.resident->elems)) return rc;
         // ... [update the parameter] once its last reader has been queued as well
-        auto sg = sgd_at.find(i);
-        if (sg != sgd_at.end()) {
-            for (uint32_t id : sg->second) {
-                const anl_output& a = t.after[id];
-                const bool background = i + 1 < items.size() && !sgd_foreground;
-                if (int rc = update_part(a, 0, a.sgd_master->elems, background)) return rc;
-            }
-        }
+        if (int rc = updates_due(i)) return rc;
     }
     return comm_join(dev, stream);
 }
@@ -754,6 +751,7 @@ struct anl_graph {
     int64_t built_sym = -2;
     cudaGraphExec_t exec = nullptr;
     std::vector<std::pair<uint32_t, anl_buffer*>> resident_in, resident_out;
+    uint64_t placed_key = 0;     // hash of what the capture baked in besides pointers: update targets, rate, scale, reduce mode
 };
 
 // ── exception fence ──────────────────────────────────────────────────────────────────────────
@@ -825,6 +823,8 @@ int anl_device_info(anl_device* dev, anl_info* info) {
 const char* anl_last_error(anl_device* dev) { return dev ? dev->err.c_str() : "no device"; }
 
 int anl_get_stats(anl_device* dev, anl_stats* out) { if (!dev || !out) return ANL_ERR_INVALID; *out = dev->stats; return ANL_OK; }
+
+void* anl_stream(anl_device* dev) { return dev ? (void*)dev->stream : nullptr; }
 
 int anl_synchronize(anl_device* dev) {
     if (!dev) return ANL_ERR_INVALID;
@@ -1148,7 +1148,17 @@ static int graph_replay_impl(anl_graph* g, const anl_input* inputs, int n_inputs
     std::vector<std::pair<uint32_t, anl_buffer*>> rin, rout;
     for (int k = 0; k < n_inputs; k++) if (inputs[k].resident) rin.push_back({inputs[k].uop_idx, inputs[k].resident});
     for (int k = 0; k < n_placed; k++) if (placed[k].resident) rout.push_back({placed[k].uop_idx + (placed[k].allreduce ? 0x80000000u : 0u) + (placed[k].sgd_master ? 0x40000000u : 0u), placed[k].resident});
-    if (g->built && (sym != g->built_sym || rin != g->resident_in || rout != g->resident_out)) graph_drop(g);
+    // the learning rate, the gradient scale, the update's targets and the reduce mode are kernel
+    // arguments inside the capture as well: a caller that changes one gets a new capture, not stale values
+    uint64_t pkey = 1469598103934665603ull;
+    for (int k = 0; k < n_placed; k++) {
+        const anl_output& p = placed[k];
+        struct { uint32_t id; int mode; const void* m; const void* q; float lr, scale; } rec;
+        std::memset(&rec, 0, sizeof rec);
+        rec.id = p.uop_idx; rec.mode = p.allreduce; rec.m = p.sgd_master; rec.q = p.sgd_param; rec.lr = p.sgd_lr; rec.scale = p.sgd_scale;
+        pkey = fnv1a(&rec, sizeof rec, pkey);
+    }
+    if (g->built && (sym != g->built_sym || rin != g->resident_in || rout != g->resident_out || pkey != g->placed_key)) graph_drop(g);
     int rc = ANL_OK;
     bool host_fed = !g->built;      // a replay whose leaves and outputs are all resident need not wait for the GPU
     if (!g->built) {
@@ -1178,7 +1188,7 @@ static int graph_replay_impl(anl_graph* g, const anl_input* inputs, int n_inputs
             if (graph) cudaGraphDestroy(graph);
         }
         if (rc != ANL_OK) { graph_drop(g); *n_outs = 0; return rc; }
-        g->built = true; g->built_sym = sym; g->resident_in = rin; g->resident_out = rout;
+        g->built = true; g->built_sym = sym; g->resident_in = rin; g->resident_out = rout; g->placed_key = pkey;
         dev->stats.graph_captures++;
     } else {
         // replay: refresh host-fed leaves in place

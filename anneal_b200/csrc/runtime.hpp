@@ -140,8 +140,7 @@ int comm_allreduce_async(anl_device* dev, void* ptr, int64_t elems, int dtype, c
 bool comm_can_shard(anl_device* dev);
 int comm_reduce_scatter_async(anl_device* dev, void* ptr, int64_t elems, int dtype, cudaStream_t stream);
 int comm_allgather_async(anl_device* dev, void* ptr, int64_t elems, int dtype);
-int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream,
-               bool background = false);
+int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream);
 int comm_join(anl_device* dev, cudaStream_t stream);
 
 // autotuning (beam.cpp)

@@ -1,12 +1,15 @@
 // anl_sum_f32_static: the split scalar reduction (partials kernel + finish kernel) with its scratch
 // in a fixed device array instead of pool memory, for callers that must not reach the CUDA
-// allocator.  It mirrors, launch for launch, what the code generator emits for SUM over one f32
-// buffer when it splits the reduction over several blocks: every block reduces one contiguous chunk
-// with 256 lanes striding it, lanes are combined by an xor-shuffle butterfly and then across the
-// eight warps in ascending order, and one thread adds the partials in ascending order.  Nothing here
-// allocates: no cudaMalloc/cudaFree, no pool, no NVRTC.
+// allocator.  For n >= 65536 it mirrors, launch for launch, what the code generator emits for SUM
+// over one f32 buffer (the generator splits a reduction over several blocks from that length on;
+// shorter sums it runs in one block, so there the order of the additions differs from this file's
+// and the two agree to rounding, not bit for bit): every block reduces one contiguous chunk with 256
+// lanes striding it, lanes are combined by an xor-shuffle butterfly and then across the eight warps
+// in ascending order, and one thread adds the partials in ascending order.  Nothing here allocates:
+// no cudaMalloc/cudaFree, no pool, no NVRTC.
 #include <cuda_runtime.h>
 
+#include <atomic>
 #include <cstdio>
 
 #include "../../include/anneal_cuda.h"
@@ -47,8 +50,10 @@ __global__ void static_sum_finish(const float* __restrict__ scratch, int parts, 
     }
 }
 
-// device address of g_sum_scratch per device ordinal; the symbol's name is only a host-side handle
-float* g_scratch_addr[64] = {};
+// device address of g_sum_scratch per device ordinal; the symbol's name is only a host-side handle.
+// Two host threads that make the first call on one device together both resolve the same address
+// and store the same value; the atomic makes that store and the later loads well defined.
+std::atomic<float*> g_scratch_addr[64] = {};
 
 void set_err(char* err, size_t cap, const char* msg) { if (err && cap) std::snprintf(err, cap, "%s", msg); }
 
@@ -65,12 +70,14 @@ extern "C" int anl_sum_f32_static(const float* x, int64_t n, float* out, void* s
     int dev = 0;
     cudaError_t e = cudaGetDevice(&dev);
     if (e != cudaSuccess || dev < 0 || dev >= 64) { set_err(err, err_cap, "static sum: no current CUDA device"); return ANL_ERR_NO_DEVICE; }
-    if (!g_scratch_addr[dev]) {
+    float* scratch = g_scratch_addr[dev].load(std::memory_order_acquire);
+    if (!scratch) {
         // first call on this device: resolve the array's device address (the current device is `dev`)
         void* p = nullptr;
         e = cudaGetSymbolAddress(&p, g_sum_scratch);
         if (e != cudaSuccess || !p) { set_err(err, err_cap, cudaGetErrorString(e)); return ANL_ERR_CUDA; }
-        g_scratch_addr[dev] = static_cast<float*>(p);
+        scratch = static_cast<float*>(p);
+        g_scratch_addr[dev].store(scratch, std::memory_order_release);
     }
     // same split the code generator picks for one output: about four blocks per SM, chunks of >= 4096
     long long parts = n / 4096;
@@ -78,8 +85,8 @@ extern "C" int anl_sum_f32_static(const float* x, int64_t n, float* out, void* s
     if (parts < 1) parts = 1;
     const long long chunk = (n + parts - 1) / parts;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    static_sum_partials<<<(unsigned)parts, kThreads, 0, s>>>(x, n, chunk, g_scratch_addr[dev]);
-    static_sum_finish<<<1, 32, 0, s>>>(g_scratch_addr[dev], (int)parts, out);
+    static_sum_partials<<<(unsigned)parts, kThreads, 0, s>>>(x, n, chunk, scratch);
+    static_sum_finish<<<1, 32, 0, s>>>(scratch, (int)parts, out);
     e = cudaGetLastError();
     if (e != cudaSuccess) { set_err(err, err_cap, cudaGetErrorString(e)); return ANL_ERR_CUDA; }
     return ANL_OK;

@@ -257,6 +257,13 @@ int anl_sum_f32_static(const float* x, int64_t n, float* out, void* stream, char
 /* blocks until all work queued on the device has finished */
 int anl_synchronize(anl_device* dev);
 
+/* The cudaStream_t this device queues its kernels and copies on (non-blocking: it is not ordered
+ * with the default stream).  A caller that launches work of its own on device buffers — through
+ * anl_sum_f32_static, say — passes this handle to stay in order with uploads, runs and downloads;
+ * anl_synchronize then covers that work too.  No counterpart in the reference, whose queue is
+ * private to its owner goroutine (backend/webgpu/open.go:63-82). */
+void* anl_stream(anl_device* dev);
+
 #ifdef __cplusplus
 }
 #endif

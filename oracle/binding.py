@@ -39,6 +39,7 @@ def lib():
         L.orc_bind.argtypes = [C.c_void_p, C.c_char_p, C.c_int64]
         L.orc_run.argtypes = [C.c_void_p, C.c_int]
         L.orc_run_item.argtypes = [C.c_void_p, C.c_int, C.c_int]
+        L.orc_run_item_sampled.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int]
         L.orc_buffer_elems.restype = C.c_int64
         L.orc_buffer_elems.argtypes = [C.c_void_p, C.c_uint32]
         L.orc_get_buffer.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_int64]
@@ -95,6 +96,34 @@ class OracleExecutor:
                 L.orc_get_buffer(h, ob.uop_idx, a.ctypes.data, n)
                 out[ob.uop_idx] = a
             return out
+        finally:
+            L.orc_free(h)
+
+    def sample_item(self, item, inputs: Dict[int, np.ndarray], flat, binding: Optional[Dict[str, int]] = None):
+        """The values kernel ``item`` stores at the flat output positions ``flat`` (row-major over its
+        output), given float32 arrays for every buffer it reads. A benchmark-size contraction is
+        checked this way on a few thousand outputs: n*K terms instead of M*N*K. Returns the positions
+        in ascending order and the values at them."""
+        from anneal_b200 import kir
+        L = lib()
+        blob = kir.serialize([item])
+        h = L.orc_load(blob, len(blob))
+        try:
+            err = L.orc_error(h)
+            if err:
+                raise OracleError(err.decode())
+            for b in item.bufs[1:]:
+                if b.uop_idx not in inputs:
+                    raise OracleError(f"sample_item: no data for input buffer {b.uop_idx}")
+                a = np.ascontiguousarray(inputs[b.uop_idx], dtype=np.float32).reshape(-1)
+                L.orc_set_input(h, b.uop_idx, b.dtype.code, a.ctypes.data, a.size)
+            for k, v in (binding or {}).items():
+                L.orc_bind(h, k.encode(), int(v))
+            idx = np.ascontiguousarray(np.sort(np.asarray(flat, dtype=np.int64)))
+            out = np.empty(idx.size, dtype=np.float32)
+            if L.orc_run_item_sampled(h, 0, idx.ctypes.data, idx.size, out.ctypes.data, self.threads):
+                raise OracleError(L.orc_error(h).decode())
+            return idx, out
         finally:
             L.orc_free(h)
 

@@ -514,6 +514,7 @@ int orc_num_items(const orc *o) { return o->n_items; }
 int orc_set_input(orc *o, uint32_t id, int dtype, const float *data, int64_t n) {
     buffer *b = get_buf(o, id, dtype, n);
     b->dtype = dtype;
+#pragma omp parallel for schedule(static) if (n > (1 << 16))
     for (int64_t i = 0; i < n; i++) {
         if (dtype == DT_F16) b->data[i].f = f16_round_f(data[i]);
         else if (dtype == DT_BF16) b->data[i].f = bf16_trunc(data[i]);
@@ -535,6 +536,81 @@ int orc_run(orc *o, int threads) {
 int orc_run_item(orc *o, int i, int threads) {
     if (o->err[0] || i < 0 || i >= o->n_items) return 1;
     return run_item(o, &o->items[i], threads);
+}
+/* Value of the STORE body of item i, narrowed as the store narrows it, at the given flat output
+ * positions (row-major over the kernel's loop ranges, codegen/lower.go:196-222), without touching
+ * the output buffer.  A contraction with K terms then costs n*K instead of M*N*K, which lets a
+ * benchmark-size kernel be compared on a few thousand outputs.  Every input buffer must hold data
+ * (orc_set_input, or an earlier kernel).  Positions should arrive sorted: sub-expressions that do
+ * not read the ranges that changed are re-used, exactly as in a full run. */
+int orc_run_item_sampled(orc *o, int i, const int64_t *flat, int64_t n, float *out, int threads) {
+    if (o->err[0] || i < 0 || i >= o->n_items) return 1;
+    const item *it = &o->items[i];
+    if (it->n_nodes == 0) { snprintf(o->err, sizeof o->err, "oracle: item without AST"); return 1; }
+    const node *sink = &it->nodes[it->n_nodes - 1];
+    if (sink->op != OP_SINK) { snprintf(o->err, sizeof o->err, "oracle: last node is not SINK"); return 1; }
+    const node *end = &it->nodes[sink->src[0]];
+    const node *store = &it->nodes[end->src[0]];
+    int body = store->src[1];
+    int lslots[16], nl = 0; int64_t lsize[16];
+    ectx proto; memset(&proto, 0, sizeof proto); proto.o = o; proto.it = it;
+    for (int s = 1; s < end->nsrc; s++) {
+        const node *r = &it->nodes[end->src[s]];
+        if (r->op == OP_RANGE && (r->flags & 7) != 1 && nl < 16) { lslots[nl] = r->range_slot; lsize[nl] = range_bound(&proto, r); nl++; }
+    }
+    int64_t total = 1; for (int l = 0; l < nl; l++) total *= lsize[l];
+    for (int64_t k = 0; k < n; k++) if (flat[k] < 0 || flat[k] >= total) { snprintf(o->err, sizeof o->err, "oracle: sampled position outside the output"); return 1; }
+    val *bufdata[64]; int64_t bufelems[64]; int64_t strides[64][8];
+    if (it->n_bufs > 64) { snprintf(o->err, sizeof o->err, "oracle: too many buffers"); return 1; }
+    val dummy; dummy.u = 0;
+    for (int b = 0; b < it->n_bufs; b++) {
+        const bufdesc *bd = &it->bufs[b];
+        if (b == 0) { bufdata[0] = &dummy; bufelems[0] = 0; }     /* the body never reads its own output */
+        else {
+            buffer *bf = find_buf(o, bd->id);
+            if (!bf) { snprintf(o->err, sizeof o->err, "oracle: input buffer %u has no data", bd->id); return 1; }
+            bufdata[b] = bf->data; bufelems[b] = bf->elems;
+        }
+        int64_t st = 1;
+        for (int d = bd->rank - 1; d >= 0; d--) { strides[b][d] = st; st *= (bd->shape[d] ? bd->shape[d] : 1); }
+    }
+    int out_dt = it->bufs[0].dtype;
+    int nthreads = threads > 0 ? threads : 1;
+    if (n < 8) nthreads = 1;
+#pragma omp parallel num_threads(nthreads)
+    {
+#ifdef _OPENMP
+        int tid = omp_get_thread_num(), nt = omp_get_num_threads();
+#else
+        int tid = 0, nt = 1;
+#endif
+        ectx c = proto;
+        c.bufdata = bufdata; c.bufelems = bufelems; c.strides = strides;
+        c.rval = calloc(it->n_ranges ? it->n_ranges : 1, sizeof(int32_t));
+        c.rver = calloc(it->n_ranges ? it->n_ranges : 1, sizeof(uint64_t));
+        c.cache = calloc(it->n_nodes, sizeof(val));
+        c.cver = calloc(it->n_nodes, sizeof(uint64_t));
+        for (int l = 0; l < nl; l++) { c.rval[lslots[l]] = -1; c.rver[lslots[l]] = 1; }
+        const node *bn = &it->nodes[body];
+        int body_is_float = (bn->cls == C_F32 || bn->cls == C_F16);
+        int64_t lo = n * tid / nt, hi = n * (tid + 1) / nt;
+        for (int64_t k = lo; k < hi; k++) {
+            int64_t rem = flat[k];
+            for (int l = nl - 1; l >= 0; l--) {
+                int32_t v = (int32_t)(rem % lsize[l]); rem /= lsize[l];
+                if (c.rval[lslots[l]] != v) { c.rval[lslots[l]] = v; c.rver[lslots[l]]++; }
+            }
+            val v = eval(&c, body);
+            if (out_dt == DT_F16 || out_dt == DT_BF16 || (out_dt == DT_F32 && !body_is_float)) {
+                float fv = as_f(bn, v);
+                if (out_dt == DT_F16) fv = f16_round_f(fv);
+                else if (out_dt == DT_BF16) fv = bf16_trunc(fv);
+                out[k] = fv;
+            } else memcpy(&out[k], &v, 4);
+        }
+        free(c.rval); free(c.rver); free(c.cache); free(c.cver);
+    }
+    return 0;
 }
 int64_t orc_buffer_elems(orc *o, uint32_t id) { buffer *b = find_buf(o, id); return b ? b->elems : -1; }
 int orc_get_buffer(orc *o, uint32_t id, float *out, int64_t n) {

@@ -1,0 +1,78 @@
+"""Kernel-by-kernel parity at benchmark size.
+
+The CPU oracle cannot run a 3 TFLOP step, but it can evaluate any one kernel at a few thousand of
+its output positions (``OracleExecutor.sample_item``): a contraction with K terms then costs n*K.
+The device runs the whole schedule once with every output kept (no slot shared, so nothing is
+overwritten and every fused launch still has to produce each kernel's buffer); each kernel is then
+checked on its own: the oracle is given the DEVICE's values of that kernel's inputs and must
+reproduce the device's values of its output at the sampled positions.  An error in any kernel —
+a wrong tile, a dropped k-block, an operand read with the wrong major-ness — shows in that kernel's
+row, and errors do not compound from kernel to kernel.
+"""
+import dataclasses
+
+import numpy as np
+
+
+def unaliased(items):
+    """Copies of ``items`` in which no output shares a slot: the device returns all of them."""
+    out = []
+    for it in items:
+        bufs = [dataclasses.replace(b) for b in it.bufs]
+        bufs[0].slot = -1
+        out.append(dataclasses.replace(it, bufs=bufs))
+    return out
+
+
+def sample_positions(shape, n, rng):
+    """n positions of a row-major output: corners, tile edges of the contraction kernels (multiples
+    of 128 and 256 and their neighbours) and uniformly drawn ones."""
+    total = int(np.prod(shape)) if len(shape) else 1
+    if total <= n:
+        return np.arange(total, dtype=np.int64)
+    picks = [0, total - 1]
+    if len(shape) >= 2:
+        rows, cols = int(np.prod(shape[:-1])), int(shape[-1])
+        edge_r = sorted({r for b in (0, 127, 128, 255, 256, rows // 2, rows - 129, rows - 1) for r in (b,) if 0 <= r < rows})
+        edge_c = sorted({c for b in (0, 31, 32, 127, 128, 255, 256, cols // 2, cols - 33, cols - 1) for c in (b,) if 0 <= c < cols})
+        picks += [r * cols + c for r in edge_r for c in edge_c]
+    picks = np.array(picks, dtype=np.int64)
+    rest = rng.integers(0, total, size=max(n - picks.size, 0), dtype=np.int64)
+    return np.unique(np.concatenate([picks, rest]))
+
+
+def elementwise_error(got, want, floor):
+    """max over elements of |got - want| / max(|want|, floor)."""
+    got = np.asarray(got, np.float64)
+    want = np.asarray(want, np.float64)
+    return float((np.abs(got - want) / np.maximum(np.abs(want), floor)).max()) if want.size else 0.0
+
+
+def check_every_kernel(cuda, oracle, items, inputs, tol, binding=None, samples=4096, seed=0, tol_of=None):
+    """Runs ``items`` on the device keeping every output, then checks each kernel against the oracle
+    at sampled positions.  Per element: |device - oracle| <= tol * max(|oracle|, floor), floor = the
+    root mean square of the oracle's sampled values of that kernel (an element that cancels to
+    nearly zero is held to the accuracy of a typical element of its buffer, not to a relative error
+    no finite-precision sum can meet).  Returns a list of (kernel, worst error) and the device's
+    values."""
+    keep = unaliased(items)
+    got = cuda.run(keep, inputs, binding)
+    known = dict(inputs)
+    known.update(got)
+    rng = np.random.default_rng(seed)
+    report = []
+    for k, it in enumerate(keep):
+        ob = it.bufs[0]
+        dev_out = got[ob.uop_idx]
+        assert np.isfinite(dev_out).all(), f"kernel {k}: device produced non-finite values"
+        sym = list(binding.values())[0] if binding else 0          # the one bound extent (0 marks it in a shape)
+        shape = tuple(sym if s == 0 else s for s in ob.shape)
+        pos = sample_positions(shape, samples, rng)
+        idx, want = oracle.sample_item(it, known, pos, binding)
+        assert np.isfinite(want).all(), f"kernel {k}: oracle produced non-finite values"
+        floor = max(float(np.sqrt(np.mean(np.square(want, dtype=np.float64)))), 1e-30)
+        e = elementwise_error(dev_out[idx], want, floor)
+        t = tol_of(k, it) if tol_of else tol
+        report.append((k, e))
+        assert e <= t, f"kernel {k} (output {ob.shape}, {len(it.bufs) - 1} inputs): element error {e:.3e} > {t:.1e} on {idx.size} sampled outputs"
+    return report, got

@@ -1,0 +1,140 @@
+"""The benchmark configurations at their full sizes, every kernel against the CPU oracle on sampled
+outputs (see fullsize.py), and the 100-step loss trajectories the contract asks for.
+
+Tolerances are the contract's: f32 elementwise 1e-5, f32 reductions and contractions 1e-4,
+f16-storage kernels 2e-3, loss trajectories 1e-3 over 100 steps; errors per element, relative to
+max(|oracle value|, RMS of the kernel's sampled oracle values)."""
+import numpy as np
+import pytest
+
+from anneal_b200 import realize as R, workloads as W
+from anneal_b200.realize import leaf_inputs
+from anneal_b200.train import ResidentTrainer
+from fullsize import check_every_kernel, unaliased
+from util import schedule
+
+pytestmark = pytest.mark.gpu
+
+
+def _with_materialised_operands(build):
+    R.MATERIALIZE_CONTRACTION_OPERANDS = True
+    try:
+        return build()
+    finally:
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+
+
+def test_c4_every_kernel_at_full_size(cuda, oracle):
+    """Wide MLP, batch 8192, 4 x 4096 wide, 1000 classes, f16 storage: the exact schedule the bench
+    times.  All 14 contractions (K = 4096, 8192 and 1000) run on the tcgen05 kernels and each is
+    compared with the oracle's serial ascending f32 sum on >= 4096 outputs, as are the GELU, bias,
+    cross-entropy and bias-gradient kernels; 2e-3 per element."""
+    m = W.WideMLP()
+    x, y = m.make_inputs()
+
+    def build():
+        g = m.graph(x, y)
+        items, out_ids = R.build_schedule(g.targets())
+        return g, items, out_ids
+    g, items, out_ids = _with_materialised_operands(build)
+    inputs = leaf_inputs(g.targets())
+    before = cuda.stats()["gemm_launched"]
+    report, kept = check_every_kernel(cuda, oracle, items, inputs, 2e-3, samples=4096)
+    assert cuda.stats()["gemm_launched"] - before == 14
+    assert len(report) == len(items)
+    # the schedule as the bench runs it (slots shared, only final outputs returned) gives the same
+    # loss and gradients as the run that kept every buffer
+    got = cuda.run(items, inputs)
+    assert set(got) == set(out_ids)
+    for k in out_ids:
+        assert np.array_equal(got[k], kept[k]), k
+
+
+def test_c3_softmax_full_size_against_oracle(cuda, oracle):
+    """softmax forward + backward over 8192 x 8192 f32, one row-chain launch on the device; every
+    scheduled kernel (row max, row sums, adjoint sums, the tie count inside the last one) against
+    the oracle: the per-row kernels on 2048 rows each, dx on 4096 sampled elements plus whole rows."""
+    s = W.SoftmaxFwdBwd(8192, 8192)
+    ts, _ = s.graph()
+    items, out_ids, inputs = schedule(ts)
+    k0 = cuda.stats()["kernels_launched"]
+    report, kept = check_every_kernel(cuda, oracle, items, inputs, 1e-4, samples=2048)
+    assert len(report) == len(items) == 5
+    # whole rows of dx (the elementwise kernel with its per-row tie count), first, middle and last
+    it = unaliased(items)[-1]
+    known = dict(inputs)
+    known.update(kept)
+    rows = np.array([0, 4095, 8191], dtype=np.int64)
+    pos = (rows[:, None] * 8192 + np.arange(8192, dtype=np.int64)[None, :]).reshape(-1)
+    idx, want = oracle.sample_item(it, known, pos)
+    dx = kept[out_ids[0]]
+    floor = float(np.sqrt(np.mean(np.square(want, dtype=np.float64))))
+    err = np.abs(dx[idx].astype(np.float64) - want) / np.maximum(np.abs(want), floor)
+    assert err.max() <= 1e-4, err.max()
+    # rows of a softmax gradient sum to zero
+    assert np.abs(dx.reshape(8192, 8192).sum(1, dtype=np.float64)).max() < 1e-5
+    assert cuda.stats()["kernels_launched"] - k0 >= 1
+
+
+def test_c5_symbolic_mlp_full_width_largest_batch(cuda, oracle):
+    """1024 -> 4096 -> 1024 with the batch bound to 65536 (the largest of the cycle): forward, the
+    input-gradient and both weight-gradient contractions (K = 1024, 4096 and 65536) on the f32
+    tiled kernel, every kernel against the oracle's serial sums on sampled outputs; 1e-4."""
+    m = W.DynMLP()
+    b = 65536
+    xb, yb = m.inputs(b)
+    out, loss, grads, ins = m.graph(b, xb, yb)
+    items, out_ids, inputs = schedule([out] + grads)
+    report, kept = check_every_kernel(cuda, oracle, items, inputs, 1e-4, binding={"n": b}, samples=2048)
+    assert len(report) == len(items)
+    # and the smallest batch through the same plans
+    R.reset()
+    x1, y1 = m.inputs(1)
+    out, loss, grads, ins = m.graph(1, x1, y1)
+    items, out_ids, inputs = schedule([out] + grads)
+    check_every_kernel(cuda, oracle, items, inputs, 1e-4, binding={"n": 1}, samples=2048)
+
+
+def _trajectory(cuda, oracle, make_model, steps, materialize):
+    m = make_model()
+    ref = make_model()
+    x, y = (m.x, m.y) if hasattr(m, "x") else m.make_inputs()
+    tr = ResidentTrainer(cuda, m, m.lr, use_graph=True, materialize=materialize)
+    dev_losses, ref_losses = [], []
+    for _ in range(steps):
+        dev_losses.append(tr.step(x, y))
+        R.reset()
+        R.MATERIALIZE_CONTRACTION_OPERANDS = materialize
+        try:
+            g = ref.graph() if hasattr(ref, "x") else ref.graph(x, y)
+            items, out_ids, inputs = schedule(g.targets())
+        finally:
+            R.MATERIALIZE_CONTRACTION_OPERANDS = False
+        out = oracle.run(items, inputs)
+        ref_losses.append(float(out[out_ids[0]][0]))
+        for p, gid in zip(ref.params, out_ids[1:]):
+            p.sgd_step(out[gid] * np.float32(g.grad_scale), ref.lr)
+    return np.array(dev_losses), np.array(ref_losses), tr, ref
+
+
+def test_c2_cnn_loss_trajectory_100_steps(cuda, oracle):
+    """Small CNN at full size (batch 32, 28 x 28): 100 steps of device-resident training (graph
+    replay, on-device SGD) against the reference's host loop (fresh graph each step, oracle,
+    host SGD); losses within 1e-3 at every step."""
+    dev, ref, tr, rm = _trajectory(cuda, oracle, W.SmallCNN, 100, True)
+    d = np.abs(dev - ref)
+    assert d.max() < 1e-3, (d.max(), dev[-1], ref[-1])
+    assert ref[-1] < ref[0]
+
+
+def test_c4_wide_mlp_loss_trajectory_100_steps_reduced_width(cuda, oracle):
+    """The wide MLP's arithmetic (f16 storage, f32 accumulation, GELU, cross-entropy, f32 masters
+    re-quantised after every update) at a width the oracle can afford for 100 steps; the
+    contractions still run on the tcgen05 kernels.  Losses within 1e-3 at every step."""
+    make = lambda: W.WideMLP(batch=256, width=256, classes=72, depth=2)
+    g0 = cuda.stats()["gemm_launched"]
+    dev, ref, tr, rm = _trajectory(cuda, oracle, make, 100, True)
+    assert cuda.stats()["gemm_launched"] - g0 >= 8 * 100
+    d = np.abs(dev - ref)
+    assert d.max() < 1e-3, (d.max(), dev[-1], ref[-1])
+    assert ref[-1] < ref[0]

@@ -18,7 +18,8 @@ pytestmark = pytest.mark.gpu
 
 def _static_sum(cuda, xbuf, n, outbuf):
     err = C.create_string_buffer(256)
-    rc = cuda.L.anl_sum_f32_static(xbuf.device_ptr, n, outbuf.device_ptr, None, err, 256)
+    # queued on the device's own stream: ordered after the upload of x, before the download of out
+    rc = cuda.L.anl_sum_f32_static(xbuf.device_ptr, n, outbuf.device_ptr, cuda.stream, err, 256)
     return rc, err.value.decode()
 
 
@@ -33,9 +34,7 @@ def test_static_sum_matches_scheduled_sum_twice(cuda):
         want = cuda.run(items, {x.node.idx: xbuf})[out_ids[0]][0]
         rc, msg = _static_sum(cuda, xbuf, n, out)
         assert rc == 0, msg
-        cuda.synchronize()     # the default stream is not the device's stream: wait before reading
-        import torch
-        torch.cuda.synchronize()
+        cuda.synchronize()
         got = out.download()[0]
         mags = float(np.abs(data.astype(np.float64)).sum())
         assert abs(float(got) - float(want)) <= 1e-5 * mags, (n, got, want)

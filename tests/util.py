@@ -21,9 +21,29 @@ def rel_err(got, want, floor=None):
     return float(np.abs(got - want).max() / scale) if want.size else 0.0
 
 
+def elementwise_err(got, want, floor=None):
+    """max over elements of |got - want| / max(|want|, floor); the floor defaults to the root mean
+    square of ``want``: an entry that cancels to nearly zero is held to the accuracy of a typical
+    entry of its buffer instead of to a relative error no finite-precision sum can meet."""
+    got = np.asarray(got, dtype=np.float64)
+    want = np.asarray(want, dtype=np.float64)
+    if not want.size:
+        return 0.0
+    if floor is None:
+        floor = float(np.sqrt(np.mean(want * want)))
+    floor = max(floor, 1e-30)
+    return float((np.abs(got - want) / np.maximum(np.abs(want), floor)).max())
+
+
+#: the per-element bound is this many times the bound on the max-normalised error: the floor is the
+#: RMS, typically a third to a fifth of the largest magnitude
+ELEMENTWISE_SLACK = 4.0
+
+
 def compare(cuda, oracle, tensors, tol, binding=None, what=""):
-    """Every final output of the schedule, CUDA against oracle, relative to the
-    output's largest magnitude."""
+    """Every final output of the schedule, CUDA against oracle: the largest error relative to the
+    output's largest magnitude must be within ``tol``, and every element's error relative to
+    max(its own magnitude, the output's RMS) within ``ELEMENTWISE_SLACK * tol``."""
     items, out_ids, inputs = schedule(tensors)
     want = oracle.run(items, inputs, binding)
     got = cuda.run(items, inputs, binding)
@@ -35,4 +55,6 @@ def compare(cuda, oracle, tensors, tol, binding=None, what=""):
         e = rel_err(got[k], want[k])
         worst = max(worst, e)
         assert e <= tol, f"{what}: buffer {k}: rel err {e:.3e} > {tol:.1e}"
+        pe = elementwise_err(got[k], want[k])
+        assert pe <= ELEMENTWISE_SLACK * tol, f"{what}: buffer {k}: element err {pe:.3e} > {ELEMENTWISE_SLACK * tol:.1e}"
     return worst, {k: got[k] for k in got}, want, out_ids
