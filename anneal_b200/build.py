@@ -11,7 +11,7 @@ LIBDIR = os.path.join(HERE, "lib")
 SO = os.path.join(LIBDIR, "libanneal_cuda.so")
 SOURCES = ["kir.cpp", "codegen.cpp", "comm.cpp", "runtime.cu", "gemm.cu", "gemm_f32.cu", "static_sum.cu", "beam.cpp"]
 NVCC = os.environ.get("NVCC", "/usr/local/cuda/bin/nvcc")
-FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a",
+FLAGS = ["-std=c++17", "-O3", "-lineinfo", "-gencode", "arch=compute_100a,code=sm_100a", "-I", LIBDIR,
          "-Xcompiler", "-fPIC,-Wall,-Wno-unused-function", "-cudart", "static"]
 
 
@@ -27,6 +27,15 @@ def build(force: bool = False, verbose: bool = False) -> str:
     if not force and not _stale():
         return SO
     os.makedirs(LIBDIR, exist_ok=True)
+    # the two-CTA contraction kernel is compiled at run time: its text travels inside the library
+    with open(os.path.join(CSRC, "gemm_pair_kernel.cuh")) as f:
+        text = f.read()
+    assert ')ANLSRC"' not in text
+    inc = os.path.join(LIBDIR, "gemm_pair_src.inc")
+    lit = 'R"ANLSRC(' + text + ')ANLSRC"\n'
+    if not os.path.exists(inc) or open(inc).read() != lit:
+        with open(inc, "w") as f:
+            f.write(lit)
     objs = []
     for src in SOURCES:
         obj = os.path.join(LIBDIR, src.rsplit(".", 1)[0] + ".o")

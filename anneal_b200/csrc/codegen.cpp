@@ -1465,6 +1465,69 @@ struct Gen {
         return true;
     }
 
+    // The elementwise kernel `it` as a device function for the contraction kernel's epilogue: eight
+    // consecutive outputs of one row at a time, paired f16 arithmetic, the value of parameter
+    // `acc_param` at the output position taken from registers instead of memory.  Only kernels the
+    // paired-f16 vector path covers qualify; everything else stays a launch of its own.
+    bool build_epilogue(int acc_param, int64_t M, int64_t Ncols, EpilogueRendered& out) {
+        if (!analyse()) return false;
+        if (!reduces.empty() || has_sym) return fail("epilogue: not a static elementwise kernel");
+        if (loop_ranges.size() != 2 || N(loop_ranges[0]).arg != M || N(loop_ranges[1]).arg != Ncols) return fail("epilogue: iteration space differs from the contraction's output");
+        if (it.bufs[0].dtype != DT_F16 || (int)it.bufs.size() > 8) return fail("epilogue: output is not f16 or too many operands");
+        std::vector<int> vloads;
+        const int V = pick_vector(vloads);
+        if (V != 8 || !h2_eligible(V)) return fail("epilogue: not a paired-f16 vector kernel");
+        reset_emit();
+        h2 = true;
+        const int r0 = loop_ranges[0], r1 = loop_ranges[1];
+        bool saw_acc = false;
+        cur_top = &prelude;
+        int vi = 0;
+        for (int i = 0; i < n; i++) {
+            if (N(i).op != OP_INDEX || i == dst || !is_live(i)) continue;
+            const int p = (int)N(N(i).src[0]).arg;
+            if (p != acc_param) continue;
+            // must be exactly the contraction's own output position
+            Lin f = flat_index(i);
+            bool ok0, ok1;
+            if (f.c != 0 || f.t.size() != 2 || lin_coef(f, r0, ok0) != Ncols || !ok0 || lin_coef(f, r1, ok1) != 1 || !ok1) return fail("epilogue: the consumer reads the contraction at another position");
+            vec_load[i] = "acc";
+            saw_acc = true;
+        }
+        if (!saw_acc) return fail("epilogue: the consumer does not read the contraction");
+        for (int i : vloads) {
+            if (vec_load.count(i)) continue;
+            const int p = (int)N(N(i).src[0]).arg;
+            Lin f = flat_index(i);
+            const std::string arr = "v" + std::to_string(vi++);
+            stmt(-1, "__half2 " + arr + "_raw[4];");
+            stmt(-1, "ldv_<__half2, 4>(reinterpret_cast<const __half2*>(data" + std::to_string(p) + " + " + render(f, -1) + "), " + arr + "_raw);");
+            vec_load[i] = arr + "_raw";
+        }
+        cur_top = nullptr;
+        vec_range = r1;
+        const std::string v = val_h2(body);
+        if (!err.empty()) return false;
+        std::ostringstream k;
+        k << "#define LANES 1\n#define TOUTS 1\n#define RC_LAYOUT 1\n" << preamble();
+        k << "__device__ __forceinline__ void epi8_(const int row, const int col, const __half2* __restrict__ acc, __half2* __restrict__ out, const void* const* ep) {\n";
+        k << "  const int r" << N(r0).aux << " = row; (void)r" << N(r0).aux << ";\n";
+        k << "  const int r" << N(r1).aux << " = col; (void)r" << N(r1).aux << ";\n";
+        out.params.clear();
+        for (int b = 1; b < (int)it.bufs.size(); b++) {
+            if (b == acc_param) continue;
+            if (it.bufs[b].dtype != DT_F16) return fail("epilogue: an operand is not f16");
+            k << "  const __half* __restrict__ data" << b << " = reinterpret_cast<const __half*>(ep[" << out.params.size() << "]);\n";
+            out.params.push_back(b);
+        }
+        if (out.params.size() > 6) return fail("epilogue: more than six operands");
+        k << prelude.code;
+        k << "  _Pragma(\"unroll\") for (int u = 0; u < 4; u++) {\n" << top.code << "    out[u] = " << v << ";\n  }\n}\n";
+        out.source = k.str();
+        out.note = "epilogue of " + std::to_string(out.params.size()) + " operands";
+        return true;
+    }
+
     bool run(Rendered& out) {
         if (!analyse()) return false;
         if (it.bufs.empty()) return fail("codegen: kernel has no output buffer");
@@ -1531,6 +1594,37 @@ bool match_contraction(const Item& item, Contraction& c) {
     c.in_dtype = item.bufs[pa].dtype;
     if (item.bufs[pb].dtype != c.in_dtype) return false;
     c.out_dtype = item.bufs[0].dtype;
+    return true;
+}
+
+bool render_gemm_epilogue(const Item& consumer, int acc_param, int64_t M, int64_t N, EpilogueRendered& out, std::string& err) {
+    CodegenOpts o;
+    Gen g(consumer, o);
+    bool ok = g.build_epilogue(acc_param, M, N, out);
+    if (!ok) err = g.err.empty() ? "epilogue: rejected" : g.err;
+    return ok && g.err.empty();
+}
+
+bool match_column_sum(const Item& item, int& src_param, int64_t& rows, int64_t& cols) {
+    CodegenOpts o;
+    Gen g(item, o);
+    if (!g.analyse() || g.has_sym) return false;
+    if (g.reduces.size() != 1 || g.reduces[0] != g.body || g.loop_ranges.size() != 1) return false;
+    const Node& red = g.N(g.body);
+    if ((int)red.aux != OP_ADD || red.dtype != DT_F16 || item.bufs[0].dtype != DT_F16) return false;
+    std::vector<int> rr;
+    for (size_t s = 1; s < red.src.size(); s++) if (g.N(red.src[s]).op == OP_RANGE) rr.push_back(red.src[s]);
+    if (rr.size() != 1) return false;
+    const int src = red.src[0];
+    if (g.N(src).op != OP_INDEX || g.N(g.N(src).src[0]).op != OP_PARAM) return false;
+    const int p = (int)g.N(g.N(src).src[0]).arg;
+    if (p < 1 || p >= (int)item.bufs.size() || item.bufs[p].dtype != DT_F16) return false;
+    const int64_t n = g.N(g.loop_ranges[0]).arg, m = g.N(rr[0]).arg;
+    Lin f = g.flat_index(src);
+    bool ok0, ok1;
+    if (f.c != 0 || f.t.size() != 2 || g.lin_coef(f, rr[0], ok0) != n || !ok0 || g.lin_coef(f, g.loop_ranges[0], ok1) != 1 || !ok1) return false;
+    if (item.bufs[p].elems(0) != m * n) return false;
+    src_param = p; rows = m; cols = n;
     return true;
 }
 

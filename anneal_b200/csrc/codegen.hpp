@@ -26,6 +26,9 @@ struct CodegenOpts {
     int vector_width = 0;      // 0 = heuristic, 1 disables 128-bit accesses
     int split = 0;             // blocks per output for KC_REDUCE_SPLIT; 0 = heuristic, 1 = never split
     bool debug_bounds = false; // clamp every load and record violations in a status word
+    // contraction kernels (0 = heuristic): tile width, ring depth, raster group (-1: none), streaming
+    // stores, one-CTA kernel forced
+    int gemm_tile_n = 0, gemm_stages = 0, gemm_group_m = 0, gemm_stream_stores = 0, gemm_single_cta = 0;
 };
 
 struct Launch {
@@ -69,6 +72,24 @@ struct Contraction {
 // Contraction selection (the schedule/kernels.go hook the CUDA device adds): true when `item`
 // is such a kernel.  Leading output ranges are folded into M when they are contiguous with it.
 bool match_contraction(const Item& item, Contraction& out);
+
+// An elementwise kernel that reads a contraction's output at the output's own position, rendered as
+// a device function for the contraction kernel's epilogue (the reference splices such a consumer
+// into the reduce kernel, schedule/schedule.go:197-233; here the splice happens at launch time, on
+// the accumulator's registers, so the scheduled kernels stay what the reference would schedule):
+//   __device__ void epi8_(int row, int col, const __half2* acc, __half2* out, const void* const* ep)
+// maps the 8 narrowed accumulator values at (row, col .. col+7) to the consumer's 8 outputs, with
+// the arithmetic of the stand-alone kernel (paired f16, bit for bit).  `params` lists the consumer's
+// other parameter numbers in the order ep[] expects them.
+struct EpilogueRendered {
+    std::string source, note;
+    std::vector<int> params;
+};
+bool render_gemm_epilogue(const Item& consumer, int acc_param, int64_t M, int64_t N, EpilogueRendered& out, std::string& err);
+
+// True when `item` is out[n] = SUM_m src[m * cols + n] over one f16 buffer with an f16 result: the
+// bias gradient of a linear layer (tensor/gradient_ruleset.go:207-233 applied to nn.go:154-162).
+bool match_column_sum(const Item& item, int& src_param, int64_t& rows, int64_t& cols);
 
 // Row chain: consecutive kernels that all iterate the same outer ("row") range, reduce only over
 // ranges inside the row, and hand each other one value per row (a softmax forward+backward is five

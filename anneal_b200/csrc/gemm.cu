@@ -17,14 +17,26 @@
 //
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in a host-visible
 // status word and the CTA drains and frees its tensor memory instead of spinning.
+//
+// This file holds the one-CTA kernel (outputs with fewer than 256 rows) and the host side of both
+// kernels.  The two-CTA kernel that the large contractions run on is gemm_pair_kernel.cuh: it is
+// compiled at run time, once per configuration (operand major-ness, tile width, ring depth, raster,
+// fused elementwise consumer), so that the consumer's generated code can sit in its epilogue and the
+// tunables are compile-time constants a search can vary.
 #include <cuda_fp16.h>
 
 #include <cstdlib>
 #include <cstring>
 
+#include "gemm_pair_kernel.cuh"      // PairGemmArgs only: the device code is compiled at run time
 #include "runtime.hpp"
 
 namespace anl {
+
+// text of gemm_pair_kernel.cuh, written beside the objects by the build step
+static const char* const kPairKernelSource =
+#include "gemm_pair_src.inc"
+    ;
 
 constexpr int BM = 128, BN = 256, BK = 64, STAGES = 4;
 constexpr int A_TILE_BYTES = BM * BK * 2;          // 16 KiB
@@ -40,8 +52,7 @@ struct GemmPlan {
     bool a_mn = false, b_mn = false;     // MN-major operands
     int64_t lda = 0, ldb = 0;            // elements between consecutive rows of the 2-D global views
     bool f32 = false;                    // f32 operands: the FP32-pipe kernel instead of tcgen05
-    int* status_host = nullptr;          // mapped, host-visible
-    int* status_dev = nullptr;
+    GemmTuning tune;                     // zero fields: heuristics
 };
 
 __device__ __forceinline__ uint32_t smem_u32(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
@@ -302,239 +313,6 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
     }
 }
 
-// ── two-CTA variant ─────────────────────────────────────────────────────────────────────────────
-// A pair of CTAs on neighbouring SMs (a cluster of 2) computes one 256x256 tile with
-// tcgen05.mma.cta_group::2: each CTA holds 128 rows of A, HALF of B (128 of the 256 columns) and
-// the 128x256 accumulator of its own rows; the tensor cores of both SMs read both halves of B.  Per
-// k-block a CTA therefore moves 32 KiB through shared memory instead of 48 KiB for the same math,
-// which is what the one-CTA kernel is short of (shared-memory bandwidth, not DRAM).  The even CTA
-// leads: it owns the "full" barriers (both CTAs' loads complete on them) and issues the MMAs; its
-// commits release the stage and publish the accumulator in both CTAs.  No load is multicast.
-constexpr int STAGES2 = 6;
-constexpr int B2_TILE_BYTES = (BN / 2) * BK * 2;               // 16 KiB: this CTA's half of B
-constexpr int SMEM2_BYTES = STAGES2 * (A_TILE_BYTES + B2_TILE_BYTES) + 1024;
-
-__device__ __forceinline__ uint32_t cluster_ctarank() { uint32_t r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
-__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
-    uint32_t r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
-}
-__device__ __forceinline__ void cluster_sync_all() {
-    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
-    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
-}
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
-}
-__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst, const CUtensorMap* map, int c0, int c1, uint32_t leader_bar) {
-    asm volatile(
-        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
-        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar) : "memory");
-}
-__device__ __forceinline__ void umma_f16_pair(uint32_t tmem_d, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
-        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
-        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
-__device__ __forceinline__ void umma_commit_pair(uint32_t cluster_bar) {
-    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
-}
-
-__device__ __forceinline__ bool mbar_wait_cluster(uint32_t bar, uint32_t parity, const volatile int* failed) {
-    // like mbar_wait, but acquires at cluster scope: the data guarded by the barrier was written by the partner CTA
-    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
-        if (failed && (i & 255u) == 255u && *failed) return false;
-        uint32_t done;
-        asm volatile(
-            "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
-            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
-        if (done) return true;
-    }
-    return false;
-}
-__device__ __forceinline__ void st_cluster_u32(uint32_t cluster_addr, int v) {
-    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
-}
-
-// BNT = tile width in columns (256, or 128 when that fills the last wave of tiles better)
-template <bool A_MN, bool B_MN, int BNT>
-__global__ void __launch_bounds__(GEMM_THREADS, 1)
-gemm_f16_tcgen05_pair(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_b, const GemmArgs g) {
-    extern __shared__ uint8_t smem_raw[];
-    __shared__ __align__(8) uint64_t full_bar[STAGES2], empty_bar[STAGES2], acc_full[2], acc_empty[2];
-    // tile queue: the leader's producer draws tile numbers from the global counter and publishes each
-    // one in both CTAs; a slot is recycled once all ten consumers of the pair have read it
-    __shared__ __align__(8) uint64_t tq_full[TQ], tq_empty[TQ];
-    __shared__ int tile_ring[TQ];
-    __shared__ uint32_t tmem_base_slot;
-    __shared__ volatile int failed;
-
-    constexpr int BHALF_BYTES = (BNT / 2) * BK * 2;            // this CTA's half of the B tile
-    constexpr int STAGE_B = A_TILE_BYTES + BHALF_BYTES;
-    const uint32_t smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const uint32_t rank = cluster_ctarank();            // 0 leads
-    const int tiles_m = (g.M + 2 * BM - 1) / (2 * BM);
-    const int num_tiles = tiles_m * g.tiles_n;
-    const int kblocks = (g.K + BK - 1) / BK;
-
-    if (threadIdx.x == 0) {
-        for (int s = 0; s < STAGES2; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 8); }
-        for (int q = 0; q < TQ; q++) { mbar_init(smem_u32(&tq_full[q]), 1); mbar_init(smem_u32(&tq_empty[q]), 10); }
-        failed = 0;
-        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-    }
-    if (warp == 1) {
-        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
-        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    cluster_sync_all();                                  // both CTAs' barriers exist before any remote signal
-    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-    const uint32_t tmem_base = tmem_base_slot;
-
-    if (warp == 0) {
-        if (lane == 0) {
-            uint32_t stage = 0, phase = 0;
-            bool ok = true;
-            uint32_t qs = 0, qphase = 0;
-            int next = rank == 0 ? atomicAdd(g.tile_counter, 1) : 0;
-            while (ok) {
-                int t;
-                if (rank == 0) {
-                    if (!mbar_wait(smem_u32(&tq_empty[qs]), qphase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 15; break; }
-                    t = next;
-                    if (t >= num_tiles) t = -1;
-                    else next = atomicAdd(g.tile_counter, 1);
-                    tile_ring[qs] = t;
-                    st_cluster_u32(map_to_cta(smem_u32(&tile_ring[qs]), 1), t);
-                    mbar_arrive(smem_u32(&tq_full[qs]));
-                    mbar_arrive_cluster(map_to_cta(smem_u32(&tq_full[qs]), 1));
-                } else {
-                    if (!mbar_wait_cluster(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; *(volatile int*)g.status = 16; break; }
-                    t = *(volatile int*)&tile_ring[qs];
-                    mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
-                }
-                if (++qs == TQ) { qs = 0; qphase ^= 1; }
-                if (t < 0) { if (rank == 0) retire_tile_counter(g.tile_counter, (int)gridDim.x / 2); break; }
-                const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM;          // this CTA's rows of A
-                const int n0 = (t / tiles_m) * BNT + (int)rank * (BNT / 2);          // this CTA's half of B
-                for (int kb = 0; kb < kblocks; kb++) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
-                    const uint32_t own_fb = smem_u32(&full_bar[stage]);
-                    const uint32_t fb = map_to_cta(own_fb, 0);                     // loads of both CTAs complete on the leader's barrier
-                    const uint32_t sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
-                    if (rank == 0) mbar_expect_tx(own_fb, 2 * STAGE_B);
-                    const int k0 = kb * BK;
-                    if (A_MN) { for (int j = 0; j < BM / 64; j++) tma_load_2d_pair(sa + j * (BK * 128), &map_a, m0 + 64 * j, k0, fb); }
-                    else tma_load_2d_pair(sa, &map_a, k0, m0, fb);
-                    if (B_MN) { for (int j = 0; j < BNT / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
-                    else tma_load_2d_pair(sb, &map_b, k0, n0, fb);
-                    if (++stage == STAGES2) { stage = 0; phase ^= 1; }
-                }
-            }
-            if (!ok) failed = 1;
-        }
-    } else if (warp == 1) {
-        if (lane == 0 && rank == 0) {
-            // M = 256 across the pair (M >> 4 = 16 at bit 24), N = 256
-            const uint32_t idesc = (1u << 4) | ((A_MN ? 1u : 0u) << 15) | ((B_MN ? 1u : 0u) << 16) | ((uint32_t)(BNT >> 3) << 17) | ((uint32_t)((2 * BM) >> 4) << 24);
-            uint32_t stage = 0, phase = 0, acc = 0, acc_phase = 0;
-            bool ok = true;
-            uint32_t qs = 0, qphase = 0;
-            while (ok) {
-                if (!mbar_wait(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; *(volatile int*)g.status = 17; break; }
-                const int t = tile_ring[qs];
-                mbar_arrive(smem_u32(&tq_empty[qs]));
-                if (++qs == TQ) { qs = 0; qphase ^= 1; }
-                if (t < 0) break;
-                if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const uint32_t tmem_d = tmem_base + acc * BNT;
-                for (int kb = 0; kb < kblocks; kb++) {
-                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 13; break; }
-                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const uint32_t sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
-#pragma unroll
-                    for (int k = 0; k < BK / 16; k++) {
-                        const uint64_t ad = A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
-                        const uint64_t bd = B_MN ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
-                        umma_f16_pair(tmem_d, ad, bd, idesc, (kb | k) != 0);
-                    }
-                    const uint32_t eb = smem_u32(&empty_bar[stage]);
-                    umma_commit_pair(map_to_cta(eb, 0));       // frees the stage here ...
-                    umma_commit_pair(map_to_cta(eb, 1));       // ... and in the partner CTA
-                    if (++stage == STAGES2) { stage = 0; phase ^= 1; }
-                }
-                if (!ok) break;
-                const uint32_t af = smem_u32(&acc_full[acc]);
-                umma_commit_pair(map_to_cta(af, 0));
-                umma_commit_pair(map_to_cta(af, 1));
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-            }
-            if (!ok) failed = 1;
-        }
-    } else {
-        const int quad = warp & 3;
-        uint32_t acc = 0, acc_phase = 0;
-        bool ok = true;
-        uint32_t qs = 0, qphase = 0;
-        while (ok) {
-            if (!mbar_wait_cluster(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 18; failed = 1; } break; }
-            const int t = *(volatile int*)&tile_ring[qs];
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
-            if (++qs == TQ) { qs = 0; qphase ^= 1; }
-            if (t < 0) break;
-            const int m0 = (t % tiles_m) * (2 * BM) + (int)rank * BM, n0 = (t / tiles_m) * BNT;
-            if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-            const int row = m0 + quad * 32 + lane;
-            __half* drow = g.d + (size_t)row * g.ldd + n0;
-            const bool row_ok = row < g.M;
-            const bool vec_ok = (g.ldd % 8 == 0);
-#pragma unroll 1
-            for (int c = 0; c < BNT / 32; c++) {
-                uint32_t v[32];
-                tmem_ld32(tmem_base + ((uint32_t)(quad * 32) << 16) + acc * BNT + c * 32, v);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                const int col = n0 + c * 32;
-                if (!row_ok || col >= g.N) continue;
-                if (vec_ok && col + 32 <= g.N) {
-                    uint4* dst = reinterpret_cast<uint4*>(drow + c * 32);
-#pragma unroll
-                    for (int q = 0; q < 4; q++) {
-                        __half2 h0 = __floats2half2_rn(__uint_as_float(v[q * 8 + 0]), __uint_as_float(v[q * 8 + 1]));
-                        __half2 h1 = __floats2half2_rn(__uint_as_float(v[q * 8 + 2]), __uint_as_float(v[q * 8 + 3]));
-                        __half2 h2 = __floats2half2_rn(__uint_as_float(v[q * 8 + 4]), __uint_as_float(v[q * 8 + 5]));
-                        __half2 h3 = __floats2half2_rn(__uint_as_float(v[q * 8 + 6]), __uint_as_float(v[q * 8 + 7]));
-                        uint4 o;
-                        o.x = *reinterpret_cast<uint32_t*>(&h0); o.y = *reinterpret_cast<uint32_t*>(&h1);
-                        o.z = *reinterpret_cast<uint32_t*>(&h2); o.w = *reinterpret_cast<uint32_t*>(&h3);
-                        dst[q] = o;
-                    }
-                } else {
-#pragma unroll
-                    for (int j = 0; j < 32; j++)
-                        if (col + j < g.N) drow[c * 32 + j] = __float2half_rn(__uint_as_float(v[j]));
-                }
-            }
-            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-            __syncwarp();
-            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));   // the leader waits for both CTAs' epilogues
-            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
-        }
-    }
-    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
-    __syncthreads();
-    cluster_sync_all();                                  // the leader's MMAs read the partner's shared memory: leave together
-    if (warp == 1) {
-        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
-    }
-}
 
 static int encode_map(anl_device* dev, CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
                       uint32_t box_inner, uint32_t box_outer) {
@@ -549,7 +327,65 @@ static int encode_map(anl_device* dev, CUtensorMap* map, const void* base, uint6
     return ANL_OK;
 }
 
-int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
+// Host-visible status word and tile counters of this device.  A launch draws tile numbers from the
+// counter that belongs to its stream, so contractions queued on different streams cannot disturb
+// each other's draw; launches on one stream run one after the other and share one.
+static int ensure_gemm_state(anl_device* dev) {
+    if (!dev->gemm_status_host) {
+        if (cudaHostAlloc((void**)&dev->gemm_status_host, 64, cudaHostAllocMapped) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot allocate the status word");
+        *dev->gemm_status_host = 0;
+        if (cudaHostGetDevicePointer((void**)&dev->gemm_status_dev, dev->gemm_status_host, 0) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot map the status word");
+    }
+    if (!dev->gemm_tile_counter) {
+        const size_t bytes = (size_t)anl_device::kGemmCounterSlots * 256;
+        if (cudaMalloc((void**)&dev->gemm_tile_counter, bytes) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot allocate the tile counters");
+        if (cudaMemset(dev->gemm_tile_counter, 0, bytes) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot clear the tile counters");   // launches leave them zeroed again
+    }
+    if (!dev->gemm_attr_set) {
+        cudaFuncSetAttribute(gemm_f16_tcgen05<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        cudaFuncSetAttribute(gemm_f16_tcgen05<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
+        dev->gemm_attr_set = true;
+    }
+    return ANL_OK;
+}
+
+static int* tile_counter_for(anl_device* dev, cudaStream_t stream) {
+    int slot = -1;
+    for (size_t k = 0; k < dev->gemm_counter_streams.size(); k++) if (dev->gemm_counter_streams[k] == stream) slot = (int)k;
+    if (slot < 0) {
+        if ((int)dev->gemm_counter_streams.size() < anl_device::kGemmCounterSlots) { dev->gemm_counter_streams.push_back(stream); slot = (int)dev->gemm_counter_streams.size() - 1; }
+        else slot = 0;      // more streams than slots: those share the first one (never the case for this runtime's three)
+    }
+    return dev->gemm_tile_counter + slot * 64;
+}
+
+// A barrier wait that ran out leaves its code in the status word and the tile counters undefined (a
+// CTA that gives up does not sign off).  Called where the host has just waited for the device: report
+// once, clear the word and zero the counters so that later launches, replays included, start clean.
+int gemm_check_status(anl_device* dev) {
+    if (!dev->gemm_status_host || *dev->gemm_status_host == 0) return ANL_OK;
+    const int code = *dev->gemm_status_host;
+    cudaDeviceSynchronize();
+    if (dev->gemm_tile_counter) cudaMemset(dev->gemm_tile_counter, 0, (size_t)anl_device::kGemmCounterSlots * 256);
+    *dev->gemm_status_host = 0;
+    return dev->fail(ANL_ERR_CUDA, "gemm: a launch timed out on a barrier (code " + std::to_string(code) + "); its output is incomplete");
+}
+
+// Test hook: puts the device in the state a timed-out barrier wait leaves behind (a code in the
+// status word, a tile counter that was not signed off), without making any wait run out.
+int gemm_inject_status(anl_device* dev, int code, int counter_value) {
+    if (int rc = ensure_gemm_state(dev)) return rc;
+    cudaStreamSynchronize(dev->stream);
+    int words[2] = {counter_value, 0};
+    for (int k = 0; k < anl_device::kGemmCounterSlots; k++)
+        if (cudaMemcpy(dev->gemm_tile_counter + k * 64, words, sizeof words, cudaMemcpyHostToDevice) != cudaSuccess) return dev->fail(ANL_ERR_CUDA, "gemm: cannot write the tile counter");
+    *dev->gemm_status_host = code;
+    return ANL_OK;
+}
+
+int plan_gemm(const Item& item, const GemmTuning& tune, Plan& plan) {
     Contraction c;
     if (!match_contraction(item, c)) return ANL_ERR_UNSUPPORTED;
     const bool dynamic = c.m_sym || c.k_sym;
@@ -573,6 +409,7 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
     if (c.M < 64 || c.N < 64 || c.K < 32) return ANL_ERR_UNSUPPORTED;          // not worth a 128x256 tile
     auto gp = std::make_shared<GemmPlan>();
     gp->c = c;
+    gp->tune = tune;
     // A: either k contiguous (K-major, row stride a_sm) or m contiguous (MN-major, row stride a_sk)
     if (c.a_sk == 1 && c.a_sm >= c.K) { gp->a_mn = false; gp->lda = c.a_sm; }
     else if (c.a_sm == 1 && c.a_sk >= c.M) { gp->a_mn = true; gp->lda = c.a_sk; }
@@ -583,31 +420,6 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
     // TMA: 16-byte aligned bases and row strides
     if (gp->lda % 8 || gp->ldb % 8 || c.a_off % 8 || c.b_off % 8) return ANL_ERR_UNSUPPORTED;
     if (c.M >= (1ll << 31) || c.N >= (1ll << 31) || c.K >= (1ll << 31)) return ANL_ERR_UNSUPPORTED;
-    static int* status_host = nullptr;
-    static int* status_dev = nullptr;
-    if (!status_host) {
-        if (cudaHostAlloc((void**)&status_host, 64, cudaHostAllocMapped) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
-        *status_host = 0;
-        if (cudaHostGetDevicePointer((void**)&status_dev, status_host, 0) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
-    }
-    gp->status_host = status_host; gp->status_dev = status_dev;
-    if (!dev->gemm_tile_counter) {
-        if (cudaMalloc((void**)&dev->gemm_tile_counter, 256) != cudaSuccess) return ANL_ERR_UNSUPPORTED;
-        if (cudaMemset(dev->gemm_tile_counter, 0, 256) != cudaSuccess) return ANL_ERR_UNSUPPORTED;   // launches leave it zeroed again
-    }
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaFuncSetAttribute(gemm_f16_tcgen05<false, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        cudaFuncSetAttribute(gemm_f16_tcgen05<false, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        cudaFuncSetAttribute(gemm_f16_tcgen05<true, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-        cudaFuncSetAttribute(gemm_f16_tcgen05<true, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM_BYTES);
-#define ANL_PAIR_ATTR(AM, BM_) \
-        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<AM, BM_, 256>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES); \
-        cudaFuncSetAttribute(gemm_f16_tcgen05_pair<AM, BM_, 128>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM2_BYTES);
-        ANL_PAIR_ATTR(false, false) ANL_PAIR_ATTR(false, true) ANL_PAIR_ATTR(true, false) ANL_PAIR_ATTR(true, true)
-#undef ANL_PAIR_ATTR
-        attr_set = true;
-    }
     plan.gemm = gp;
     plan.r.klass = KC_GEMM;
     plan.r.note = std::string("gemm tcgen05 ") + (gp->a_mn ? "A:MN" : "A:K") + (gp->b_mn ? " B:MN" : " B:K") + " M=" + std::to_string(c.M) + " N=" + std::to_string(c.N) + " K=" + std::to_string(c.K);
@@ -615,12 +427,12 @@ int plan_gemm(anl_device* dev, const Item& item, Plan& plan) {
 }
 
 // SMs the persistent GEMM may occupy.  When gradients are reduced while the backward pass is still
-// running, a few SMs are left free so that the collective's blocks (and the update kernels behind
-// them) find a place at once instead of waiting for a 150-SM persistent grid to drain.
+// running, a few SMs can be left free so that the collective's blocks (and the update kernels behind
+// them) find a place at once instead of waiting for a persistent grid to drain.
 static int gemm_sm_budget(anl_device* dev) {
-    static const int env = std::getenv("ANNEAL_GEMM_SMS") ? std::atoi(std::getenv("ANNEAL_GEMM_SMS")) : 0;
+    if (!dev) return 148;                                  // rendering without a device: a B200's count
     int sms = dev->prop.multiProcessorCount;
-    int want = env > 0 ? env : (dev->nranks > 1 ? sms - dev->comm_reserved_sms : sms);
+    int want = dev->nranks > 1 ? sms - dev->comm_reserved_sms : sms;
     want = std::max(2, std::min(want, sms));
     return want & ~1;
 }
@@ -643,7 +455,84 @@ bool gemm_taken(const Plan& plan, int64_t sym_value) {
     return gemm_f32_worth(c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K);
 }
 
-int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream, int64_t m_begin, int64_t m_end) {
+bool gemm_pair_eligible(const Plan& plan) {
+    if (!plan.gemm || plan.gemm_dynamic || plan.r.klass != KC_GEMM || plan.gemm->f32) return false;
+    const Contraction& c = plan.gemm->c;
+    return plan.gemm->tune.single_cta == 0 && c.M >= 2 * BM && c.N >= BN / 2;
+}
+void gemm_shape(const Plan& plan, int64_t* M, int64_t* N, int64_t* K) { *M = plan.gemm->c.M; *N = plan.gemm->c.N; *K = plan.gemm->c.K; }
+
+// ── the run-time compiled two-CTA kernel ──────────────────────────────────────────────────────
+namespace {
+
+struct PairVariant { int bnt, stages, group_m, stream_stores; bool a_mn, b_mn; };
+
+int pair_smem_bytes(int bnt, int stages) { return stages * (A_TILE_BYTES + (bnt / 2) * BK * 2) + 1024; }
+
+// ring depth that fits beside the static barriers: 227 KiB per CTA
+int max_stages(int bnt) { int s = 8; while (s > 2 && pair_smem_bytes(bnt, s) > 227 * 1024 - 512) s--; return s; }
+
+std::string pair_source(const PairVariant& v, const std::string& epilogue) {
+    std::string s;
+    s += "#define ANL_PAIR_GEMM_DEVICE_CODE 1\n";
+    s += "#define CFG_A_MN " + std::to_string(v.a_mn ? 1 : 0) + "\n#define CFG_B_MN " + std::to_string(v.b_mn ? 1 : 0) + "\n";
+    s += "#define CFG_BNT " + std::to_string(v.bnt) + "\n#define CFG_STAGES " + std::to_string(v.stages) + "\n";
+    s += "#define CFG_GROUP_M " + std::to_string(v.group_m) + "\n#define CFG_STREAM_STORES " + std::to_string(v.stream_stores) + "\n";
+    s += "#define CFG_EPI " + std::string(epilogue.empty() ? "0" : "1") + "\n";
+    s += epilogue;
+    s += kPairKernelSource;
+    return s;
+}
+
+int get_pair_kernel(anl_device* dev, const PairVariant& v, const std::string& epilogue, CUfunction* fn) {
+    std::shared_ptr<Module> m;
+    if (int rc = compile_source(dev, pair_source(v, epilogue), m)) return rc;
+    auto f = m->fn.find("gemm_f16_tcgen05_pair");
+    if (f != m->fn.end()) { *fn = f->second; return ANL_OK; }
+    CUresult cr = dev->drv.ModuleGetFunction(fn, m->mod, "gemm_f16_tcgen05_pair");
+    if (cr != CUDA_SUCCESS) return dev->fail(ANL_ERR_CUDA, "gemm: pair kernel entry point missing");
+    cr = dev->drv.FuncSetAttribute(*fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, pair_smem_bytes(v.bnt, v.stages));
+    if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return dev->fail(ANL_ERR_CUDA, std::string("gemm: cuFuncSetAttribute: ") + (e ? e : "?")); }
+    m->fn["gemm_f16_tcgen05_pair"] = *fn;
+    return ANL_OK;
+}
+
+PairVariant choose_variant(anl_device* dev, const GemmPlan& gp, int64_t M) {
+    const Contraction& c = gp.c;
+    PairVariant v{};
+    v.a_mn = gp.a_mn; v.b_mn = gp.b_mn;
+    const int npairs = gemm_sm_budget(dev) / 2;
+    const int tm2 = (int)((M + 2 * BM - 1) / (2 * BM));
+    if (gp.tune.tile_n == 128 || gp.tune.tile_n == 256) v.bnt = gp.tune.tile_n;
+    else {
+        // The narrow tile fills the last wave of tiles better but stages 1.5x the bytes per flop and
+        // measured 25% slower on 4096x4096x8192 (it becomes L2-bound), so it is only taken when the
+        // wide tile would leave most pairs idle.
+        auto fill = [&](int bnt) { long long t = (long long)tm2 * ((c.N + bnt - 1) / bnt); long long w = (t + npairs - 1) / npairs; return (double)t / (double)(w * npairs); };
+        v.bnt = (fill(128) * 0.7 > fill(256)) ? 128 : 256;
+    }
+    v.stages = gp.tune.stages > 0 ? std::max(2, std::min(gp.tune.stages, max_stages(v.bnt))) : std::min(6, max_stages(v.bnt));
+    v.group_m = gp.tune.group_m > 0 ? gp.tune.group_m : (gp.tune.group_m < 0 ? 0 : kDefaultGroupM);
+    v.stream_stores = gp.tune.stream_stores > 0 ? 1 : 0;
+    return v;
+}
+
+}  // namespace
+
+int gemm_pair_source(anl_device* dev, const Plan& plan, const std::string& epilogue, std::string& out) {
+    if (!gemm_pair_eligible(plan)) return ANL_ERR_UNSUPPORTED;
+    out = pair_source(choose_variant(dev, *plan.gemm, plan.gemm->c.M), epilogue);
+    return ANL_OK;
+}
+
+int gemm_prepare(anl_device* dev, const Plan& plan, const std::string& epilogue) {
+    if (!gemm_pair_eligible(plan)) return ANL_OK;
+    CUfunction fn;
+    return get_pair_kernel(dev, choose_variant(dev, *plan.gemm, plan.gemm->c.M), epilogue, &fn);
+}
+
+int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream, int64_t m_begin, int64_t m_end,
+                const GemmFusion* fusion) {
     const GemmPlan& gp = *plan.gemm;
     const Contraction& c = gp.c;
     // an optional row window [m_begin, m_end) of the output: the caller splits a contraction so that
@@ -651,11 +540,13 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
     const bool window = m_end >= 0;
     if (window && (gp.f32 || c.m_sym || m_begin < 0 || m_end > c.M || m_begin >= m_end || (m_begin % 8)))
         return dev->fail(ANL_ERR_INVALID, "gemm: bad row window");
+    if (fusion && (window || gp.f32)) return dev->fail(ANL_ERR_INVALID, "gemm: a fused consumer needs the whole f16 contraction");
     const int64_t M = window ? m_end - m_begin : c.M;
     if (gp.f32)
         return launch_gemm_f32(dev, (const float*)bufs[c.a_param] + c.a_off, (const float*)bufs[c.b_param] + c.b_off, (float*)bufs[0],
                                c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K, c.a_sm, c.a_sk, c.b_sn, c.b_sk, stream);
-    if (*gp.status_host != 0) return dev->fail(ANL_ERR_CUDA, "gemm: an earlier launch timed out on a barrier (code " + std::to_string(*gp.status_host) + ")");
+    if (int rc = ensure_gemm_state(dev)) return rc;
+    if (*dev->gemm_status_host != 0) return dev->fail(ANL_ERR_CUDA, "gemm: an earlier launch timed out on a barrier (code " + std::to_string(*dev->gemm_status_host) + ")");
     const __half* a = (const __half*)bufs[c.a_param] + c.a_off + (window ? m_begin * c.a_sm : 0);
     const __half* b = (const __half*)bufs[c.b_param] + c.b_off;
     CUtensorMap ma, mb;
@@ -663,6 +554,44 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
     if (gp.a_mn) rc = encode_map(dev, &ma, a, (uint64_t)M, (uint64_t)c.K, (uint64_t)gp.lda, 64, BK);
     else rc = encode_map(dev, &ma, a, (uint64_t)c.K, (uint64_t)M, (uint64_t)gp.lda, BK, BM);
     if (rc) return rc;
+    int* const counter = tile_counter_for(dev, stream);
+    if (gemm_pair_eligible(plan) && M >= 2 * BM) {
+        const PairVariant v = choose_variant(dev, gp, M);
+        // B is loaded in halves of bnt/2 columns, so its tensor map gets a box of that many rows
+        if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
+        else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, v.bnt / 2);
+        if (rc) return rc;
+        CUfunction fn;
+        if ((rc = get_pair_kernel(dev, v, fusion && fusion->epilogue ? *fusion->epilogue : std::string(), &fn))) return rc;
+        PairGemmArgs g{};
+        __half* out0 = (__half*)bufs[0] + (window ? m_begin * c.N : 0);
+        g.d_raw = (!fusion || fusion->store_raw) ? out0 : nullptr;
+        g.d_out = fusion ? fusion->d_out : nullptr;
+        g.colsum = fusion ? fusion->colsum : nullptr;
+        if (fusion) for (int k = 0; k < 6; k++) g.ep[k] = fusion->ep[k];
+        g.M = (int)M; g.N = (int)c.N; g.K = (int)c.K; g.ldd = (int)c.N;
+        g.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM)); g.tiles_n = (int)((c.N + v.bnt - 1) / v.bnt);
+        g.status = dev->gemm_status_dev;
+        g.tile_counter = counter;
+        const int npairs = gemm_sm_budget(dev) / 2;
+        const int pairs = std::min(g.tiles_m * g.tiles_n, npairs);
+        CUlaunchConfig cfg{};
+        cfg.gridDimX = 2 * pairs; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+        cfg.blockDimX = GEMM_THREADS; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+        cfg.sharedMemBytes = pair_smem_bytes(v.bnt, v.stages);
+        cfg.hStream = (CUstream)stream;
+        CUlaunchAttribute at[1];
+        at[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+        at[0].value.clusterDim.x = 2; at[0].value.clusterDim.y = 1; at[0].value.clusterDim.z = 1;
+        cfg.attrs = at; cfg.numAttrs = 1;
+        void* params[3] = {&ma, &mb, &g};
+        CUresult cr = dev->drv.LaunchKernelEx(&cfg, fn, params, nullptr);
+        if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return dev->fail(ANL_ERR_CUDA, std::string("gemm: pair launch: ") + (e ? e : "?")); }
+        dev->stats.kernels_launched++;
+        dev->stats.gemm_launched++;
+        return ANL_OK;
+    }
+    if (fusion) return dev->fail(ANL_ERR_INVALID, "gemm: a fused consumer needs the two-CTA kernel");
     if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
     else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, BN);
     if (rc) return rc;
@@ -670,48 +599,8 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
     g.d = (__half*)bufs[0] + (window ? m_begin * c.N : 0);
     g.M = (int)M; g.N = (int)c.N; g.K = (int)c.K; g.ldd = (int)c.N;
     g.tiles_m = (int)((M + BM - 1) / BM); g.tiles_n = (int)((c.N + BN - 1) / BN);
-    g.status = gp.status_dev;
-    g.tile_counter = dev->gemm_tile_counter;
-    static const bool pair_ok = std::getenv("ANNEAL_GEMM_PAIR") ? std::atoi(std::getenv("ANNEAL_GEMM_PAIR")) != 0 : true;
-    if (pair_ok && M >= 2 * BM && c.N >= BN / 2) {
-        // two-CTA tiles, 256 rows by 256 or 128 columns.  The narrow tile fills the last wave of tiles
-        // better but stages 1.5x the bytes per flop and measured 25% slower on 4096x4096x8192 (it
-        // becomes L2-bound), so it is only taken when the wide tile would leave most pairs idle.
-        const int npairs = gemm_sm_budget(dev) / 2;
-        const int tm2 = (int)((M + 2 * BM - 1) / (2 * BM));
-        auto fill = [&](int bnt) { long long t = (long long)tm2 * ((c.N + bnt - 1) / bnt); long long w = (t + npairs - 1) / npairs; return (double)t / (double)(w * npairs); };
-        const int bnt = (fill(128) * 0.7 > fill(256)) ? 128 : 256;
-        // B is loaded in halves of bnt/2 columns, so its tensor map gets a box of that many rows
-        if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
-        else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, bnt / 2);
-        if (rc) return rc;
-        g.tiles_n = (int)((c.N + bnt - 1) / bnt);
-        int tiles2 = tm2 * g.tiles_n;
-        int pairs = std::min(tiles2, npairs);
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(2 * pairs); cfg.blockDim = dim3(GEMM_THREADS); cfg.dynamicSmemBytes = SMEM2_BYTES; cfg.stream = stream;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension; at[0].val.clusterDim.x = 2; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
-        cfg.attrs = at; cfg.numAttrs = 1;
-        cudaError_t le;
-#define ANL_PAIR_LAUNCH(AM, BM_, W) cudaLaunchKernelEx(&cfg, gemm_f16_tcgen05_pair<AM, BM_, W>, ma, mb, g)
-        if (bnt == 256) {
-            if (gp.a_mn && gp.b_mn) le = ANL_PAIR_LAUNCH(true, true, 256);
-            else if (gp.a_mn) le = ANL_PAIR_LAUNCH(true, false, 256);
-            else if (gp.b_mn) le = ANL_PAIR_LAUNCH(false, true, 256);
-            else le = ANL_PAIR_LAUNCH(false, false, 256);
-        } else {
-            if (gp.a_mn && gp.b_mn) le = ANL_PAIR_LAUNCH(true, true, 128);
-            else if (gp.a_mn) le = ANL_PAIR_LAUNCH(true, false, 128);
-            else if (gp.b_mn) le = ANL_PAIR_LAUNCH(false, true, 128);
-            else le = ANL_PAIR_LAUNCH(false, false, 128);
-        }
-#undef ANL_PAIR_LAUNCH
-        if (le != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm: pair launch: ") + cudaGetErrorString(le));
-        dev->stats.kernels_launched++;
-        dev->stats.gemm_launched++;
-        return ANL_OK;
-    }
+    g.status = dev->gemm_status_dev;
+    g.tile_counter = counter;
     int tiles = g.tiles_m * g.tiles_n;
     int grid = std::min(tiles, gemm_sm_budget(dev));
     if (gp.a_mn && gp.b_mn) gemm_f16_tcgen05<true, true><<<grid, GEMM_THREADS, SMEM_BYTES, stream>>>(ma, mb, g);
@@ -722,6 +611,25 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
     if (e != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm: launch: ") + cudaGetErrorString(e));
     dev->stats.kernels_launched++;
     dev->stats.gemm_launched++;
+    return ANL_OK;
+}
+
+// Finishes a bias gradient whose per-32-row partial column sums a contraction's epilogue left in
+// `partials` [parts, N]: ascending sum in f32, one narrowing to f16 — the arithmetic of the REDUCE the
+// schedule holds for it (f32 accumulator, narrowed once), with the rows grouped by 32.
+__global__ void __launch_bounds__(256) colsum_finish(const float* __restrict__ partials, int parts, int n, __half* __restrict__ out) {
+    const int col = blockIdx.x * blockDim.x + threadIdx.x;
+    if (col >= n) return;
+    float acc = 0.0f;
+    for (int p = 0; p < parts; p++) acc = acc + partials[(size_t)p * n + col];
+    out[col] = __float2half_rn(acc);
+}
+
+int launch_colsum_finish(anl_device* dev, const float* partials, int64_t parts, int64_t n, void* out, cudaStream_t stream) {
+    colsum_finish<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(partials, (int)parts, (int)n, (__half*)out);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm: column-sum finish: ") + cudaGetErrorString(e));
+    dev->stats.kernels_launched++;
     return ANL_OK;
 }
 

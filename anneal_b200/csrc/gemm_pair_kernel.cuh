@@ -1,0 +1,416 @@
+// Two-CTA tcgen05 contraction kernel, compiled at run time (NVRTC, sm_100a) once per configuration.
+//
+//   D[M,N] = sum_k A[m,k] * B[n,k]   f16 operands, f32 accumulation in tensor memory, ONE rounding
+//   to f16 (the arithmetic of an f16 REDUCE in the reference: f32 accumulator, operands widened,
+//   narrowed once, codegen/lower.go:654-719), then — optionally — the elementwise kernel that the
+//   schedule runs next on that value (bias add, GELU, the GELU-backward product), evaluated on the
+//   narrowed value in the accumulator's registers exactly as the separate kernel would evaluate it
+//   after reading it back (the reference fuses such consumers into the reduce kernel itself,
+//   schedule/schedule.go:197-233), and — optionally — per-32-row partial column sums of what was
+//   stored (the bias gradient that the schedule computes from it with a REDUCE over the rows).
+//
+// A pair of CTAs on neighbouring SMs (a cluster of 2) computes one 256 x BNT tile with
+// tcgen05.mma.cta_group::2: each CTA stages its 128 rows of A and HALF of the B tile and holds the
+// 128 x BNT accumulator of its own rows; the tensor cores of both SMs read both halves of B.  The
+// even CTA leads: it owns the "full" barriers (both CTAs' TMA loads complete on them) and issues the
+// MMAs; its commits release the stage and publish the accumulator in both CTAs.  No load is
+// multicast: every CTA issues its own.  Warp roles: 0 TMA producer, 1 MMA issuer (owns the tensor
+// memory allocation), 2-5 epilogue (one 32-lane quadrant of tensor memory each).  Two accumulators
+// let the epilogue of tile i run under the main loop of tile i+1.  Tile numbers are drawn from a
+// global counter, so a pair that starts late (its SMs were busy with a collective) takes fewer.
+//
+// Every wait on an mbarrier is bounded; a wait that runs out records a code in a host-visible status
+// word, the roles of the CTA drain and the tensor memory is freed.
+//
+// The host prepends the configuration:
+//   CFG_A_MN, CFG_B_MN   1 when the operand's m / n index is the contiguous one (else k is)
+//   CFG_BNT              tile width in columns: 256 or 128
+//   CFG_STAGES           depth of the shared-memory ring of k-blocks
+//   CFG_GROUP_M          raster: tiles are numbered down groups of this many tile rows, so the pairs
+//                        working at the same time share few A row blocks AND few B column blocks
+//                        (0: down whole columns of tiles)
+//   CFG_EPI              1 when a fused elementwise consumer epi8_() has been prepended
+//   CFG_STREAM_STORES    1: outputs are written with the streaming hint (they are not read again by
+//                        this kernel and should not push operand tiles out of L2)
+// and, when CFG_EPI is 1, the text of
+//   __device__ void epi8_(int row, int col, const __half2* acc, __half2* out, const void* const* ep)
+// which maps 8 consecutive narrowed values acc[0..3] at (row, col..col+7) to the 8 outputs.
+#pragma once
+
+struct PairGemmArgs {
+    void* d_raw;            // [M, ldd] f16: the contraction itself; null when nothing else reads it
+    void* d_out;            // [M, ldd] f16: output of the fused consumer; null without one
+    float* colsum;          // [ceil(M/32), N] f32 partial column sums of the last value stored; null when not wanted
+    const void* ep[6];      // operands of the fused consumer, in its parameter order
+    int M, N, K, ldd;
+    int tiles_m, tiles_n;   // in 256-row pair tiles and BNT-column tiles
+    int* status;
+    int* tile_counter;      // [0] next tile number, [1] pairs that have signed off; both zero between launches
+};
+
+#ifdef ANL_PAIR_GEMM_DEVICE_CODE
+
+#include <cuda_fp16.h>
+
+struct alignas(64) TensorMap { unsigned long long opaque[16]; };
+
+constexpr int BM = 128, BK = 64;
+constexpr int BNT = CFG_BNT, NSTAGE = CFG_STAGES;
+constexpr int A_TILE_BYTES = BM * BK * 2;
+constexpr int BHALF_BYTES = (BNT / 2) * BK * 2;
+constexpr int STAGE_B = A_TILE_BYTES + BHALF_BYTES;
+constexpr int TQ = 4;
+constexpr unsigned WAIT_LIMIT = 1u << 20;
+
+__device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void mbar_init(unsigned bar, unsigned count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+__device__ __forceinline__ void mbar_expect_tx(unsigned bar, unsigned bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive(unsigned bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(unsigned cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+// Bounded waits: false when the phase did not complete within WAIT_LIMIT polls, or when another
+// role of this CTA has already given up (`failed`, in shared memory).
+__device__ __forceinline__ bool mbar_wait(unsigned bar, unsigned parity, const volatile int* failed) {
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        if (failed && (i & 255u) == 255u && *failed) return false;
+        unsigned done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ bool mbar_wait_cluster(unsigned bar, unsigned parity, const volatile int* failed) {
+    // acquires at cluster scope: the data guarded by the barrier was written by the partner CTA
+    for (unsigned i = 0; i < WAIT_LIMIT; i++) {
+        if (failed && (i & 255u) == 255u && *failed) return false;
+        unsigned done;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.b32 %0, 1, 0, p;\n}\n"
+            : "=r"(done) : "r"(bar), "r"(parity) : "memory");
+        if (done) return true;
+    }
+    return false;
+}
+__device__ __forceinline__ unsigned cluster_ctarank() { unsigned r; asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r)); return r; }
+__device__ __forceinline__ unsigned map_to_cta(unsigned saddr, unsigned rank) {
+    unsigned r; asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank)); return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+    asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void st_cluster_u32(unsigned cluster_addr, int v) {
+    asm volatile("st.shared::cluster.u32 [%0], %1;" ::"r"(cluster_addr), "r"(v) : "memory");
+}
+// both CTAs' loads complete on the leader's barrier; no multicast
+__device__ __forceinline__ void tma_load_2d_pair(unsigned dst, const TensorMap* map, int c0, int c1, unsigned leader_bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+        ::"r"(dst), "l"(map), "r"(c0), "r"(c1), "r"(leader_bar) : "memory");
+}
+// Shared-memory matrix descriptor, 128-byte swizzle: bits [0,14) start address >> 4, [16,30) leading
+// byte offset >> 4, [32,46) stride byte offset >> 4, [46,48) version 1, [61,64) layout type 2.
+__device__ __forceinline__ unsigned long long make_desc(unsigned saddr, unsigned lbo_bytes, unsigned sbo_bytes) {
+    unsigned long long d = 0;
+    d |= (unsigned long long)((saddr >> 4) & 0x3FFF);
+    d |= (unsigned long long)((lbo_bytes >> 4) & 0x3FFF) << 16;
+    d |= (unsigned long long)((sbo_bytes >> 4) & 0x3FFF) << 32;
+    d |= (unsigned long long)1 << 46;
+    d |= (unsigned long long)2 << 61;
+    return d;
+}
+__device__ __forceinline__ void umma_f16_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void umma_commit_pair(unsigned cluster_bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
+}
+__device__ __forceinline__ void tmem_ld32(unsigned taddr, unsigned* v) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+        "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+        : "=r"(v[0]), "=r"(v[1]), "=r"(v[2]), "=r"(v[3]), "=r"(v[4]), "=r"(v[5]), "=r"(v[6]), "=r"(v[7]),
+          "=r"(v[8]), "=r"(v[9]), "=r"(v[10]), "=r"(v[11]), "=r"(v[12]), "=r"(v[13]), "=r"(v[14]), "=r"(v[15]),
+          "=r"(v[16]), "=r"(v[17]), "=r"(v[18]), "=r"(v[19]), "=r"(v[20]), "=r"(v[21]), "=r"(v[22]), "=r"(v[23]),
+          "=r"(v[24]), "=r"(v[25]), "=r"(v[26]), "=r"(v[27]), "=r"(v[28]), "=r"(v[29]), "=r"(v[30]), "=r"(v[31])
+        : "r"(taddr) : "memory");
+}
+
+// The tile counter must read zero when a launch starts.  The launch cleans up after itself: a pair
+// that has drawn a number past the end signs off on the second word, and the last to sign off zeroes
+// both.  Nobody draws after its own sign-off, so the reset cannot race with a draw.
+__device__ __forceinline__ void retire_tile_counter(int* counter, int drawers) {
+    __threadfence();
+    if (atomicAdd(counter + 1, 1) == drawers - 1) {
+        counter[0] = 0;
+        counter[1] = 0;
+        __threadfence();
+    }
+}
+
+// tile number -> (tile row, tile column)
+__device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int& tm, int& tn) {
+    if (CFG_GROUP_M <= 0 || CFG_GROUP_M >= tiles_m) { tm = t % tiles_m; tn = t / tiles_m; return; }
+    const int per_group = CFG_GROUP_M * tiles_n;
+    const int grp = t / per_group, first = grp * CFG_GROUP_M;
+    const int rows = (tiles_m - first) < CFG_GROUP_M ? (tiles_m - first) : CFG_GROUP_M;
+    const int r = t - grp * per_group;
+    tm = first + r % rows; tn = r / rows;
+}
+
+__device__ __forceinline__ void store16(void* p, uint4 v) {
+#if CFG_STREAM_STORES
+    __stcs(reinterpret_cast<uint4*>(p), v);
+#else
+    *reinterpret_cast<uint4*>(p) = v;
+#endif
+}
+
+// Sum over the 32 lanes of a warp of x[j], for each j in [0, 32): on return lane j holds column j's
+// sum in x[0].  Recursive halving: 31 shuffles instead of 160, and a fixed order of additions.
+__device__ __forceinline__ void warp_column_sums(float (&x)[32], int lane) {
+#pragma unroll
+    for (int off = 16; off >= 1; off >>= 1) {
+        const bool upper = (lane & off) != 0;
+#pragma unroll
+        for (int i = 0; i < off; i++) {
+            const float send = upper ? x[i] : x[i + off];
+            const float keep = upper ? x[i + off] : x[i];
+            x[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
+        }
+    }
+}
+
+extern "C" __global__ void __launch_bounds__(192, 1)
+gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b, const PairGemmArgs g) {
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) unsigned long long full_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2];
+    // tile queue: the leader's producer draws tile numbers from the global counter and publishes each
+    // one in both CTAs; a slot is recycled once all ten consumers of the pair have read it
+    __shared__ __align__(8) unsigned long long tq_full[TQ], tq_empty[TQ];
+    __shared__ int tile_ring[TQ];
+    __shared__ unsigned tmem_base_slot;
+    __shared__ volatile int failed;
+
+    const unsigned smem_base = (smem_u32(smem_raw) + 1023u) & ~1023u;   // swizzle atoms need 1 KiB alignment
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const unsigned rank = cluster_ctarank();            // 0 leads
+    const int tiles_m = g.tiles_m;
+    const int num_tiles = tiles_m * g.tiles_n;
+    const int kblocks = (g.K + BK - 1) / BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < NSTAGE; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 8); }
+        for (int q = 0; q < TQ; q++) { mbar_init(smem_u32(&tq_full[q]), 1); mbar_init(smem_u32(&tq_empty[q]), 10); }
+        failed = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        // 512 columns: two 128 x BNT f32 accumulators (BNT <= 256)
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(&tmem_base_slot)), "r"(512) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                  // both CTAs' barriers exist before any remote signal
+    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+    const unsigned tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ── producer ──
+        if (lane == 0) {
+            unsigned stage = 0, phase = 0;
+            bool ok = true;
+            unsigned qs = 0, qphase = 0;
+            int next = rank == 0 ? atomicAdd(g.tile_counter, 1) : 0;
+            while (ok) {
+                int t;
+                if (rank == 0) {
+                    if (!mbar_wait(smem_u32(&tq_empty[qs]), qphase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 15; break; }
+                    t = next;
+                    if (t >= num_tiles) t = -1;
+                    else next = atomicAdd(g.tile_counter, 1);      // drawn one tile ahead: its latency hides behind this tile's loads
+                    tile_ring[qs] = t;
+                    st_cluster_u32(map_to_cta(smem_u32(&tile_ring[qs]), 1), t);
+                    mbar_arrive(smem_u32(&tq_full[qs]));
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&tq_full[qs]), 1));
+                } else {
+                    if (!mbar_wait_cluster(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; *(volatile int*)g.status = 16; break; }
+                    t = *(volatile int*)&tile_ring[qs];
+                    mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
+                }
+                if (++qs == TQ) { qs = 0; qphase ^= 1; }
+                if (t < 0) { if (rank == 0) retire_tile_counter(g.tile_counter, (int)gridDim.x / 2); break; }
+                int tm, tn;
+                tile_coords(t, tiles_m, g.tiles_n, tm, tn);
+                const int m0 = tm * (2 * BM) + (int)rank * BM;           // this CTA's rows of A
+                const int n0 = tn * BNT + (int)rank * (BNT / 2);         // this CTA's half of B
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
+                    const unsigned own_fb = smem_u32(&full_bar[stage]);
+                    const unsigned fb = map_to_cta(own_fb, 0);
+                    const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
+                    if (rank == 0) mbar_expect_tx(own_fb, 2 * STAGE_B);
+                    const int k0 = kb * BK;
+                    if (CFG_A_MN) { for (int j = 0; j < BM / 64; j++) tma_load_2d_pair(sa + j * (BK * 128), &map_a, m0 + 64 * j, k0, fb); }
+                    else tma_load_2d_pair(sa, &map_a, k0, m0, fb);
+                    if (CFG_B_MN) { for (int j = 0; j < BNT / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
+                    else tma_load_2d_pair(sb, &map_b, k0, n0, fb);
+                    if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
+                }
+            }
+            if (!ok) failed = 1;
+        }
+    } else if (warp == 1) {
+        // ── MMA issuer (leader CTA only) ──
+        if (lane == 0 && rank == 0) {
+            // instruction descriptor: f32 accumulate, f16 x f16, majors, N >> 3 at bit 17, M >> 4 at bit 24 (256 across the pair)
+            const unsigned idesc = (1u << 4) | ((CFG_A_MN ? 1u : 0u) << 15) | ((CFG_B_MN ? 1u : 0u) << 16) | ((unsigned)(BNT >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
+            unsigned stage = 0, phase = 0, acc = 0, acc_phase = 0;
+            bool ok = true;
+            unsigned qs = 0, qphase = 0;
+            while (ok) {
+                if (!mbar_wait(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; *(volatile int*)g.status = 17; break; }
+                const int t = tile_ring[qs];
+                mbar_arrive(smem_u32(&tq_empty[qs]));
+                if (++qs == TQ) { qs = 0; qphase ^= 1; }
+                if (t < 0) break;
+                if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
+                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                const unsigned tmem_d = tmem_base + acc * BNT;
+                for (int kb = 0; kb < kblocks; kb++) {
+                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 13; break; }
+                    asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                    const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BK / 16; k++) {
+                        // K-major: 16 k-elements = 32 bytes inside the 128-byte row, 8-row groups 1 KiB apart.
+                        // MN-major: 16 k-rows = two 1 KiB atoms, 64-wide m/n groups one box (BK*128 B) apart.
+                        const unsigned long long ad = CFG_A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
+                        const unsigned long long bd = CFG_B_MN ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+                        umma_f16_pair(tmem_d, ad, bd, idesc, (kb | k) != 0);
+                    }
+                    const unsigned eb = smem_u32(&empty_bar[stage]);
+                    umma_commit_pair(map_to_cta(eb, 0));       // frees the stage here ...
+                    umma_commit_pair(map_to_cta(eb, 1));       // ... and in the partner CTA
+                    if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
+                }
+                if (!ok) break;
+                const unsigned af = smem_u32(&acc_full[acc]);
+                umma_commit_pair(map_to_cta(af, 0));
+                umma_commit_pair(map_to_cta(af, 1));
+                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
+            if (!ok) failed = 1;
+        }
+    } else {
+        // ── epilogue: warps 2..5, tensor-memory lane quadrant = warp % 4 ──
+        const int quad = warp & 3;
+        unsigned acc = 0, acc_phase = 0;
+        bool ok = true;
+        unsigned qs = 0, qphase = 0;
+        __half* const d_raw = (__half*)g.d_raw;
+#if CFG_EPI
+        __half* const d_out = (__half*)g.d_out;
+#endif
+        while (ok) {
+            if (!mbar_wait_cluster(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 18; failed = 1; } break; }
+            const int t = *(volatile int*)&tile_ring[qs];
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
+            if (++qs == TQ) { qs = 0; qphase ^= 1; }
+            if (t < 0) break;
+            int tm, tn;
+            tile_coords(t, tiles_m, g.tiles_n, tm, tn);
+            const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BNT;
+            if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+            const int row = m0 + quad * 32 + lane;
+            const size_t row_off = (size_t)row * g.ldd;
+            const bool row_ok = row < g.M;
+            const bool vec_ok = (g.ldd % 8 == 0);
+#pragma unroll 1
+            for (int c = 0; c < BNT / 32; c++) {
+                unsigned v[32];
+                tmem_ld32(tmem_base + ((unsigned)(quad * 32) << 16) + acc * BNT + c * 32, v);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                const int col = n0 + c * 32;
+                if (col >= g.N) continue;                  // warp-uniform
+                // the single narrowing of the f32 accumulator
+                __half2 h[16];
+#pragma unroll
+                for (int j = 0; j < 16; j++) h[j] = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
+                if (vec_ok) {
+#if CFG_EPI
+                    __half2 o[16];
+#endif
+#pragma unroll
+                    for (int q = 0; q < 4; q++) {
+                        const bool on = row_ok && col + q * 8 < g.N;     // N is a multiple of 8 here: a group of 8 is all in or all out
+                        if (on && d_raw) store16(d_raw + row_off + col + q * 8, *reinterpret_cast<const uint4*>(&h[q * 4]));
+#if CFG_EPI
+                        if (on) {
+                            epi8_(row, col + q * 8, &h[q * 4], &o[q * 4], g.ep);
+                            store16(d_out + row_off + col + q * 8, *reinterpret_cast<const uint4*>(&o[q * 4]));
+                        } else {
+                            o[q * 4] = o[q * 4 + 1] = o[q * 4 + 2] = o[q * 4 + 3] = __float2half2_rn(0.0f);
+                        }
+#else
+                        if (!on) h[q * 4] = h[q * 4 + 1] = h[q * 4 + 2] = h[q * 4 + 3] = __float2half2_rn(0.0f);
+#endif
+                    }
+                    if (g.colsum) {
+                        // partial column sums over this warp's 32 rows of what was stored (rows and columns
+                        // outside the matrix contribute zero); lane j ends up with column col + j
+                        float x[32];
+#pragma unroll
+                        for (int j = 0; j < 16; j++) {
+#if CFG_EPI
+                            const float2 f = __half22float2(o[j]);
+#else
+                            const float2 f = __half22float2(h[j]);
+#endif
+                            x[2 * j] = f.x; x[2 * j + 1] = f.y;
+                        }
+                        warp_column_sums(x, lane);
+                        if (col + lane < g.N) g.colsum[(size_t)((m0 + quad * 32) >> 5) * g.N + col + lane] = x[0];
+                    }
+                } else if (row_ok) {
+                    // row stride not a multiple of 16 bytes (no fused consumer on this route): scalar stores
+#pragma unroll
+                    for (int j = 0; j < 16; j++) {
+                        if (col + 2 * j < g.N) d_raw[row_off + col + 2 * j] = __low2half(h[j]);
+                        if (col + 2 * j + 1 < g.N) d_raw[row_off + col + 2 * j + 1] = __high2half(h[j]);
+                    }
+                }
+            }
+            asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));   // the leader waits for both CTAs' epilogues
+            if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+        }
+    }
+    asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
+    __syncthreads();
+    cluster_sync_all();                                  // the leader's MMAs read the partner's shared memory: leave together
+    if (warp == 1) {
+        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
+    }
+}
+
+#endif  // ANL_PAIR_GEMM_DEVICE_CODE

@@ -170,7 +170,8 @@ int ensure_driver(anl_device* dev) {
     };
     bool ok = get("cuModuleLoadData", (void**)&dev->drv.ModuleLoadData) && get("cuModuleUnload", (void**)&dev->drv.ModuleUnload) &&
               get("cuModuleGetFunction", (void**)&dev->drv.ModuleGetFunction) && get("cuLaunchKernel", (void**)&dev->drv.LaunchKernel) &&
-              get("cuGetErrorString", (void**)&dev->drv.GetErrorString) && get("cuTensorMapEncodeTiled", (void**)&dev->drv.TensorMapEncodeTiled);
+              get("cuGetErrorString", (void**)&dev->drv.GetErrorString) && get("cuTensorMapEncodeTiled", (void**)&dev->drv.TensorMapEncodeTiled) &&
+              get("cuLaunchKernelEx", (void**)&dev->drv.LaunchKernelEx) && get("cuFuncSetAttribute", (void**)&dev->drv.FuncSetAttribute);
     if (!ok) return dev->fail(ANL_ERR_CUDA, "cuda: driver entry points unavailable");
     dev->drv.loaded = true;
     return ANL_OK;
@@ -228,9 +229,15 @@ static int get_function(anl_device* dev, Module& m, const std::string& name, CUf
 }
 
 static bool opts_default(const CodegenOpts& o) { return !o.block_threads && !o.reduce_lanes && !o.vector_width && !o.split; }
+static GemmTuning tuning_of(const CodegenOpts& o) {
+    GemmTuning t;
+    t.tile_n = o.gemm_tile_n; t.stages = o.gemm_stages; t.group_m = o.gemm_group_m; t.stream_stores = o.gemm_stream_stores; t.single_cta = o.gemm_single_cta;
+    return t;
+}
 
 int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::shared_ptr<Plan>& out) {
-    int64_t ok[5] = {opts.block_threads, opts.reduce_lanes, opts.vector_width, opts.split, opts.debug_bounds};
+    int64_t ok[10] = {opts.block_threads, opts.reduce_lanes, opts.vector_width, opts.split, opts.debug_bounds,
+                      opts.gemm_tile_n, opts.gemm_stages, opts.gemm_group_m, opts.gemm_stream_stores, opts.gemm_single_cta};
     uint64_t key = fnv1a(ok, sizeof ok, structure_hash(item));
     if (!item.source.empty()) key = fnv1a(item.source.data(), item.source.size(), key);
     auto it = dev->plans.find(key);
@@ -248,7 +255,7 @@ int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::sh
         p->r.main.outputs_per_block = 1;
     } else {
         bool routed = false;
-        if (opts_default(opts) && !(dev->flags & ANL_OPEN_NO_GEMM)) routed = plan_gemm(dev, item, *p) == ANL_OK;
+        if (opts_default(opts) && !(dev->flags & ANL_OPEN_NO_GEMM)) routed = plan_gemm(item, tuning_of(opts), *p) == ANL_OK;
         if (!routed || p->gemm_dynamic) {
             std::string err;
             if (!render_cuda(item, opts, p->r, err)) return dev->fail(ANL_ERR_UNSUPPORTED, err);
@@ -543,6 +550,30 @@ int try_row_chain(anl_device* dev, const std::vector<Item>& items, size_t first,
     return ANL_OK;
 }
 
+
+// ── a contraction and the elementwise kernel behind it as one launch ────────────────────────────
+// The schedule keeps what the reference would schedule: item i a dense contraction, item i+1 an
+// elementwise kernel that reads it at the output's own position (bias add, activation, the product
+// with an activation's derivative), possibly a later item that sums item i+1's output over the rows
+// (a bias gradient).  At launch the three run as one contraction kernel: the consumer's generated
+// code sits in the epilogue on the narrowed accumulator registers, the contraction's own output is
+// still written when anything else reads it, and per-32-row column sums go to scratch memory for a
+// small finish kernel.  Values are those of the separate kernels (the consumer bit for bit; the
+// bias gradient sums the same f16 values in f32 in another order).
+static std::shared_ptr<FusedEpilogue> fused_epilogue_for(anl_device* dev, const Item& gemm, const Item& consumer, int64_t M, int64_t N) {
+    uint64_t hk[2] = {structure_hash(gemm), structure_hash(consumer)};
+    int acc = 0, hits = 0;
+    for (size_t b = 1; b < consumer.bufs.size(); b++) if (consumer.bufs[b].id == gemm.bufs[0].id) { acc = (int)b; hits++; }
+    uint64_t key = fnv1a(hk, sizeof hk, (uint64_t)acc * 1315423911ull + 7);
+    auto f = dev->fused.find(key);
+    if (f != dev->fused.end()) return f->second;
+    auto fe = std::make_shared<FusedEpilogue>();
+    std::string err;
+    if (hits == 1 && consumer.source.empty() && consumer.sym_vars.empty() && render_gemm_epilogue(consumer, acc, M, N, fe->epi, err)) { fe->on = true; fe->acc_param = acc; }
+    dev->fused[key] = fe;
+    return fe;
+}
+
 int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& binds, Table& t, cudaStream_t stream, bool keep_scratch = false) {
     CodegenOpts opts; opts.debug_bounds = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;
     // A parameter may only be updated once every kernel of this schedule that reads it has been
@@ -611,6 +642,9 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         }
         return ANL_OK;
     };
+    struct Absorbed { void* partials; int64_t parts, cols; };
+    std::unordered_map<size_t, Absorbed> absorbed;      // item index -> column sums a contraction's epilogue computes for it
+    const bool fusion_on = !(dev->flags & (ANL_OPEN_NO_EPILOGUE_FUSION | ANL_OPEN_NO_GEMM | ANL_OPEN_BEAM));
     // [update the parameter] hooks that fall due once item `at` has been queued
     auto updates_due = [&](size_t at) -> int {
         auto sg = sgd_at.find(at);
@@ -623,7 +657,7 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
     };
     for (size_t i = 0; i < items.size(); i++) {
         const Item& it = items[i];
-        if (chains_on) {
+        if (chains_on && !absorbed.count(i)) {
             size_t used = 0;
             int rc = try_row_chain(dev, items, i, t, stream, &used);
             if (rc != ANL_OK) return rc;
@@ -655,6 +689,82 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         std::vector<void*> ptrs;
         for (auto& b : it.bufs) ptrs.push_back(t.bufs[b.id].ptr);
         auto ra = t.after.find(it.bufs[0].id);
+        {
+            auto ab = absorbed.find(i);
+            if (ab != absorbed.end()) {
+                // a bias gradient whose partial column sums an earlier contraction's epilogue produced
+                if (int rc = launch_colsum_finish(dev, (const float*)ab->second.partials, ab->second.parts, ab->second.cols, ptrs[0], stream)) return rc;
+                if (keep_scratch) t.owned.push_back(ab->second.partials); else dev->release(ab->second.partials);
+                dev->stats.colsums_fused++;
+                if (ra != t.after.end() && ra->second.allreduce)
+                    if (int rc = reduce_part(ra->second, 0, ra->second.resident->elems)) return rc;
+                if (int rc = updates_due(i)) return rc;
+                continue;
+            }
+        }
+        if (fusion_on && ra == t.after.end() && i != tail_split && gemm_pair_eligible(*plan)) {
+            int64_t M = 0, N = 0, K = 0;
+            gemm_shape(*plan, &M, &N, &K);
+            const uint32_t out_id = it.bufs[0].id;
+            // the elementwise consumer, if it is the very next item
+            std::shared_ptr<FusedEpilogue> fe;
+            if (i + 1 < items.size() && N % 8 == 0 && !absorbed.count(i + 1)) {
+                fe = fused_epilogue_for(dev, it, items[i + 1], M, N);
+                if (fe->on) {
+                    // the consumer's output must not live in memory this contraction still reads
+                    void* o1 = t.bufs[items[i + 1].bufs[0].id].ptr;
+                    for (void* q : ptrs) if (q == o1) fe.reset();
+                }
+                if (fe && !fe->on) fe.reset();
+            }
+            const Item* last = fe ? &items[i + 1] : &it;          // the kernel whose output the epilogue stores last
+            // a later item that sums that output over the rows
+            size_t cs_item = 0; bool have_cs = false;
+            if (N % 8 == 0) {
+                for (size_t r = i + 1 + (fe ? 1 : 0); r < items.size() && !have_cs; r++) {
+                    if (absorbed.count(r) || items[r].bufs.size() != 2 || items[r].bufs[1].id != last->bufs[0].id || items[r].bufs[0].slot >= 0) continue;
+                    int sp = 0; int64_t rows = 0, cols = 0;
+                    if (match_column_sum(items[r], sp, rows, cols) && rows == M && cols == N) { cs_item = r; have_cs = true; }
+                }
+            }
+            if (fe || have_cs) {
+                GemmFusion fz;
+                if (fe) {
+                    fz.epilogue = &fe->epi.source;
+                    fz.d_out = t.bufs[items[i + 1].bufs[0].id].ptr;
+                    for (size_t k = 0; k < fe->epi.params.size(); k++) fz.ep[k] = t.bufs[items[i + 1].bufs[fe->epi.params[k]].id].ptr;
+                    // the contraction itself is stored only when something besides the consumer wants it
+                    bool wanted = false;
+                    for (uint32_t fid : t.finals) if (fid == out_id) wanted = true;
+                    for (size_t r = i + 2; r < items.size() && !wanted; r++)
+                        for (size_t b = 1; b < items[r].bufs.size(); b++) if (items[r].bufs[b].id == out_id) wanted = true;
+                    fz.store_raw = wanted;
+                }
+                void* partials = nullptr;
+                const int64_t parts = (M + 31) / 32;
+                if (have_cs) {
+                    if (int rc = dev->alloc((size_t)parts * (size_t)N * 4, &partials)) return rc;
+                    fz.colsum = (float*)partials;
+                    absorbed[cs_item] = Absorbed{partials, parts, N};
+                }
+                cudaEvent_t e0 = nullptr, e1 = nullptr;
+                if (dev->profiling) { cudaEventCreate(&e0); cudaEventCreate(&e1); cudaEventRecord(e0, stream); }
+                int rc = launch_gemm(dev, *plan, ptrs.data(), item_sym(it, binds), stream, 0, -1, &fz);
+                if (dev->profiling) { cudaEventRecord(e1, stream); dev->prof.push_back({e0, e1, KC_GEMM, gemm_flops(*plan, 0)}); }
+                if (rc) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
+                if (int rc2 = updates_due(i)) return rc2;
+                if (fe) {
+                    dev->stats.epilogues_fused++;
+                    // hooks of the consumer, which this launch has just run
+                    auto rb = t.after.find(items[i + 1].bufs[0].id);
+                    if (rb != t.after.end() && rb->second.allreduce)
+                        if (int rc3 = reduce_part(rb->second, 0, rb->second.resident->elems)) return rc3;
+                    if (int rc3 = updates_due(i + 1)) return rc3;
+                    i += 1;
+                }
+                continue;
+            }
+        }
         if (i == tail_split && ra != t.after.end()) {
             // The last all-reduced gradient has nothing left to hide behind.  Its contraction is
             // launched as two row windows; the first half is reduced across ranks and applied while
@@ -716,8 +826,10 @@ int collect_outputs(anl_device* dev, Table& t, const anl_output* placed, int n_p
         }
         outs[n++] = o;
     }
-    cudaError_t e = (may_return_early && !to_host && rc == ANL_OK) ? cudaSuccess : cudaStreamSynchronize(stream);
+    const bool waited = !(may_return_early && !to_host && rc == ANL_OK);
+    cudaError_t e = waited ? cudaStreamSynchronize(stream) : cudaSuccess;
     if (rc == ANL_OK && e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("cuda: ") + cudaGetErrorString(e));
+    if (rc == ANL_OK && waited) rc = gemm_check_status(dev);
     if (rc != ANL_OK) {
         std::lock_guard<std::mutex> lk(g_owned_mu);
         for (float* p : mine) { g_owned_outputs.erase(p); std::free(p); }
@@ -735,7 +847,10 @@ Bindings make_bindings(const anl_binding* binds, int n) {
 
 CodegenOpts opts_from(const int* o, unsigned flags) {
     CodegenOpts c;
-    if (o) { c.block_threads = o[0]; c.reduce_lanes = o[1]; c.vector_width = o[2]; c.split = o[3]; c.debug_bounds = o[4] != 0; }
+    if (o) {
+        c.block_threads = o[0]; c.reduce_lanes = o[1]; c.vector_width = o[2]; c.split = o[3]; c.debug_bounds = o[4] != 0;
+        c.gemm_tile_n = o[5]; c.gemm_stages = o[6]; c.gemm_group_m = o[7]; c.gemm_stream_stores = o[8]; c.gemm_single_cta = o[9];
+    }
     if (flags & ANL_OPEN_DEBUG_BOUNDS) c.debug_bounds = true;
     return c;
 }
@@ -800,6 +915,7 @@ void anl_close(anl_device* dev) {
     dev->trim();
     for (auto& kv : dev->live) cudaFree(kv.first);
     if (dev->gemm_tile_counter) cudaFree(dev->gemm_tile_counter);
+    if (dev->gemm_status_host) cudaFreeHost(dev->gemm_status_host);
     for (auto& r : dev->prof) { cudaEventDestroy(r.e0); cudaEventDestroy(r.e1); }
     if (dev->timer0) { cudaEventDestroy(dev->timer0); cudaEventDestroy(dev->timer1); }
     if (dev->comm_event) cudaEventDestroy(dev->comm_event);
@@ -824,6 +940,12 @@ const char* anl_last_error(anl_device* dev) { return dev ? dev->err.c_str() : "n
 
 int anl_get_stats(anl_device* dev, anl_stats* out) { if (!dev || !out) return ANL_ERR_INVALID; *out = dev->stats; return ANL_OK; }
 
+int anl_gemm_inject_status(anl_device* dev, int code, int counter_value) {
+    if (!dev) return ANL_ERR_INVALID;
+    cudaSetDevice(dev->ordinal);
+    return gemm_inject_status(dev, code, counter_value);
+}
+
 void* anl_stream(anl_device* dev) { return dev ? (void*)dev->stream : nullptr; }
 
 int anl_synchronize(anl_device* dev) {
@@ -834,7 +956,7 @@ int anl_synchronize(anl_device* dev) {
     CK(dev, cudaStreamSynchronize(dev->stream));
     if (dev->comm_stream) CK(dev, cudaStreamSynchronize(dev->comm_stream));
     if (dev->copy_stream) CK(dev, cudaStreamSynchronize(dev->copy_stream));
-    return ANL_OK;
+    return gemm_check_status(dev);
 }
 
 static int run_impl(anl_device* dev, const uint8_t* blob, size_t blob_len, const anl_input* inputs, int n_inputs,
@@ -914,6 +1036,33 @@ static int lower_chain_impl(const uint8_t* blob, size_t blob_len, int first, int
     if (src && src_cap) { size_t n = std::min(src_cap - 1, r.source.size()); std::memcpy(src, r.source.data(), n); src[n] = 0; }
     if (src_len) *src_len = r.source.size();
     if (note && note_cap) std::snprintf(note, note_cap, "%s", r.note.c_str());
+    return ANL_OK;
+}
+
+static int lower_gemm_impl(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, int fuse_next, const int* o,
+                           char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap) {
+    std::vector<Item> items; std::string err;
+    auto say = [&](const std::string& m) { if (dev) dev->err = m; if (note && note_cap) std::snprintf(note, note_cap, "%s", m.c_str()); };
+    if (!parse_kir(blob, blob_len, items, err)) { say(err); return ANL_ERR_INVALID; }
+    if (index < 0 || index >= (int)items.size()) { say("lower_gemm: item index out of range"); return ANL_ERR_INVALID; }
+    Plan p;
+    if (plan_gemm(items[index], tuning_of(opts_from(o, 0)), p) != ANL_OK || !gemm_pair_eligible(p)) { say("lower_gemm: the item does not run on the two-CTA contraction kernel"); return ANL_ERR_UNSUPPORTED; }
+    std::string epilogue, what = p.r.note;
+    if (fuse_next) {
+        if (index + 1 >= (int)items.size()) { say("lower_gemm: no next item to fuse"); return ANL_ERR_UNSUPPORTED; }
+        int64_t M, N, K; gemm_shape(p, &M, &N, &K);
+        int acc = 0, hits = 0;
+        for (size_t b = 1; b < items[index + 1].bufs.size(); b++) if (items[index + 1].bufs[b].id == items[index].bufs[0].id) { acc = (int)b; hits++; }
+        EpilogueRendered er;
+        if (hits != 1 || N % 8 != 0 || !render_gemm_epilogue(items[index + 1], acc, M, N, er, err)) { say(err.empty() ? "lower_gemm: the next item does not read this contraction once" : err); return ANL_ERR_UNSUPPORTED; }
+        epilogue = er.source;
+        what += "; " + er.note;
+    }
+    std::string out;
+    if (int rc = gemm_pair_source(dev, p, epilogue, out)) return rc;
+    if (src && src_cap) { size_t n = std::min(src_cap - 1, out.size()); std::memcpy(src, out.data(), n); src[n] = 0; }
+    if (src_len) *src_len = out.size();
+    if (note && note_cap) std::snprintf(note, note_cap, "%s", what.c_str());
     return ANL_OK;
 }
 
@@ -1202,6 +1351,9 @@ static int graph_replay_impl(anl_graph* g, const anl_input* inputs, int n_inputs
         }
         if (rc != ANL_OK) { *n_outs = 0; return rc; }
     }
+    // a contraction of an earlier replay that gave up on a barrier left its code in the host-visible
+    // status word: report it here instead of replaying on top of a tile counter it left dirty
+    if (int src = gemm_check_status(dev)) { *n_outs = 0; return src; }
     cudaError_t e = cudaGraphLaunch(g->exec, dev->stream);
     if (e != cudaSuccess) { *n_outs = 0; return dev->fail(ANL_ERR_CUDA, std::string("graph: launch: ") + cudaGetErrorString(e)); }
     dev->stats.graph_replays++;
@@ -1227,6 +1379,10 @@ int anl_lower(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, 
 }
 int anl_lower_chain(const uint8_t* blob, size_t blob_len, int first, int count, char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap) {
     return fenced(nullptr, "lower_chain", [&] { return lower_chain_impl(blob, blob_len, first, count, src, src_cap, src_len, note, note_cap); });
+}
+int anl_lower_gemm(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, int fuse_next, const int* o,
+                   char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap) {
+    return fenced(dev, "lower_gemm", [&] { return lower_gemm_impl(dev, blob, blob_len, index, fuse_next, o, src, src_cap, src_len, note, note_cap); });
 }
 int anl_benchmark(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o, int warmup, int iterations, anl_bench_result* out) {
     return fenced(dev, "benchmark", [&] { return benchmark_impl(dev, blob, blob_len, index, o, warmup, iterations, out); });

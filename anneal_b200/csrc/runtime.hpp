@@ -23,6 +23,8 @@ struct DriverApi {
     CUresult (*ModuleGetFunction)(CUfunction*, CUmodule, const char*) = nullptr;
     CUresult (*LaunchKernel)(CUfunction, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, unsigned, CUstream, void**, void**) = nullptr;
     CUresult (*GetErrorString)(CUresult, const char**) = nullptr;
+    CUresult (*LaunchKernelEx)(const CUlaunchConfig*, CUfunction, void**, void**) = nullptr;
+    CUresult (*FuncSetAttribute)(CUfunction, CUfunction_attribute, int) = nullptr;
     CUresult (*TensorMapEncodeTiled)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
                                      const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
                                      CUtensorMapL2promotion, CUtensorMapFloatOOBfill) = nullptr;
@@ -36,10 +38,37 @@ struct Module {
 
 // One item ready to launch: rendered source, compiled entry points, or a GEMM route.
 struct GemmPlan;
+
+// Tunables of the tcgen05 contraction kernels, the retargeted form of the reference's Tile / Upcast
+// choices for matmul (codegen/opt.go:206-307, 318-556).  Zero means "let the heuristic decide".
+struct GemmTuning {
+    int tile_n = 0;         // 256 or 128 columns per tile
+    int stages = 0;         // depth of the shared-memory ring
+    int group_m = 0;        // raster group in tile rows; -1: down whole columns
+    int stream_stores = 0;  // 1: streaming hint on the output stores
+    int single_cta = 0;     // 1: the one-CTA kernel even where a CTA pair applies
+};
+constexpr int kDefaultGroupM = 8;
+
+// What the epilogue of one contraction launch does besides (or instead of) storing the contraction.
+struct GemmFusion {
+    const std::string* epilogue = nullptr;   // generated epi8_() of the elementwise consumer, or null
+    void* d_out = nullptr;                   // the consumer's output buffer
+    const void* ep[6] = {nullptr, nullptr, nullptr, nullptr, nullptr, nullptr};   // its other operands
+    bool store_raw = true;                   // false when nothing but the consumer reads the contraction
+    float* colsum = nullptr;                 // [ceil(M/32), N] partial column sums of the last value stored
+};
 // Several consecutive items rendered as one row-chain kernel (codegen.hpp ChainRendered).
 struct ChainPlan {
     ChainRendered r;
     CUfunction fn = nullptr;
+};
+
+// A contraction and the elementwise kernel behind it, prepared to run as one launch.
+struct FusedEpilogue {
+    bool on = false;
+    EpilogueRendered epi;
+    int acc_param = 0;
 };
 
 struct Plan {
@@ -79,6 +108,7 @@ struct anl_device {
     anl::DriverApi drv;
     std::unordered_map<uint64_t, std::shared_ptr<anl::Plan>> plans;   // structure hash ^ opts → plan
     std::unordered_map<uint64_t, std::shared_ptr<anl::Module>> modules;  // source hash → module
+    std::unordered_map<uint64_t, std::shared_ptr<anl::FusedEpilogue>> fused;   // (contraction, consumer) -> generated epilogue, or a record that they do not fuse
     std::unordered_map<uint64_t, std::shared_ptr<anl::ChainPlan>> chains; // hash of member items → fused kernel, or null if they do not fuse
     std::multimap<size_t, void*> pool;                                // free device blocks by size
     std::unordered_map<void*, size_t> live;                           // blocks handed out
@@ -91,7 +121,12 @@ struct anl_device {
     std::unordered_map<uint64_t, BeamEntry> beam_cache;
     std::string beam_cache_path;
     bool beam_loaded = false;
-    int* gemm_tile_counter = nullptr;     // device word the persistent GEMM draws tile numbers from
+    static constexpr int kGemmCounterSlots = 16;
+    int* gemm_tile_counter = nullptr;     // device words the persistent GEMMs draw tile numbers from, 256 bytes per stream
+    std::vector<cudaStream_t> gemm_counter_streams;   // slot k belongs to this stream
+    int* gemm_status_host = nullptr;      // mapped, host-visible: code of a barrier wait that ran out
+    int* gemm_status_dev = nullptr;
+    bool gemm_attr_set = false;
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
     bool comm_pending = false;
@@ -121,9 +156,20 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 
 // hand-written contraction kernels (gemm.cu); returns ANL_OK and fills plan.gemm if the item is a
 // dense SUM-of-products over buffers that they cover, ANL_ERR_UNSUPPORTED otherwise
-int plan_gemm(anl_device* dev, const Item& item, Plan& plan);
+int plan_gemm(const Item& item, const GemmTuning& tune, Plan& plan);
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream,
-                int64_t m_begin = 0, int64_t m_end = -1);
+                int64_t m_begin = 0, int64_t m_end = -1, const GemmFusion* fusion = nullptr);
+// true when the plan runs on the two-CTA kernel, the one that can carry a fused consumer
+bool gemm_pair_eligible(const Plan& plan);
+void gemm_shape(const Plan& plan, int64_t* M, int64_t* N, int64_t* K);
+// compiles the kernel variant a launch of this plan (with this epilogue text) will use
+int gemm_prepare(anl_device* dev, const Plan& plan, const std::string& epilogue);
+// the source that would be compiled, for inspection
+int gemm_pair_source(anl_device* dev, const Plan& plan, const std::string& epilogue, std::string& out);
+int launch_colsum_finish(anl_device* dev, const float* partials, int64_t parts, int64_t n, void* out, cudaStream_t stream);
+// reports (once) a barrier wait that ran out in an earlier contraction launch and resets the state
+int gemm_check_status(anl_device* dev);
+int gemm_inject_status(anl_device* dev, int code, int counter_value);
 // rows of a static f16 contraction's output, or 0 when the plan is not one (no row windows then)
 int64_t gemm_window_rows(const Plan& plan, int64_t* row_elems);
 double gemm_flops(const Plan& plan, int64_t sym_value);

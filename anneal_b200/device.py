@@ -47,7 +47,7 @@ class _Bench(C.Structure):
 class _Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("kernels_launched", "gemm_launched", "nvrtc_compiles", "nvrtc_cache_hits",
                                           "lower_cache_hits", "h2d_bytes", "d2h_bytes", "graph_replays",
-                                          "graph_captures", "device_allocs")]
+                                          "graph_captures", "device_allocs", "epilogues_fused", "colsums_fused")]
 
 
 class _Prof(C.Structure):
@@ -84,6 +84,7 @@ def load_library():
     L.anl_device_info.argtypes = [vp, C.POINTER(_Info)]
     L.anl_get_stats.argtypes = [vp, C.POINTER(_Stats)]
     L.anl_synchronize.argtypes = [vp]
+    L.anl_gemm_inject_status.argtypes = [vp, i, i]
     L.anl_stream.argtypes = [vp]
     L.anl_stream.restype = vp
     L.anl_run.argtypes = [vp, u8p, C.c_size_t, C.POINTER(_Input), i, C.POINTER(_Binding), i,
@@ -93,6 +94,7 @@ def load_library():
     L.anl_lower.argtypes = [vp, u8p, C.c_size_t, i, C.POINTER(i), C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t),
                             C.POINTER(i), C.POINTER(i), C.POINTER(C.c_int64), C.c_char_p, C.c_size_t]
     L.anl_lower_chain.argtypes = [u8p, C.c_size_t, i, i, C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t), C.c_char_p, C.c_size_t]
+    L.anl_lower_gemm.argtypes = [vp, u8p, C.c_size_t, i, i, C.POINTER(i), C.c_char_p, C.c_size_t, C.POINTER(C.c_size_t), C.c_char_p, C.c_size_t]
     L.anl_compile_check.argtypes = [C.c_char_p, C.c_char_p, C.c_size_t]
     L.anl_benchmark.argtypes = [vp, u8p, C.c_size_t, i, C.POINTER(i), i, i, C.POINTER(_Bench)]
     L.anl_graph_create.argtypes = [vp, u8p, C.c_size_t, C.POINTER(vp)]
@@ -143,10 +145,27 @@ ABI_SYMBOLS = [
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_begin_stored", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum", "anl_allgather",
     "anl_comm_destroy", "anl_comm_set_timeout", "anl_comm_wait", "anl_comm_abort", "anl_comm_inject_delay", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
-    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search", "anl_stream",
+    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search", "anl_stream", "anl_lower_gemm", "anl_gemm_inject_status",
 ]
 
 KERNEL_CLASSES = {0: "elementwise", 1: "reduce", 2: "reduce_split", 3: "gemm", 4: "raw"}
+
+
+#: include/anneal_cuda.h ANL_NUM_OPTS
+NUM_OPTS = 10
+
+
+def _opts(opts):
+    """{block_threads, reduce_lanes, vector_width, split, debug_bounds, tile_n, stages, group_m,
+    stream_stores, single_cta} as the C array the library expects, shorter lists padded with 0."""
+    if not opts:
+        return None
+    return (C.c_int * NUM_OPTS)(*(list(opts) + [0] * NUM_OPTS)[:NUM_OPTS])
+
+
+def gemm_opts(tile_n=0, stages=0, group_m=0, stream_stores=0, single_cta=0):
+    """An opts list that only sets the contraction kernel's tunables."""
+    return [0, 0, 0, 0, 0, tile_n, stages, group_m, stream_stores, single_cta]
 
 
 def lower(items, index: int = 0, opts: Optional[Sequence[int]] = None):
@@ -158,7 +177,7 @@ def lower(items, index: int = 0, opts: Optional[Sequence[int]] = None):
     note = C.create_string_buffer(512)
     n = C.c_size_t()
     klass, block, opb = C.c_int(), C.c_int(), C.c_int64()
-    o = (C.c_int * 5)(*(list(opts) + [0] * 5)[:5]) if opts else None
+    o = _opts(opts)
     while True:
         src = C.create_string_buffer(cap)
         rc = L.anl_lower(None, blob, len(blob), index, o, src, cap, C.byref(n), C.byref(klass), C.byref(block),
@@ -183,6 +202,21 @@ def lower_chain(items, first: int, count: int) -> dict:
     rc = L.anl_lower_chain(blob, len(blob), first, count, src, cap, C.byref(n), note, 512)
     if rc:
         raise DeviceError(f"cuda: lower_chain: {note.value.decode()} (status {rc})")
+    return {"source": src.value.decode(), "note": note.value.decode()}
+
+
+def lower_gemm(items, index: int, fuse_next: bool = False, opts: Optional[Sequence[int]] = None) -> dict:
+    """Source of the two-CTA tcgen05 kernel for contraction items[index], with items[index+1] in its
+    epilogue when ``fuse_next``; raises if the item does not take that kernel or the pair does not fuse."""
+    L = load_library()
+    blob = kir.serialize(items)
+    cap = 1 << 18
+    src = C.create_string_buffer(cap)
+    note = C.create_string_buffer(512)
+    n = C.c_size_t()
+    rc = L.anl_lower_gemm(None, blob, len(blob), index, 1 if fuse_next else 0, _opts(opts), src, cap, C.byref(n), note, 512)
+    if rc:
+        raise DeviceError(f"cuda: lower_gemm: {note.value.decode()} (status {rc})")
     return {"source": src.value.decode(), "note": note.value.decode()}
 
 
@@ -271,6 +305,7 @@ class Device:
     BEAM = 4
     NO_ROW_CHAIN = 8
     TAIL_SPLIT = 16
+    NO_EPILOGUE_FUSION = 32
 
     def __init__(self, ordinal: Optional[int] = None, flags: int = 0):
         self.L = load_library()
@@ -397,7 +432,7 @@ class Device:
     def benchmark(self, item, warmup: int = 2, iterations: int = 5, opts: Optional[Sequence[int]] = None):
         blob = kir.serialize([item])
         r = _Bench()
-        o = (C.c_int * 5)(*(list(opts) + [0] * 5)[:5]) if opts else None
+        o = _opts(opts)
         self._check(self.L.anl_benchmark(self.h, blob, len(blob), 0, o, warmup, iterations, C.byref(r)))
         return {n: getattr(r, n) for n, _ in _Bench._fields_}
 

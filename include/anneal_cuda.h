@@ -99,6 +99,8 @@ typedef struct { double min_us, median_us, max_us, mean_us, stddev_us, cv; } anl
 typedef struct {
     uint64_t kernels_launched, gemm_launched, nvrtc_compiles, nvrtc_cache_hits, lower_cache_hits;
     uint64_t h2d_bytes, d2h_bytes, graph_replays, graph_captures, device_allocs;
+    uint64_t epilogues_fused;   /* elementwise kernels run inside the epilogue of the contraction before them */
+    uint64_t colsums_fused;     /* row-sum kernels finished from partial sums a contraction's epilogue left */
 } anl_stats;
 
 /* ── lifecycle: webgpu.Open / Device.Close / AdapterName / HasShaderF16 (backend/webgpu/open.go:89-175) ── */
@@ -112,6 +114,7 @@ int anl_get_stats(anl_device* dev, anl_stats* out);
 #define ANL_OPEN_NO_GEMM 2u        /* never route contractions to the tensor-core kernels */
 #define ANL_OPEN_NO_ROW_CHAIN 8u    /* launch every item on its own instead of fusing per-row kernel chains */
 #define ANL_OPEN_BEAM 4u           /* apply / search autotuned transforms (the reference's ANNEAL_BEAM=1) */
+#define ANL_OPEN_NO_EPILOGUE_FUSION 32u /* launch a contraction, its elementwise consumer and a bias gradient separately */
 #define ANL_OPEN_TAIL_SPLIT 16u    /* split the last all-reduced contraction into two row windows even on one rank
                                       (done by itself when ranks > 1; the flag exists to test the path on one GPU) */
 
@@ -130,10 +133,14 @@ int anl_run(anl_device* dev, const uint8_t* blob, size_t blob_len,
 void anl_outputs_free(anl_output* outs, int n_outs);
 
 /* ── codegen.Lower + RenderWGSL (codegen/lower.go:98-105, codegen/wgsl.go:36-39), CUDA flavour ──
- * Renders item `index` of the blob to CUDA C without touching the GPU.  `opts` is 5 ints:
- * {block_threads, reduce_lanes, vector_width, split, debug_bounds}; 0 means "choose".  The
+ * Renders item `index` of the blob to CUDA C without touching the GPU.  `opts` (NULL, or
+ * ANL_NUM_OPTS ints, in every call that takes them) is {block_threads, reduce_lanes, vector_width,
+ * split, debug_bounds} for generated kernels followed by {tile_n, stages, group_m, stream_stores,
+ * single_cta} for the tcgen05 contraction kernels — the reference's Local / Upcast / Vectorize /
+ * Tile choices (codegen/opt.go:57-72) retargeted; 0 means "choose", group_m -1 "no grouping".  The
  * source is copied to `src` (capacity src_cap, always NUL-terminated) and its full length is
  * returned in *src_len; `klass`, `block`, `outputs_per_block` describe the launch. */
+#define ANL_NUM_OPTS 10
 int anl_lower(anl_device* dev_or_null, const uint8_t* blob, size_t blob_len, int index, const int* opts,
               char* src, size_t src_cap, size_t* src_len, int* klass, int* block, int64_t* outputs_per_block,
               char* note, size_t note_cap);
@@ -143,6 +150,15 @@ int anl_lower(anl_device* dev_or_null, const uint8_t* blob, size_t blob_len, int
  * reason in `note` otherwise.  anl_run does this by itself; the call exists for inspection. */
 int anl_lower_chain(const uint8_t* blob, size_t blob_len, int first, int count,
                     char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap);
+
+/* The source of the two-CTA tcgen05 contraction kernel as it would be compiled for item `index`
+ * (a dense f16 sum of products with at least 256 output rows), with the elementwise kernel of item
+ * index+1 in its epilogue when `fuse_next` is not 0; ANL_ERR_UNSUPPORTED with the reason in `note`
+ * when the item does not take that kernel or the next item does not fuse.  anl_run makes this choice
+ * by itself; the call exists for inspection (the reference prints its kernels the same way,
+ * cmd_kernels.go:59-96) and needs no GPU. */
+int anl_lower_gemm(anl_device* dev_or_null, const uint8_t* blob, size_t blob_len, int index, int fuse_next, const int* opts,
+                   char* src, size_t src_cap, size_t* src_len, char* note, size_t note_cap);
 
 /* NVRTC-compiles CUDA C for sm_100a; needs no GPU.  Returns ANL_ERR_COMPILE with the log in `log`. */
 int anl_compile_check(const char* src, char* log, size_t log_cap);
@@ -256,6 +272,13 @@ int anl_sum_f32_static(const float* x, int64_t n, float* out, void* stream, char
 
 /* blocks until all work queued on the device has finished */
 int anl_synchronize(anl_device* dev);
+
+/* Diagnostic: leaves the device as a contraction launch does whose bounded barrier wait ran out — a
+ * non-zero code in the host-visible status word and tile counters holding `counter_value` — without
+ * any kernel waiting or failing.  The next call that waits for the device (anl_run, a replay,
+ * anl_synchronize) must then return ANL_ERR_CUDA once, and the calls after it must run correctly
+ * again.  No counterpart in the reference. */
+int anl_gemm_inject_status(anl_device* dev, int code, int counter_value);
 
 /* The cudaStream_t this device queues its kernels and copies on (non-blocking: it is not ordered
  * with the default stream).  A caller that launches work of its own on device buffers — through

@@ -39,7 +39,7 @@ def lib():
         L.orc_bind.argtypes = [C.c_void_p, C.c_char_p, C.c_int64]
         L.orc_run.argtypes = [C.c_void_p, C.c_int]
         L.orc_run_item.argtypes = [C.c_void_p, C.c_int, C.c_int]
-        L.orc_run_item_sampled.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_int]
+        L.orc_run_item_sampled.argtypes = [C.c_void_p, C.c_int, C.c_void_p, C.c_int64, C.c_void_p, C.c_void_p, C.c_int]
         L.orc_buffer_elems.restype = C.c_int64
         L.orc_buffer_elems.argtypes = [C.c_void_p, C.c_uint32]
         L.orc_get_buffer.argtypes = [C.c_void_p, C.c_uint32, C.c_void_p, C.c_int64]
@@ -99,11 +99,13 @@ class OracleExecutor:
         finally:
             L.orc_free(h)
 
-    def sample_item(self, item, inputs: Dict[int, np.ndarray], flat, binding: Optional[Dict[str, int]] = None):
+    def sample_item(self, item, inputs: Dict[int, np.ndarray], flat, binding: Optional[Dict[str, int]] = None, noise: bool = False):
         """The values kernel ``item`` stores at the flat output positions ``flat`` (row-major over its
         output), given float32 arrays for every buffer it reads. A benchmark-size contraction is
         checked this way on a few thousand outputs: n*K terms instead of M*N*K. Returns the positions
-        in ascending order and the values at them."""
+        in ascending order and the values at them; with ``noise`` also the modelled standard deviation
+        of each value's rounding error (first-order propagation of independent roundings), which
+        is what tells a sum whose terms cancel from a wrong result."""
         from anneal_b200 import kir
         L = lib()
         blob = kir.serialize([item])
@@ -121,9 +123,10 @@ class OracleExecutor:
                 L.orc_bind(h, k.encode(), int(v))
             idx = np.ascontiguousarray(np.sort(np.asarray(flat, dtype=np.int64)))
             out = np.empty(idx.size, dtype=np.float32)
-            if L.orc_run_item_sampled(h, 0, idx.ctypes.data, idx.size, out.ctypes.data, self.threads):
+            sigma = np.zeros(idx.size, dtype=np.float64) if noise else None
+            if L.orc_run_item_sampled(h, 0, idx.ctypes.data, idx.size, out.ctypes.data, sigma.ctypes.data if noise else None, self.threads):
                 raise OracleError(L.orc_error(h).decode())
-            return idx, out
+            return (idx, out, sigma) if noise else (idx, out)
         finally:
             L.orc_free(h)
 

@@ -29,6 +29,19 @@
  * ranges they read changes: the values are identical to recomputing them per
  * element and full-size schedules stay tractable.
  *
+ * Difference-noise model (sampled evaluation only, optional): beside each value the evaluator can
+ * carry the variance of the difference a second, equally valid evaluation would show.  Two
+ * implementations of these kernels legitimately differ in three places only: the order in which a
+ * REDUCE adds its terms (each partial sum rounds to f32, unit roundoff 2^-24), the approximation of
+ * exp2 / log2 / sin and of the f16-class reciprocal and division (a few f32 units), and — as a
+ * consequence — an f16 rounding that such a small difference tips to the neighbouring value (from
+ * there on it is a difference of whole f16 units, which later roundings pass on unchanged).
+ * Everything else (f16 and f32 add, sub, mul, compare, select) rounds identically everywhere and
+ * only propagates what it is given, to first order.  A comparison can then tell "differs by more
+ * than the stated tolerance" from "is a sum whose terms cancel, so that any two orders of addition
+ * differ by this much" — the row statistics of a softmax gradient that are zero in exact arithmetic
+ * are the case in point.  The model is not part of the reference; it changes no value.
+ *
  * Parity status: pinned by the known-answer vectors that are literal in the
  * reference's own tests (backend/webgpu/webgpu_test.go:84-359,
  * schedule/schedule_test.go:809-915, tensor/nn/train_test.go:71-144,
@@ -225,6 +238,9 @@ typedef struct {
     val **bufdata; int64_t *bufelems; int64_t (*strides)[8];
     int32_t *rval; uint64_t *rver;      /* per range: current value, version */
     val *cache; uint64_t *cver;         /* per node: cached value and the version sum it was computed at */
+    double *nvar, *qvar;                /* per node, when not NULL: modelled variance of the difference between two valid
+                                           evaluations: the part that is still continuous, and the part that f16 roundings
+                                           have already turned into whole-unit differences */
 } ectx;
 
 static inline uint64_t dep_version(const ectx *c, const node *n) {
@@ -256,6 +272,23 @@ static int64_t range_bound(const ectx *c, const node *r) {
     return r->arg;
 }
 
+#define U32 5.9604644775390625e-08   /* 2^-24 */
+#define U16 4.8828125e-04            /* 2^-11 */
+/* variance an approximated function adds: two f32 units of its result */
+static inline double approx_var(double r) { return (2.0 * U32 * r) * (2.0 * U32 * r); }
+/* an f16 rounding of r whose argument carries variance v.  A difference well below one unit tips
+ * the rounding to the neighbouring value with probability ~ sigma / ulp and then counts a whole
+ * unit: variance sigma * ulp.  A difference of a unit or more comes through as it is, plus the two
+ * roundings' own variance. */
+static inline double f16_tip_var(double v, double r) {
+    double a = fabs(r) < 6.103515625e-05 ? 6.103515625e-05 : fabs(r);     /* below 2^-14 the spacing stays 2^-24 */
+    double ulp = 2.0 * U16 * a, sg = sqrt(v);
+    return sg < ulp ? sg * ulp : v + ulp * ulp / 6.0;
+}
+static inline int rounds_f16(const node *n) { return n->cls == C_F16 && !n->widen; }
+static inline double nv(const ectx *c, int i) { return c->nvar ? c->nvar[i] : 0.0; }
+static inline double qv(const ectx *c, int i) { return c->qvar ? c->qvar[i] : 0.0; }
+
 static val eval_reduce(ectx *c, const node *n) {
     const item *it = c->it;
     int rop = (int)n->aux;
@@ -270,12 +303,19 @@ static val eval_reduce(ectx *c, const node *n) {
         if (r->op != OP_RANGE) continue;
         slots[nl] = r->range_slot; bound[nl] = range_bound(c, r); nl++;
     }
+    double vacc = 0.0, qacc = 0.0;
     for (int l = 0; l < nl; l++) if (bound[l] <= 0) goto done;
     for (int l = 0; l < nl; l++) { c->rval[slots[l]] = 0; c->rver[slots[l]]++; }
     for (;;) {
         val e = eval(c, n->src[0]);
         if (isf) {
             float x = e.f;
+            if (c->nvar) {
+                double ve = c->nvar[n->src[0]], qe = c->qvar[n->src[0]];
+                if (rop == OP_ADD) { double r = (double)acc.f + (double)x; vacc += ve + (U32 * r) * (U32 * r) / 3.0; qacc += qe; }
+                else if (rop == OP_MUL) { vacc = vacc * (double)x * (double)x + ve * (double)acc.f * (double)acc.f; qacc = qacc * (double)x * (double)x + qe * (double)acc.f * (double)acc.f; }
+                else { if (ve > vacc) vacc = ve; if (qe > qacc) qacc = qe; }
+            }
             if (rop == OP_ADD) acc.f = acc.f + x;
             else if (rop == OP_MUL) acc.f = acc.f * x;
             else if (rop == OP_MAX) acc.f = (x != x || acc.f != acc.f) ? (x != x ? acc.f : x) : (acc.f < x ? x : acc.f);
@@ -294,7 +334,8 @@ static val eval_reduce(ectx *c, const node *n) {
         if (l < 0) break;
     }
 done:
-    if (n->dtype == DT_F16) acc.f = f16_round_f(acc.f);   /* f16(acc): the single narrowing */
+    if (n->dtype == DT_F16) { acc.f = f16_round_f(acc.f); qacc += f16_tip_var(vacc, (double)acc.f); vacc = 0.0; }   /* f16(acc): the single narrowing */
+    if (c->nvar) { c->nvar[n - c->it->nodes] = vacc; c->qvar[n - c->it->nodes] = qacc; }
     return acc;
 }
 
@@ -384,6 +425,40 @@ static val eval(ectx *c, int i) {
         else r.i = n->op == OP_CMPLT ? a.i < b.i : n->op == OP_CMPNE ? a.i != b.i : a.i == b.i;
         break; }
     default: break;
+    }
+    if (c->nvar && isf && n->op != OP_REDUCE) {
+        /* first-order propagation; operand values come from the cache the evaluation above filled */
+        double v = 0.0, q = 0.0, rr = (double)r.f;
+        #define VAL(k) ((double)as_f(&nodes[s[k]], c->cache[s[k]]))
+        #define CVAL(k) (nodes[s[k]].op == OP_CONST ? (double)as_f(&nodes[s[k]], nodes[s[k]].cval) : nodes[s[k]].op == OP_RANGE ? (double)c->rval[nodes[s[k]].range_slot] : VAL(k))
+        /* LIN1(d): one operand with derivative d; LIN2(da, db): two */
+        #define LIN1(d) do { double d_ = (d); v = d_ * d_ * nv(c, s[0]); q = d_ * d_ * qv(c, s[0]); } while (0)
+        #define LIN2(da, db) do { double a_ = (da), b_ = (db); v = a_ * a_ * nv(c, s[0]) + b_ * b_ * nv(c, s[1]); q = a_ * a_ * qv(c, s[0]) + b_ * b_ * qv(c, s[1]); } while (0)
+        switch (n->op) {
+        case OP_INDEX: break;
+        case OP_WHERE: { int k = eval(c, s[0]).i ? 1 : 2; v = nv(c, s[k]); q = qv(c, s[k]); break; }
+        case OP_CAST: { const node *sn = &nodes[s[0]]; if (sn->cls == C_F32 || sn->cls == C_F16) LIN1(1.0); break; }
+        case OP_BITCAST: case OP_NEG: case OP_TRUNC: LIN1(1.0); break;
+        case OP_EXP2: LIN1(0.6931471805599453 * rr); v += approx_var(rr); break;
+        case OP_LOG2: { double a = CVAL(0); LIN1(a != 0.0 ? 1.0 / (a * 0.6931471805599453) : 0.0); v += approx_var(rr) + (2.0 * U32) * (2.0 * U32); break; }
+        case OP_SIN: LIN1(1.0); v += approx_var(rr) + (2.0 * U32) * (2.0 * U32); break;
+        case OP_SQRT: LIN1(rr != 0.0 ? 0.5 / rr : 0.0); break;
+        case OP_RECIP: LIN1(rr * rr); if (rounds_f16(n)) v += approx_var(rr); break;
+        case OP_ADD: case OP_SUB: LIN2(1.0, 1.0); break;
+        case OP_MUL: { double a = CVAL(0), b = CVAL(1); LIN2(b, a); break; }
+        case OP_FDIV: { double a = CVAL(0), b = CVAL(1); if (b != 0.0) LIN2(1.0 / b, a / (b * b)); if (rounds_f16(n)) v += approx_var(rr); break; }
+        case OP_MAX: { double a = nv(c, s[0]) + qv(c, s[0]), b = nv(c, s[1]) + qv(c, s[1]); int k = a > b ? 0 : 1; v = nv(c, s[k]); q = qv(c, s[k]); break; }
+        case OP_MULACC: { double b = CVAL(1), d = CVAL(2); v = nv(c, s[0]) + d * d * nv(c, s[1]) + b * b * nv(c, s[2]); q = qv(c, s[0]) + d * d * qv(c, s[1]) + b * b * qv(c, s[2]); break; }
+        default: LIN1(1.0); v += approx_var(rr); break;
+        }
+        if (rounds_f16(n) && v > 0.0) { q += f16_tip_var(v, rr); v = 0.0; }
+        #undef LIN1
+        #undef LIN2
+        #undef VAL
+        #undef CVAL
+        if (!(v == v) || v > 1e300) v = 1e300;
+        if (!(q == q) || q > 1e300) q = 1e300;
+        c->nvar[i] = v; c->qvar[i] = q;
     }
     c->cache[i] = r; c->cver[i] = ver;
     return r;
@@ -542,8 +617,10 @@ int orc_run_item(orc *o, int i, int threads) {
  * the output buffer.  A contraction with K terms then costs n*K instead of M*N*K, which lets a
  * benchmark-size kernel be compared on a few thousand outputs.  Every input buffer must hold data
  * (orc_set_input, or an earlier kernel).  Positions should arrive sorted: sub-expressions that do
- * not read the ranges that changed are re-used, exactly as in a full run. */
-int orc_run_item_sampled(orc *o, int i, const int64_t *flat, int64_t n, float *out, int threads) {
+ * not read the ranges that changed are re-used, exactly as in a full run.  `noise_sigma`, when not
+ * NULL, receives for each position the modelled standard deviation of the difference between two
+ * valid evaluations of the kernel (see the header). */
+int orc_run_item_sampled(orc *o, int i, const int64_t *flat, int64_t n, float *out, double *noise_sigma, int threads) {
     if (o->err[0] || i < 0 || i >= o->n_items) return 1;
     const item *it = &o->items[i];
     if (it->n_nodes == 0) { snprintf(o->err, sizeof o->err, "oracle: item without AST"); return 1; }
@@ -590,6 +667,8 @@ int orc_run_item_sampled(orc *o, int i, const int64_t *flat, int64_t n, float *o
         c.rver = calloc(it->n_ranges ? it->n_ranges : 1, sizeof(uint64_t));
         c.cache = calloc(it->n_nodes, sizeof(val));
         c.cver = calloc(it->n_nodes, sizeof(uint64_t));
+        c.nvar = noise_sigma ? calloc(it->n_nodes, sizeof(double)) : NULL;
+        c.qvar = noise_sigma ? calloc(it->n_nodes, sizeof(double)) : NULL;
         for (int l = 0; l < nl; l++) { c.rval[lslots[l]] = -1; c.rver[lslots[l]] = 1; }
         const node *bn = &it->nodes[body];
         int body_is_float = (bn->cls == C_F32 || bn->cls == C_F16);
@@ -601,14 +680,17 @@ int orc_run_item_sampled(orc *o, int i, const int64_t *flat, int64_t n, float *o
                 if (c.rval[lslots[l]] != v) { c.rval[lslots[l]] = v; c.rver[lslots[l]]++; }
             }
             val v = eval(&c, body);
+            const int tracked = c.nvar && body_is_float && bn->op != OP_CONST && bn->op != OP_RANGE;
+            double var = tracked ? c.nvar[body] : 0.0, qvr = tracked ? c.qvar[body] : 0.0;
             if (out_dt == DT_F16 || out_dt == DT_BF16 || (out_dt == DT_F32 && !body_is_float)) {
                 float fv = as_f(bn, v);
-                if (out_dt == DT_F16) fv = f16_round_f(fv);
+                if (out_dt == DT_F16) { fv = f16_round_f(fv); if (var > 0.0) { qvr += f16_tip_var(var, (double)fv); var = 0.0; } }
                 else if (out_dt == DT_BF16) fv = bf16_trunc(fv);
                 out[k] = fv;
             } else memcpy(&out[k], &v, 4);
+            if (noise_sigma) noise_sigma[k] = sqrt(var + qvr);
         }
-        free(c.rval); free(c.rver); free(c.cache); free(c.cver);
+        free(c.rval); free(c.rver); free(c.cache); free(c.cver); free(c.nvar); free(c.qvar);
     }
     return 0;
 }

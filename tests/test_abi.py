@@ -209,3 +209,40 @@ def test_damaged_blobs_never_crash_the_library():
         r = subprocess.run([sys.executable, helper, str(seed), "4000"], capture_output=True, text=True, timeout=300)
         assert r.returncode == 0, (seed, r.returncode, r.stderr[-400:])
         assert "rejected=" in r.stdout
+
+
+def test_contraction_kernel_sources_compile_with_and_without_a_fused_consumer(lib):
+    """The two-CTA tcgen05 kernel is compiled at run time; every variant the wide MLP needs — the three
+    operand layouts, the bias + GELU consumer, the logits' bias add, the GELU-backward product —
+    must get through NVRTC for sm_100a on a box without a GPU."""
+    R.reset()
+    R.MATERIALIZE_CONTRACTION_OPERANDS = True
+    try:
+        m = W.WideMLP(batch=512, width=256, classes=136, depth=2)
+        items, _ = R.build_schedule(m.graph().targets())
+    finally:
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+    plain = fused = 0
+    layouts = set()
+    for i in range(len(items)):
+        try:
+            r = device.lower_gemm(items, i)
+        except device.DeviceError:
+            continue
+        plain += 1
+        layouts.add(r["note"].split(" M=")[0])
+        device.compile_check(r["source"])
+        try:
+            f = device.lower_gemm(items, i, fuse_next=True)
+        except device.DeviceError:
+            continue
+        fused += 1
+        assert "void epi8_(" in f["source"] and "#define CFG_EPI 1" in f["source"]
+        device.compile_check(f["source"])
+    assert plain == 7 and fused == 5, (plain, fused)
+    assert layouts == {"gemm tcgen05 A:K B:K", "gemm tcgen05 A:K B:MN", "gemm tcgen05 A:MN B:MN"}
+    # the tunables are compile-time constants of the source
+    tuned = device.lower_gemm(items, 0, opts=device.gemm_opts(tile_n=128, stages=4, group_m=-1, stream_stores=1))["source"]
+    for line in ("#define CFG_BNT 128", "#define CFG_STAGES 4", "#define CFG_GROUP_M 0", "#define CFG_STREAM_STORES 1"):
+        assert line in tuned
+    device.compile_check(tuned)

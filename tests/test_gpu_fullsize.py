@@ -42,6 +42,12 @@ def test_c4_every_kernel_at_full_size(cuda, oracle):
     report, kept = check_every_kernel(cuda, oracle, items, inputs, 2e-3, samples=4096)
     assert cuda.stats()["gemm_launched"] - before == 14
     assert len(report) == len(items)
+    # the noise allowance must not be what lets a contraction through: on those it stays a small
+    # fraction of the 2e-3 bound (it matters only for the sums that cancel)
+    from anneal_b200 import device as D
+    for (k, err, slack), it in zip(report, items):
+        if len(it.bufs[0].shape) == 2 and "contraction" in D.lower(items, k)["note"]:
+            assert slack <= 0.25 * 2e-3, (k, slack)
     # the schedule as the bench runs it (slots shared, only final outputs returned) gives the same
     # loss and gradients as the run that kept every buffer
     got = cuda.run(items, inputs)
@@ -66,11 +72,12 @@ def test_c3_softmax_full_size_against_oracle(cuda, oracle):
     known.update(kept)
     rows = np.array([0, 4095, 8191], dtype=np.int64)
     pos = (rows[:, None] * 8192 + np.arange(8192, dtype=np.int64)[None, :]).reshape(-1)
-    idx, want = oracle.sample_item(it, known, pos)
+    idx, want, sigma = oracle.sample_item(it, known, pos, noise=True)
     dx = kept[out_ids[0]]
     floor = float(np.sqrt(np.mean(np.square(want, dtype=np.float64))))
-    err = np.abs(dx[idx].astype(np.float64) - want) / np.maximum(np.abs(want), floor)
-    assert err.max() <= 1e-4, err.max()
+    err = np.abs(dx[idx].astype(np.float64) - want)
+    assert (err <= 1e-4 * np.maximum(np.abs(want), floor) + 6.0 * sigma).all(), (err / floor).max()
+    assert 6.0 * sigma.max() <= 0.25 * 1e-4 * floor          # dx itself is well conditioned: the bound is the stated one
     # rows of a softmax gradient sum to zero
     assert np.abs(dx.reshape(8192, 8192).sum(1, dtype=np.float64)).max() < 1e-5
     assert cuda.stats()["kernels_launched"] - k0 >= 1
@@ -87,6 +94,8 @@ def test_c5_symbolic_mlp_full_width_largest_batch(cuda, oracle):
     items, out_ids, inputs = schedule([out] + grads)
     report, kept = check_every_kernel(cuda, oracle, items, inputs, 1e-4, binding={"n": b}, samples=2048)
     assert len(report) == len(items)
+    for k, err, slack in report:
+        assert slack <= 0.6 * 1e-4, (k, slack)      # 65536 f32 partial sums round: about half the bound, never more
     # and the smallest batch through the same plans
     R.reset()
     x1, y1 = m.inputs(1)
@@ -130,11 +139,14 @@ def test_c2_cnn_loss_trajectory_100_steps(cuda, oracle):
 def test_c4_wide_mlp_loss_trajectory_100_steps_reduced_width(cuda, oracle):
     """The wide MLP's arithmetic (f16 storage, f32 accumulation, GELU, cross-entropy, f32 masters
     re-quantised after every update) at a width the oracle can afford for 100 steps; the
-    contractions still run on the tcgen05 kernels.  Losses within 1e-3 at every step."""
+    contractions still run on the tcgen05 kernels.  The loss itself is an f16 value here: near 4.8
+    its spacing is 2^-8 = 3.9e-3, so two trajectories that differ by ONE unit in the last place of
+    the loss differ by 8e-4 relative.  The bound is 1e-3 relative to the loss at every step."""
     make = lambda: W.WideMLP(batch=256, width=256, classes=72, depth=2)
     g0 = cuda.stats()["gemm_launched"]
     dev, ref, tr, rm = _trajectory(cuda, oracle, make, 100, True)
     assert cuda.stats()["gemm_launched"] - g0 >= 8 * 100
-    d = np.abs(dev - ref)
+    d = np.abs(dev - ref) / np.abs(ref)
     assert d.max() < 1e-3, (d.max(), dev[-1], ref[-1])
+    assert (d == 0).mean() > 0.8                       # most steps agree exactly
     assert ref[-1] < ref[0]
