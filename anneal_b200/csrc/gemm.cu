@@ -466,6 +466,7 @@ void gemm_shape(const Plan& plan, int64_t* M, int64_t* N, int64_t* K) { *M = pla
 namespace {
 
 struct PairVariant { int bnt, stages, group_m, stream_stores; bool a_mn, b_mn; };
+constexpr int kDefaultStages = 6;
 
 int pair_smem_bytes(int bnt, int stages) { return stages * (A_TILE_BYTES + (bnt / 2) * BK * 2) + 1024; }
 
@@ -511,7 +512,7 @@ PairVariant choose_variant(anl_device* dev, const GemmPlan& gp, int64_t M) {
         auto fill = [&](int bnt) { long long t = (long long)tm2 * ((c.N + bnt - 1) / bnt); long long w = (t + npairs - 1) / npairs; return (double)t / (double)(w * npairs); };
         v.bnt = (fill(128) * 0.7 > fill(256)) ? 128 : 256;
     }
-    v.stages = gp.tune.stages > 0 ? std::max(2, std::min(gp.tune.stages, max_stages(v.bnt))) : std::min(6, max_stages(v.bnt));
+    v.stages = gp.tune.stages > 0 ? std::max(2, std::min(gp.tune.stages, max_stages(v.bnt))) : std::min(kDefaultStages, max_stages(v.bnt));
     v.group_m = gp.tune.group_m > 0 ? gp.tune.group_m : (gp.tune.group_m < 0 ? 0 : kDefaultGroupM);
     v.stream_stores = gp.tune.stream_stores > 0 ? 1 : 0;
     return v;

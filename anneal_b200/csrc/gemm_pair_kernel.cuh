@@ -373,7 +373,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                         if (!on) h[q * 4] = h[q * 4 + 1] = h[q * 4 + 2] = h[q * 4 + 3] = __float2half2_rn(0.0f);
 #endif
                     }
-                    if (g.colsum) {
+                    if (g.colsum && m0 + quad * 32 < g.M) {      // warp-uniform: groups of 32 rows that start inside the matrix
                         // partial column sums over this warp's 32 rows of what was stored (rows and columns
                         // outside the matrix contribute zero); lane j ends up with column col + j
                         float x[32];

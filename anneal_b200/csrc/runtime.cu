@@ -121,6 +121,19 @@ __global__ void __launch_bounds__(256, 6) sgd_kernel(float* __restrict__ master,
     }
 }
 
+// Benchmark operands: finite values of magnitude 0.5 .. 1 with random signs and mantissas (f16 pairs or
+// f32 words), so that a timed contraction switches as many bits as one fed with real activations; a
+// zero-filled operand lets the tensor cores idle and flatters the clock.
+__global__ void fill_benchmark_pattern(unsigned* __restrict__ p, long long words, int f16, unsigned seed) {
+    long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const long long stride = (long long)gridDim.x * blockDim.x;
+    for (; i < words; i += stride) {
+        unsigned x = (unsigned)i * 2654435761u + seed;
+        x ^= x >> 15; x *= 2246822519u; x ^= x >> 13; x *= 3266489917u; x ^= x >> 16;
+        p[i] = f16 ? ((x & 0x83FF83FFu) | 0x38003800u) : ((x & 0x807FFFFFu) | 0x3F000000u);
+    }
+}
+
 static unsigned grid_for(long long n, int block, int sms) {
     long long g = (n + block - 1) / block;
     long long cap = (long long)sms * 16;
@@ -1075,7 +1088,9 @@ int anl_compile_check(const char* src, char* log, size_t log_cap) {
 
 // Benchmarker.Benchmark (backend/webgpu/benchmark.go:18-208): the reference times submit+wait with
 // the host clock and reports min/median/max/mean/stddev/CV; here each iteration is bracketed by CUDA
-// events on the launching stream.  Inputs are zero-filled device buffers, as the reference's are.
+// events on the launching stream.  The reference's inputs are zero-filled buffers; here float
+// operands get finite pseudo-random values, because a tensor-core kernel fed with zeros draws less
+// power and clocks higher than it ever does on data.
 static int benchmark_impl(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, const int* o, int warmup, int iterations, anl_bench_result* out) {
     if (!dev || !out || iterations <= 0) return ANL_ERR_INVALID;
     cudaSetDevice(dev->ordinal);
@@ -1091,7 +1106,9 @@ static int benchmark_impl(anl_device* dev, const uint8_t* blob, size_t blob_len,
     for (auto& b : it.bufs) {
         void* p = nullptr; size_t by = (size_t)b.elems(0) * dt_storage_bytes(b.dtype);
         if ((rc = dev->alloc(by, &p))) break;
-        cudaMemsetAsync(p, 0, by ? by : 4, dev->stream);
+        if (dt_is_float(b.dtype) && b.dtype != DT_BF16 && by >= 4)
+            fill_benchmark_pattern<<<grid_for((long long)(by / 4), 256, dev->prop.multiProcessorCount), 256, 0, dev->stream>>>((unsigned*)p, (long long)(by / 4), b.dtype == DT_F16, 0x9E3779B9u * (unsigned)(ptrs.size() + 1));
+        else cudaMemsetAsync(p, 0, by ? by : 4, dev->stream);
         ptrs.push_back(p);
     }
     std::vector<double> us;
@@ -1196,9 +1213,46 @@ int anl_buffer_upload_commit(anl_buffer* buf) {
     buf->staged_elems = 0;
     return ANL_OK;
 }
+// Read-back without stalling the host.  `begin` queues, behind everything already queued on the compute
+// stream, a copy of the buffer's first `elems` values (widened to f32) into `host` — pinned memory,
+// or the copy is not asynchronous — and returns at once; `wait` blocks until the last copy begun on
+// this buffer has landed.  A training loop reads step i's loss this way while step i+1 runs.
+int anl_buffer_download_begin(anl_buffer* buf, float* host, int64_t elems) {
+    if (!buf || !host || elems <= 0 || elems > buf->elems) return ANL_ERR_INVALID;
+    anl_device* dev = buf->dev;
+    cudaSetDevice(dev->ordinal);
+    if (!buf->dl_done) CK(dev, cudaEventCreateWithFlags(&buf->dl_done, cudaEventDisableTiming));
+    const void* src = buf->ptr;
+    if (buf->dtype == DT_F16) {
+        if (!buf->dl_stage || buf->dl_stage_elems < elems) {
+            if (buf->dl_stage) dev->release(buf->dl_stage);
+            if (int rc = dev->alloc((size_t)elems * 4, &buf->dl_stage)) return rc;
+            buf->dl_stage_elems = elems;
+        }
+        cvt_f16_to_f32<<<grid_for(elems, 256, dev->prop.multiProcessorCount), 256, 0, dev->stream>>>((const __half*)buf->ptr, (float*)buf->dl_stage, elems);
+        CK(dev, cudaGetLastError());
+        dev->stats.kernels_launched++;
+        src = buf->dl_stage;
+    }
+    CK(dev, cudaMemcpyAsync(host, src, (size_t)elems * 4, cudaMemcpyDeviceToHost, dev->stream));
+    CK(dev, cudaEventRecord(buf->dl_done, dev->stream));
+    buf->dl_pending = true;
+    dev->stats.d2h_bytes += (uint64_t)elems * 4;
+    return ANL_OK;
+}
+int anl_buffer_download_wait(anl_buffer* buf) {
+    if (!buf) return ANL_ERR_INVALID;
+    if (!buf->dl_pending) return buf->dev->fail(ANL_ERR_INVALID, "buffer: download_wait without download_begin");
+    cudaSetDevice(buf->dev->ordinal);
+    CK(buf->dev, cudaEventSynchronize(buf->dl_done));
+    buf->dl_pending = false;
+    return ANL_OK;
+}
 void anl_buffer_release(anl_buffer* buf) {
     if (!buf) return;
     cudaStreamSynchronize(buf->dev->stream);
+    if (buf->dl_stage) buf->dev->release(buf->dl_stage);
+    if (buf->dl_done) cudaEventDestroy(buf->dl_done);
     if (buf->stage) {
         if (buf->dev->copy_stream) cudaStreamSynchronize(buf->dev->copy_stream);
         buf->dev->release(buf->stage);

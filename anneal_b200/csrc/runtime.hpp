@@ -48,7 +48,7 @@ struct GemmTuning {
     int stream_stores = 0;  // 1: streaming hint on the output stores
     int single_cta = 0;     // 1: the one-CTA kernel even where a CTA pair applies
 };
-constexpr int kDefaultGroupM = 8;
+constexpr int kDefaultGroupM = 2;     // measured best or within 1% of best on every wide-MLP shape (sweep over -1, 2, 4, 8, 16)
 
 // What the epilogue of one contraction launch does besides (or instead of) storing the contraction.
 struct GemmFusion {
@@ -94,6 +94,11 @@ struct anl_buffer {
     bool staged_stored = false;   // the staged bytes are already in the buffer's storage format
     cudaEvent_t stage_ready = nullptr, stage_free = nullptr;
     bool stage_free_recorded = false;
+    // asynchronous read-back: widening block for f16 buffers, event behind the last copy begun
+    void* dl_stage = nullptr;
+    int64_t dl_stage_elems = 0;
+    cudaEvent_t dl_done = nullptr;
+    bool dl_pending = false;
 };
 
 struct anl_device {

@@ -108,6 +108,8 @@ def load_library():
     L.anl_buffer_upload_begin_stored.argtypes = [vp, vp, C.c_int64]
     L.anl_buffer_upload_commit.argtypes = [vp]
     L.anl_buffer_download.argtypes = [vp, vp, C.c_int64]
+    L.anl_buffer_download_begin.argtypes = [vp, vp, C.c_int64]
+    L.anl_buffer_download_wait.argtypes = [vp]
     L.anl_buffer_release.argtypes = [vp]
     L.anl_buffer_release.restype = None
     L.anl_buffer_view.argtypes = [vp, C.c_int64, C.c_int64, C.POINTER(vp)]
@@ -145,7 +147,7 @@ ABI_SYMBOLS = [
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_begin_stored", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum", "anl_allgather",
     "anl_comm_destroy", "anl_comm_set_timeout", "anl_comm_wait", "anl_comm_abort", "anl_comm_inject_delay", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
-    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search", "anl_stream", "anl_lower_gemm", "anl_gemm_inject_status",
+    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search", "anl_stream", "anl_lower_gemm", "anl_gemm_inject_status", "anl_buffer_download_begin", "anl_buffer_download_wait",
 ]
 
 KERNEL_CLASSES = {0: "elementwise", 1: "reduce", 2: "reduce_split", 3: "gemm", 4: "raw"}
@@ -286,6 +288,19 @@ class ResidentBuffer:
         a = np.empty(self.elems, dtype=np.float32)
         self.dev._check(self.dev.L.anl_buffer_download(self.h, a.ctypes.data, a.size))
         return a
+
+    def download_begin(self, host: np.ndarray):
+        """Queue a read-back of the first ``host.size`` values into ``host`` (float32, contiguous,
+        pinned) behind the work already queued; returns at once. ``download_wait`` completes it."""
+        if host.dtype != np.float32 or not host.flags["C_CONTIGUOUS"]:
+            raise ValueError("download_begin: a contiguous float32 array is required")
+        self._dl = host
+        self.dev._check(self.dev.L.anl_buffer_download_begin(self.h, host.ctypes.data, host.size))
+        return self
+
+    def download_wait(self):
+        self.dev._check(self.dev.L.anl_buffer_download_wait(self.h))
+        return self._dl
 
     @property
     def device_ptr(self) -> int:

@@ -125,6 +125,14 @@ class ResidentTrainer:
             self.dev.sgd_step(self.master, self.store, self.grad, self.lr, self.grad_scale / self.world)
         return None if self.resident_inputs else float(self.loss_host[0])
 
+    def loss_begin(self, slot: np.ndarray) -> None:
+        """Resident-input mode: queue the read-back of the loss of the step just issued into ``slot``
+        (one pinned float32) and return at once; the value is there after ``loss_wait``."""
+        self.loss_res.download_begin(slot)
+
+    def loss_wait(self) -> float:
+        return float(self.loss_res.download_wait()[0])
+
     def loss(self) -> float:
         if self.resident_inputs:
             return float(self.loss_res.download()[0])

@@ -196,6 +196,12 @@ void anl_graph_release(anl_graph* g);
 int anl_buffer_create(anl_device* dev, int dtype, int64_t elems, anl_buffer** out);
 int anl_buffer_upload(anl_buffer* buf, const float* data, int64_t elems);
 int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems);
+/* Read-back that does not stall the host: `begin` queues the copy of the first `elems` values (as
+ * float32) into `host` (pinned memory) behind the work already queued and returns; `wait` blocks
+ * until the last copy begun on this buffer has landed.  Lets a loop read step i's loss while step
+ * i+1 runs (the reference reads every output back before Run returns, executor.go:205-240). */
+int anl_buffer_download_begin(anl_buffer* buf, float* host, int64_t elems);
+int anl_buffer_download_wait(anl_buffer* buf);
 /* Pipelined upload of the next batch (the data-loader side of examples/mlp.go:111-142, where the
  * reference re-uploads x and y inside Run every step).  `upload_begin` queues the host-to-device
  * copy on a copy stream into a staging block and returns; the buffer still holds the previous

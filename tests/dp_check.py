@@ -1,6 +1,8 @@
 """Run by `torch.distributed.run` on 2+ GPUs (see test_gpu_multi.py): the three ways of applying
 the gradients across ranks — sharded update, all-reduce with full update, and one bucket all-reduce
-after the backward pass — must leave identical parameters, and every rank must hold the same ones."""
+after the backward pass — must leave identical parameters, every rank must hold the same ones, and
+N ranks with batch B each must train like ONE rank with the N batches concatenated (same seeds):
+the data-parallel step is the big-batch step, up to the f16 rounding of each rank's gradients."""
 import os
 import sys
 
@@ -15,7 +17,6 @@ from anneal_b200.train import ResidentTrainer                 # noqa: E402
 
 
 def main():
-    os.environ.pop("NCCL_DEBUG", None)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     dist.init_process_group("gloo", rank=rank, world_size=world)
     dev = Device(local)
@@ -49,6 +50,29 @@ def main():
         ok = False
         if rank == 0:
             print("ranks hold different parameters after the sharded update", flush=True)
+    # one rank, batch N*B: the same samples in rank order, through the same trainer without a collective
+    if rank == 0:
+        R.reset()
+        B = 512
+        big = W.WideMLP(batch=world * B, width=2048, classes=72, depth=2)
+        parts = [W.WideMLP(batch=B, width=2048, classes=72, depth=2, rank=r).make_inputs() for r in range(world)]
+        xb = np.concatenate([p[0] for p in parts])
+        yb = np.concatenate([p[1] for p in parts])
+        one = ResidentTrainer(dev, big, 0.05, world=1, use_graph=True, resident_inputs=True)
+        one.load_batch(xb, yb)
+        for _ in range(3):
+            one.step()
+        ref = np.concatenate(one.parameters())
+        start = np.concatenate([p.value for p in big.params])
+        moved = float(np.abs(ref - start).max())
+        d = float(np.abs(results[1] - ref).max())
+        # each rank rounds its own gradient to f16 before the sum; the big batch rounds once
+        if not (moved > 0 and d <= 4e-3 * moved):
+            ok = False
+            print(f"{world} ranks x batch {B} differ from one rank x batch {world * B} by {d:.3e} (the parameters moved by {moved:.3e})", flush=True)
+        else:
+            print(f"DP_BIG_BATCH ok: difference {d:.3e}, parameters moved by {moved:.3e}", flush=True)
+    dist.barrier()
     flags = [None] * world
     dist.all_gather_object(flags, bool(ok))
     dev.synchronize()

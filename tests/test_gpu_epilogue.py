@@ -55,11 +55,16 @@ def test_fused_launches_equal_separate_launches(batch, width, classes):
     assert sf["gemm_launched"] == sp["gemm_launched"]
     assert sf["kernels_launched"] == sp["kernels_launched"] - 5, (sf, sp)      # 5 consumers gone; each bias gradient is still one (smaller) launch
     bias_grads = {it.bufs[0].uop_idx for it in keep if len(it.bufs[0].shape) == 1 and it.bufs[0].uop_idx in out_ids}
+    where = {it.bufs[0].uop_idx: (n, it.bufs[0].shape) for n, it in enumerate(keep)}
     for k in plain:
         if k in bias_grads:
             assert rel_err(fused[k], plain[k]) <= 1e-3, (k, rel_err(fused[k], plain[k]))
-        else:
-            assert np.array_equal(fused[k], plain[k]), (k, rel_err(fused[k], plain[k]))
+        elif not np.array_equal(fused[k], plain[k]):
+            n, shape = where[k]
+            bad = np.argwhere(fused[k].reshape(shape) != plain[k].reshape(shape))
+            raise AssertionError(f"kernel {n} output {shape}: {len(bad)} of {fused[k].size} values differ; rows {bad[:, 0].min()}..{bad[:, 0].max()}, "
+                                 f"columns {bad[:, -1].min()}..{bad[:, -1].max()}; first {bad[0]}: fused {fused[k].reshape(shape)[tuple(bad[0])]} separate {plain[k].reshape(shape)[tuple(bad[0])]}; "
+                                 f"distinct rows {len(np.unique(bad[:, 0]))}, distinct columns {len(np.unique(bad[:, -1]))}")
 
 
 def test_fused_launches_against_the_oracle(cuda, oracle):

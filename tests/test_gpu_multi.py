@@ -1,4 +1,5 @@
-"""Data-parallel update paths on two GPUs, when the box has them (one process per GPU)."""
+"""Data-parallel update paths and the loss of a rank, on two GPUs when the box has them (one process
+per GPU; skipped on a one-GPU box)."""
 import os
 import subprocess
 import sys
@@ -24,3 +25,15 @@ def test_sharded_update_equals_allreduce_update_on_two_ranks():
                         "--master-addr", "127.0.0.1", "--master-port", "29533", os.path.join(here, "dp_check.py")],
                        capture_output=True, text=True, timeout=600, env=env)
     assert r.returncode == 0 and "DP_CHECK OK" in r.stdout, (r.stdout[-2000:], r.stderr[-2000:])
+
+
+@pytest.mark.skipif(_gpu_count() < 2, reason="needs two GPUs")
+def test_a_rank_that_leaves_between_steps_is_survived():
+    """rank_failure_check.py: the peer exits cleanly between steps; the survivor's next collective is
+    ended by the watchdog with ANL_ERR_COMM, further collectives refuse, a new communicator recovers."""
+    here = os.path.dirname(os.path.abspath(__file__))
+    env = dict(os.environ, NCCL_NVLS_ENABLE="0")
+    r = subprocess.run([sys.executable, "-m", "torch.distributed.run", "--nnodes=1", "--nproc-per-node", "2",
+                        "--master-addr", "127.0.0.1", "--master-port", "29534", os.path.join(here, "rank_failure_check.py")],
+                       capture_output=True, text=True, timeout=300, env=env)
+    assert "RANK_FAILURE OK" in r.stdout, (r.stdout[-2000:], r.stderr[-2000:])
