@@ -9,6 +9,12 @@
 // one are compared to 1e-4 of the output's largest magnitude, because lanes change the order of
 // the f32 additions.  Results persist in a line-per-entry JSON file keyed by the kernel's
 // structure hash and guarded by the hash of its default source (codegen/beam.go:147-190).
+//
+// A dense f16 contraction is searched too — it is where the reference's Tile / Upcast / Vectorize
+// act (codegen/opt.go:206-307, 318-556) — but over the hand-written kernel's own tunables: tile
+// width, depth of the shared-memory ring, raster group, and a flag word (1 streaming stores, 2 the
+// one-CTA kernel).  None of them changes the order of the additions inside a tile, so the guard is
+// bit-identity.
 #include <algorithm>
 #include <cmath>
 #include <cstdio>
@@ -100,8 +106,108 @@ static void beam_cache_store(anl_device* dev, uint64_t key, uint64_t src_hash, c
     }
 }
 
+CodegenOpts gemm_beam_opts(const int* o, bool debug) {
+    CodegenOpts c; c.debug_bounds = debug;
+    c.gemm_tile_n = o[0]; c.gemm_stages = o[1]; c.gemm_group_m = o[2]; c.gemm_stream_stores = o[3] & 1; c.gemm_single_cta = (o[3] >> 1) & 1;
+    return c;
+}
+
+static bool is_tensor_contraction(anl_device* dev, const Item& it) {
+    Contraction c;
+    return !(dev->flags & ANL_OPEN_NO_GEMM) && it.source.empty() && match_contraction(it, c) && c.in_dtype == DT_F16 && c.out_dtype == DT_F16 && !c.m_sym && !c.k_sym;
+}
+
+// Search over the contraction kernel's tunables.  Same beam, same cache; the key is salted so that
+// a kernel's entry for the generated route (device opened without the tensor-core kernels) and for
+// this route do not collide, and the guard is the hash of the kernel text plus the default plan's note.
+static int beam_search_gemm(anl_device* dev, const Item& it, int width, int depth, anl_beam_result* out) {
+    bool debug = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;
+    int base_o[4] = {0, 0, 0, 0};
+    std::shared_ptr<Plan> base_plan;
+    if (int rc = get_plan(dev, it, gemm_beam_opts(base_o, debug), base_plan)) return rc;
+    if (base_plan->r.klass != KC_GEMM) return dev->fail(ANL_ERR_UNSUPPORTED, "beam: the contraction is not routed to the tensor-core kernel");
+    std::string src;
+    if (gemm_pair_source(dev, *base_plan, "", src) != ANL_OK) src = base_plan->r.note;
+    const uint64_t key = structure_hash(it) ^ 0x67656d6d5f74756eull, src_hash = fnv1a(src.data(), src.size());
+    int cached[4];
+    if (beam_cache_lookup(dev, key, src_hash, cached)) {
+        std::memcpy(out->opts, cached, sizeof cached);
+        out->from_cache = 1; out->best_us = dev->beam_cache[key].us;
+        return ANL_OK;
+    }
+    std::vector<void*> ptrs(it.bufs.size(), nullptr);
+    int rc = ANL_OK;
+    for (size_t b = 0; b < it.bufs.size() && rc == ANL_OK; b++) {
+        int64_t n = it.bufs[b].elems(0);
+        rc = dev->alloc((size_t)n * dt_storage_bytes(it.bufs[b].dtype), &ptrs[b]);
+        if (rc == ANL_OK && b > 0) {
+            std::vector<float> h((size_t)n); fill(h, (int)b);
+            rc = upload_f32(dev, ptrs[b], it.bufs[b].dtype, h.data(), n, dev->stream);
+            cudaStreamSynchronize(dev->stream);
+        }
+    }
+    const int64_t on = it.bufs[0].elems(0);
+    std::vector<float> ref((size_t)on), got((size_t)on);
+    auto run_one = [&](const int* o, double* us, std::vector<float>& result) -> int {
+        std::shared_ptr<Plan> p;
+        int r = get_plan(dev, it, gemm_beam_opts(o, debug), p);
+        if (r) return r;
+        if (p->r.klass != KC_GEMM) return ANL_ERR_UNSUPPORTED;
+        cudaMemsetAsync(ptrs[0], 0xFF, (size_t)on * dt_storage_bytes(it.bufs[0].dtype), dev->stream);
+        if ((r = time_plan(dev, *p, it, ptrs, us))) return r;
+        if ((r = download_f32(dev, result.data(), ptrs[0], it.bufs[0].dtype, on, dev->stream))) return r;
+        return cudaStreamSynchronize(dev->stream) == cudaSuccess ? ANL_OK : dev->fail(ANL_ERR_CUDA, "beam: sync failed");
+    };
+    double base_us = 0;
+    if (rc == ANL_OK) rc = run_one(base_o, &base_us, ref);
+    if (rc == ANL_OK) {
+        const int tile_v[] = {256, 128};
+        const int stage_v[] = {4, 5, 6, 7};
+        const int group_v[] = {-1, 1, 2, 4, 8, 16};
+        const int flag_v[] = {1, 2};
+        if (width <= 0) width = 4;
+        if (depth <= 0) depth = 4;
+        std::vector<Cand> frontier = {Cand{{0, 0, 0, 0}, base_us}};
+        Cand best = frontier[0];
+        std::vector<std::string> seen = {"0,0,0,0"};
+        for (int d = 0; d < depth; d++) {
+            std::vector<Cand> next;
+            for (const Cand& c : frontier) {
+                auto try_set = [&](int knob, int value) {
+                    Cand n = c; n.o[knob] = value;
+                    char k[64]; std::snprintf(k, sizeof k, "%d,%d,%d,%d", n.o[0], n.o[1], n.o[2], n.o[3]);
+                    if (std::find(seen.begin(), seen.end(), k) != seen.end()) return;
+                    seen.push_back(k);
+                    out->candidates_tried++;
+                    double us = 0;
+                    if (run_one(n.o, &us, got) != ANL_OK || std::memcmp(got.data(), ref.data(), got.size() * 4) != 0) { out->candidates_rejected++; return; }
+                    n.us = us;
+                    next.push_back(n);
+                };
+                for (int v : tile_v) try_set(0, v);
+                for (int v : stage_v) try_set(1, v);
+                for (int v : group_v) try_set(2, v);
+                for (int v : flag_v) try_set(3, v);
+            }
+            if (next.empty()) break;
+            std::sort(next.begin(), next.end(), [](const Cand& a, const Cand& b) { return a.us < b.us; });
+            if ((int)next.size() > width) next.resize(width);
+            if (next[0].us >= best.us) break;
+            best = next[0];
+            frontier = next;
+        }
+        std::memcpy(out->opts, best.o, sizeof best.o);
+        out->base_us = base_us; out->best_us = best.us;
+        beam_cache_store(dev, key, src_hash, best.o, best.us);
+        dev->err.clear();
+    }
+    for (void* p : ptrs) dev->release(p);
+    return rc;
+}
+
 int beam_search(anl_device* dev, const Item& it, int width, int depth, anl_beam_result* out) {
     std::memset(out, 0, sizeof *out);
+    if (is_tensor_contraction(dev, it)) return beam_search_gemm(dev, it, width, depth, out);
     for (auto& b : it.bufs) if (b.symbolic()) return dev->fail(ANL_ERR_UNSUPPORTED, "beam: symbolic ranges are not searched (codegen/opt.go:108-111)");
     if (!it.source.empty()) return dev->fail(ANL_ERR_UNSUPPORTED, "beam: pre-rendered items are not searched");
     bool debug = (dev->flags & ANL_OPEN_DEBUG_BOUNDS) != 0;

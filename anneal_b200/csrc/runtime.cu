@@ -657,7 +657,7 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
     };
     struct Absorbed { void* partials; int64_t parts, cols; };
     std::unordered_map<size_t, Absorbed> absorbed;      // item index -> column sums a contraction's epilogue computes for it
-    const bool fusion_on = !(dev->flags & (ANL_OPEN_NO_EPILOGUE_FUSION | ANL_OPEN_NO_GEMM | ANL_OPEN_BEAM));
+    const bool fusion_on = !(dev->flags & (ANL_OPEN_NO_EPILOGUE_FUSION | ANL_OPEN_NO_GEMM));
     // [update the parameter] hooks that fall due once item `at` has been queued
     auto updates_due = [&](size_t at) -> int {
         auto sg = sgd_at.find(at);
@@ -687,14 +687,15 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             // BeamApplyToItems (codegen/beam.go:470-541): cached winner, else search now
             bool sym = false; for (auto& b : it.bufs) if (b.symbolic()) sym = true;
             Contraction c;
-            bool gemm = !(dev->flags & ANL_OPEN_NO_GEMM) && match_contraction(it, c) && c.in_dtype == DT_F16;
-            if (!sym && !gemm) {
+            bool gemm = !(dev->flags & ANL_OPEN_NO_GEMM) && match_contraction(it, c) && c.in_dtype == DT_F16 && c.out_dtype == DT_F16 && !c.m_sym && !c.k_sym;
+            if (!sym) {
                 if (!dev->beam_loaded) { beam_cache_load(dev, ""); dev->beam_loaded = true; }
                 anl_beam_result br;
                 cudaStreamCaptureStatus cs = cudaStreamCaptureStatusNone;
                 cudaStreamIsCapturing(stream, &cs);
                 if (cs == cudaStreamCaptureStatusNone && beam_search(dev, it, 0, 0, &br) == ANL_OK) {
-                    use.block_threads = br.opts[0]; use.reduce_lanes = br.opts[1]; use.vector_width = br.opts[2]; use.split = br.opts[3];
+                    if (gemm) use = gemm_beam_opts(br.opts, use.debug_bounds);     // the tensor-core kernel's own tunables
+                    else { use.block_threads = br.opts[0]; use.reduce_lanes = br.opts[1]; use.vector_width = br.opts[2]; use.split = br.opts[3]; }
                 }
             }
         }

@@ -196,6 +196,8 @@ int comm_join(anl_device* dev, cudaStream_t stream);
 
 // autotuning (beam.cpp)
 int beam_search(anl_device* dev, const Item& it, int width, int depth, anl_beam_result* out);
+// the contraction kernel's tunables as a search result packs them: {tile_n, stages, group_m, flags}
+CodegenOpts gemm_beam_opts(const int* o, bool debug);
 void beam_cache_load(anl_device* dev, const std::string& path);
 bool beam_cache_lookup(anl_device* dev, uint64_t key, uint64_t src_hash, int* opts);   // 2*M*N*K of a routed contraction
 

@@ -4,9 +4,11 @@
 
 Prints one JSON line. `value` is samples/s with the batch already resident in HBM; `e2e` repeats
 the measurement through the public API with the batch in pinned host memory, the host→device copy
-and the loss read-back inside the timed region. `--impl reference` times the CPU restatement of the
-reference's kernels (the reference itself needs a Go toolchain and a graphics stack, neither
-exists here) on a bounded sample of the same workload.
+and the loss read-back inside the timed region. On one GPU the line also carries `sustained` (the
+same step looped for seconds, with the clocks it ran at) and `configs` (the other four benchmark
+configurations and the update pass, a few hundred milliseconds each). `--impl reference` times the
+CPU restatement of the reference's kernels (the reference itself needs a Go toolchain and a graphics
+stack, neither exists here) on a bounded sample of the same workload.
 """
 from __future__ import annotations
 
@@ -26,6 +28,12 @@ sys.path.insert(0, ROOT)
 METRIC = "train_step_samples_per_s"
 UNIT = "samples/s"
 CFG = dict(batch=8192, width=4096, classes=1000, depth=4)
+
+
+#: DRAM bytes (read + write) of one launch of the dominant kernel from a separate ncu capture; a
+#: constant of that capture, not a measurement of this run
+PAIR_GEMM_TRAFFIC = {"bytes": 351.7e6, "of": "one 4096x4096x8192 weight-gradient launch under ncu, 160 MB algorithmic (operands 128 MB, output 32 MB)"}
+ROW_CHAIN_TRAFFIC = {"bytes": 775.7e6, "of": "one row_chain launch over 8192x8192 under ncu, 805.3 MB algorithmic"}
 
 
 def flops_per_step(batch, width, classes, depth):
@@ -149,49 +157,69 @@ def peaks():
         return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
 
 
-def cpu_baseline(sample_batch: int, threads: int):
-    """The oracle, all host threads, on `sample_batch` rows of the same network."""
-    from anneal_b200 import realize as R, workloads as W
-    from anneal_b200.realize import leaf_inputs
-    from oracle.binding import OracleExecutor
-    R.reset()
-    R.MATERIALIZE_CONTRACTION_OPERANDS = True
-    try:
-        m = W.WideMLP(batch=sample_batch, width=CFG["width"], classes=CFG["classes"], depth=CFG["depth"])
-        x, y = m.make_inputs()
-        g = m.graph(x, y)
-        items, _ = R.build_schedule(g.targets())
-    finally:
-        R.MATERIALIZE_CONTRACTION_OPERANDS = False
-    inputs = leaf_inputs(g.targets())
-    ex = OracleExecutor(threads)
-    t0 = time.perf_counter()
-    ex.run(items, inputs)
-    dt = time.perf_counter() - t0
-    R.reset()
-    return sample_batch / dt, dt
+#: rows of the wide MLP's batch that one CPU step computes, in `cpu_baseline` and in `--impl reference` alike
+CPU_SAMPLE_BATCH = 2
+
+
+class CpuStep:
+    """One train step of the wide MLP on `sample_batch` rows through the oracle on all host threads.
+    The schedule is built once; each call times one run of it."""
+
+    def __init__(self, sample_batch: int, threads: int):
+        from anneal_b200 import realize as R, workloads as W
+        from anneal_b200.realize import leaf_inputs
+        from oracle.binding import OracleExecutor
+        R.reset()
+        R.MATERIALIZE_CONTRACTION_OPERANDS = True
+        try:
+            m = W.WideMLP(batch=sample_batch, width=CFG["width"], classes=CFG["classes"], depth=CFG["depth"])
+            x, y = m.make_inputs()
+            g = m.graph(x, y)
+            self.items, _ = R.build_schedule(g.targets())
+        finally:
+            R.MATERIALIZE_CONTRACTION_OPERANDS = False
+        self.inputs = leaf_inputs(g.targets())
+        self.ex = OracleExecutor(threads)
+        self.batch = sample_batch
+        R.reset()
+
+    def __call__(self) -> float:
+        t0 = time.perf_counter()
+        self.ex.run(self.items, self.inputs)
+        return time.perf_counter() - t0
 
 
 def run_reference(args):
+    """The reference arm: the CPU port of the reference's kernels, all host threads, `--warmup` untimed
+    and `--steps` timed steps of CPU_SAMPLE_BATCH rows each, cut short when a time budget runs out
+    (the line says how many steps were timed)."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
     threads = os.cpu_count() or 1
-    sample = 2
-    for _ in range(args.warmup if args.warmup < 1 else 1):
-        cpu_baseline(1, threads)
-    vals = []
-    for _ in range(max(1, min(args.steps, 3))):
-        v, dt = cpu_baseline(sample, threads)
-        vals.append((v, dt))
-    v = max(x[0] for x in vals)
-    ms = min(x[1] for x in vals) * 1e3
-    desc = f"batch {sample} of {CFG['batch']} rows, full widths; cost is linear in the batch"
+    budget_s = 150.0
+    step = CpuStep(CPU_SAMPLE_BATCH, threads)
+    t_start = time.perf_counter()
+    warm = 0
+    for _ in range(max(args.warmup, 0)):
+        step()
+        warm += 1
+        if time.perf_counter() - t_start > budget_s / 4:
+            break
+    times = []
+    for _ in range(max(args.steps, 1)):
+        times.append(step())
+        if time.perf_counter() - t_start > budget_s:
+            break
+    ms = 1e3 * sum(times) / len(times)
+    v = CPU_SAMPLE_BATCH / (ms / 1e3)
+    desc = f"{CPU_SAMPLE_BATCH} rows of the {CFG['batch']}-row batch per step, full widths, {len(times)} timed steps after {warm} warm-up"
     print(json.dumps({
-        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(vals),
-        "warmup": 1, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
+        "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
-        "config": {"workload": "wide_mlp_train_step", **CFG, "per_gpu_batch": CFG["batch"]},
+        "config": {"workload": "wide_mlp_train_step", **CFG, "per_gpu_batch": CFG["batch"], "sample_batch": CPU_SAMPLE_BATCH,
+                   "steps_requested": args.steps, "warmup_requested": args.warmup, "time_budget_s": budget_s},
         "cpu_baseline": {"value": v, "unit": UNIT, "cores": threads, "kind": "port", "sample": desc},
         "e2e": {"value": v, "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
@@ -204,8 +232,10 @@ def run_ours(args):
     from anneal_b200.device import Device
     from anneal_b200.train import ResidentTrainer
 
-    if not args.nccl_debug:
-        os.environ.pop("NCCL_DEBUG", None)       # NCCL prints its banner on stdout; rank 0 prints one JSON line
+    # NCCL writes its log to stdout, where rank 0 prints its one JSON line: when a log was asked for and
+    # no file was named, send it to stderr instead (the setting itself is left alone)
+    if os.environ.get("NCCL_DEBUG") and not os.environ.get("NCCL_DEBUG_FILE"):
+        os.environ["NCCL_DEBUG_FILE"] = "/dev/stderr"
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
@@ -268,10 +298,8 @@ def run_ours(args):
         gp = prof["gemm"]
         ach = gp["flops"] / (gp["total_ms"] / 1e3) / 1e12
         peak = pk["bf16_tflops"]
-        # DRAM bytes of one weight-gradient launch (4096x4096x8192, 160 MB algorithmic) from the ncu
-        # capture summarised in profiles/gemm_f16_tcgen05_pair_wide_mlp.md; not measured in this run
-        roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": 351.7e6,
-                "traffic_of": "one 4096x4096x8192 launch under ncu (algorithmic 160 MB)",
+        roof = {"bound": "tensor", "achieved": ach, "peak": peak, "unit": "TFLOP/s", "frac": ach / peak, "traffic": PAIR_GEMM_TRAFFIC["bytes"],
+                "traffic_of": PAIR_GEMM_TRAFFIC["of"],
                 "peak_kind": f"{pk_kind} burst dense 16-bit", "kernel": "gemm_f16_tcgen05_pair", "launches": gp["launches"],
                 "frac_of_sustained_peak": ach / pk.get("bf16_tflops_sustained", peak),
                 "avg_launch_ms": gp["total_ms"] / gp["launches"],
@@ -296,13 +324,20 @@ def run_ours(args):
         yh[:] = y
         host.append((xh, yh))
     e2e_loss = None
+    loss_slots = [pinned_array(1), pinned_array(1)]
 
     def e2e_steps(n):
+        # every step: its batch comes up from pinned host memory (copy stream, under the previous
+        # step), its loss goes down to the host; the host reads step i-1's loss while step i runs
+        # and only the last read waits
         nonlocal e2e_loss
         for i in range(n):
             tr2.step()                       # commits the staged batch, then the captured step
+            if i > 0:
+                e2e_loss = tr2.loss_wait()   # step i-1's loss: on the host by now
+            tr2.loss_begin(loss_slots[i % 2])
             tr2.prefetch(*host[(i + 1) % 2])  # next batch: host -> device behind this step
-            e2e_loss = tr2.loss()            # device -> host, waits for the step
+        e2e_loss = tr2.loss_wait()
 
     tr2.prefetch(*host[0])
     e2e_steps(max(args.warmup, 1))
@@ -322,16 +357,58 @@ def run_ours(args):
         ms2 = float(t[0])
     e2e = {"value": CFG["batch"] * world * args.steps / (ms2 / 1e3), "unit": UNIT,
            "h2d_bytes_per_step": int((x.size + y.size) * np.dtype(hdt).itemsize), "host_batch_dtype": np.dtype(hdt).name, "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps,
-           "how": "batch i+1 copied from pinned host memory on a copy stream while step i runs; loss read back every step",
+           "how": "batch i+1 copied from pinned host memory on a copy stream while step i runs; every step's loss is copied to the host behind the step and read there while the next step runs",
            "host_cpus_bound": len(numa_cpus) if numa_cpus else None,
            "loss": e2e_loss}
+
+    # the same step looped for seconds: what the clocks settle at under the power limit, and the
+    # step rate there (the burst above lasts tens of milliseconds)
+    sustained = None
+    if world == 1 and args.sustained_s > 0:
+        n_sus = max(50, int(args.sustained_s * 1e3 / (ms / args.steps)))
+        s2 = ClockSampler(local)
+        s2.start()
+        time.sleep(0.25)
+        for _ in range(20):
+            tr.step()
+        dev.synchronize()
+        s2.reset()
+        dev.timer_start()
+        for _ in range(n_sus):
+            tr.step()
+        ms_sus = dev.timer_stop()
+        ck = s2.stop()
+        per = ms_sus / n_sus
+        tf = flops_per_step(**CFG) / (per / 1e3) / 1e12
+        sustained = {"steps": n_sus, "seconds": ms_sus / 1e3, "ms_per_step": per, "value": CFG["batch"] / (per / 1e3), "unit": UNIT,
+                     "step_tflops": tf, "frac_of_sustained_peak": tf / pk.get("bf16_tflops_sustained", pk["bf16_tflops"]),
+                     "peak_sustained_tflops": pk.get("bf16_tflops_sustained"), "clocks": ck,
+                     "ms_times_sm_mhz": per * ck["sm_mhz"] if ck.get("sm_mhz") else None,
+                     "burst_ms_times_sm_mhz": (ms / args.steps) * clocks["sm_mhz"] if clocks.get("sm_mhz") else None,
+                     "note": "whole-step FLOP rate (contractions and everything else) against the sustained dense 16-bit GEMM peak; clocks sampled, never set"}
+
+    # the other configurations and the update pass, a few hundred milliseconds each
+    configs = None
+    if world == 1 and not args.no_configs:
+        configs = {}
+        for name, (st, wu) in {"mlp": (300, 20), "cnn": (100, 10), "softmax": (30, 5), "sgd": (30, 5), "dynmlp": (20, 3)}.items():
+            try:
+                r = measure_other(dev, name, st, wu)
+                configs[name] = {k: r[k] for k in ("metric", "unit", "value", "ms_per_step", "dtype", "config", "steps", "gpu_launches") if k in r}
+                if "roofline" in r:
+                    configs[name]["roofline"] = r["roofline"]
+            except Exception as e:                      # a failing side measurement must not lose the headline line
+                configs[name] = {"error": str(e)[:300]}
 
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
         threads = os.cpu_count() or 1
-        v, dt = cpu_baseline(8, threads)      # about 20 s on 16 host threads
-        cpu = {"value": v, "unit": UNIT, "cores": threads, "kind": "port",
-               "sample": f"batch 8 of {CFG['batch']} rows, full widths, one step ({dt:.1f} s); cost grows linearly with the batch beside a small fixed part, so a larger sample can only favour the CPU"}
+        step = CpuStep(CPU_SAMPLE_BATCH, threads)
+        step()                                # one untimed step
+        dts = [step() for _ in range(2)]
+        dt = sum(dts) / len(dts)
+        cpu = {"value": CPU_SAMPLE_BATCH / dt, "unit": UNIT, "cores": threads, "kind": "port",
+               "sample": f"{CPU_SAMPLE_BATCH} rows of the {CFG['batch']}-row batch per step, full widths, 2 timed steps after 1 warm-up ({dt:.1f} s per step); the same sample as --impl reference"}
 
     if rank == 0:
         fl = flops_per_step(**CFG)
@@ -344,7 +421,8 @@ def run_ours(args):
                        "optimizer": "sgd lr=1e-3 on f32 masters, in the timed region", "loss": loss_value},
             "e2e": e2e, "gpu_launches": int(launches), "graph_replays": int(graph_replays), "clocks": clocks,
             "step_tflops": fl * world / (ms / args.steps / 1e3) / 1e12,
-            "roofline": roof, "cpu_baseline": cpu,
+            "roofline": roof, "cpu_baseline": cpu, "sustained": sustained, "configs": configs,
+            "fused": {k: int(dev.stats()[k]) for k in ("epilogues_fused", "colsums_fused")},
             "kernel_classes": {k: {"launches": v["launches"], "ms": round(v["total_ms"], 3)} for k, v in prof.items()},
         }
         print(json.dumps(out))
@@ -353,15 +431,18 @@ def run_ours(args):
     dev.close()
 
 
-def run_other(args):
-    """The other four configurations, one GPU: samples/s (or GB/s for the bandwidth-bound one) with
-    inputs resident, timed with CUDA events over graph replays."""
+def measure_other(dev, workload, steps, warmup, materialize=-1, dyn_batches="1,17,256,4096,65536"):
+    """One of the other four configurations (or the update pass) on one GPU: samples/s, or GB/s for
+    the bandwidth-bound ones, with inputs resident, timed with CUDA events over graph replays."""
     from anneal_b200 import realize as R, workloads as W
-    from anneal_b200.device import Device
-    from anneal_b200.realize import leaf_inputs
     from anneal_b200.train import ResidentTrainer
     from anneal_b200.uop import dtypes
-    dev = Device(int(os.environ.get("LOCAL_RANK", "0")))
+
+    class A:
+        pass
+    args = A()
+    args.workload, args.steps, args.warmup, args.materialize, args.dyn_batches = workload, steps, warmup, materialize, dyn_batches
+    launches0 = dev.stats()["kernels_launched"]
     out = {"data": "synthetic", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup, "higher_is_better": True}
     if args.workload in ("mlp", "cnn"):
         m = W.MLP() if args.workload == "mlp" else W.SmallCNN()
@@ -396,15 +477,15 @@ def run_other(args):
         for _ in range(args.steps):
             dev.replay(items, inputs, None, placed)
         ms = dev.timer_stop()
+        for bb in (xb, gb, ob):
+            bb.release()
         algo = 3 * s.x.size * 4
         pk, kind = peaks()
         gbs = algo * args.steps / (ms / 1e3) / 1e9
         out.update(metric="softmax_fwd_bwd_hbm_gbs", unit="GB/s", value=gbs, ms_per_step=ms / args.steps, dtype="f32",
                    config={"workload": "softmax_fwd_bwd_8192x8192", "kernels_per_step": len(items), "algorithmic_bytes": algo},
                    roofline={"bound": "hbm", "achieved": gbs, "peak": pk["hbm_gbs"], "unit": "GB/s", "frac": gbs / pk["hbm_gbs"],
-                             # DRAM bytes of one launch from the ncu capture summarised in
-                             # profiles/row_chain_softmax_8192.md (rate x duration); not measured in this run
-                             "traffic": 775.7e6, "traffic_of": "one row_chain launch under ncu (algorithmic 805.3 MB)",
+                             "traffic": ROW_CHAIN_TRAFFIC["bytes"], "traffic_of": ROW_CHAIN_TRAFFIC["of"],
                              "peak_kind": kind + " copy", "kernel": "row_chain",
                              "note": "the whole schedule is this one launch; timed over graph replays"})
     elif args.workload == "sgd":
@@ -422,6 +503,8 @@ def run_other(args):
         for _ in range(args.steps):
             dev.sgd_step(mb, pb, gb, 1e-3, 1.0)
         ms = dev.timer_stop()
+        for bb in (mb, pb, gb):
+            bb.release()
         algo = n * 12
         pk, kind = peaks()
         gbs = algo * args.steps / (ms / 1e3) / 1e9
@@ -464,8 +547,15 @@ def run_other(args):
         R.MATERIALIZE_CONTRACTION_OPERANDS = False
         out.update(metric=METRIC, unit=UNIT, value=res[str(batches[-1])]["samples_per_s"], ms_per_step=res[str(batches[-1])]["us_per_replay"] / 1e3, dtype="f32",
                    config={"workload": "dynmlp_symbolic_batch", "per_batch": res, "nvrtc_compiles": dev.stats()["nvrtc_compiles"]})
-    out["gpu_launches"] = int(dev.stats()["kernels_launched"])
-    print(json.dumps(out))
+    out["gpu_launches"] = int(dev.stats()["kernels_launched"] - launches0)
+    R.reset()
+    return out
+
+
+def run_other(args):
+    from anneal_b200.device import Device
+    dev = Device(int(os.environ.get("LOCAL_RANK", "0")))
+    print(json.dumps(measure_other(dev, args.workload, args.steps, args.warmup, args.materialize, args.dyn_batches)))
     dev.close()
 
 
@@ -482,9 +572,10 @@ def main():
     ap.add_argument("--materialize", type=int, default=-1, help="mlp/cnn: 1/0 forces contraction operands to be buffers or expressions")
     ap.add_argument("--e2e-f32-host", action="store_true", help="e2e: host batches as float32 rows (converted on the device) instead of rows already rounded to the f16 storage format")
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-configs", action="store_true", help="one GPU: skip the other configurations' side measurements")
+    ap.add_argument("--sustained-s", type=float, default=3.0, help="one GPU: seconds the step is looped for the sustained record (0 skips it)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="all-reduce the whole gradient bucket after the backward pass")
-    ap.add_argument("--nccl-debug", action="store_true", help="leave NCCL_DEBUG as set in the environment")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference(args)

@@ -175,7 +175,10 @@ int anl_benchmark(anl_device* dev, const uint8_t* blob, size_t blob_len, int ind
  * (bit-identical without a REDUCE, 1e-4 relative with one).  The winner is stored in a disk cache
  * (`cache_path`, or $ANNEAL_BEAM_CACHE, or ~/.cache/anneal/beam_cache_cuda.json) keyed by the
  * kernel's structure hash and guarded by its default source hash.  A device opened with
- * ANL_OPEN_BEAM applies cached winners in anl_run and searches on a miss. */
+ * ANL_OPEN_BEAM applies cached winners in anl_run and searches on a miss.
+ * A dense f16 contraction (routed to the tcgen05 kernels) is searched over that kernel's tunables
+ * instead: `opts` is then {tile_n, stages, group_m, flags} with flags bit 0 = streaming stores,
+ * bit 1 = one-CTA kernel, and the guard is bit-identity (none of them reorders a sum). */
 typedef struct { int opts[4]; double base_us, best_us; int candidates_tried, candidates_rejected, from_cache; } anl_beam_result;
 int anl_beam_search(anl_device* dev, const uint8_t* blob, size_t blob_len, int index, int width, int depth,
                     const char* cache_path, anl_beam_result* out);

@@ -59,3 +59,36 @@ def test_tuned_device_gives_the_same_results(oracle, tmp_path, monkeypatch):
         assert np.abs(got - want).max() <= 1e-4 * np.abs(want).max()
     finally:
         dev.close()
+
+
+def test_contraction_search_covers_the_tensor_core_kernel(cuda, tmp_path):
+    """A dense f16 contraction is searched over the tcgen05 kernel's own tunables (tile width, ring
+    depth, raster group, flags); every candidate must reproduce the default configuration's output
+    bit for bit, the winner is cached, and a device opened with the search applied gives the same
+    values as one without."""
+    from anneal_b200.uop import dtypes
+    rng = np.random.default_rng(3)
+    a = Tensor.new_leaf((1024, 512), dtypes.float16).set_data(rng.standard_normal(1024 * 512) * 0.1)
+    w = Tensor.new_leaf((768, 512), dtypes.float16).set_data(rng.standard_normal(768 * 512) * 0.1)
+    y = a.matmul(w.permute((1, 0)))
+    items, out_ids, inputs = schedule([y])
+    cache = str(tmp_path / "gemm_beam.json")
+    r1 = cuda.beam_search(items[0], cache_path=cache)
+    assert not r1["from_cache"] and r1["tried"] >= 10, r1
+    assert r1["rejected"] == 0, r1                       # no tunable reorders a sum
+    assert r1["best_us"] <= r1["base_us"] * 1.0001
+    r2 = cuda.beam_search(items[0], cache_path=cache)
+    assert r2["from_cache"] and r2["opts"] == r1["opts"]
+    want = cuda.run(items, inputs)[out_ids[0]]
+    os.environ["ANNEAL_BEAM_CACHE"] = cache
+    try:
+        tuned = Device(0, Device.BEAM)
+        try:
+            g0 = tuned.stats()["gemm_launched"]
+            got = tuned.run(items, inputs)[out_ids[0]]
+            assert tuned.stats()["gemm_launched"] - g0 == 1
+        finally:
+            tuned.close()
+    finally:
+        os.environ.pop("ANNEAL_BEAM_CACHE", None)
+    assert np.array_equal(got, want)
