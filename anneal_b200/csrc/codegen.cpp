@@ -17,7 +17,13 @@
 //    f32 partials to scratch memory, a finish kernel combines them in ascending order and applies
 //    the epilogue, so results do not depend on scheduling;
 //  * loads whose index cannot be proven inside the buffer (the guarded load of a PAD,
-//    schedule/index.go:101-134) are clamped: WGSL defines out-of-range reads, CUDA does not.
+//    schedule/index.go:101-134) are clamped: WGSL defines out-of-range reads, CUDA does not;
+//  * guards that compare a SMALL static range with constants are decided while generating: a
+//    convolution reaches the device as a sum of K padded slices, each live for exactly one value of
+//    the patch index k (tensor/nn/nn.go:256-276), i.e. K selects per multiply.  A reduce loop over
+//    such a range is emitted once per value of the range, an output range of that kind becomes a
+//    switch over its values, and in every copy the guards fold to true or false — what is left is the
+//    one live slice, a direct convolution with the bounds checks of its padding and no im2col buffer.
 //
 // Arithmetic follows codegen/wgsl.go:240-447: f16 values use native half add/sub/mul outside
 // reductions and are widened to f32 inside an f16 reduction with a single narrowing at the end
@@ -104,6 +110,11 @@ struct Gen {
     std::vector<int> reduces;              // REDUCE nodes in node order
     bool has_sym = false;
 
+    // ranges that hold one known value while the code around them is being rendered (enumeration)
+    std::map<int, int64_t> fixed_range;
+    void fix_range(int r, int64_t v) { fixed_range[r] = v; lin_memo.clear(); }
+    void unfix_range(int r) { fixed_range.erase(r); lin_memo.clear(); }
+
     std::vector<Atom> atoms;
     std::map<std::string, int> atom_key;
     std::vector<int> range_atom;           // node → atom
@@ -170,6 +181,107 @@ struct Gen {
             atoms.push_back(a);
         }
         return true;
+    }
+
+    // ── guards decided at generation time ─────────────────────────────────────────────────────
+    std::set<int> enum_reduce;              // REDUCE nodes whose single small range is emitted value by value
+    std::vector<int> enum_out;              // small output ranges turned into a switch over their values
+
+    // Which ranges an integer comparison reads once its operands are in canonical affine form (the
+    // scheduler's reshape chains mention every range of the kernel; (n*7056 + hw*9 + k) % 9 is k).
+    // False when something other than ranges decides it.
+    bool guard_ranges(int i, std::vector<bool>& reads) {
+        const Node& nd = N(i);
+        if ((nd.op != OP_CMPLT && nd.op != OP_CMPEQ && nd.op != OP_CMPNE) || !is_live(i)) return false;
+        if (!is_intlike(nd.src[0]) || !is_intlike(nd.src[1])) return false;
+        Lin d = ladd(lin(nd.src[0]), lin(nd.src[1]), -1);
+        std::function<bool(const Lin&)> only_ranges = [&](const Lin& l) {
+            for (auto& t : l.t) { const Atom& a = atoms[t.first]; if (a.kind == Atom::OPAQUE) return false; if (a.kind != Atom::RANGE && !only_ranges(a.inner)) return false; }
+            return true;
+        };
+        if (!only_ranges(d)) return false;
+        reads.assign(all_ranges.size(), false);
+        bool any = false;
+        for (size_t r = 0; r < all_ranges.size(); r++) if (lin_reads(d, all_ranges[r])) { reads[r] = true; any = true; }
+        return any;
+    }
+    // Fraction of the value combinations of `ranges` for which guard `g` holds (1 where it does not fold).
+    double guard_truth(int g, const std::vector<int>& ranges) {
+        int64_t combos = 1;
+        for (int r : ranges) combos *= N(r).arg;
+        int64_t yes = 0;
+        const Node& nd = N(g);
+        for (int64_t cs = 0; cs < combos; cs++) {
+            int64_t rem = cs;
+            for (int e = (int)ranges.size() - 1; e >= 0; e--) { fixed_range[ranges[e]] = rem % N(ranges[e]).arg; rem /= N(ranges[e]).arg; }
+            lin_memo.clear();
+            Lin d = ladd(lin(nd.src[0]), lin(nd.src[1]), -1);
+            bool t = true;
+            if (d.is_const()) t = nd.op == OP_CMPLT ? d.c < 0 : nd.op == OP_CMPEQ ? d.c == 0 : d.c != 0;
+            if (t) yes++;
+        }
+        for (int r : ranges) fixed_range.erase(r);
+        lin_memo.clear();
+        return (double)yes / (double)combos;
+    }
+
+    // Decides which small ranges are enumerated.  A set of ranges qualifies when at least four guards
+    // read exactly that set and, averaged over the set's value combinations, those guards hold less
+    // than three times out of four: they select slices (a patch index equal to a constant) instead of
+    // merely trimming a border (a padded row, true almost everywhere).
+    void plan_enumeration() {
+        enum_reduce.clear(); enum_out.clear();
+        if (has_sym || opts.debug_bounds) return;
+        const size_t nr = all_ranges.size();
+        std::map<std::vector<int>, std::vector<int>> by_set;       // ranges read (node indices, sorted) -> guards
+        std::vector<bool> reads;
+        for (int i = 0; i < n; i++) {
+            if (!guard_ranges(i, reads)) continue;
+            std::vector<int> key; int64_t prod = 1; bool ok = true;
+            for (size_t r = 0; r < nr; r++) if (reads[r]) {
+                const Node& rn = N(all_ranges[r]);
+                if (rn.symbolic() || rn.arg < 2 || rn.arg > 128) { ok = false; break; }
+                key.push_back(all_ranges[r]); prod *= rn.arg;
+            }
+            if (ok && !key.empty() && prod <= 128) by_set[key].push_back(i);
+        }
+        struct Cand { std::vector<int> ranges; double score; };
+        std::vector<Cand> outs;
+        for (auto& kv : by_set) {
+            if (kv.second.size() < 4) continue;
+            double frac = 0;
+            for (int g : kv.second) frac += guard_truth(g, kv.first);
+            frac /= (double)kv.second.size();
+            if (frac > 0.75) continue;
+            // a single reduce range: value-by-value loop of the REDUCE that owns it
+            if (kv.first.size() == 1 && N(kv.first[0]).axis() == 1) {
+                for (int red : reduces) {
+                    std::vector<int> rr;
+                    for (size_t s2 = 1; s2 < N(red).src.size(); s2++) if (N(N(red).src[s2]).op == OP_RANGE) rr.push_back(N(red).src[s2]);
+                    if (rr.size() == 1 && rr[0] == kv.first[0]) enum_reduce.insert(red);
+                }
+                continue;
+            }
+            bool all_out = true;
+            for (int r : kv.first) if (std::find(loop_ranges.begin(), loop_ranges.end(), r) == loop_ranges.end()) all_out = false;
+            if (all_out) outs.push_back(Cand{kv.first, (double)kv.second.size() * (1.0 - frac)});
+        }
+        std::sort(outs.begin(), outs.end(), [](const Cand& x, const Cand& y) { return x.score > y.score; });
+        std::set<int> chosen; int64_t prod = 1;
+        for (auto& c : outs) {
+            int64_t p2 = prod;
+            for (int r : c.ranges) if (!chosen.count(r)) p2 *= N(r).arg;
+            if (p2 > 128) continue;
+            for (int r : c.ranges) chosen.insert(r);
+            prod = p2;
+        }
+        for (int r : loop_ranges) if (chosen.count(r)) enum_out.push_back(r);
+    }
+
+    // forget what was rendered inside reduce loop `red` (ctx == red), so that it can be rendered again
+    void forget_loop(int red) {
+        for (auto it = memo.begin(); it != memo.end();) { if (it->first.second == red) it = memo.erase(it); else ++it; }
+        loop[red] = Block();
     }
 
     bool depends_on_reduce(int node, int red) const {
@@ -270,7 +382,7 @@ struct Gen {
         Lin r;
         switch (nd.op) {
             case OP_CONST: r = lconst(nd.arg); break;
-            case OP_RANGE: r = latom(range_atom[i]); break;
+            case OP_RANGE: { auto fx = fixed_range.find(i); r = fx != fixed_range.end() ? lconst(fx->second) : latom(range_atom[i]); break; }
             case OP_ADD: r = ladd(lin(nd.src[0]), lin(nd.src[1])); break;
             case OP_SUB: r = ladd(lin(nd.src[0]), lin(nd.src[1]), -1); break;
             case OP_NEG: r = lscale(lin(nd.src[0]), -1); break;
@@ -405,6 +517,8 @@ struct Gen {
     }
 
     std::string range_name(int r) const {
+        auto fx = fixed_range.find(r);
+        if (fx != fixed_range.end()) return std::to_string(fx->second);
         std::string s = "r" + std::to_string(N(r).aux);
         return r == vec_range ? "(" + s + " + u)" : s;
     }
@@ -440,6 +554,7 @@ struct Gen {
         char b[64]; std::snprintf(b, sizeof b, "%af", (double)f);
         return std::string(b);
     }
+    static bool is_zero_lit(const std::string& e) { return e == "0x0p+0f" || e == "__float2half_rn(0x0p+0f)"; }
     // x * 1.0 is x bit for bit in IEEE arithmetic (the gradient of a sum multiplies by ones)
     bool is_float_one(int i) const {
         const Node& nd = N(i);
@@ -642,6 +757,24 @@ struct Gen {
             if (!isf) pe = std::string("(") + at + ")__float_as_int(" + pe + ")";
             stmt(-1, "for (int p = 0; p < SPLIT; p++) " + acc + " = " + combine(rop, acc_c, acc, pe) + ";");
         } else {
+            if (enum_reduce.count(i) && lanes == 1 && rr.size() == 1) {
+                // one copy of the loop body per value of the range: the guards that read it fold away, and
+                // so does every term of the body that they switch off
+                const int R = rr[0];
+                for (int64_t kk = 0; kk < N(R).arg; kk++) {
+                    fix_range(R, kk);
+                    forget_loop(i);
+                    std::string e = val(nd.src[0], i);
+                    std::string ef = (isf && cls(nd.src[0]) == CF16) ? "__half2float(" + e + ")" : e;
+                    if (rop == OP_ADD && is_zero_lit(e) && loop[i].code.empty()) continue;       // nothing live for this value
+                    T().code += "  {   // r" + std::to_string(N(R).aux) + " = " + std::to_string(kk) + "\n" + loop[i].code;
+                    T().code += "    " + acc + " = " + combine(rop, acc_c, acc, ef) + ";\n  }\n";
+                }
+                unfix_range(R);
+                forget_loop(i);
+                if (nd.dtype == DT_F16) return "__float2half_rn(" + acc + ")";
+                return acc;
+            }
             // row-chain stage sweeping the row in chunks: the wide loads must be known before the body is rendered
             bool chunked = false;
             std::string wide;
@@ -772,7 +905,14 @@ struct Gen {
                 case OP_RECIP: e = h ? "__float2half_rn(rcp_h_(" + af(0) + "))" : "__frcp_rn(" + af(0) + ")"; break;
                 case OP_TRUNC: e = wrap("truncf(" + af(0) + ")"); break;
                 case OP_NEG: e = h ? "__hneg(" + ac(0) + ")" : "(-" + ac(0) + ")"; break;
-                case OP_ADD: e = h ? "__hadd(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " + " + ac(1) + ")"; break;
+                case OP_ADD: {
+                    // x + 0 where the zero is what a guard folded to (a padded slice that is not live):
+                    // the value of x, at worst with the sign of a zero changed
+                    std::string x0 = ac(0), x1 = ac(1);
+                    if (is_zero_lit(x0)) return x1;
+                    if (is_zero_lit(x1)) return x0;
+                    e = h ? "__hadd(" + x0 + ", " + x1 + ")" : "(" + x0 + " + " + x1 + ")"; break;
+                }
                 case OP_SUB: e = h ? "__hsub(" + ac(0) + ", " + ac(1) + ")" : "(" + ac(0) + " - " + ac(1) + ")"; break;
                 case OP_MUL:
                     if (is_float_one(nd.src[0]) && cls(nd.src[1]) == c) return ac(1);
@@ -1203,6 +1343,7 @@ struct Gen {
             }
             lanes = L;
         }
+        if (!enum_reduce.empty() && opts.reduce_lanes == 0) lanes = 1;      // value-by-value loops are per thread
         if (lanes > threads) lanes = threads;
         touts = threads / lanes;
     }
@@ -1341,7 +1482,7 @@ struct Gen {
     }
 
     bool build_reduce(Rendered& out) {
-        if (opts.reduce_lanes == 0 && opts.split <= 1) {
+        if (opts.reduce_lanes == 0 && opts.split <= 1 && enum_out.empty() && enum_reduce.empty()) {
             size_t ninv = 0; int64_t inner = 1;
             for (int k = (int)loop_ranges.size() - 1; k >= 0; k--) {
                 int r = loop_ranges[k];
@@ -1370,7 +1511,10 @@ struct Gen {
                 split = (int)std::max<int64_t>(1, std::min<int64_t>(s, 1024));
             }
         }
-        if (split > 1) return build_split(out, split, total, rmax);
+        if (split > 1 && enum_out.empty()) return build_split(out, split, total, rmax);
+        // a switch over output ranges is only safe where the threads that synchronise share the case:
+        // no cooperation at all (one lane per output) or one output per block
+        if (!enum_out.empty() && !(lanes == 1 || touts == 1)) enum_out.clear();
 
         reset_emit();
         reduce_combine_mode = "group";
@@ -1385,10 +1529,29 @@ struct Gen {
         k << "  const bool valid = g < " << total_expr() << ";\n";
         k << "  if (!valid) g = " << total_expr() << " - 1;\n";
         k << decompose("g");
-        std::string v = val(body, -1);
-        if (!err.empty()) return false;
-        k << top.code;
-        k << "  if (valid && lane == 0) data0[g] = " << store_value(v, body) << ";\n";
+        if (enum_out.empty()) {
+            std::string v = val(body, -1);
+            if (!err.empty()) return false;
+            k << top.code;
+            k << "  if (valid && lane == 0) data0[g] = " << store_value(v, body) << ";\n";
+        } else {
+            // one case per combination of the enumerated output ranges; inside a case they are constants
+            std::string sel = "0";
+            int64_t cases = 1;
+            for (int r : enum_out) { sel = "(" + sel + " * " + std::to_string(N(r).arg) + " + r" + std::to_string(N(r).aux) + ")"; cases *= N(r).arg; }
+            k << "  switch (" << sel << ") {\n";
+            for (int64_t cs = 0; cs < cases; cs++) {
+                int64_t rem = cs;
+                for (int e = (int)enum_out.size() - 1; e >= 0; e--) { fix_range(enum_out[e], rem % N(enum_out[e]).arg); rem /= N(enum_out[e]).arg; }
+                top = Block(); loop.clear(); memo.clear();
+                std::string v = val(body, -1);
+                if (!err.empty()) return false;
+                k << "  case " << cs << ": {\n" << top.code;
+                k << "  if (valid && lane == 0) data0[g] = " << store_value(v, body) << ";\n  } break;\n";
+            }
+            for (int r : enum_out) unfix_range(r);
+            k << "  }\n";
+        }
         k << "}\n";
         out.klass = KC_REDUCE;
         out.source = k.str();
@@ -1399,6 +1562,8 @@ struct Gen {
         out.main.sym_trailing = sym_output() ? total : 0;
         out.uses_sym = has_sym;
         out.note = std::string("reduce ") + (rc_layout ? "RC" : "OC") + " lanes=" + std::to_string(lanes) + " touts=" + std::to_string(touts);
+        if (!enum_reduce.empty()) out.note += " value-by-value reduce";
+        if (!enum_out.empty()) out.note += " switch over " + std::to_string(enum_out.size()) + " output ranges";
         return true;
     }
 
@@ -1528,10 +1693,13 @@ struct Gen {
         return true;
     }
 
+    bool opts_untuned() const { return !opts.reduce_lanes && !opts.split; }
+
     bool run(Rendered& out) {
         if (!analyse()) return false;
         if (it.bufs.empty()) return fail("codegen: kernel has no output buffer");
         if (static_total() >= ((int64_t)1 << 31)) return fail("codegen: more than 2^31 outputs");
+        if (!reduces.empty() && opts_untuned()) plan_enumeration();
         bool ok = reduces.empty() ? build_elementwise(out) : build_reduce(out);
         return ok && err.empty();
     }

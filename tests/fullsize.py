@@ -65,8 +65,9 @@ def check_every_kernel(cuda, oracle, items, inputs, tol, binding=None, samples=4
     additions in a REDUCE, another approximation of exp2, an f16 rounding tipped by either).  For a
     well-conditioned kernel sigma is far below tol * floor and the check is the stated tolerance;
     for a sum whose terms cancel — the row statistics of a softmax gradient that are zero in exact
-    arithmetic — it is what makes a comparison possible at all.  Returns a list of
-    (kernel, worst error / floor, worst NOISE_SIGMAS * sigma / floor) and the device's values."""
+    arithmetic — it is what makes a comparison possible at all.  Returns the device's values and a
+    list of (kernel, worst error relative to max(|oracle|, floor), worst ratio of the noise
+    allowance to the tolerance term): a ratio well below 1 says the check was the stated tolerance."""
     keep = unaliased(items)
     got = cuda.run(keep, inputs, binding)
     known = dict(inputs)
@@ -88,7 +89,8 @@ def check_every_kernel(cuda, oracle, items, inputs, tol, binding=None, samples=4
         d = np.abs(dev_out[idx].astype(np.float64) - w)
         allowed = t * np.maximum(np.abs(w), floor) + NOISE_SIGMAS * sigma
         worst = int(np.argmax(d / allowed))
-        report.append((k, float(d.max() / floor), float(NOISE_SIGMAS * sigma.max() / floor)))
+        scale = np.maximum(np.abs(w), floor)
+        report.append((k, float((d / scale).max()), float((NOISE_SIGMAS * sigma / (t * scale)).max())))
         assert (d <= allowed).all(), (f"kernel {k} (output {ob.shape}, {len(it.bufs) - 1} inputs): |device - oracle| = {d[worst]:.3e} at position {idx[worst]} "
                                       f"(oracle {w[worst]:.6e}, floor {floor:.3e}, sigma {sigma[worst]:.3e}) exceeds {allowed[worst]:.3e}; {idx.size} sampled outputs")
     return report, got

@@ -47,7 +47,7 @@ def test_c4_every_kernel_at_full_size(cuda, oracle):
     from anneal_b200 import device as D
     for (k, err, slack), it in zip(report, items):
         if len(it.bufs[0].shape) == 2 and "contraction" in D.lower(items, k)["note"]:
-            assert slack <= 0.5 * 2e-3, (k, slack)
+            assert slack <= 0.5, (k, slack)
     # the schedule as the bench runs it (slots shared, only final outputs returned) gives the same
     # loss and gradients as the run that kept every buffer
     got = cuda.run(items, inputs)
@@ -97,7 +97,7 @@ def test_c5_symbolic_mlp_full_width_largest_batch(cuda, oracle):
     # 65536 f32 partial sums round: six modelled standard deviations of that are as large as the
     # 1e-4 bound itself on the weight gradients (K = 65536), a third of it elsewhere
     for k, err, slack in report:
-        assert slack <= 1.5 * 1e-4, (k, slack)
+        assert slack <= 1.5, (k, slack)
     # and the smallest batch through the same plans
     R.reset()
     x1, y1 = m.inputs(1)
@@ -106,16 +106,17 @@ def test_c5_symbolic_mlp_full_width_largest_batch(cuda, oracle):
     check_every_kernel(cuda, oracle, items, inputs, 1e-4, binding={"n": 1}, samples=2048)
 
 
-def _trajectory(cuda, oracle, make_model, steps, materialize):
+def _trajectory(cuda, oracle, make_model, steps, materialize, oracle_materialize=None):
     m = make_model()
     ref = make_model()
     x, y = (m.x, m.y) if hasattr(m, "x") else m.make_inputs()
     tr = ResidentTrainer(cuda, m, m.lr, use_graph=True, materialize=materialize)
+    oracle_materialize = materialize if oracle_materialize is None else oracle_materialize
     dev_losses, ref_losses = [], []
     for _ in range(steps):
         dev_losses.append(tr.step(x, y))
         R.reset()
-        R.MATERIALIZE_CONTRACTION_OPERANDS = materialize
+        R.MATERIALIZE_CONTRACTION_OPERANDS = oracle_materialize
         try:
             g = ref.graph() if hasattr(ref, "x") else ref.graph(x, y)
             items, out_ids, inputs = schedule(g.targets())
@@ -131,8 +132,15 @@ def _trajectory(cuda, oracle, make_model, steps, materialize):
 def test_c2_cnn_loss_trajectory_100_steps(cuda, oracle):
     """Small CNN at full size (batch 32, 28 x 28): 100 steps of device-resident training (graph
     replay, on-device SGD) against the reference's host loop (fresh graph each step, oracle,
-    host SGD); losses within 1e-3 at every step."""
-    dev, ref, tr, rm = _trajectory(cuda, oracle, W.SmallCNN, 100, True)
+    host SGD); losses within 1e-3 at every step.  The device runs the schedule as the reference
+    emits it — the convolutions' im2col a sum of 9 or 72 padded slices inside the contraction, which
+    the generator turns into direct convolutions, no im2col buffer.  The oracle evaluates the same
+    graph with the im2col written to a buffer first: the very same f32 operations in the same order
+    (a copy is exact; test_oracle_golden.py checks the two schedules agree bit for bit on a small
+    case), eight times faster on the CPU than re-evaluating 72 selects per multiply."""
+    k0 = cuda.stats()["kernels_launched"]
+    dev, ref, tr, rm = _trajectory(cuda, oracle, W.SmallCNN, 100, False, oracle_materialize=True)
+    assert len(tr.items) == 21          # as scheduled by the reference's rules: no im2col kernels
     d = np.abs(dev - ref)
     assert d.max() < 1e-3, (d.max(), dev[-1], ref[-1])
     assert ref[-1] < ref[0]

@@ -353,3 +353,25 @@ def maxpool_tie_check(case):
 @pytest.mark.parametrize("case", GOLD["maxpool_ties"]["cases"], ids=lambda c: str(c["shape"]))
 def test_maxpool_ties_split_equally(case):
     maxpool_tie_check(case)
+
+
+def test_cnn_schedule_with_and_without_im2col_buffers_agree_bit_for_bit(oracle):
+    """A convolution's im2col as an expression inside the contraction (the reference's schedule) and
+    as a buffer written first (the operand-materialising rule) are the same f32 operations in the
+    same order; the GPU trajectory test relies on it to keep the oracle's 100 steps affordable."""
+    from anneal_b200 import realize as R, workloads as W
+    from util import schedule
+    res = []
+    for mat in (False, True):
+        R.reset()
+        R.MATERIALIZE_CONTRACTION_OPERANDS = mat
+        try:
+            m = W.SmallCNN(batch=4, hw=12)
+            items, out_ids, inputs = schedule(m.graph().targets())
+        finally:
+            R.MATERIALIZE_CONTRACTION_OPERANDS = False
+        out = oracle.run(items, inputs)
+        res.append([out[k] for k in out_ids])
+    assert len(res[0]) == 7
+    for a, b in zip(*res):
+        assert np.array_equal(a.view(np.uint32), b.view(np.uint32))
