@@ -1498,7 +1498,7 @@ struct Gen {
         int64_t rmax = 0; bool rsym = false;
         for (int r : reduces) { int64_t t = reduce_total(r); if (t == 0) rsym = true; rmax = std::max(rmax, t); }
         if (rsym) rmax = 0;
-        int64_t est_total = sym_output() ? total * 1024 : total;
+        int64_t est_total = sym_output() ? total * (opts.sym_hint > 0 ? opts.sym_hint : 1024) : total;
         choose_layout(est_total, rmax);
 
         // split one long reduction over several blocks?

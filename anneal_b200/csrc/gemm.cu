@@ -392,7 +392,7 @@ int plan_gemm(const Item& item, const GemmTuning& tune, Plan& plan) {
     if (c.in_dtype == DT_F32 && c.out_dtype == DT_F32) {
         if (c.a_sk != 1 && c.a_sm != 1) return ANL_ERR_UNSUPPORTED;
         if (c.b_sk != 1 && c.b_sn != 1) return ANL_ERR_UNSUPPORTED;
-        if (!dynamic && !gemm_f32_worth(c.M, c.N, c.K)) return ANL_ERR_UNSUPPORTED;
+        if (!dynamic && !gemm_f32_worth(c.M, c.N, c.K, c.a_sm, c.a_sk, c.b_sn, c.b_sk)) return ANL_ERR_UNSUPPORTED;
         if (c.N < 64) return ANL_ERR_UNSUPPORTED;
         auto gp = std::make_shared<GemmPlan>();
         gp->c = c; gp->f32 = true;
@@ -452,7 +452,7 @@ bool gemm_taken(const Plan& plan, int64_t sym_value) {
     if (!plan.gemm) return false;
     if (!plan.gemm_dynamic) return plan.r.klass == KC_GEMM;
     const Contraction& c = plan.gemm->c;
-    return gemm_f32_worth(c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K);
+    return gemm_f32_worth(c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K, c.a_sm, c.a_sk, c.b_sn, c.b_sk);
 }
 
 bool gemm_pair_eligible(const Plan& plan) {
@@ -465,7 +465,7 @@ void gemm_shape(const Plan& plan, int64_t* M, int64_t* N, int64_t* K) { *M = pla
 // ── the run-time compiled two-CTA kernel ──────────────────────────────────────────────────────
 namespace {
 
-struct PairVariant { int bnt, stages, group_m, stream_stores; bool a_mn, b_mn; };
+struct PairVariant { int bnt, stages, group_m, stream_stores; bool a_mn, b_mn; bool split_tail; };
 constexpr int kDefaultStages = 7;      // the deepest ring that fits beside a 256-wide tile; 1% faster than 6 on every large shape measured
 
 int pair_smem_bytes(int bnt, int stages) { return stages * (A_TILE_BYTES + (bnt / 2) * BK * 2) + 1024; }
@@ -515,6 +515,7 @@ PairVariant choose_variant(anl_device* dev, const GemmPlan& gp, int64_t M) {
     v.stages = gp.tune.stages > 0 ? std::max(2, std::min(gp.tune.stages, max_stages(v.bnt))) : std::min(kDefaultStages, max_stages(v.bnt));
     v.group_m = gp.tune.group_m > 0 ? gp.tune.group_m : (gp.tune.group_m < 0 ? 0 : kDefaultGroupM);
     v.stream_stores = gp.tune.stream_stores > 0 ? 1 : 0;
+    v.split_tail = gp.tune.no_split_tail == 0;
     return v;
 }
 
@@ -558,10 +559,14 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
     int* const counter = tile_counter_for(dev, stream);
     if (gemm_pair_eligible(plan) && M >= 2 * BM) {
         const PairVariant v = choose_variant(dev, gp, M);
-        // B is loaded in halves of bnt/2 columns, so its tensor map gets a box of that many rows
+        // B is loaded in halves of bnt/2 columns, so its tensor map gets a box of that many rows; a
+        // second map with half that box serves the half-width tiles of the last wave
+        CUtensorMap mbh;
         if (gp.b_mn) rc = encode_map(dev, &mb, b, (uint64_t)c.N, (uint64_t)c.K, (uint64_t)gp.ldb, 64, BK);
         else rc = encode_map(dev, &mb, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, v.bnt / 2);
         if (rc) return rc;
+        if (gp.b_mn) mbh = mb;
+        else if ((rc = encode_map(dev, &mbh, b, (uint64_t)c.K, (uint64_t)c.N, (uint64_t)gp.ldb, BK, v.bnt / 4))) return rc;
         CUfunction fn;
         if ((rc = get_pair_kernel(dev, v, fusion && fusion->epilogue ? *fusion->epilogue : std::string(), &fn))) return rc;
         PairGemmArgs g{};
@@ -575,7 +580,12 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
         g.status = dev->gemm_status_dev;
         g.tile_counter = counter;
         const int npairs = gemm_sm_budget(dev) / 2;
-        const int pairs = std::min(g.tiles_m * g.tiles_n, npairs);
+        // Last wave: when the tiles left over after the full waves would occupy at most half of the
+        // pairs, they are drawn as half-width tiles and the wave costs half a tile instead of a whole one.
+        const int whole = g.tiles_m * g.tiles_n;
+        const int rest = whole % npairs;
+        g.full_tiles = (v.split_tail && v.bnt == 256 && whole > npairs && rest > 0 && 2 * rest <= npairs) ? whole - rest : whole;
+        const int pairs = std::min(whole + (whole - g.full_tiles), npairs);
         CUlaunchConfig cfg{};
         cfg.gridDimX = 2 * pairs; cfg.gridDimY = 1; cfg.gridDimZ = 1;
         cfg.blockDimX = GEMM_THREADS; cfg.blockDimY = 1; cfg.blockDimZ = 1;
@@ -585,7 +595,7 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
         at[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
         at[0].value.clusterDim.x = 2; at[0].value.clusterDim.y = 1; at[0].value.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
-        void* params[3] = {&ma, &mb, &g};
+        void* params[4] = {&ma, &mb, &mbh, &g};
         CUresult cr = dev->drv.LaunchKernelEx(&cfg, fn, params, nullptr);
         if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return dev->fail(ANL_ERR_CUDA, std::string("gemm: pair launch: ") + (e ? e : "?")); }
         dev->stats.kernels_launched++;

@@ -183,17 +183,167 @@ __global__ void __launch_bounds__(F_THREADS, ANL_F32_MINBLOCKS) gemm_f32_simt(co
     }
 }
 
-// Whether a contraction of these extents is worth the tiled kernel: below this the generated
-// one-thread-per-output kernel finishes sooner (a 128x128 tile would leave most SMs idle).
-bool gemm_f32_worth(int64_t M, int64_t N, int64_t K) {
-    if (M <= 0 || N <= 0 || K <= 0) return false;
-    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return false;
+// ── contractions with a handful of rows, or a handful of terms ─────────────────────────────────────
+// The symbolic-batch MLP is replayed with batches of 1 and 17 as well as 65536.  With few rows a
+// 128x128 tile is almost empty, and the generated one-block-per-output kernel reads the whole weight
+// matrix once per ROW; these kernels read it once per group of up to 16 rows, which is what the
+// bytes cost.  All accumulate in f32 with fused multiply-add; the order of the additions differs
+// from the reference's serial loop where lanes or warps share one sum (tolerance: 1e-4 relative).
+constexpr int S_MR = 16;          // rows per pass
+constexpr int S_KC = 256;         // k chunk staged in shared memory
+
+// D[m, n] = sum_k A[m, k] * B[n, k], both k-contiguous (a forward layer x · Wᵀ): one warp per output
+// column, the 16 rows of A staged chunk by chunk in shared memory and shared by the block's 8 warps.
+__global__ void __launch_bounds__(256) gemm_f32_few_rows_dot(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ d,
+                                                              int M, int N, int K, long long a_sm, long long b_sn, int ldd) {
+    __shared__ float As[S_MR][S_KC];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x * 8 + warp, m0 = blockIdx.y * S_MR;
+    float acc[S_MR];
+#pragma unroll
+    for (int m = 0; m < S_MR; m++) acc[m] = 0.0f;
+    const float* brow = b + (long long)(n < N ? n : N - 1) * b_sn;
+    for (int k0 = 0; k0 < K; k0 += S_KC) {
+        for (int i = threadIdx.x; i < S_MR * S_KC; i += 256) {
+            const int m = i / S_KC, k = i % S_KC;
+            As[m][k] = (m0 + m < M && k0 + k < K) ? a[(long long)(m0 + m) * a_sm + k0 + k] : 0.0f;
+        }
+        __syncthreads();
+#pragma unroll
+        for (int half = 0; half < S_KC / 128; half++) {
+            const int kk = half * 128 + lane * 4;
+            float bv[4];
+#pragma unroll
+            for (int j = 0; j < 4; j++) bv[j] = (k0 + kk + j < K) ? brow[k0 + kk + j] : 0.0f;
+#pragma unroll
+            for (int m = 0; m < S_MR; m++) {
+                const float4 av = *reinterpret_cast<const float4*>(&As[m][kk]);
+                acc[m] = fmaf(av.x, bv[0], acc[m]); acc[m] = fmaf(av.y, bv[1], acc[m]);
+                acc[m] = fmaf(av.z, bv[2], acc[m]); acc[m] = fmaf(av.w, bv[3], acc[m]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int m = 0; m < S_MR; m++) {
+        float v = acc[m];
+#pragma unroll
+        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+        if (lane == 0 && n < N && m0 + m < M) d[(long long)(m0 + m) * ldd + n] = v;
+    }
+}
+
+// D[m, n] = sum_k A[m, k] * B[k, n]: A k-contiguous, B n-contiguous (an input gradient dY · W).
+// A block owns 64 columns; its 8 warps take every 8th k, each lane two columns, and the warps'
+// partial sums are added in warp order through shared memory.
+constexpr int S_KA = 128;         // k chunk of the n-contiguous form
+__global__ void __launch_bounds__(256) gemm_f32_few_rows_axpy(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ d,
+                                                               int M, int N, int K, long long a_sm, long long b_sk, int ldd) {
+    __shared__ float As[S_MR][S_KA];
+    __shared__ float part[8][S_MR][64 + 1];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * 64, m0 = blockIdx.y * S_MR;
+    const int c0 = n0 + lane * 2;
+    const bool c_ok0 = c0 < N, c_ok1 = c0 + 1 < N;
+    float acc[S_MR][2];
+#pragma unroll
+    for (int m = 0; m < S_MR; m++) acc[m][0] = acc[m][1] = 0.0f;
+    for (int k0 = 0; k0 < K; k0 += S_KA) {
+        for (int i = threadIdx.x; i < S_MR * S_KA; i += 256) {
+            const int m = i / S_KA, k = i % S_KA;
+            As[m][k] = (m0 + m < M && k0 + k < K) ? a[(long long)(m0 + m) * a_sm + k0 + k] : 0.0f;
+        }
+        __syncthreads();
+        const int kend = (K - k0) < S_KA ? (K - k0) : S_KA;
+        for (int k = warp; k < kend; k += 8) {
+            const float* brow = b + (long long)(k0 + k) * b_sk;
+            const float b0 = c_ok0 ? brow[c0] : 0.0f, b1 = c_ok1 ? brow[c0 + 1] : 0.0f;
+#pragma unroll
+            for (int m = 0; m < S_MR; m++) {
+                const float av = As[m][k];
+                acc[m][0] = fmaf(av, b0, acc[m][0]);
+                acc[m][1] = fmaf(av, b1, acc[m][1]);
+            }
+        }
+        __syncthreads();
+    }
+#pragma unroll
+    for (int m = 0; m < S_MR; m++) { part[warp][m][lane * 2] = acc[m][0]; part[warp][m][lane * 2 + 1] = acc[m][1]; }
+    __syncthreads();
+    for (int i = threadIdx.x; i < S_MR * 64; i += 256) {
+        const int m = i / 64, c = i % 64;
+        float v = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 8; w++) v += part[w][m][c];
+        if (m0 + m < M && n0 + c < N) d[(long long)(m0 + m) * ldd + n0 + c] = v;
+    }
+}
+
+// D[m, n] = sum_k A[k, m] * B[k, n] with few terms (a weight gradient at a small batch): every thread
+// four consecutive columns of one row, the terms added in ascending k like the reference's loop.
+__global__ void __launch_bounds__(256) gemm_f32_few_terms(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ d,
+                                                           int M, int N, int K, long long a_sk, long long b_sk, int ldd, int vec) {
+    const long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    const int n4 = (N + 3) / 4;
+    const long long m = t / n4;
+    const int n = (int)(t % n4) * 4;
+    if (m >= M) return;
+    float acc[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    for (int k = 0; k < K; k++) {
+        const float av = a[(long long)k * a_sk + m];
+        const float* brow = b + (long long)k * b_sk + n;
+        if (vec) {
+            const float4 bv = *reinterpret_cast<const float4*>(brow);
+            acc[0] = fmaf(av, bv.x, acc[0]); acc[1] = fmaf(av, bv.y, acc[1]); acc[2] = fmaf(av, bv.z, acc[2]); acc[3] = fmaf(av, bv.w, acc[3]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) if (n + j < N) acc[j] = fmaf(av, brow[j], acc[j]);
+        }
+    }
+    float* out = d + m * ldd + n;
+    if (vec) *reinterpret_cast<float4*>(out) = make_float4(acc[0], acc[1], acc[2], acc[3]);
+    else for (int j = 0; j < 4; j++) if (n + j < N) out[j] = acc[j];
+}
+
+// Which hand-written kernel, if any, finishes a contraction of these extents and strides sooner than
+// the generated one-thread-per-output kernel.
+enum F32Route { F32_NONE = 0, F32_TILED, F32_FEW_ROWS_DOT, F32_FEW_ROWS_AXPY, F32_FEW_TERMS };
+static F32Route f32_route(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk) {
+    if (M <= 0 || N <= 0 || K <= 0) return F32_NONE;
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return F32_NONE;
+    if (M <= 2 * S_MR && N >= 256 && K >= 128 && (a_sk == 1 || M == 1)) {
+        if (b_sk == 1) return F32_FEW_ROWS_DOT;
+        if (b_sn == 1) return F32_FEW_ROWS_AXPY;
+    }
+    if (K <= 64 && a_sm == 1 && b_sn == 1 && M * N >= (1 << 16)) return F32_FEW_TERMS;
     const int64_t tiles = ((M + F_BM - 1) / F_BM) * ((N + F_BN - 1) / F_BN);
-    return tiles >= 16 && K >= 64 && tiles < (1ll << 31);
+    if (M > 2 * S_MR && tiles >= 16 && K >= 64 && tiles < (1ll << 31)) return F32_TILED;
+    return F32_NONE;
+}
+bool gemm_f32_worth(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk) {
+    return f32_route(M, N, K, a_sm, a_sk, b_sn, b_sk) != F32_NONE;
 }
 
 int launch_gemm_f32(anl_device* dev, const float* a, const float* b, float* d, int64_t M, int64_t N, int64_t K,
                     int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk, cudaStream_t stream) {
+    const F32Route route = f32_route(M, N, K, a_sm, a_sk, b_sn, b_sk);
+    if (route == F32_FEW_ROWS_DOT || route == F32_FEW_ROWS_AXPY || route == F32_FEW_TERMS) {
+        const int groups = (int)((M + S_MR - 1) / S_MR);
+        if (route == F32_FEW_ROWS_DOT)
+            gemm_f32_few_rows_dot<<<dim3((unsigned)((N + 7) / 8), groups), 256, 0, stream>>>(a, b, d, (int)M, (int)N, (int)K, a_sm, b_sn, (int)N);
+        else if (route == F32_FEW_ROWS_AXPY)
+            gemm_f32_few_rows_axpy<<<dim3((unsigned)((N + 63) / 64), groups), 256, 0, stream>>>(a, b, d, (int)M, (int)N, (int)K, a_sm, b_sk, (int)N);
+        else {
+            const int vec4 = (N % 4 == 0) && (b_sk % 4 == 0) && (((uintptr_t)b & 15) == 0) && (((uintptr_t)d & 15) == 0);
+            const long long threads = M * ((N + 3) / 4);
+            gemm_f32_few_terms<<<(unsigned)((threads + 255) / 256), 256, 0, stream>>>(a, b, d, (int)M, (int)N, (int)K, a_sk, b_sk, (int)N, vec4);
+        }
+        cudaError_t e0 = cudaGetLastError();
+        if (e0 != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm f32: launch: ") + cudaGetErrorString(e0));
+        dev->stats.kernels_launched++;
+        dev->stats.gemm_launched++;
+        return ANL_OK;
+    }
     GemmF32Args g;
     g.a = a; g.b = b; g.d = d;
     g.M = (int)M; g.N = (int)N; g.K = (int)K;

@@ -19,6 +19,10 @@
 // let the epilogue of tile i run under the main loop of tile i+1.  Tile numbers are drawn from a
 // global counter, so a pair that starts late (its SMs were busy with a collective) takes fewer.
 //
+// When the tile count does not fill the last wave of pairs, the tiles of that wave are drawn as two
+// half-width tiles each (second tensor map for B with half the box, N = BNT/2 in the instruction
+// descriptor, half the accumulator columns): the pairs that would have idled take the other halves.
+//
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in a host-visible status
 // word, the roles of the CTA drain and the tensor memory is freed.
 //
@@ -44,6 +48,8 @@ struct PairGemmArgs {
     const void* ep[6];      // operands of the fused consumer, in its parameter order
     int M, N, K, ldd;
     int tiles_m, tiles_n;   // in 256-row pair tiles and BNT-column tiles
+    int full_tiles;         // tile numbers below this are BNT wide; each tile from here on is drawn as two halves
+                            // of BNT/2 columns, so that the last, partly filled wave of tiles costs half a tile
     int* status;
     int* tile_counter;      // [0] next tile number, [1] pairs that have signed off; both zero between launches
 };
@@ -171,6 +177,15 @@ __device__ __forceinline__ void tile_coords(int t, int tiles_m, int tiles_n, int
     tm = first + r % rows; tn = r / rows;
 }
 
+// drawn number -> (tile row, first column, width)
+__device__ __forceinline__ void tile_of(int t, int tiles_m, int tiles_n, int full_tiles, int& tm, int& col0, int& width) {
+    int tn;
+    if (t < full_tiles) { tile_coords(t, tiles_m, tiles_n, tm, tn); col0 = tn * BNT; width = BNT; return; }
+    const int h = t - full_tiles;
+    tile_coords(full_tiles + (h >> 1), tiles_m, tiles_n, tm, tn);
+    col0 = tn * BNT + (h & 1) * (BNT / 2); width = BNT / 2;
+}
+
 __device__ __forceinline__ void store16(void* p, uint4 v) {
 #if CFG_STREAM_STORES
     __stcs(reinterpret_cast<uint4*>(p), v);
@@ -195,7 +210,8 @@ __device__ __forceinline__ void warp_column_sums(float (&x)[32], int lane) {
 }
 
 extern "C" __global__ void __launch_bounds__(192, 1)
-gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b, const PairGemmArgs g) {
+gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b, const __grid_constant__ TensorMap map_b_half,
+                      const PairGemmArgs g) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2];
     // tile queue: the leader's producer draws tile numbers from the global counter and publishes each
@@ -209,7 +225,8 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const unsigned rank = cluster_ctarank();            // 0 leads
     const int tiles_m = g.tiles_m;
-    const int num_tiles = tiles_m * g.tiles_n;
+    const int whole_tiles = tiles_m * g.tiles_n;
+    const int num_tiles = whole_tiles + (whole_tiles - g.full_tiles);     // every tile past full_tiles counts twice
     const int kblocks = (g.K + BK - 1) / BK;
 
     if (threadIdx.x == 0) {
@@ -255,21 +272,24 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 }
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
                 if (t < 0) { if (rank == 0) retire_tile_counter(g.tile_counter, (int)gridDim.x / 2); break; }
-                int tm, tn;
-                tile_coords(t, tiles_m, g.tiles_n, tm, tn);
+                int tm, col0, width;
+                tile_of(t, tiles_m, g.tiles_n, g.full_tiles, tm, col0, width);
+                const bool narrow = width != BNT;
                 const int m0 = tm * (2 * BM) + (int)rank * BM;           // this CTA's rows of A
-                const int n0 = tn * BNT + (int)rank * (BNT / 2);         // this CTA's half of B
+                const int n0 = col0 + (int)rank * (width / 2);           // this CTA's half of B
+                const unsigned stage_bytes = A_TILE_BYTES + (narrow ? BHALF_BYTES / 2 : BHALF_BYTES);
+                const TensorMap* const mb = narrow ? &map_b_half : &map_b;
                 for (int kb = 0; kb < kblocks; kb++) {
                     if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
                     const unsigned own_fb = smem_u32(&full_bar[stage]);
                     const unsigned fb = map_to_cta(own_fb, 0);
                     const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
-                    if (rank == 0) mbar_expect_tx(own_fb, 2 * STAGE_B);
+                    if (rank == 0) mbar_expect_tx(own_fb, 2 * stage_bytes);
                     const int k0 = kb * BK;
                     if (CFG_A_MN) { for (int j = 0; j < BM / 64; j++) tma_load_2d_pair(sa + j * (BK * 128), &map_a, m0 + 64 * j, k0, fb); }
                     else tma_load_2d_pair(sa, &map_a, k0, m0, fb);
-                    if (CFG_B_MN) { for (int j = 0; j < BNT / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
-                    else tma_load_2d_pair(sb, &map_b, k0, n0, fb);
+                    if (CFG_B_MN) { for (int j = 0; j < width / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
+                    else tma_load_2d_pair(sb, mb, k0, n0, fb);
                     if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
                 }
             }
@@ -279,7 +299,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
         // ── MMA issuer (leader CTA only) ──
         if (lane == 0 && rank == 0) {
             // instruction descriptor: f32 accumulate, f16 x f16, majors, N >> 3 at bit 17, M >> 4 at bit 24 (256 across the pair)
-            const unsigned idesc = (1u << 4) | ((CFG_A_MN ? 1u : 0u) << 15) | ((CFG_B_MN ? 1u : 0u) << 16) | ((unsigned)(BNT >> 3) << 17) | ((unsigned)((2 * BM) >> 4) << 24);
+            const unsigned idesc_base = (1u << 4) | ((CFG_A_MN ? 1u : 0u) << 15) | ((CFG_B_MN ? 1u : 0u) << 16) | ((unsigned)((2 * BM) >> 4) << 24);
             unsigned stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             unsigned qs = 0, qphase = 0;
@@ -289,6 +309,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 mbar_arrive(smem_u32(&tq_empty[qs]));
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
                 if (t < 0) break;
+                const unsigned idesc = idesc_base | ((unsigned)((t < g.full_tiles ? BNT : BNT / 2) >> 3) << 17);
                 if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
                 asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                 const unsigned tmem_d = tmem_base + acc * BNT;
@@ -334,9 +355,9 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
             if (++qs == TQ) { qs = 0; qphase ^= 1; }
             if (t < 0) break;
-            int tm, tn;
-            tile_coords(t, tiles_m, g.tiles_n, tm, tn);
-            const int m0 = tm * (2 * BM) + (int)rank * BM, n0 = tn * BNT;
+            int tm, n0, width;
+            tile_of(t, tiles_m, g.tiles_n, g.full_tiles, tm, n0, width);
+            const int m0 = tm * (2 * BM) + (int)rank * BM;
             if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quad * 32 + lane;
@@ -344,7 +365,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
             const bool row_ok = row < g.M;
             const bool vec_ok = (g.ldd % 8 == 0);
 #pragma unroll 1
-            for (int c = 0; c < BNT / 32; c++) {
+            for (int c = 0; c < width / 32; c++) {
                 unsigned v[32];
                 tmem_ld32(tmem_base + ((unsigned)(quad * 32) << 16) + acc * BNT + c * 32, v);
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");

@@ -280,6 +280,16 @@ int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::sh
         if (int rc = get_function(dev, *m, p->r.main.entry, &p->main)) return rc;
         if (p->r.klass == KC_REDUCE_SPLIT)
             if (int rc = get_function(dev, *m, p->r.finish.entry, &p->finish)) return rc;
+        if (p->r.klass == KC_REDUCE && p->r.uses_sym && p->r.main.sym_trailing > 0 && item.source.empty() && opts.sym_hint == 0) {
+            CodegenOpts few = opts; few.sym_hint = 1;
+            std::string err;
+            if (render_cuda(item, few, p->r_small, err) && p->r_small.klass == KC_REDUCE && p->r_small.source != p->r.source) {
+                std::shared_ptr<Module> ms;
+                if (int rc = compile_source(dev, p->r_small.source, ms)) return rc;
+                if (int rc = get_function(dev, *ms, p->r_small.main.entry, &p->main_small)) return rc;
+                p->small_below = 64;
+            }
+        }
     }
     dev->plans[key] = p;
     out = p;
@@ -330,6 +340,7 @@ static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item
         args.push_back(&scratch);
     }
     if (plan.r.uses_sym) args.push_back(&n0);
+    if (plan.main_small && sym_value < plan.small_below) return launch_one(dev, plan.main_small, plan.r_small.main, sym_value, args, stream);
     int rc = launch_one(dev, plan.main, plan.r.main, sym_value, args, stream);
     if (rc == ANL_OK && plan.r.klass == KC_REDUCE_SPLIT) rc = launch_one(dev, plan.finish, plan.r.finish, sym_value, args, stream);
     if (scratch) { if (keep_scratch) keep_scratch->push_back(scratch); else dev->release(scratch); }

@@ -47,6 +47,7 @@ struct GemmTuning {
     int group_m = 0;        // raster group in tile rows; -1: down whole columns
     int stream_stores = 0;  // 1: streaming hint on the output stores
     int single_cta = 0;     // 1: the one-CTA kernel even where a CTA pair applies
+    int no_split_tail = 0;  // 1: the tiles of a partly filled last wave stay whole
 };
 constexpr int kDefaultGroupM = 2;     // measured best or within 1% of best on every wide-MLP shape (sweep over -1, 2, 4, 8, 16)
 
@@ -74,6 +75,12 @@ struct FusedEpilogue {
 struct Plan {
     Rendered r;
     CUfunction main = nullptr, finish = nullptr;
+    // A kernel whose output count follows the bound batch is laid out twice when that changes the
+    // layout: for a large batch (threads spread over the outputs) and for a handful of rows (threads
+    // cooperate on each output); both are compiled on first use, the launch picks by the bound value.
+    Rendered r_small;
+    CUfunction main_small = nullptr;
+    int64_t small_below = 0;     // bound values below this take the small-batch layout
     std::shared_ptr<GemmPlan> gemm;
     bool gemm_dynamic = false;   // a symbolic extent decides per launch between `gemm` and the rendered kernel
 };
@@ -180,7 +187,7 @@ int64_t gemm_window_rows(const Plan& plan, int64_t* row_elems);
 double gemm_flops(const Plan& plan, int64_t sym_value);
 // true when this launch (with the symbolic extent bound to sym_value) goes to the contraction kernel
 bool gemm_taken(const Plan& plan, int64_t sym_value);
-bool gemm_f32_worth(int64_t M, int64_t N, int64_t K);
+bool gemm_f32_worth(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk);
 int launch_gemm_f32(anl_device* dev, const float* a, const float* b, float* d, int64_t M, int64_t N, int64_t K,
                     int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk, cudaStream_t stream);
 

@@ -153,6 +153,12 @@ def _r_shrink(u, n, adj, s):
 def _r_flip(u, n, adj, s): return [adj.flip([f != 0 for f in u.arg])]
 
 
+#: The reference materialises the adjoint in front of a max-reduce's backward only because the fused
+#: kernel would otherwise bind more buffers than WebGPU allows (gradient_ruleset.go:309-312).  A CUDA
+#: kernel takes hundreds of pointers; with this off the adjoint stays an expression of its consumer.
+MAX_REDUCE_BARRIER = True
+
+
 def _r_contiguous(u, n, adj, s): return [adj]
 
 
@@ -166,7 +172,7 @@ def _r_reduce(u, n, adj, s):
     if rop == Op.ADD:
         return [adj.reshape(keep).expand(src_sh)]
     if rop == Op.MAX:
-        adj_m = adj.contiguous()
+        adj_m = adj.contiguous() if MAX_REDUCE_BARRIER else adj
         node_e = n.reshape(keep).expand(src_sh)
         adj_e = adj_m.reshape(keep).expand(src_sh)
         mask = s[0].cmpeq(node_e)

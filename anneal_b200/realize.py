@@ -55,13 +55,42 @@ def reset() -> None:
     U.reset_intern()
 
 
+#: buffers one fused kernel may bind when scheduling for the CUDA device.  The reference's 8
+#: (schedule/schedule.go:217-229) is WebGPU's storage-buffer limit; a CUDA kernel takes hundreds of
+#: pointers.  None keeps the reference's value.
+FUSION_BUFFER_CAP = None
+
+
 def build_schedule(tensors: Sequence[Tensor]):
+    """MATERIALIZE_CONTRACTION_OPERANDS: False — the reference's schedule; True — every contraction
+    operand that is an expression becomes a buffer; "auto" — decided per operand by what it costs
+    (schedule.materialize_contraction_operands)."""
     nodes = [t.node for t in tensors]
-    if MATERIALIZE_CONTRACTION_OPERANDS:
-        nodes = S.materialize_contraction_operands(nodes)
-    items, out_map = S.create_schedule(nodes, keep_contractions=MATERIALIZE_CONTRACTION_OPERANDS,
-                                       outputs_first=MATERIALIZE_CONTRACTION_OPERANDS)
+    mode = MATERIALIZE_CONTRACTION_OPERANDS
+    if mode:
+        nodes = S.materialize_contraction_operands(nodes, by_cost=(mode == "auto"))
+    items, out_map = S.create_schedule(nodes, max_bufs=FUSION_BUFFER_CAP, keep_contractions=bool(mode), outputs_first=bool(mode))
     return items, [out_map[n.idx] for n in nodes]
+
+
+#: Device-side companion of schedule.STATS_HOOK (the reference feeds its dashboard's compiler panel from
+#: that hook, tui/dashboard.go:68-80): if set, called after every realize / replay with what the device
+#: did for it — kernels launched, how many of them contractions on the tensor-core kernels, elementwise
+#: kernels and bias gradients that ran inside a contraction's epilogue, graph replays, compiles, bytes
+#: moved each way.  Same threading rule as the schedule hook.
+DEVICE_STATS_HOOK = None
+_DEVICE_COUNTERS = ("kernels_launched", "gemm_launched", "epilogues_fused", "colsums_fused", "graph_replays", "graph_captures",
+                    "nvrtc_compiles", "h2d_bytes", "d2h_bytes")
+
+
+def _with_device_stats(executor, call):
+    if DEVICE_STATS_HOOK is None or not hasattr(executor, "stats"):
+        return call()
+    before = executor.stats()
+    out = call()
+    after = executor.stats()
+    DEVICE_STATS_HOOK({k: after[k] - before[k] for k in _DEVICE_COUNTERS if k in after})
+    return out
 
 
 def _assign(tensors, out_ids, outputs):
@@ -78,7 +107,7 @@ def realize(*tensors: Tensor) -> None:
         raise RealizeError("tensor: realize: no backend registered")
     items, out_ids = build_schedule(tensors)
     try:
-        outputs = DEFAULT_EXECUTOR.run(items, leaf_inputs(tensors))
+        outputs = _with_device_stats(DEFAULT_EXECUTOR, lambda: DEFAULT_EXECUTOR.run(items, leaf_inputs(tensors)))
     except Exception as e:  # wrap with the caller's prefix (tensor/realize.go:70)
         raise RealizeError(f"tensor: realize: {e}") from e
     _assign(tensors, out_ids, outputs)
@@ -91,7 +120,7 @@ def realize_with_binding(binding: Dict[str, int], *tensors: Tensor) -> None:
         raise RealizeError("tensor: realize: backend does not support symbolic shapes")
     items, out_ids = build_schedule(tensors)
     try:
-        outputs = DEFAULT_EXECUTOR.run_symbolic(items, leaf_inputs(tensors), dict(binding))
+        outputs = _with_device_stats(DEFAULT_EXECUTOR, lambda: DEFAULT_EXECUTOR.run_symbolic(items, leaf_inputs(tensors), dict(binding)))
     except Exception as e:
         raise RealizeError(f"tensor: realize: {e}") from e
     _assign(tensors, out_ids, outputs)
@@ -179,7 +208,7 @@ class JIT:
             if d is not None:
                 inputs[cap] = d
         ex = DEFAULT_EXECUTOR
-        outputs = ex.run(self.items, inputs) if binding is None else ex.run_symbolic(self.items, inputs, dict(binding))
+        outputs = _with_device_stats(ex, lambda: ex.run(self.items, inputs) if binding is None else ex.run_symbolic(self.items, inputs, dict(binding)))
         _assign(tensors, self.out_ids, outputs)
         self.replays += 1
 

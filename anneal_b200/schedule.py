@@ -36,6 +36,20 @@ MAX_KERNEL_BUFFERS = 8
 
 
 @dataclass
+class CompilerStats:
+    """schedule/stats.go:3-12: what one scheduling run produced."""
+    uops: int            # nodes of the tensor-level graph that was scheduled
+    kernels: int         # kernels in the schedule
+    fused: int           # reduce kernels spliced into their consumer (schedule/schedule.go:122-287)
+    pass_name: str = "memory_plan"
+
+
+#: schedule/stats.go:14-18: if set, called by create_schedule after each successful run, synchronously
+#: in the caller's thread; set before training, clear (None) when done; not safe for concurrent change
+STATS_HOOK = None
+
+
+@dataclass
 class Buffer:
     """schedule/exec.go:6-13."""
     uop_idx: int
@@ -266,8 +280,43 @@ def _is_view_of_buffer(u: U.UOp, realized) -> bool:
     return u.op == Op.BUFFER or u.idx in realized or u.op in (Op.CONTIGUOUS, Op.REDUCE_AXIS)
 
 
-def materialize_contraction_operands(roots: List[U.UOp]) -> List[U.UOp]:
-    """Rewrite the graph so that both operands of every ``SUM(MUL(a, b))`` are views of buffers.
+#: an operand expression is written to a buffer when it would otherwise be evaluated at least this
+#: many times per element (once per output column, or row, of the contraction it feeds)
+MATERIALIZE_MIN_REUSE = 8
+
+_GATHER_OPS = None
+
+
+def _is_gather(o: U.UOp) -> bool:
+    """True when the expression only moves data: movement ops, PAD and sums of such slices (the
+    im2col a convolution builds from K padded slices, tensor/nn/nn.go:256-276).  On this device a
+    gather costs one guarded load per use — the generator resolves which slice is live — so writing
+    it out (K times the input's size) and reading it back is the dearer option."""
+    global _GATHER_OPS
+    if _GATHER_OPS is None:
+        _GATHER_OPS = set(U.MOVEMENT) | {Op.ADD, Op.CONST, Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS}
+    stack, seen = [o], set()
+    while stack:
+        u = stack.pop()
+        if u.idx in seen:
+            continue
+        seen.add(u.idx)
+        if u.op not in _GATHER_OPS:
+            return False
+        if u.op in (Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS):
+            continue                       # a buffer (or a kernel of its own): the expression ends here
+        stack.extend(u.src)
+    return True
+
+
+def materialize_contraction_operands(roots: List[U.UOp], by_cost: bool = False) -> List[U.UOp]:
+    """Rewrite the graph so that the operands of a ``SUM(MUL(a, b))`` are views of buffers.
+
+    ``by_cost`` decides per operand instead of wrapping all of them: an expression is written to a
+    buffer when the contraction would re-evaluate it at least MATERIALIZE_MIN_REUSE times per
+    element (the other operand's free extent: every output column needs the same row of A) and it
+    does arithmetic; a pure gather stays an expression (see ``_is_gather``), and so does anything
+    feeding a matrix-vector product, where nothing is re-used.
 
     An operand that is an expression (an activation of the previous layer's output, a masked
     adjoint) is wrapped in CONTIGUOUS *below* its movement ops, at the point where it still has its
@@ -278,6 +327,9 @@ def materialize_contraction_operands(roots: List[U.UOp]) -> List[U.UOp]:
     sink = U.new(Op.SINK, dtypes.void, tuple(roots))
     topo = U.toposort(sink)[:-1]
     chosen = set()
+    shapes: Dict[int, tuple] = {}
+    for u in topo:
+        node_shape(u, shapes)
     for u in topo:
         if u.op == Op.REDUCE_AXIS and u.arg[0] == Op.ADD and u.src[0].op == Op.MUL:
             # a contraction multiplies two operands broadcast along different axes: both reach the
@@ -291,9 +343,17 @@ def materialize_contraction_operands(roots: List[U.UOp]) -> List[U.UOp]:
                 operands.append(o)
                 expanded.append(ex)
             if all(expanded):
+                out_elems = math.prod(d for d in node_shape(u, shapes) if isinstance(d, int)) or 1
                 for o in operands:
-                    if o.op not in (Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS, Op.CONST):
-                        chosen.add(o.idx)
+                    if o.op in (Op.BUFFER, Op.CONTIGUOUS, Op.REDUCE_AXIS, Op.CONST):
+                        continue
+                    if by_cost:
+                        own = math.prod(d for d in node_shape(o, shapes) if isinstance(d, int)) or 1
+                        k = math.prod(node_shape(u.src[0], shapes)[a] for a in u.arg[1] if isinstance(node_shape(u.src[0], shapes)[a], int)) or 1
+                        reuse = max(1, out_elems * k // max(own, 1))      # times each element of this operand is multiplied
+                        if reuse < MATERIALIZE_MIN_REUSE or _is_gather(o):
+                            continue
+                    chosen.add(o.idx)
     if not chosen:
         return list(roots)
     out: Dict[int, U.UOp] = {}
@@ -509,6 +569,8 @@ def create_schedule(outputs: Sequence[U.UOp], max_bufs: Optional[int] = None,
     out_map_ids = {out_buf[placeholders[o.idx].idx].idx for o in outputs}
     memory_plan(ordered, out_map_ids)
     out_map = {o.idx: out_buf[placeholders[o.idx].idx].idx for o in outputs}
+    if STATS_HOOK is not None:
+        STATS_HOOK(CompilerStats(len(topo), len(ordered), sum(1 for k in kernels.values() if k.fused_into is not None)))
     return ordered, out_map
 
 

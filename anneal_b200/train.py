@@ -26,9 +26,11 @@ def _round_up(n: int, m: int = 128) -> int:
 
 class ResidentTrainer:
     def __init__(self, dev: Device, model, lr: float, world: int = 1, use_graph: bool = True,
-                 materialize: bool = True, resident_inputs: bool = False, overlap: bool = True,
+                 materialize="auto", resident_inputs: bool = False, overlap: bool = True,
                  force_allreduce: bool = False, shard_update: bool = False):
         self.dev, self.model, self.lr, self.world, self.use_graph = dev, model, float(lr), world, use_graph
+        # materialize: which contraction operands are written to buffers first — "auto" decides per
+        # operand by cost (schedule.materialize_contraction_operands), True all of them, False none
         self.overlap = overlap
         self.shard_update = shard_update
         prev = R.MATERIALIZE_CONTRACTION_OPERANDS

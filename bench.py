@@ -448,7 +448,7 @@ def measure_other(dev, workload, steps, warmup, materialize=-1, dyn_batches="1,1
         m = W.MLP() if args.workload == "mlp" else W.SmallCNN()
         # the im2col of a convolution is a 9- or 72-term padded sum: as an operand expression it is
         # re-evaluated inside every step of the contraction's reduce loop, as a buffer it is written once
-        mat = True if args.materialize < 0 else bool(args.materialize)
+        mat = "auto" if args.materialize < 0 or args.materialize == 2 else bool(args.materialize)
         tr = ResidentTrainer(dev, m, m.lr, use_graph=True, materialize=mat, resident_inputs=True)
         tr.load_batch(m.x, m.y)
         for _ in range(args.warmup):
@@ -569,7 +569,7 @@ def main():
                     help="wide_mlp is the headline configuration; the others print a one-GPU line for the remaining configurations")
     ap.add_argument("--shard-update", action="store_true", help="N>1: reduce-scatter, update this rank's shard, all-gather, instead of all-reducing and updating everything on every rank (measured slower on 8 GPUs: 3.82 against 3.64 ms per step)")
     ap.add_argument("--dyn-batches", default="1,17,256,4096,65536", help="dynmlp: batch sizes bound in turn; the last one is reported")
-    ap.add_argument("--materialize", type=int, default=-1, help="mlp/cnn: 1/0 forces contraction operands to be buffers or expressions")
+    ap.add_argument("--materialize", type=int, default=-1, help="mlp/cnn: 1/0 forces contraction operands to be buffers or expressions; default: decided per operand by cost")
     ap.add_argument("--e2e-f32-host", action="store_true", help="e2e: host batches as float32 rows (converted on the device) instead of rows already rounded to the f16 storage format")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="one GPU: skip the other configurations' side measurements")

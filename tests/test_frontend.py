@@ -185,3 +185,23 @@ def test_row_major_strides_known_answers():
     assert S._strides((n, 16)) == [16, 1]
     assert S._strides((U.Var("m", 1, 32), 4, 8)) == [32, 8, 1]
     assert S._strides((U.Var("k", 1, 8),)) == [1]
+
+
+def test_stats_hook_reports_each_scheduling_run():
+    """schedule/stats.go:14-18: the hook is called once per successful CreateSchedule with the graph size,
+    the kernel count and the number of reduce kernels spliced into their consumers."""
+    from anneal_b200 import schedule as S, workloads as W
+    seen = []
+    S.STATS_HOOK = seen.append
+    try:
+        R.reset()
+        m = W.MLP(batch=8, dims=(16, 12, 10))
+        items, _ = R.build_schedule(m.graph().targets())
+    finally:
+        S.STATS_HOOK = None
+    assert len(seen) == 1
+    st = seen[0]
+    assert st.kernels == len(items) and st.uops > st.kernels and st.fused >= 1 and st.pass_name == "memory_plan"
+    R.reset()
+    R.build_schedule(W.MLP(batch=8, dims=(16, 12, 10)).graph().targets())
+    assert len(seen) == 1               # cleared hook: no further calls

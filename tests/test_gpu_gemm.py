@@ -72,10 +72,12 @@ def test_gemm_f32_small_stays_on_generated_kernel(cuda, oracle):
     assert n == 0
 
 
-@pytest.mark.parametrize("b,gemms", [(3, 0), (300, 4), (2100, 5)])
+@pytest.mark.parametrize("b,gemms", [(1, 5), (3, 5), (17, 5), (32, 5), (300, 4), (2100, 5)])
 def test_gemm_f32_symbolic_batch(cuda, oracle, b, gemms):
     """The bound batch is M of the forward/input-gradient contractions and K of the weight-gradient
-    ones; one compiled plan serves every binding and picks the kernel per launch.
+    ones; one compiled plan serves every binding and picks the kernel per launch: the few-row and
+    few-term kernels up to 32 rows (one pass over the weights for all rows), the tiled kernel from
+    there on where it has enough tiles, the generated kernel otherwise.
 
     The tiled kernel accumulates with fused multiply-adds, the oracle rounds the product first, so a
     hidden pre-activation within rounding distance of zero can land on the other side of the ReLU

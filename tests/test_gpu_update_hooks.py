@@ -94,3 +94,28 @@ def test_pre_rendered_kernel_uses_all_three_launch_dimensions(cuda):
     out = cuda.run([it], {910002: x})[910001].reshape(6, 12, 40)
     want = x.reshape(6, 12, 40) + (100 * np.arange(6)[:, None, None] + np.arange(12)[None, :, None])
     assert np.array_equal(out, want.astype(np.float32))
+
+
+def test_device_stats_hook_reports_what_a_realize_launched(cuda):
+    """The device-side companion of the schedule's stats hook: launches, tensor-core contractions,
+    kernels that ran inside a contraction's epilogue, bytes moved, per realize."""
+    from anneal_b200 import realize as RR
+    R.reset()
+    R.MATERIALIZE_CONTRACTION_OPERANDS = "auto"
+    seen = []
+    RR.DEFAULT_EXECUTOR = cuda
+    RR.DEVICE_STATS_HOOK = seen.append
+    try:
+        m = W.WideMLP(batch=512, width=256, classes=136, depth=2)
+        x, y = m.make_inputs()
+        g = m.graph(x, y)
+        RR.realize(*g.targets())
+    finally:
+        RR.DEVICE_STATS_HOOK = None
+        RR.DEFAULT_EXECUTOR = None
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+    assert len(seen) == 1
+    st = seen[0]
+    assert st["gemm_launched"] == 8 and st["epilogues_fused"] == 5 and st["colsums_fused"] == 2
+    assert st["kernels_launched"] > st["gemm_launched"] and st["h2d_bytes"] > 0 and st["d2h_bytes"] > 0
+    assert np.isfinite(g.loss.data).all()
