@@ -28,8 +28,8 @@ struct CodegenOpts {
     bool debug_bounds = false; // clamp every load and record violations in a status word
     int sym_hint = 0;          // value the bound batch is expected to have when a kernel is laid out for it; 0 = 1024
     // contraction kernels (0 = heuristic): tile width, ring depth, raster group (-1: none), streaming
-    // stores, one-CTA kernel forced
-    int gemm_tile_n = 0, gemm_stages = 0, gemm_group_m = 0, gemm_stream_stores = 0, gemm_single_cta = 0;
+    // stores, one-CTA kernel forced, last wave kept in whole tiles
+    int gemm_tile_n = 0, gemm_stages = 0, gemm_group_m = 0, gemm_stream_stores = 0, gemm_single_cta = 0, gemm_whole_tail = 0;
 };
 
 struct Launch {

@@ -244,13 +244,13 @@ static int get_function(anl_device* dev, Module& m, const std::string& name, CUf
 static bool opts_default(const CodegenOpts& o) { return !o.block_threads && !o.reduce_lanes && !o.vector_width && !o.split; }
 static GemmTuning tuning_of(const CodegenOpts& o) {
     GemmTuning t;
-    t.tile_n = o.gemm_tile_n; t.stages = o.gemm_stages; t.group_m = o.gemm_group_m; t.stream_stores = o.gemm_stream_stores; t.single_cta = o.gemm_single_cta;
+    t.tile_n = o.gemm_tile_n; t.stages = o.gemm_stages; t.group_m = o.gemm_group_m; t.stream_stores = o.gemm_stream_stores; t.single_cta = o.gemm_single_cta; t.no_split_tail = o.gemm_whole_tail;
     return t;
 }
 
 int get_plan(anl_device* dev, const Item& item, const CodegenOpts& opts, std::shared_ptr<Plan>& out) {
-    int64_t ok[10] = {opts.block_threads, opts.reduce_lanes, opts.vector_width, opts.split, opts.debug_bounds,
-                      opts.gemm_tile_n, opts.gemm_stages, opts.gemm_group_m, opts.gemm_stream_stores, opts.gemm_single_cta};
+    int64_t ok[11] = {opts.block_threads, opts.reduce_lanes, opts.vector_width, opts.split, opts.debug_bounds,
+                      opts.gemm_tile_n, opts.gemm_stages, opts.gemm_group_m, opts.gemm_stream_stores, opts.gemm_single_cta, opts.gemm_whole_tail};
     uint64_t key = fnv1a(ok, sizeof ok, structure_hash(item));
     if (!item.source.empty()) key = fnv1a(item.source.data(), item.source.size(), key);
     auto it = dev->plans.find(key);
@@ -874,7 +874,7 @@ CodegenOpts opts_from(const int* o, unsigned flags) {
     CodegenOpts c;
     if (o) {
         c.block_threads = o[0]; c.reduce_lanes = o[1]; c.vector_width = o[2]; c.split = o[3]; c.debug_bounds = o[4] != 0;
-        c.gemm_tile_n = o[5]; c.gemm_stages = o[6]; c.gemm_group_m = o[7]; c.gemm_stream_stores = o[8]; c.gemm_single_cta = o[9];
+        c.gemm_tile_n = o[5]; c.gemm_stages = o[6]; c.gemm_group_m = o[7]; c.gemm_stream_stores = o[8]; c.gemm_single_cta = o[9]; c.gemm_whole_tail = o[10];
     }
     if (flags & ANL_OPEN_DEBUG_BOUNDS) c.debug_bounds = true;
     return c;
@@ -892,6 +892,15 @@ struct anl_graph {
     cudaGraphExec_t exec = nullptr;
     std::vector<std::pair<uint32_t, anl_buffer*>> resident_in, resident_out;
     uint64_t placed_key = 0;     // hash of what the capture baked in besides pointers: update targets, rate, scale, reduce mode
+    // Captures for other bindings of the same schedule (a symbolic batch cycling through a few
+    // values, tensor/jit.go:86-118 replaySym): parked with their buffers instead of being rebuilt
+    // every time the bound value changes.
+    struct Parked {
+        Table table; cudaGraphExec_t exec; int64_t sym; uint64_t placed_key, kernels, gemms;
+        std::vector<std::pair<uint32_t, anl_buffer*>> rin, rout;
+    };
+    std::vector<Parked> parked;
+    static constexpr size_t kMaxParked = 7;
 };
 
 // ── exception fence ──────────────────────────────────────────────────────────────────────────
@@ -1351,6 +1360,36 @@ static void graph_drop(anl_graph* g) {
     g->built = false;
 }
 
+// The current capture does not fit this call's binding or placements: park it, and bring back a
+// parked one that does, if there is one.
+static void graph_switch(anl_graph* g, int64_t sym, const std::vector<std::pair<uint32_t, anl_buffer*>>& rin,
+                         const std::vector<std::pair<uint32_t, anl_buffer*>>& rout, uint64_t pkey) {
+    if (g->built) {
+        if (g->parked.size() >= anl_graph::kMaxParked) {
+            // oldest out: wait for it, then free its graph and buffers
+            cudaStreamSynchronize(g->dev->stream);
+            anl_graph::Parked& old = g->parked.front();
+            if (old.exec) cudaGraphExecDestroy(old.exec);
+            for (void* p : old.table.owned) g->dev->release(p);
+            g->parked.erase(g->parked.begin());
+        }
+        anl_graph::Parked pk;
+        pk.table = std::move(g->table); pk.exec = g->exec; pk.sym = g->built_sym; pk.placed_key = g->placed_key;
+        pk.kernels = g->kernels_per_replay; pk.gemms = g->gemms_per_replay; pk.rin = g->resident_in; pk.rout = g->resident_out;
+        g->parked.push_back(std::move(pk));
+        g->table = Table(); g->exec = nullptr; g->built = false;
+    }
+    for (size_t k = 0; k < g->parked.size(); k++) {
+        anl_graph::Parked& pk = g->parked[k];
+        if (pk.sym != sym || pk.placed_key != pkey || pk.rin != rin || pk.rout != rout) continue;
+        g->table = std::move(pk.table); g->exec = pk.exec; g->built_sym = pk.sym; g->placed_key = pk.placed_key;
+        g->kernels_per_replay = pk.kernels; g->gemms_per_replay = pk.gemms; g->resident_in = pk.rin; g->resident_out = pk.rout;
+        g->built = true;
+        g->parked.erase(g->parked.begin() + k);
+        return;
+    }
+}
+
 static int graph_replay_impl(anl_graph* g, const anl_input* inputs, int n_inputs, const anl_binding* binds, int n_binds,
                      const anl_output* placed, int n_placed, anl_output* outs, int* n_outs) {
     if (!g || !n_outs) return ANL_ERR_INVALID;
@@ -1373,7 +1412,7 @@ static int graph_replay_impl(anl_graph* g, const anl_input* inputs, int n_inputs
         rec.id = p.uop_idx; rec.mode = p.allreduce; rec.m = p.sgd_master; rec.q = p.sgd_param; rec.lr = p.sgd_lr; rec.scale = p.sgd_scale;
         pkey = fnv1a(&rec, sizeof rec, pkey);
     }
-    if (g->built && (sym != g->built_sym || rin != g->resident_in || rout != g->resident_out || pkey != g->placed_key)) graph_drop(g);
+    if (g->built && (sym != g->built_sym || rin != g->resident_in || rout != g->resident_out || pkey != g->placed_key)) graph_switch(g, sym, rin, rout, pkey);
     int rc = ANL_OK;
     bool host_fed = !g->built;      // a replay whose leaves and outputs are all resident need not wait for the GPU
     if (!g->built) {
@@ -1431,6 +1470,11 @@ static int graph_replay_impl(anl_graph* g, const anl_input* inputs, int n_inputs
 void anl_graph_release(anl_graph* g) {
     if (!g) return;
     cudaStreamSynchronize(g->dev->stream);
+    for (auto& pk : g->parked) {
+        if (pk.exec) cudaGraphExecDestroy(pk.exec);
+        for (void* p : pk.table.owned) g->dev->release(p);
+    }
+    g->parked.clear();
     graph_drop(g);
     delete g;
 }

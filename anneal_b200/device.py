@@ -154,20 +154,20 @@ KERNEL_CLASSES = {0: "elementwise", 1: "reduce", 2: "reduce_split", 3: "gemm", 4
 
 
 #: include/anneal_cuda.h ANL_NUM_OPTS
-NUM_OPTS = 10
+NUM_OPTS = 11
 
 
 def _opts(opts):
     """{block_threads, reduce_lanes, vector_width, split, debug_bounds, tile_n, stages, group_m,
-    stream_stores, single_cta} as the C array the library expects, shorter lists padded with 0."""
+    stream_stores, single_cta, whole_tail} as the C array the library expects, shorter lists padded with 0."""
     if not opts:
         return None
     return (C.c_int * NUM_OPTS)(*(list(opts) + [0] * NUM_OPTS)[:NUM_OPTS])
 
 
-def gemm_opts(tile_n=0, stages=0, group_m=0, stream_stores=0, single_cta=0):
+def gemm_opts(tile_n=0, stages=0, group_m=0, stream_stores=0, single_cta=0, whole_tail=0):
     """An opts list that only sets the contraction kernel's tunables."""
-    return [0, 0, 0, 0, 0, tile_n, stages, group_m, stream_stores, single_cta]
+    return [0, 0, 0, 0, 0, tile_n, stages, group_m, stream_stores, single_cta, whole_tail]
 
 
 def lower(items, index: int = 0, opts: Optional[Sequence[int]] = None):

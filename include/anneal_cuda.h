@@ -136,11 +136,11 @@ void anl_outputs_free(anl_output* outs, int n_outs);
  * Renders item `index` of the blob to CUDA C without touching the GPU.  `opts` (NULL, or
  * ANL_NUM_OPTS ints, in every call that takes them) is {block_threads, reduce_lanes, vector_width,
  * split, debug_bounds} for generated kernels followed by {tile_n, stages, group_m, stream_stores,
- * single_cta} for the tcgen05 contraction kernels — the reference's Local / Upcast / Vectorize /
+ * single_cta, whole_tail} for the tcgen05 contraction kernels — the reference's Local / Upcast / Vectorize /
  * Tile choices (codegen/opt.go:57-72) retargeted; 0 means "choose", group_m -1 "no grouping".  The
  * source is copied to `src` (capacity src_cap, always NUL-terminated) and its full length is
  * returned in *src_len; `klass`, `block`, `outputs_per_block` describe the launch. */
-#define ANL_NUM_OPTS 10
+#define ANL_NUM_OPTS 11
 int anl_lower(anl_device* dev_or_null, const uint8_t* blob, size_t blob_len, int index, const int* opts,
               char* src, size_t src_cap, size_t* src_len, int* klass, int* block, int64_t* outputs_per_block,
               char* note, size_t note_cap);

@@ -394,3 +394,29 @@ def test_c4_wide_mlp_full_size_step(cuda):
     # softmax - onehot, whose entries sum to zero over the classes (each row of both sums to one)
     db_head = got[out_ids[-1]].astype(np.float64)
     assert abs(db_head.sum()) <= 2e-3 * np.abs(db_head).sum()
+
+
+def test_symbolic_replay_keeps_one_capture_per_bound_batch(cuda, oracle):
+    """A schedule replayed with the batch cycling through a few values (the shape of the reference's
+    dynamic-batch example) is captured once per value: coming back to a value relaunches its parked
+    CUDA graph instead of capturing again, and the results stay those of an eager run."""
+    R.MATERIALIZE_CONTRACTION_OPERANDS = "auto"
+    try:
+        m = W.DynMLP(din=256, hidden=512, dout=128, max_batch=1024)
+        out, loss, grads, ins = m.graph(8)
+        items, out_ids = R.build_schedule([out] + grads)
+    finally:
+        R.MATERIALIZE_CONTRACTION_OPERANDS = False
+    params = {p.t.node.idx: p.value for p in m.params}
+    c0 = cuda.stats()["graph_captures"]
+    for cycle in range(3):
+        for b in (1, 17, 300):
+            x, y = m.inputs(b)
+            inputs = dict(params)
+            inputs[ins["x"].node.idx], inputs[ins["y"].node.idx] = x, y
+            got = cuda.replay(items, inputs, {"n": b})
+            if cycle == 2:
+                want = cuda.run(items, inputs, {"n": b})
+                for k in out_ids:
+                    assert np.array_equal(got[k], want[k]), (b, k)
+    assert cuda.stats()["graph_captures"] - c0 == 3
