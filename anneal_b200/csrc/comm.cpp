@@ -202,6 +202,45 @@ int anl_comm_abort(anl_device* dev) {
     return ANL_OK;
 }
 
+}  // extern "C"
+
+namespace anl {
+// Waits for `stream` under the watchdog.  A collective may sit on the communication stream (eager
+// launches) or inside a captured graph that was launched on the compute stream (replays): in both
+// cases the host must not block without a limit while a communicator with a timeout exists.
+int wait_stream_watched(anl_device* dev, cudaStream_t stream, const char* what) {
+    if (!stream) return ANL_OK;
+    if (!(dev->nccl_comm && dev->comm_timeout_ms > 0)) {
+        cudaError_t e = cudaStreamSynchronize(stream);
+        return e == cudaSuccess ? ANL_OK : dev->fail(ANL_ERR_CUDA, std::string("cuda: ") + what + ": " + cudaGetErrorString(e));
+    }
+    Nccl& n = nccl();
+    const auto t0 = std::chrono::steady_clock::now();
+    for (;;) {
+        cudaError_t q = cudaStreamQuery(stream);
+        if (q == cudaSuccess) return ANL_OK;
+        if (q != cudaErrorNotReady) return dev->fail(ANL_ERR_CUDA, std::string("cuda: ") + what + ": " + cudaGetErrorString(q));
+        if (dev->nccl_comm && n.CommGetAsyncError) {
+            int ae = 0;
+            if (n.CommGetAsyncError(dev->nccl_comm, &ae) == 0 && ae != 0) {
+                abort_comm(dev);
+                cudaStreamSynchronize(stream);      // the aborted collective's kernels leave; the rest of the queue drains
+                return dev->fail(ANL_ERR_COMM, std::string("nccl: asynchronous error: ") + (n.GetErrorString ? n.GetErrorString(ae) : "?") + "; communicator aborted");
+            }
+        }
+        auto ms = std::chrono::duration_cast<std::chrono::milliseconds>(std::chrono::steady_clock::now() - t0).count();
+        if (ms >= dev->comm_timeout_ms) {
+            abort_comm(dev);
+            cudaStreamSynchronize(stream);
+            return dev->fail(ANL_ERR_COMM, "nccl: collective did not finish within " + std::to_string(dev->comm_timeout_ms) + " ms (a peer is missing or stalled); communicator aborted");
+        }
+        std::this_thread::sleep_for(std::chrono::microseconds(50));
+    }
+}
+}  // namespace anl
+
+extern "C" {
+
 int anl_comm_wait(anl_device* dev) {
     if (!dev) return ANL_ERR_INVALID;
     if (!dev->comm_stream) return ANL_OK;

@@ -498,7 +498,17 @@ int get_pair_kernel(anl_device* dev, const PairVariant& v, const std::string& ep
     return ANL_OK;
 }
 
-PairVariant choose_variant(anl_device* dev, const GemmPlan& gp, int64_t M) {
+PairVariant choose_variant(anl_device* dev, const GemmPlan& gp_in, int64_t M) {
+    // the plan's own tunables (a search result) first, then the device's defaults, then the heuristics
+    GemmPlan gp = gp_in;
+    if (dev) {
+        const GemmTuning& d = dev->gemm_defaults;
+        if (!gp.tune.tile_n) gp.tune.tile_n = d.tile_n;
+        if (!gp.tune.stages) gp.tune.stages = d.stages;
+        if (!gp.tune.group_m) gp.tune.group_m = d.group_m;
+        if (!gp.tune.stream_stores) gp.tune.stream_stores = d.stream_stores;
+        if (!gp.tune.no_split_tail) gp.tune.no_split_tail = d.no_split_tail;
+    }
     const Contraction& c = gp.c;
     PairVariant v{};
     v.a_mn = gp.a_mn; v.b_mn = gp.b_mn;

@@ -852,8 +852,11 @@ int collect_outputs(anl_device* dev, Table& t, const anl_output* placed, int n_p
         outs[n++] = o;
     }
     const bool waited = !(may_return_early && !to_host && rc == ANL_OK);
-    cudaError_t e = waited ? cudaStreamSynchronize(stream) : cudaSuccess;
-    if (rc == ANL_OK && e != cudaSuccess) rc = dev->fail(ANL_ERR_CUDA, std::string("cuda: ") + cudaGetErrorString(e));
+    if (waited) {
+        // a captured step carries its collectives on this stream: wait under the watchdog
+        int wrc = wait_stream_watched(dev, stream, "run");
+        if (rc == ANL_OK) rc = wrc;
+    }
     if (rc == ANL_OK && waited) rc = gemm_check_status(dev);
     if (rc != ANL_OK) {
         std::lock_guard<std::mutex> lk(g_owned_mu);
@@ -974,6 +977,15 @@ const char* anl_last_error(anl_device* dev) { return dev ? dev->err.c_str() : "n
 
 int anl_get_stats(anl_device* dev, anl_stats* out) { if (!dev || !out) return ANL_ERR_INVALID; *out = dev->stats; return ANL_OK; }
 
+int anl_gemm_set_defaults(anl_device* dev, const int* o) {
+    if (!dev) return ANL_ERR_INVALID;
+    GemmTuning t;
+    if (o) { t.tile_n = o[5]; t.stages = o[6]; t.group_m = o[7]; t.stream_stores = o[8]; t.single_cta = o[9]; t.no_split_tail = o[10]; }
+    if (t.tile_n != 0 && t.tile_n != 128 && t.tile_n != 256) return dev->fail(ANL_ERR_INVALID, "gemm defaults: tile_n must be 0, 128 or 256");
+    dev->gemm_defaults = t;
+    return ANL_OK;
+}
+
 int anl_gemm_inject_status(anl_device* dev, int code, int counter_value) {
     if (!dev) return ANL_ERR_INVALID;
     cudaSetDevice(dev->ordinal);
@@ -987,7 +999,7 @@ int anl_synchronize(anl_device* dev) {
     // with a communication timeout set, the collective stream is waited for under the watchdog first:
     // the compute stream may itself be waiting for a collective that will never finish
     if (dev->comm_stream && dev->comm_timeout_ms > 0) if (int rc = anl_comm_wait(dev)) return rc;
-    CK(dev, cudaStreamSynchronize(dev->stream));
+    if (int rc = wait_stream_watched(dev, dev->stream, "synchronize")) return rc;      // replays carry their collectives here
     if (dev->comm_stream) CK(dev, cudaStreamSynchronize(dev->comm_stream));
     if (dev->copy_stream) CK(dev, cudaStreamSynchronize(dev->copy_stream));
     return gemm_check_status(dev);
@@ -1177,8 +1189,7 @@ int anl_buffer_download(anl_buffer* buf, float* data, int64_t elems) {
     if (!buf || !data || elems > buf->elems) return ANL_ERR_INVALID;
     cudaSetDevice(buf->dev->ordinal);
     if (int rc = download_f32(buf->dev, data, buf->ptr, buf->dtype, elems, buf->dev->stream)) return rc;
-    CK(buf->dev, cudaStreamSynchronize(buf->dev->stream));
-    return ANL_OK;
+    return wait_stream_watched(buf->dev, buf->dev->stream, "download");
 }
 // Pipelined upload, first half: the copy stream moves `elems` floats from (pinned) host memory
 // into the buffer's staging block and returns at once.  The buffer's contents are untouched, so

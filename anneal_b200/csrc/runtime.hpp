@@ -139,6 +139,7 @@ struct anl_device {
     int* gemm_status_host = nullptr;      // mapped, host-visible: code of a barrier wait that ran out
     int* gemm_status_dev = nullptr;
     bool gemm_attr_set = false;
+    anl::GemmTuning gemm_defaults;        // device-wide tunables of the contraction kernels; a plan's own non-zero fields win
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
     bool comm_pending = false;
@@ -200,6 +201,9 @@ int comm_reduce_scatter_async(anl_device* dev, void* ptr, int64_t elems, int dty
 int comm_allgather_async(anl_device* dev, void* ptr, int64_t elems, int dtype);
 int launch_sgd(anl_device* dev, anl_buffer* master, anl_buffer* param, anl_buffer* grad, float lr, float scale, cudaStream_t stream);
 int comm_join(anl_device* dev, cudaStream_t stream);
+// cudaStreamSynchronize under the collective watchdog: with a communicator and a timeout set the
+// wait is a bounded poll that aborts the communicator at the deadline (ANL_ERR_COMM)
+int wait_stream_watched(anl_device* dev, cudaStream_t stream, const char* what);
 
 // autotuning (beam.cpp)
 int beam_search(anl_device* dev, const Item& it, int width, int depth, anl_beam_result* out);

@@ -85,6 +85,7 @@ def load_library():
     L.anl_get_stats.argtypes = [vp, C.POINTER(_Stats)]
     L.anl_synchronize.argtypes = [vp]
     L.anl_gemm_inject_status.argtypes = [vp, i, i]
+    L.anl_gemm_set_defaults.argtypes = [vp, C.POINTER(i)]
     L.anl_stream.argtypes = [vp]
     L.anl_stream.restype = vp
     L.anl_run.argtypes = [vp, u8p, C.c_size_t, C.POINTER(_Input), i, C.POINTER(_Binding), i,
@@ -147,7 +148,7 @@ ABI_SYMBOLS = [
     "anl_buffer_create", "anl_buffer_upload", "anl_buffer_upload_begin", "anl_buffer_upload_begin_stored", "anl_buffer_upload_commit", "anl_buffer_download", "anl_buffer_release", "anl_buffer_device_ptr",
     "anl_buffer_elems", "anl_buffer_view", "anl_sgd_step", "anl_comm_unique_id", "anl_comm_init", "anl_allreduce_sum", "anl_allgather",
     "anl_comm_destroy", "anl_comm_set_timeout", "anl_comm_wait", "anl_comm_abort", "anl_comm_inject_delay", "anl_host_alloc", "anl_host_free", "anl_synchronize", "anl_timer_start", "anl_timer_stop",
-    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search", "anl_stream", "anl_lower_gemm", "anl_gemm_inject_status", "anl_buffer_download_begin", "anl_buffer_download_wait",
+    "anl_profile_enable", "anl_profile_read", "anl_sum_f32_static", "anl_beam_search", "anl_stream", "anl_lower_gemm", "anl_gemm_inject_status", "anl_buffer_download_begin", "anl_buffer_download_wait", "anl_gemm_set_defaults",
 ]
 
 KERNEL_CLASSES = {0: "elementwise", 1: "reduce", 2: "reduce_split", 3: "gemm", 4: "raw"}
@@ -515,6 +516,10 @@ class Device:
         self._check(self.L.anl_profile_read(self.h, arr, 8, C.byref(n)))
         return {KERNEL_CLASSES.get(arr[k].klass, str(arr[k].klass)): {"launches": arr[k].launches, "total_ms": arr[k].total_ms,
                                                                        "flops": arr[k].flops} for k in range(n.value)}
+
+    def gemm_defaults(self, **kw):
+        """Device-wide tunables of the contraction kernel (see ``gemm_opts``); no arguments: heuristics."""
+        self._check(self.L.anl_gemm_set_defaults(self.h, _opts(gemm_opts(**kw)) if kw else None))
 
     @property
     def stream(self) -> int:

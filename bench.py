@@ -214,7 +214,7 @@ def run_reference(args):
     ms = 1e3 * sum(times) / len(times)
     v = CPU_SAMPLE_BATCH / (ms / 1e3)
     desc = f"{CPU_SAMPLE_BATCH} rows of the {CFG['batch']}-row batch per step, full widths, {len(times)} timed steps after {warm} warm-up"
-    print(json.dumps({
+    emit(json.dumps({
         "impl": "reference", "metric": METRIC, "value": v, "unit": UNIT, "n_gpus": args.gpus, "steps": len(times),
         "warmup": warm, "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
         "dtype": "f16", "data": "synthetic",
@@ -252,6 +252,9 @@ def run_ours(args):
         if world > 1:
             dist.barrier()
 
+    if args.gemm_tuning:
+        names = ("tile_n", "stages", "group_m", "stream_stores", "single_cta", "whole_tail")
+        dev.gemm_defaults(**{n: int(v) for n, v in zip(names, args.gemm_tuning.split(","))})
     model = W.WideMLP(rank=rank, **CFG)
     x, y = model.make_inputs()
     R.reset()
@@ -425,7 +428,7 @@ def run_ours(args):
             "fused": {k: int(dev.stats()[k]) for k in ("epilogues_fused", "colsums_fused")},
             "kernel_classes": {k: {"launches": v["launches"], "ms": round(v["total_ms"], 3)} for k, v in prof.items()},
         }
-        print(json.dumps(out))
+        emit(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()
     dev.close()
@@ -555,8 +558,28 @@ def measure_other(dev, workload, steps, warmup, materialize=-1, dyn_batches="1,1
 def run_other(args):
     from anneal_b200.device import Device
     dev = Device(int(os.environ.get("LOCAL_RANK", "0")))
-    print(json.dumps(measure_other(dev, args.workload, args.steps, args.warmup, args.materialize, args.dyn_batches)))
+    emit(json.dumps(measure_other(dev, args.workload, args.steps, args.warmup, args.materialize, args.dyn_batches)))
     dev.close()
+
+
+_REAL_STDOUT = None
+
+
+def keep_stdout_for_the_json_line():
+    """Libraries below (NCCL prints its version and, when asked, its log on stdout) must not share
+    the stream on which the one JSON line goes out: file descriptor 1 is pointed at stderr for the
+    life of the process and the line is written through a saved copy."""
+    global _REAL_STDOUT
+    if _REAL_STDOUT is None:
+        sys.stdout.flush()
+        _REAL_STDOUT = os.fdopen(os.dup(1), "w")
+        os.dup2(2, 1)
+
+
+def emit(line: str):
+    out = _REAL_STDOUT or sys.stdout
+    out.write(line + "\n")
+    out.flush()
 
 
 def main():
@@ -571,12 +594,14 @@ def main():
     ap.add_argument("--dyn-batches", default="1,17,256,4096,65536", help="dynmlp: batch sizes bound in turn; the last one is reported")
     ap.add_argument("--materialize", type=int, default=-1, help="mlp/cnn: 1/0 forces contraction operands to be buffers or expressions; default: decided per operand by cost")
     ap.add_argument("--e2e-f32-host", action="store_true", help="e2e: host batches as float32 rows (converted on the device) instead of rows already rounded to the f16 storage format")
+    ap.add_argument("--gemm-tuning", default="", help="tile_n,stages,group_m,stream_stores,single_cta,whole_tail for the contraction kernel (0 = heuristic); for A/B runs")
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-configs", action="store_true", help="one GPU: skip the other configurations' side measurements")
     ap.add_argument("--sustained-s", type=float, default=3.0, help="one GPU: seconds the step is looped for the sustained record (0 skips it)")
     ap.add_argument("--no-graph", action="store_true", help="launch kernels one by one instead of replaying a CUDA graph")
     ap.add_argument("--no-overlap", action="store_true", help="all-reduce the whole gradient bucket after the backward pass")
     args = ap.parse_args()
+    keep_stdout_for_the_json_line()
     if args.impl == "reference":
         run_reference(args)
     elif args.workload != "wide_mlp":

@@ -282,6 +282,12 @@ int anl_sum_f32_static(const float* x, int64_t n, float* out, void* stream, char
 /* blocks until all work queued on the device has finished */
 int anl_synchronize(anl_device* dev);
 
+/* Device-wide tunables of the tcgen05 contraction kernel, for a deployment that has searched them
+ * offline (anl_beam_search) and wants them applied to every contraction without opening the device
+ * in search mode: `opts` as everywhere (ANL_NUM_OPTS ints; only the contraction fields are read,
+ * NULL resets to the built-in heuristics).  A plan's own tunables, when a search set them, win. */
+int anl_gemm_set_defaults(anl_device* dev, const int* opts);
+
 /* Diagnostic: leaves the device as a contraction launch does whose bounded barrier wait ran out — a
  * non-zero code in the host-visible status word and tile counters holding `counter_value` — without
  * any kernel waiting or failing.  The next call that waits for the device (anl_run, a replay,

@@ -5,6 +5,7 @@ ANL_ERR_COMM, later collectives must refuse, and after a new communicator (of on
 must go on.  NVLS is off (NCCL_NVLS_ENABLE=0, set by the launcher) and no kernel of this library uses
 multicast memory."""
 import os
+import signal
 import sys
 import time
 
@@ -20,6 +21,9 @@ from anneal_b200.uop import dtypes                            # noqa: E402
 
 
 def main():
+    # whatever happens, no rank outlives this: a stuck process would keep its GPU busy for the next user
+    signal.signal(signal.SIGALRM, lambda *_: os._exit(3))
+    signal.alarm(120)
     rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
     assert world == 2
     dist.init_process_group("gloo", rank=rank, world_size=world)
@@ -30,7 +34,9 @@ def main():
     dev.comm_set_timeout(3000)
     m = W.WideMLP(batch=256, width=512, classes=72, depth=2, rank=rank)
     x, y = m.make_inputs()
-    tr = ResidentTrainer(dev, m, 0.05, world=world, use_graph=True, resident_inputs=True)
+    # one bucket all-reduce after the backward pass, launched eagerly: exactly ONE collective is in
+    # flight when the peer is missing, so the abort has nothing queued behind it to clean up
+    tr = ResidentTrainer(dev, m, 0.05, world=world, use_graph=False, resident_inputs=True, overlap=False)
     tr.load_batch(x, y)
     for _ in range(2):
         tr.step()
@@ -46,7 +52,7 @@ def main():
     problems = []
     t0 = time.time()
     try:
-        tr.step()                      # queues the step; its all-reduce waits for a peer that is gone
+        tr.step()                      # queues the step; its one all-reduce waits for a peer that is gone
         dev.synchronize()
         problems.append("the step after the peer left did not fail")
     except DeviceError as e:
