@@ -315,12 +315,12 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
 
 
 static int encode_map(anl_device* dev, CUtensorMap* map, const void* base, uint64_t inner, uint64_t outer, uint64_t row_stride_elems,
-                      uint32_t box_inner, uint32_t box_outer) {
+                      uint32_t box_inner, uint32_t box_outer, bool f32 = false) {
     cuuint64_t dims[2] = {inner, outer};
-    cuuint64_t strides[1] = {row_stride_elems * 2};
+    cuuint64_t strides[1] = {row_stride_elems * (f32 ? 4 : 2)};
     cuuint32_t box[2] = {box_inner, box_outer};
     cuuint32_t estr[2] = {1, 1};
-    CUresult r = dev->drv.TensorMapEncodeTiled(map, CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+    CUresult r = dev->drv.TensorMapEncodeTiled(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
     if (r != CUDA_SUCCESS) { const char* s = nullptr; dev->drv.GetErrorString(r, &s); return dev->fail(ANL_ERR_CUDA, std::string("gemm: cuTensorMapEncodeTiled: ") + (s ? s : "?")); }
@@ -465,7 +465,8 @@ void gemm_shape(const Plan& plan, int64_t* M, int64_t* N, int64_t* K) { *M = pla
 // ── the run-time compiled two-CTA kernel ──────────────────────────────────────────────────────
 namespace {
 
-struct PairVariant { int bnt, stages, group_m, stream_stores; bool a_mn, b_mn; bool split_tail; };
+struct PairVariant { int bnt, stages, group_m, stream_stores; bool a_mn, b_mn; bool split_tail; bool tf32 = false; };
+constexpr int kTf32ChunkK = 1024;       // k extent the 3 x TF32 form accumulates in tensor memory before adding to the output in f32
 constexpr int kDefaultStages = 7;      // the deepest ring that fits beside a 256-wide tile; 1% faster than 6 on every large shape measured
 
 int pair_smem_bytes(int bnt, int stages) { return stages * (A_TILE_BYTES + (bnt / 2) * BK * 2) + 1024; }
@@ -480,6 +481,7 @@ std::string pair_source(const PairVariant& v, const std::string& epilogue) {
     s += "#define CFG_BNT " + std::to_string(v.bnt) + "\n#define CFG_STAGES " + std::to_string(v.stages) + "\n";
     s += "#define CFG_GROUP_M " + std::to_string(v.group_m) + "\n#define CFG_STREAM_STORES " + std::to_string(v.stream_stores) + "\n";
     s += "#define CFG_EPI " + std::string(epilogue.empty() ? "0" : "1") + "\n";
+    s += "#define CFG_TF32 " + std::string(v.tf32 ? "1" : "0") + "\n";
     s += epilogue;
     s += kPairKernelSource;
     return s;
@@ -543,8 +545,174 @@ int gemm_prepare(anl_device* dev, const Plan& plan, const std::string& epilogue)
     return get_pair_kernel(dev, choose_variant(dev, *plan.gemm, plan.gemm->c.M), epilogue, &fn);
 }
 
+// ── f32 contractions on the tensor cores: 3 x TF32 ────────────────────────────────────────────
+// hi = the operand rounded to TF32 (11 significant bits, round to nearest, ties away), lo = operand - hi
+// (exact in f32), itself rounded to TF32.
+__global__ void __launch_bounds__(256) split_tf32(const float* __restrict__ src, long long ld, long long rows, long long cols, long long ldo,
+                                                  float* __restrict__ hi, float* __restrict__ lo) {
+    const long long per_row = ldo >> 2;
+    const long long total = rows * per_row;
+    for (long long t = (long long)blockIdx.x * blockDim.x + threadIdx.x; t < total; t += (long long)gridDim.x * blockDim.x) {
+        const long long r = t / per_row, c = (t - r * per_row) << 2;
+        float v[4], h[4], l[4];
+        const float* p = src + r * ld + c;
+        if (c + 3 < cols && (reinterpret_cast<uintptr_t>(p) & 15) == 0) {
+            const float4 q = *reinterpret_cast<const float4*>(p);
+            v[0] = q.x; v[1] = q.y; v[2] = q.z; v[3] = q.w;
+        } else {
+#pragma unroll
+            for (int j = 0; j < 4; j++) v[j] = (c + j < cols) ? p[j] : 0.0f;
+        }
+#pragma unroll
+        for (int j = 0; j < 4; j++) {
+            unsigned u, w;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v[j]));
+            h[j] = __uint_as_float(u);
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w) : "f"(v[j] - h[j]));     // the tensor core would cut it; rounding halves that error
+            l[j] = __uint_as_float(w);
+        }
+        *reinterpret_cast<float4*>(hi + r * ldo + c) = make_float4(h[0], h[1], h[2], h[3]);
+        *reinterpret_cast<float4*>(lo + r * ldo + c) = make_float4(l[0], l[1], l[2], l[3]);
+    }
+}
+
+// The same split for an operand stored with its row index contiguous (element (r, k) at src[k * ld + r]):
+// written out k-contiguous through a 32 x 32 shared-memory tile, so the tensor-core kernel sees one
+// operand layout.  Block (32, 8); grid (ceil(k / 32), ceil(rows / 32)), rows folded into y then z.
+__global__ void __launch_bounds__(256) split_tf32_transposed(const float* __restrict__ src, long long ld, long long rows, long long cols, long long ldo,
+                                                             float* __restrict__ hi, float* __restrict__ lo) {
+    __shared__ float tile[32][33];
+    const long long k0 = (long long)blockIdx.x * 32;
+    const long long r0 = ((long long)blockIdx.z * gridDim.y + blockIdx.y) * 32;
+    if (r0 >= rows) return;
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        const long long k = k0 + threadIdx.y + j, r = r0 + threadIdx.x;
+        tile[threadIdx.y + j][threadIdx.x] = (k < cols && r < rows) ? src[k * ld + r] : 0.0f;
+    }
+    __syncthreads();
+#pragma unroll
+    for (int j = 0; j < 32; j += 8) {
+        const long long r = r0 + threadIdx.y + j, k = k0 + threadIdx.x;
+        if (r < rows && k < ldo) {
+            const float v = tile[threadIdx.x][threadIdx.y + j];
+            unsigned u, w;
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(u) : "f"(v));
+            const float h = __uint_as_float(u);
+            asm("cvt.rna.tf32.f32 %0, %1;" : "=r"(w) : "f"(v - h));
+            hi[r * ldo + k] = h;
+            lo[r * ldo + k] = __uint_as_float(w);
+        }
+    }
+}
+
+// Large f32 contractions take the two-CTA tensor-core kernel in 3 x TF32 form unless the device was
+// opened with ANL_OPEN_NO_TF32X3: at least one full pair tile, a k extent worth a pipeline, and
+// operands contiguous along k or along their row index.
+static bool tf32x3_shape_ok(const Contraction& c, int64_t M, int64_t K) {
+    if (M < 2 * BM || c.N < BN / 2 || K < 128) return false;
+    if ((double)M * (double)c.N * (double)K < 2.0e9) return false;
+    if (M >= (1ll << 31) || c.N >= (1ll << 31) || K >= (1ll << 31)) return false;
+    if (!(c.a_sk == 1 || c.a_sm == 1) || !(c.b_sk == 1 || c.b_sn == 1)) return false;
+    return true;
+}
+static bool tf32x3_applies(anl_device* dev, const Contraction& c, int64_t M, int64_t K) {
+    return !(dev->flags & ANL_OPEN_NO_TF32X3) && tf32x3_shape_ok(c, M, K);
+}
+static PairVariant tf32_variant() {
+    PairVariant v{};
+    v.a_mn = v.b_mn = false;        // the split pre-pass hands both operands over k-contiguous
+    v.bnt = 256; v.tf32 = true; v.split_tail = false;
+    v.stages = std::min(kDefaultStages, max_stages(256));
+    v.group_m = kDefaultGroupM;
+    return v;
+}
+bool gemm_tf32_eligible(const Plan& plan) {
+    if (!plan.gemm || plan.gemm_dynamic || plan.r.klass != KC_GEMM || !plan.gemm->f32) return false;
+    return tf32x3_shape_ok(plan.gemm->c, plan.gemm->c.M, plan.gemm->c.K);
+}
+int gemm_tf32_source(const Plan& plan, std::string& out, std::string& note) {
+    if (!gemm_tf32_eligible(plan)) return ANL_ERR_UNSUPPORTED;
+    const PairVariant v = tf32_variant();
+    out = pair_source(v, std::string());
+    const Contraction& c = plan.gemm->c;
+    note = std::string("gemm tcgen05 3xTF32 A:") + (c.a_sk == 1 ? "K" : "MN") + " B:" + (c.b_sk == 1 ? "K" : "MN") + " (both rewritten k-contiguous by the split pre-pass) M=" + std::to_string(c.M) + " N=" + std::to_string(c.N) + " K=" + std::to_string(c.K);
+    return ANL_OK;
+}
+
+static int launch_gemm_tf32x3(anl_device* dev, const GemmPlan& gp, const float* a, const float* b, float* d, int64_t M, int64_t K,
+                              cudaStream_t stream, std::vector<void*>* keep_scratch) {
+    const Contraction& c = gp.c;
+    const int64_t N = c.N;
+    if (int rc = ensure_gemm_state(dev)) return rc;
+    if (*dev->gemm_status_host != 0) return dev->fail(ANL_ERR_CUDA, "gemm: an earlier launch timed out on a barrier (code " + std::to_string(*dev->gemm_status_host) + ")");
+    // both operands are rewritten as [rows, K] with k contiguous (rows = m or n), K padded to 4 floats
+    const bool a_mn = !(c.a_sk == 1), b_mn = !(c.b_sk == 1);
+    const int64_t ldo = (K + 3) & ~3ll;
+    void* scratch[4] = {nullptr, nullptr, nullptr, nullptr};
+    const size_t a_bytes = (size_t)M * ldo * 4, b_bytes = (size_t)N * ldo * 4;
+    int rc = ANL_OK;
+    for (int k = 0; k < 4 && rc == ANL_OK; k++) rc = dev->alloc(k < 2 ? a_bytes : b_bytes, &scratch[k]);
+    auto done = [&](int code) {
+        for (void* p : scratch) if (p) { if (keep_scratch) keep_scratch->push_back(p); else dev->release(p); }
+        return code;
+    };
+    if (rc) return done(rc);
+    float *a_hi = (float*)scratch[0], *a_lo = (float*)scratch[1], *b_hi = (float*)scratch[2], *b_lo = (float*)scratch[3];
+    const int sms = dev->prop.multiProcessorCount;
+    auto split = [&](const float* src, bool mn, int64_t rows, int64_t ld, float* hi, float* lo) {
+        if (!mn) {
+            const unsigned grid = (unsigned)std::max<int64_t>(1, std::min<int64_t>((rows * (ldo / 4) + 255) / 256, (int64_t)sms * 16));
+            split_tf32<<<grid, 256, 0, stream>>>(src, ld, rows, K, ldo, hi, lo);
+        } else {
+            const int64_t rt = (rows + 31) / 32;
+            const unsigned gy = (unsigned)std::min<int64_t>(rt, 32768), gz = (unsigned)((rt + gy - 1) / gy);
+            split_tf32_transposed<<<dim3((unsigned)((ldo + 31) / 32), gy, gz), dim3(32, 8), 0, stream>>>(src, ld, rows, K, ldo, hi, lo);
+        }
+    };
+    split(a, a_mn, M, a_mn ? c.a_sk : c.a_sm, a_hi, a_lo);
+    split(b, b_mn, N, b_mn ? c.b_sk : c.b_sn, b_hi, b_lo);
+    if (cudaGetLastError() != cudaSuccess) return done(dev->fail(ANL_ERR_CUDA, "gemm: operand split launch failed"));
+    dev->stats.kernels_launched += 2;
+
+    const PairVariant v = tf32_variant();
+    CUfunction fn;
+    if ((rc = get_pair_kernel(dev, v, std::string(), &fn))) return done(rc);
+    constexpr int BK32 = 32;
+    CUtensorMap ma_hi, ma_lo, mb_hi, mb_lo;
+    auto enc_a = [&](CUtensorMap* m, const float* base) { return encode_map(dev, m, base, (uint64_t)K, (uint64_t)M, (uint64_t)ldo, BK32, BM, true); };
+    auto enc_b = [&](CUtensorMap* m, const float* base) { return encode_map(dev, m, base, (uint64_t)K, (uint64_t)N, (uint64_t)ldo, BK32, v.bnt / 2, true); };
+    if ((rc = enc_a(&ma_hi, a_hi)) || (rc = enc_a(&ma_lo, a_lo)) || (rc = enc_b(&mb_hi, b_hi)) || (rc = enc_b(&mb_lo, b_lo))) return done(rc);
+    PairGemmArgs g{};
+    g.d_raw = d; g.d_out = nullptr; g.colsum = nullptr;
+    g.M = (int)M; g.N = (int)N; g.ldd = (int)N;
+    g.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM)); g.tiles_n = (int)((N + v.bnt - 1) / v.bnt);
+    g.full_tiles = g.tiles_m * g.tiles_n;
+    g.status = dev->gemm_status_dev;
+    g.tile_counter = tile_counter_for(dev, stream);
+    const int npairs = gemm_sm_budget(dev) / 2;
+    const int pairs = std::min(g.full_tiles, npairs);
+    CUlaunchConfig cfg{};
+    cfg.gridDimX = 2 * pairs; cfg.gridDimY = 1; cfg.gridDimZ = 1;
+    cfg.blockDimX = GEMM_THREADS; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.sharedMemBytes = pair_smem_bytes(v.bnt, v.stages);
+    cfg.hStream = (CUstream)stream;
+    CUlaunchAttribute at[1];
+    at[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
+    at[0].value.clusterDim.x = 2; at[0].value.clusterDim.y = 1; at[0].value.clusterDim.z = 1;
+    cfg.attrs = at; cfg.numAttrs = 1;
+    g.K = (int)K;
+    g.chunk_kb = kTf32ChunkK / BK32;
+    void* params[6] = {&ma_hi, &mb_hi, &mb_hi, &ma_lo, &mb_lo, &g};
+    CUresult cr = dev->drv.LaunchKernelEx(&cfg, fn, params, nullptr);
+    if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return done(dev->fail(ANL_ERR_CUDA, std::string("gemm: tf32 pair launch: ") + (e ? e : "?"))); }
+    dev->stats.kernels_launched++;
+    dev->stats.gemm_launched++;
+    return done(ANL_OK);
+}
+
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream, int64_t m_begin, int64_t m_end,
-                const GemmFusion* fusion) {
+                const GemmFusion* fusion, std::vector<void*>* keep_scratch) {
     const GemmPlan& gp = *plan.gemm;
     const Contraction& c = gp.c;
     // an optional row window [m_begin, m_end) of the output: the caller splits a contraction so that
@@ -554,9 +722,13 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
         return dev->fail(ANL_ERR_INVALID, "gemm: bad row window");
     if (fusion && (window || gp.f32)) return dev->fail(ANL_ERR_INVALID, "gemm: a fused consumer needs the whole f16 contraction");
     const int64_t M = window ? m_end - m_begin : c.M;
-    if (gp.f32)
+    if (gp.f32) {
+        const int64_t Mv = c.m_sym ? sym_value : c.M, Kv = c.k_sym ? sym_value : c.K;
+        if (tf32x3_applies(dev, c, Mv, Kv))
+            return launch_gemm_tf32x3(dev, gp, (const float*)bufs[c.a_param] + c.a_off, (const float*)bufs[c.b_param] + c.b_off, (float*)bufs[0], Mv, Kv, stream, keep_scratch);
         return launch_gemm_f32(dev, (const float*)bufs[c.a_param] + c.a_off, (const float*)bufs[c.b_param] + c.b_off, (float*)bufs[0],
-                               c.m_sym ? sym_value : c.M, c.N, c.k_sym ? sym_value : c.K, c.a_sm, c.a_sk, c.b_sn, c.b_sk, stream);
+                               Mv, c.N, Kv, c.a_sm, c.a_sk, c.b_sn, c.b_sk, stream);
+    }
     if (int rc = ensure_gemm_state(dev)) return rc;
     if (*dev->gemm_status_host != 0) return dev->fail(ANL_ERR_CUDA, "gemm: an earlier launch timed out on a barrier (code " + std::to_string(*dev->gemm_status_host) + ")");
     const __half* a = (const __half*)bufs[c.a_param] + c.a_off + (window ? m_begin * c.a_sm : 0);
@@ -605,7 +777,7 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
         at[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
         at[0].value.clusterDim.x = 2; at[0].value.clusterDim.y = 1; at[0].value.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
-        void* params[4] = {&ma, &mb, &mbh, &g};
+        void* params[6] = {&ma, &mb, &mbh, &ma, &mb, &g};     // the two extra maps are read by the f32 form only
         CUresult cr = dev->drv.LaunchKernelEx(&cfg, fn, params, nullptr);
         if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return dev->fail(ANL_ERR_CUDA, std::string("gemm: pair launch: ") + (e ? e : "?")); }
         dev->stats.kernels_launched++;

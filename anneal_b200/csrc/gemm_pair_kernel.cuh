@@ -26,6 +26,17 @@
 // Every wait on an mbarrier is bounded; a wait that runs out records a code in a host-visible status
 // word, the roles of the CTA drain and the tensor memory is freed.
 //
+// f32 operands (CFG_TF32 = 1) take the same kernel in "3 x TF32" form: each operand arrives as two
+// k-contiguous f32 arrays, hi = the value rounded to TF32's 11 significant bits and lo = value - hi (exact), and
+// the tile is accumulated from three passes over K — lo·hi, hi·lo, hi·hi, smallest first — with
+// tcgen05.mma.kind::tf32, whose products of 11-bit factors are exact in the f32 accumulator.  What is
+// dropped is lo·lo (2^-22 of the product) and the bits of lo beyond TF32's reach (2^-22 of the
+// operand); the sum carries f32 accumulation like the reference's loop, in another order.  The
+// accumulator in tensor memory cuts each partial sum instead of rounding it, and that error grows with
+// the number of additions, so K is taken in chunks of chunk_kb k-blocks: the two accumulators
+// alternate between chunks instead of between tiles, and the epilogue adds each chunk's result to the
+// output in f32 round-to-nearest (the tile stays in L2 meanwhile) under the next chunk's main loop.
+//
 // The host prepends the configuration:
 //   CFG_A_MN, CFG_B_MN   1 when the operand's m / n index is the contiguous one (else k is)
 //   CFG_BNT              tile width in columns: 256 or 128
@@ -33,6 +44,7 @@
 //   CFG_GROUP_M          raster: tiles are numbered down groups of this many tile rows, so the pairs
 //                        working at the same time share few A row blocks AND few B column blocks
 //                        (0: down whole columns of tiles)
+//   CFG_TF32             1: f32 operands and output in 3 x TF32 form (no fused consumer, no column sums)
 //   CFG_EPI              1 when a fused elementwise consumer epi8_() has been prepended
 //   CFG_STREAM_STORES    1: outputs are written with the streaming hint (they are not read again by
 //                        this kernel and should not push operand tiles out of L2)
@@ -50,6 +62,8 @@ struct PairGemmArgs {
     int tiles_m, tiles_n;   // in 256-row pair tiles and BNT-column tiles
     int full_tiles;         // tile numbers below this are BNT wide; each tile from here on is drawn as two halves
                             // of BNT/2 columns, so that the last, partly filled wave of tiles costs half a tile
+    int chunk_kb;           // f32 form: k-blocks accumulated in tensor memory before the partial result is added, in f32
+                            // round-to-nearest, to what the output holds (0: all of K in one go)
     int* status;
     int* tile_counter;      // [0] next tile number, [1] pairs that have signed off; both zero between launches
 };
@@ -60,10 +74,19 @@ struct PairGemmArgs {
 
 struct alignas(64) TensorMap { unsigned long long opaque[16]; };
 
-constexpr int BM = 128, BK = 64;
+#ifndef CFG_TF32
+#define CFG_TF32 0
+#endif
+// a k-block is one 128-byte swizzle row of k: 64 f16 or 32 f32 elements
+constexpr int ESZ = CFG_TF32 ? 4 : 2;
+constexpr int BM = 128, BK = 128 / ESZ;
+constexpr int MNBOX = 64;                   // f16 elements of m (or n) in one row of an MN-major box
+constexpr int KSTEP_BYTES_MN = 16 * 128;    // one MMA's k-rows in an MN-major tile
+static_assert(!(CFG_TF32 && (CFG_A_MN || CFG_B_MN)), "the f32 form takes k-contiguous operands only: the host's split pre-pass rewrites the others");
+constexpr int PASSES = CFG_TF32 ? 3 : 1;
 constexpr int BNT = CFG_BNT, NSTAGE = CFG_STAGES;
-constexpr int A_TILE_BYTES = BM * BK * 2;
-constexpr int BHALF_BYTES = (BNT / 2) * BK * 2;
+constexpr int A_TILE_BYTES = BM * BK * ESZ;
+constexpr int BHALF_BYTES = (BNT / 2) * BK * ESZ;
 constexpr int STAGE_B = A_TILE_BYTES + BHALF_BYTES;
 constexpr int TQ = 4;
 constexpr unsigned WAIT_LIMIT = 1u << 20;
@@ -135,10 +158,17 @@ __device__ __forceinline__ unsigned long long make_desc(unsigned saddr, unsigned
     return d;
 }
 __device__ __forceinline__ void umma_f16_pair(unsigned tmem_d, unsigned long long adesc, unsigned long long bdesc, unsigned idesc, unsigned accumulate) {
+#if CFG_TF32
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::tf32 [%0], %1, %2, %3, p;\n}\n"
+        ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#else
     asm volatile(
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
         " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}\n"
         ::"r"(tmem_d), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+#endif
 }
 __device__ __forceinline__ void umma_commit_pair(unsigned cluster_bar) {
     asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_bar) : "memory");
@@ -211,7 +241,7 @@ __device__ __forceinline__ void warp_column_sums(float (&x)[32], int lane) {
 
 extern "C" __global__ void __launch_bounds__(192, 1)
 gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b, const __grid_constant__ TensorMap map_b_half,
-                      const PairGemmArgs g) {
+                      const __grid_constant__ TensorMap map_a_lo, const __grid_constant__ TensorMap map_b_lo, const PairGemmArgs g) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2];
     // tile queue: the leader's producer draws tile numbers from the global counter and publishes each
@@ -228,6 +258,8 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
     const int whole_tiles = tiles_m * g.tiles_n;
     const int num_tiles = whole_tiles + (whole_tiles - g.full_tiles);     // every tile past full_tiles counts twice
     const int kblocks = (g.K + BK - 1) / BK;
+    const int chunk_kb = (CFG_TF32 && g.chunk_kb > 0 && g.chunk_kb < kblocks) ? g.chunk_kb : kblocks;
+    const int chunks = kblocks > 0 ? (kblocks + chunk_kb - 1) / chunk_kb : 1;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
@@ -279,18 +311,25 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 const int n0 = col0 + (int)rank * (width / 2);           // this CTA's half of B
                 const unsigned stage_bytes = A_TILE_BYTES + (narrow ? BHALF_BYTES / 2 : BHALF_BYTES);
                 const TensorMap* const mb = narrow ? &map_b_half : &map_b;
-                for (int kb = 0; kb < kblocks; kb++) {
-                    if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
-                    const unsigned own_fb = smem_u32(&full_bar[stage]);
-                    const unsigned fb = map_to_cta(own_fb, 0);
-                    const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
-                    if (rank == 0) mbar_expect_tx(own_fb, 2 * stage_bytes);
-                    const int k0 = kb * BK;
-                    if (CFG_A_MN) { for (int j = 0; j < BM / 64; j++) tma_load_2d_pair(sa + j * (BK * 128), &map_a, m0 + 64 * j, k0, fb); }
-                    else tma_load_2d_pair(sa, &map_a, k0, m0, fb);
-                    if (CFG_B_MN) { for (int j = 0; j < width / 128; j++) tma_load_2d_pair(sb + j * (BK * 128), &map_b, n0 + 64 * j, k0, fb); }
-                    else tma_load_2d_pair(sb, mb, k0, n0, fb);
-                    if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
+                for (int ch = 0; ch < chunks && ok; ch++) {
+                    const int kb0 = ch * chunk_kb, nkb = (kblocks - kb0) < chunk_kb ? (kblocks - kb0) : chunk_kb;
+                    for (int it = 0; it < PASSES * nkb && ok; it++) {
+                        const int pass = it / nkb, kb = kb0 + it - pass * nkb;
+                        // 3 x TF32: pass 0 = A_lo · B_hi, pass 1 = A_hi · B_lo, pass 2 = A_hi · B_hi
+                        const TensorMap* const ma = (CFG_TF32 && pass == 0) ? &map_a_lo : &map_a;
+                        const TensorMap* const mbp = (CFG_TF32 && pass == 1) ? &map_b_lo : mb;
+                        if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
+                        const unsigned own_fb = smem_u32(&full_bar[stage]);
+                        const unsigned fb = map_to_cta(own_fb, 0);
+                        const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
+                        if (rank == 0) mbar_expect_tx(own_fb, 2 * stage_bytes);
+                        const int k0 = kb * BK;
+                        if (CFG_A_MN) { for (int j = 0; j < BM / MNBOX; j++) tma_load_2d_pair(sa + j * (BK * 128), ma, m0 + MNBOX * j, k0, fb); }
+                        else tma_load_2d_pair(sa, ma, k0, m0, fb);
+                        if (CFG_B_MN) { for (int j = 0; j < (width / 2) / MNBOX; j++) tma_load_2d_pair(sb + j * (BK * 128), mbp, n0 + MNBOX * j, k0, fb); }
+                        else tma_load_2d_pair(sb, mbp, k0, n0, fb);
+                        if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
+                    }
                 }
             }
             if (!ok) failed = 1;
@@ -299,7 +338,9 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
         // ── MMA issuer (leader CTA only) ──
         if (lane == 0 && rank == 0) {
             // instruction descriptor: f32 accumulate, f16 x f16, majors, N >> 3 at bit 17, M >> 4 at bit 24 (256 across the pair)
-            const unsigned idesc_base = (1u << 4) | ((CFG_A_MN ? 1u : 0u) << 15) | ((CFG_B_MN ? 1u : 0u) << 16) | ((unsigned)((2 * BM) >> 4) << 24);
+            // bits [4,6) accumulator f32; [7,10) and [10,13) operand formats (0 f16, 2 tf32); 15/16 majors
+            const unsigned idesc_base = (1u << 4) | ((CFG_TF32 ? 2u : 0u) << 7) | ((CFG_TF32 ? 2u : 0u) << 10) |
+                                        ((CFG_A_MN ? 1u : 0u) << 15) | ((CFG_B_MN ? 1u : 0u) << 16) | ((unsigned)((2 * BM) >> 4) << 24);
             unsigned stage = 0, phase = 0, acc = 0, acc_phase = 0;
             bool ok = true;
             unsigned qs = 0, qphase = 0;
@@ -310,31 +351,36 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
                 if (t < 0) break;
                 const unsigned idesc = idesc_base | ((unsigned)((t < g.full_tiles ? BNT : BNT / 2) >> 3) << 17);
-                if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
-                asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                const unsigned tmem_d = tmem_base + acc * BNT;
-                for (int kb = 0; kb < kblocks; kb++) {
-                    if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 13; break; }
+                for (int ch = 0; ch < chunks && ok; ch++) {
+                    const int nkb = (kblocks - ch * chunk_kb) < chunk_kb ? (kblocks - ch * chunk_kb) : chunk_kb;
+                    if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
-                    const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
+                    const unsigned tmem_d = tmem_base + acc * BNT;
+                    for (int kb = 0; kb < PASSES * nkb; kb++) {
+                        if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 13; break; }
+                        asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+                        const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
 #pragma unroll
-                    for (int k = 0; k < BK / 16; k++) {
-                        // K-major: 16 k-elements = 32 bytes inside the 128-byte row, 8-row groups 1 KiB apart.
-                        // MN-major: 16 k-rows = two 1 KiB atoms, 64-wide m/n groups one box (BK*128 B) apart.
-                        const unsigned long long ad = CFG_A_MN ? make_desc(sa + k * 2048, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
-                        const unsigned long long bd = CFG_B_MN ? make_desc(sb + k * 2048, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
-                        umma_f16_pair(tmem_d, ad, bd, idesc, (kb | k) != 0);
+                        for (int k = 0; k < 4; k++) {
+                            // One MMA covers 32 bytes of k (16 f16 or 8 tf32 elements): four per k-block.
+                            // K-major: 32 bytes inside the 128-byte row, 8-row groups 1 KiB apart.
+                            // MN-major: the MMA's k-rows are whole 128-byte rows (KSTEP_BYTES_MN of them per
+                            // step), m/n groups of one swizzle row's width one box (BK*128 B) apart.
+                            const unsigned long long ad = CFG_A_MN ? make_desc(sa + k * KSTEP_BYTES_MN, BK * 128, 1024) : make_desc(sa + k * 32, 16, 1024);
+                            const unsigned long long bd = CFG_B_MN ? make_desc(sb + k * KSTEP_BYTES_MN, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
+                            umma_f16_pair(tmem_d, ad, bd, idesc, (kb | k) != 0);
+                        }
+                        const unsigned eb = smem_u32(&empty_bar[stage]);
+                        umma_commit_pair(map_to_cta(eb, 0));       // frees the stage here ...
+                        umma_commit_pair(map_to_cta(eb, 1));       // ... and in the partner CTA
+                        if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
                     }
-                    const unsigned eb = smem_u32(&empty_bar[stage]);
-                    umma_commit_pair(map_to_cta(eb, 0));       // frees the stage here ...
-                    umma_commit_pair(map_to_cta(eb, 1));       // ... and in the partner CTA
-                    if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
+                    if (!ok) break;
+                    const unsigned af = smem_u32(&acc_full[acc]);
+                    umma_commit_pair(map_to_cta(af, 0));
+                    umma_commit_pair(map_to_cta(af, 1));
+                    if (++acc == 2) { acc = 0; acc_phase ^= 1; }
                 }
-                if (!ok) break;
-                const unsigned af = smem_u32(&acc_full[acc]);
-                umma_commit_pair(map_to_cta(af, 0));
-                umma_commit_pair(map_to_cta(af, 1));
-                if (++acc == 2) { acc = 0; acc_phase ^= 1; }
             }
             if (!ok) failed = 1;
         }
@@ -344,7 +390,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
         unsigned acc = 0, acc_phase = 0;
         bool ok = true;
         unsigned qs = 0, qphase = 0;
-        __half* const d_raw = (__half*)g.d_raw;
+        __half* const d_raw = (__half*)g.d_raw; (void)d_raw;
 #if CFG_EPI
         __half* const d_out = (__half*)g.d_out;
 #endif
@@ -358,12 +404,13 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
             int tm, n0, width;
             tile_of(t, tiles_m, g.tiles_n, g.full_tiles, tm, n0, width);
             const int m0 = tm * (2 * BM) + (int)rank * BM;
-            if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
-            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
             const int row = m0 + quad * 32 + lane;
             const size_t row_off = (size_t)row * g.ldd;
             const bool row_ok = row < g.M;
-            const bool vec_ok = (g.ldd % 8 == 0);
+            const bool vec_ok = (g.ldd % 8 == 0); (void)vec_ok;
+            for (int ch = 0; ch < chunks; ch++) {
+            if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
+            asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
             for (int c = 0; c < width / 32; c++) {
                 unsigned v[32];
@@ -371,6 +418,24 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int col = n0 + c * 32;
                 if (col >= g.N) continue;                  // warp-uniform
+#if CFG_TF32
+                // f32 result of this chunk of k: stored, or added to the sum of the chunks before it
+                if (row_ok) {
+                    float* out = reinterpret_cast<float*>(g.d_raw) + row_off + col;
+                    if ((g.ldd & 3) == 0 && col + 32 <= g.N) {
+#pragma unroll
+                        for (int q = 0; q < 8; q++) {
+                            float4 r = make_float4(__uint_as_float(v[4 * q]), __uint_as_float(v[4 * q + 1]), __uint_as_float(v[4 * q + 2]), __uint_as_float(v[4 * q + 3]));
+                            if ((ch > 0)) { const float4 o = *reinterpret_cast<const float4*>(out + 4 * q); r.x = o.x + r.x; r.y = o.y + r.y; r.z = o.z + r.z; r.w = o.w + r.w; }
+                            *reinterpret_cast<float4*>(out + 4 * q) = r;
+                        }
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 32; j++)
+                            if (col + j < g.N) out[j] = (ch > 0) ? out[j] + __uint_as_float(v[j]) : __uint_as_float(v[j]);
+                    }
+                }
+#else
                 // the single narrowing of the f32 accumulator
                 __half2 h[16];
 #pragma unroll
@@ -418,11 +483,13 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                         if (col + 2 * j + 1 < g.N) d_raw[row_off + col + 2 * j + 1] = __high2half(h[j]);
                     }
                 }
+#endif
             }
             asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&acc_empty[acc]), 0));   // the leader waits for both CTAs' epilogues
             if (++acc == 2) { acc = 0; acc_phase ^= 1; }
+            }
         }
     }
     asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory");

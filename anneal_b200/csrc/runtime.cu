@@ -326,7 +326,7 @@ int launch_plan(anl_device* dev, const Plan& plan, const Item& item, void* const
 
 static int launch_plan_inner(anl_device* dev, const Plan& plan, const Item& item, void* const* bufs, int64_t sym_value, cudaStream_t stream,
                              std::vector<void*>* keep_scratch) {
-    if (gemm_taken(plan, sym_value)) return launch_gemm(dev, plan, bufs, sym_value, stream);
+    if (gemm_taken(plan, sym_value)) return launch_gemm(dev, plan, bufs, sym_value, stream, 0, -1, nullptr, keep_scratch);
     int nb = (int)item.bufs.size();
     std::vector<void*> ptrs(bufs, bufs + nb);
     int n0 = (int)sym_value;
@@ -1092,8 +1092,17 @@ static int lower_gemm_impl(anl_device* dev, const uint8_t* blob, size_t blob_len
     if (!parse_kir(blob, blob_len, items, err)) { say(err); return ANL_ERR_INVALID; }
     if (index < 0 || index >= (int)items.size()) { say("lower_gemm: item index out of range"); return ANL_ERR_INVALID; }
     Plan p;
-    if (plan_gemm(items[index], tuning_of(opts_from(o, 0)), p) != ANL_OK || !gemm_pair_eligible(p)) { say("lower_gemm: the item does not run on the two-CTA contraction kernel"); return ANL_ERR_UNSUPPORTED; }
+    if (plan_gemm(items[index], tuning_of(opts_from(o, 0)), p) != ANL_OK || !(gemm_pair_eligible(p) || gemm_tf32_eligible(p))) { say("lower_gemm: the item does not run on the two-CTA contraction kernel"); return ANL_ERR_UNSUPPORTED; }
     std::string epilogue, what = p.r.note;
+    if (gemm_tf32_eligible(p)) {
+        if (fuse_next) { say("lower_gemm: the f32 form of the kernel takes no fused consumer"); return ANL_ERR_UNSUPPORTED; }
+        std::string out;
+        if (int rc = gemm_tf32_source(p, out, what)) return rc;
+        if (src && src_cap) { size_t n = std::min(src_cap - 1, out.size()); std::memcpy(src, out.data(), n); src[n] = 0; }
+        if (src_len) *src_len = out.size();
+        if (note && note_cap) std::snprintf(note, note_cap, "%s", what.c_str());
+        return ANL_OK;
+    }
     if (fuse_next) {
         if (index + 1 >= (int)items.size()) { say("lower_gemm: no next item to fuse"); return ANL_ERR_UNSUPPORTED; }
         int64_t M, N, K; gemm_shape(p, &M, &N, &K);

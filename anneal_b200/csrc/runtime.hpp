@@ -171,9 +171,11 @@ int download_f32(anl_device* dev, float* host, const void* src, int dtype, int64
 // dense SUM-of-products over buffers that they cover, ANL_ERR_UNSUPPORTED otherwise
 int plan_gemm(const Item& item, const GemmTuning& tune, Plan& plan);
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream,
-                int64_t m_begin = 0, int64_t m_end = -1, const GemmFusion* fusion = nullptr);
+                int64_t m_begin = 0, int64_t m_end = -1, const GemmFusion* fusion = nullptr, std::vector<void*>* keep_scratch = nullptr);
 // true when the plan runs on the two-CTA kernel, the one that can carry a fused consumer
 bool gemm_pair_eligible(const Plan& plan);
+bool gemm_tf32_eligible(const Plan& plan);
+int gemm_tf32_source(const Plan& plan, std::string& out, std::string& note);
 void gemm_shape(const Plan& plan, int64_t* M, int64_t* N, int64_t* K);
 // compiles the kernel variant a launch of this plan (with this epilogue text) will use
 int gemm_prepare(anl_device* dev, const Plan& plan, const std::string& epilogue);

@@ -322,6 +322,7 @@ class Device:
     NO_ROW_CHAIN = 8
     TAIL_SPLIT = 16
     NO_EPILOGUE_FUSION = 32
+    NO_TF32X3 = 64
 
     def __init__(self, ordinal: Optional[int] = None, flags: int = 0):
         self.L = load_library()

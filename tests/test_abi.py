@@ -246,3 +246,29 @@ def test_contraction_kernel_sources_compile_with_and_without_a_fused_consumer(li
     for line in ("#define CFG_BNT 128", "#define CFG_STAGES 4", "#define CFG_GROUP_M 0", "#define CFG_STREAM_STORES 1"):
         assert line in tuned
     device.compile_check(tuned)
+
+
+def test_f32_contraction_kernel_sources_compile_in_3xtf32_form(lib):
+    """Large f32 contractions take the two-CTA kernel with f32 operands split into TF32 halves (the split
+    pre-pass hands every operand layout over k-contiguous); the source must get through NVRTC for
+    sm_100a on a box without a GPU."""
+    from anneal_b200.tensor import Tensor
+    from anneal_b200.uop import dtypes
+    seen = set()
+    for layout in ("KK", "KM", "MK", "MM"):
+        R.reset()
+        M, N, K = 2048, 1024, 1024
+        a = Tensor.new_leaf((M, K), dtypes.float32) if layout[0] == "K" else Tensor.new_leaf((K, M), dtypes.float32).permute((1, 0))
+        b = Tensor.new_leaf((N, K), dtypes.float32).permute((1, 0)) if layout[1] == "K" else Tensor.new_leaf((K, N), dtypes.float32)
+        items, _ = R.build_schedule([a.matmul(b)])
+        r = device.lower_gemm(items, 0)
+        assert "3xTF32" in r["note"] and "#define CFG_TF32 1" in r["source"] and "kind::tf32" in r["source"]
+        assert "#define CFG_A_MN 0" in r["source"] and "#define CFG_B_MN 0" in r["source"]
+        seen.add(r["note"].split(" M=")[0])
+        device.compile_check(r["source"])
+    assert len(seen) == 4, seen
+    # a small one stays on the FP32 pipes
+    R.reset()
+    items, _ = R.build_schedule([Tensor.new_leaf((512, 640), dtypes.float32).matmul(Tensor.new_leaf((640, 136), dtypes.float32))])
+    with pytest.raises(device.DeviceError):
+        device.lower_gemm(items, 0)

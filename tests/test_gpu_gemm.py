@@ -107,3 +107,47 @@ def test_gemm_f32_symbolic_batch(cuda, oracle, b, gemms):
         assert rel_err(got[k], want[k]) <= 2e-5, (b, k)
     assert rel_err(got[dw1].reshape(1024, 512)[steady], want[dw1].reshape(1024, 512)[steady]) <= 2e-5
     assert rel_err(got[db1][steady], want[db1][steady]) <= 2e-5
+
+
+# ── large f32 contractions: the tensor-core kernel in 3 x TF32 form ──────────────────────────────
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (2100, 1000, 1031), (515, 1000, 20001)])
+@pytest.mark.parametrize("layout", ["KK", "KM", "MM", "MK"])
+def test_gemm_f32_on_tensor_cores(cuda, M, N, K, layout):
+    """Against float64 on a sample of rows: the split into TF32 halves plus chunked f32 accumulation
+    must be as close to the exact product as the FP32-pipe kernel (which the same device runs when it
+    is opened with NO_TF32X3), within a factor of 3 and within 5e-6 of the largest output, at every
+    operand layout, ragged edges and a K of many chunks."""
+    from anneal_b200 import realize as R
+    from anneal_b200.device import Device
+    R.reset()
+    a = fleaf((M, K), 1) if layout[0] == "K" else fleaf((K, M), 1).permute((1, 0))
+    b = fleaf((N, K), 2).permute((1, 0)) if layout[1] == "K" else fleaf((K, N), 2)
+    out = a.matmul(b)
+    items, out_ids, inputs = schedule([out])
+    before = cuda.stats()
+    y = cuda.run(items, inputs)[out_ids[0]].reshape(M, N)
+    after = cuda.stats()
+    assert after["gemm_launched"] - before["gemm_launched"] == 1
+    assert after["kernels_launched"] - before["kernels_launched"] == 3      # two operand splits and the contraction
+    la = [v for k, v in inputs.items() if v.size == M * K][0]
+    lb = [v for k, v in inputs.items() if v.size == N * K and v is not la][0]
+    am = la.reshape(M, K) if layout[0] == "K" else la.reshape(K, M).T
+    bm = lb.reshape(N, K) if layout[1] == "K" else lb.reshape(K, N).T
+    rows = np.random.default_rng(5).choice(M, size=48, replace=False)
+    rows[0], rows[1] = 0, M - 1
+    ref = am[rows].astype(np.float64) @ bm.astype(np.float64).T
+    scale = np.abs(ref).max()
+    err = np.abs(y[rows] - ref).max() / scale
+    plain = Device(0, flags=Device.NO_TF32X3)
+    try:
+        g0 = plain.stats()["kernels_launched"]
+        y32 = plain.run(items, inputs)[out_ids[0]].reshape(M, N)
+        assert plain.stats()["kernels_launched"] - g0 == 1
+    finally:
+        plain.close()
+    err32 = np.abs(y32[rows] - ref).max() / scale
+    assert err <= 5e-6 and err <= 3 * err32 + 1e-7, (err, err32)
+    # the two routes agree everywhere, not only on the sampled rows
+    assert np.abs(y - y32).max() / scale <= 1e-5
+    # and a replay gives the same bits
+    assert np.array_equal(cuda.run(items, inputs)[out_ids[0]].reshape(M, N), y)
