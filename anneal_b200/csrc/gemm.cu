@@ -606,16 +606,30 @@ __global__ void __launch_bounds__(256) split_tf32_transposed(const float* __rest
     }
 }
 
-// Large f32 contractions take the two-CTA tensor-core kernel in 3 x TF32 form unless the device was
-// opened with ANL_OPEN_NO_TF32X3: at least one full pair tile, a k extent worth a pipeline, and
-// operands contiguous along k or along their row index.
-static bool tf32x3_shape_ok(const Contraction& c, int64_t M, int64_t K) {
-    if (M < 2 * BM || c.N < BN / 2 || K < 128) return false;
-    if ((double)M * (double)c.N * (double)K < 2.0e9) return false;
-    if (M >= (1ll << 31) || c.N >= (1ll << 31) || K >= (1ll << 31)) return false;
-    if (!(c.a_sk == 1 || c.a_sm == 1) || !(c.b_sk == 1 || c.b_sn == 1)) return false;
-    return true;
+// out[i] = copies[0][i] + copies[1][i] + ... in that order: finishes a contraction whose K was split
+// between draws of the same tile.
+__global__ void __launch_bounds__(256) sum_split_copies(const float* __restrict__ copies, long long stride, int n_copies, long long n, float* __restrict__ out) {
+    const long long i = ((long long)blockIdx.x * blockDim.x + threadIdx.x) * 4;
+    if (i >= n) return;
+    if (i + 3 < n && (stride & 3) == 0) {
+        float4 v = *reinterpret_cast<const float4*>(copies + i);
+        for (int c = 1; c < n_copies; c++) {
+            const float4 w = *reinterpret_cast<const float4*>(copies + c * stride + i);
+            v.x += w.x; v.y += w.y; v.z += w.z; v.w += w.w;
+        }
+        *reinterpret_cast<float4*>(out + i) = v;
+    } else {
+        for (long long j = i; j < n && j < i + 4; j++) {
+            float v = copies[j];
+            for (int c = 1; c < n_copies; c++) v += copies[c * stride + j];
+            out[j] = v;
+        }
+    }
 }
+
+// f32 contractions of more than a few rows take the two-CTA tensor-core kernel in 3 x TF32 form unless
+// the device was opened with ANL_OPEN_NO_TF32X3: operands contiguous along k or along their row index.
+static bool tf32x3_shape_ok(const Contraction& c, int64_t M, int64_t K) { return gemm_tf32_shape_ok(M, c.N, K, c.a_sm, c.a_sk, c.b_sn, c.b_sk); }
 static bool tf32x3_applies(anl_device* dev, const Contraction& c, int64_t M, int64_t K) {
     return !(dev->flags & ANL_OPEN_NO_TF32X3) && tf32x3_shape_ok(c, M, K);
 }
@@ -703,12 +717,38 @@ static int launch_gemm_tf32x3(anl_device* dev, const GemmPlan& gp, const float* 
     cfg.attrs = at; cfg.numAttrs = 1;
     g.K = (int)K;
     g.chunk_kb = kTf32ChunkK / BK32;
+    // few tiles and a long K: draw every tile several times, each draw a slice of K into its own copy
+    // of the output (at least 8 k-blocks a slice), and add the copies afterwards in order
+    const int kblocks = (int)((K + BK32 - 1) / BK32);
+    int splits = std::min(npairs / std::max(1, g.full_tiles), kblocks / 8);
+    void* copies = nullptr;
+    if (splits > 1) {
+        g.kb_per_split = (kblocks + splits - 1) / splits;
+        splits = (kblocks + g.kb_per_split - 1) / g.kb_per_split;
+    }
+    if (splits > 1) {
+        g.k_splits = splits;
+        g.split_stride = (long long)(((M * N) + 3) & ~3ll);
+        if ((rc = dev->alloc((size_t)splits * (size_t)g.split_stride * 4, &copies))) return done(rc);
+        g.d_raw = copies;
+        cfg.gridDimX = 2 * std::min(g.full_tiles * splits, npairs);
+    }
+    auto done2 = [&](int code) {
+        if (copies) { if (keep_scratch) keep_scratch->push_back(copies); else dev->release(copies); }
+        return done(code);
+    };
     void* params[6] = {&ma_hi, &mb_hi, &mb_hi, &ma_lo, &mb_lo, &g};
     CUresult cr = dev->drv.LaunchKernelEx(&cfg, fn, params, nullptr);
-    if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return done(dev->fail(ANL_ERR_CUDA, std::string("gemm: tf32 pair launch: ") + (e ? e : "?"))); }
+    if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return done2(dev->fail(ANL_ERR_CUDA, std::string("gemm: tf32 pair launch: ") + (e ? e : "?"))); }
     dev->stats.kernels_launched++;
+    if (splits > 1) {
+        const long long n = (long long)M * N;
+        sum_split_copies<<<(unsigned)((n + 1023) / 1024), 256, 0, stream>>>((const float*)copies, g.split_stride, splits, n, d);
+        if (cudaGetLastError() != cudaSuccess) return done2(dev->fail(ANL_ERR_CUDA, "gemm: split sum launch failed"));
+        dev->stats.kernels_launched++;
+    }
     dev->stats.gemm_launched++;
-    return done(ANL_OK);
+    return done2(ANL_OK);
 }
 
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream, int64_t m_begin, int64_t m_end,

@@ -16,6 +16,7 @@
 #include <string>
 
 #include "runtime.hpp"
+#include <cooperative_groups.h>
 
 namespace anl {
 
@@ -189,94 +190,192 @@ __global__ void __launch_bounds__(F_THREADS, ANL_F32_MINBLOCKS) gemm_f32_simt(co
 // matrix once per ROW; these kernels read it once per group of up to 16 rows, which is what the
 // bytes cost.  All accumulate in f32 with fused multiply-add; the order of the additions differs
 // from the reference's serial loop where lanes or warps share one sum (tolerance: 1e-4 relative).
-constexpr int S_MR = 16;          // rows per pass
-constexpr int S_KC = 256;         // k chunk staged in shared memory
+constexpr int S_MR = 16;          // most rows one pass of the k-contiguous form takes
+constexpr int S_MR_AXPY = 8;      // and of the n-contiguous form
 
-// D[m, n] = sum_k A[m, k] * B[n, k], both k-contiguous (a forward layer x · Wᵀ): one warp per output
-// column, the 16 rows of A staged chunk by chunk in shared memory and shared by the block's 8 warps.
+// D[m, n] = sum_k A[m, k] * B[n, k], both k-contiguous (a forward layer x · Wᵀ): a warp owns CW output
+// columns, its lanes split k in 16-byte pieces; MR rows of A are staged in shared memory (16 KB:
+// 4096 / MR floats of each row per pass) and shared by the block's 8 warps, so one pass over the
+// weights serves MR rows.  With few column blocks the launch is a cluster of `splits` CTAs per block
+// of columns, each taking a slice of k; the slices' sums are added in rank order by the first CTA
+// through distributed shared memory (a fixed order: the same bits every launch).
+template <int MR, int CW>
 __global__ void __launch_bounds__(256) gemm_f32_few_rows_dot(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ d,
-                                                              int M, int N, int K, long long a_sm, long long b_sn, int ldd) {
-    __shared__ float As[S_MR][S_KC];
+                                                              int M, int N, int K, long long a_sm, long long b_sn, int ldd, int vec, int splits) {
+    namespace cg = cooperative_groups;
+    constexpr int KC = 4096 / MR;
+    __shared__ __align__(16) float As[MR][KC];
+    __shared__ float mine[MR][8 * CW];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n = blockIdx.x * 8 + warp, m0 = blockIdx.y * S_MR;
-    float acc[S_MR];
+    const int rank = splits > 1 ? (int)cg::this_cluster().block_rank() : 0;
+    const int nb = ((int)blockIdx.x / splits) * (8 * CW), n0 = nb + warp * CW, m0 = blockIdx.y * MR;
+    const int slice = (((K + splits - 1) / splits) + 127) & ~127;
+    const int ks0 = rank * slice, ks1 = (ks0 + slice) < K ? (ks0 + slice) : K;
+    float acc[MR][CW];
 #pragma unroll
-    for (int m = 0; m < S_MR; m++) acc[m] = 0.0f;
-    const float* brow = b + (long long)(n < N ? n : N - 1) * b_sn;
-    for (int k0 = 0; k0 < K; k0 += S_KC) {
-        for (int i = threadIdx.x; i < S_MR * S_KC; i += 256) {
-            const int m = i / S_KC, k = i % S_KC;
-            As[m][k] = (m0 + m < M && k0 + k < K) ? a[(long long)(m0 + m) * a_sm + k0 + k] : 0.0f;
+    for (int m = 0; m < MR; m++)
+#pragma unroll
+        for (int c = 0; c < CW; c++) acc[m][c] = 0.0f;
+    const float* brow[CW];
+#pragma unroll
+    for (int c = 0; c < CW; c++) brow[c] = b + (long long)(n0 + c < N ? n0 + c : N - 1) * b_sn;
+    for (int k0 = ks0; k0 < ks1; k0 += KC) {
+        const int kc = (ks1 - k0) < KC ? (ks1 - k0) : KC;
+        const int kc4 = (kc + 3) & ~3;
+        for (int i = threadIdx.x; i < MR * kc4; i += 256) {
+            const int m = i / kc4, k = i - m * kc4;
+            As[m][k] = (m0 + m < M && k < kc) ? a[(long long)(m0 + m) * a_sm + k0 + k] : 0.0f;
         }
         __syncthreads();
+        if (vec) {
+            constexpr int U = CW >= 4 ? 1 : (CW == 2 ? 2 : 4);      // 16-byte loads in flight per lane: U * CW
+            for (int kk = lane * 4; kk < kc; kk += 128 * U) {
+                float4 bv[U][CW];
 #pragma unroll
-        for (int half = 0; half < S_KC / 128; half++) {
-            const int kk = half * 128 + lane * 4;
-            float bv[4];
+                for (int u = 0; u < U; u++)
 #pragma unroll
-            for (int j = 0; j < 4; j++) bv[j] = (k0 + kk + j < K) ? brow[k0 + kk + j] : 0.0f;
+                    for (int c = 0; c < CW; c++)
+                        bv[u][c] = (kk + u * 128 < kc) ? __ldg(reinterpret_cast<const float4*>(brow[c] + k0 + kk + u * 128)) : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
-            for (int m = 0; m < S_MR; m++) {
-                const float4 av = *reinterpret_cast<const float4*>(&As[m][kk]);
-                acc[m] = fmaf(av.x, bv[0], acc[m]); acc[m] = fmaf(av.y, bv[1], acc[m]);
-                acc[m] = fmaf(av.z, bv[2], acc[m]); acc[m] = fmaf(av.w, bv[3], acc[m]);
+                for (int u = 0; u < U; u++) {
+                    if (kk + u * 128 >= kc) break;
+#pragma unroll
+                    for (int m = 0; m < MR; m++) {
+                        const float4 av = *reinterpret_cast<const float4*>(&As[m][kk + u * 128]);
+#pragma unroll
+                        for (int c = 0; c < CW; c++) {
+                            acc[m][c] = fmaf(av.x, bv[u][c].x, acc[m][c]); acc[m][c] = fmaf(av.y, bv[u][c].y, acc[m][c]);
+                            acc[m][c] = fmaf(av.z, bv[u][c].z, acc[m][c]); acc[m][c] = fmaf(av.w, bv[u][c].w, acc[m][c]);
+                        }
+                    }
+                }
+            }
+        } else {
+            for (int kk = lane; kk < kc; kk += 32) {
+                float bv[CW];
+#pragma unroll
+                for (int c = 0; c < CW; c++) bv[c] = brow[c][k0 + kk];
+#pragma unroll
+                for (int m = 0; m < MR; m++)
+#pragma unroll
+                    for (int c = 0; c < CW; c++) acc[m][c] = fmaf(As[m][kk], bv[c], acc[m][c]);
             }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int m = 0; m < S_MR; m++) {
-        float v = acc[m];
+    for (int m = 0; m < MR; m++)
 #pragma unroll
-        for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
-        if (lane == 0 && n < N && m0 + m < M) d[(long long)(m0 + m) * ldd + n] = v;
+        for (int c = 0; c < CW; c++) {
+            float v = acc[m][c];
+#pragma unroll
+            for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+            if (lane == 0) {
+                if (splits > 1) mine[m][warp * CW + c] = v;
+                else if (n0 + c < N && m0 + m < M) d[(long long)(m0 + m) * ldd + n0 + c] = v;
+            }
+        }
+    if (splits > 1) {
+        cg::cluster_group cluster = cg::this_cluster();
+        cluster.sync();
+        if (rank == 0) {
+            for (int i = threadIdx.x; i < MR * 8 * CW; i += 256) {
+                const int m = i / (8 * CW), c = i - m * (8 * CW);
+                float v = 0.0f;
+                for (int r = 0; r < splits; r++) v += cluster.map_shared_rank(&mine[0][0], r)[i];
+                if (m0 + m < M && nb + c < N) d[(long long)(m0 + m) * ldd + nb + c] = v;
+            }
+        }
+        cluster.sync();           // the other CTAs' shared memory stays until the first has read it
     }
 }
 
 // D[m, n] = sum_k A[m, k] * B[k, n]: A k-contiguous, B n-contiguous (an input gradient dY · W).
-// A block owns 64 columns; its 8 warps take every 8th k, each lane two columns, and the warps'
-// partial sums are added in warp order through shared memory.
+// A cluster of 8 CTAs owns 128 columns and splits k eight ways, so that a matrix of a few thousand
+// columns still spreads over every SM; inside a CTA the 8 warps take every 8th k of the slice, each
+// lane four columns.  The warps' partial sums are added in warp order through shared memory, the
+// CTAs' in rank order through distributed shared memory by the cluster's first CTA: a fixed order,
+// the same bits every launch.
 constexpr int S_KA = 128;         // k chunk of the n-contiguous form
-__global__ void __launch_bounds__(256) gemm_f32_few_rows_axpy(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ d,
-                                                               int M, int N, int K, long long a_sm, long long b_sk, int ldd) {
-    __shared__ float As[S_MR][S_KA];
-    __shared__ float part[8][S_MR][64 + 1];
+constexpr int S_KSPLIT = 8;
+template <int MR>
+__global__ void __cluster_dims__(S_KSPLIT, 1, 1) __launch_bounds__(256)
+gemm_f32_few_rows_axpy(const float* __restrict__ a, const float* __restrict__ b, float* __restrict__ d,
+                       int M, int N, int K, long long a_sm, long long b_sk, int ldd, int vec) {
+    namespace cg = cooperative_groups;
+    cg::cluster_group cluster = cg::this_cluster();
+    __shared__ float As[MR][S_KA];
+    __shared__ __align__(16) float part[8][MR][128];
+    __shared__ __align__(16) float mine[MR][128];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int n0 = blockIdx.x * 64, m0 = blockIdx.y * S_MR;
-    const int c0 = n0 + lane * 2;
-    const bool c_ok0 = c0 < N, c_ok1 = c0 + 1 < N;
-    float acc[S_MR][2];
+    const int rank = (int)cluster.block_rank();
+    const int n0 = (blockIdx.x / S_KSPLIT) * 128, m0 = blockIdx.y * MR;
+    const int c0 = n0 + lane * 4;
+    const int slice = (((K + S_KSPLIT - 1) / S_KSPLIT) + 7) & ~7;
+    const int ks0 = rank * slice, ks1 = (ks0 + slice) < K ? (ks0 + slice) : K;
+    float acc[MR][4];
 #pragma unroll
-    for (int m = 0; m < S_MR; m++) acc[m][0] = acc[m][1] = 0.0f;
-    for (int k0 = 0; k0 < K; k0 += S_KA) {
-        for (int i = threadIdx.x; i < S_MR * S_KA; i += 256) {
+    for (int m = 0; m < MR; m++) acc[m][0] = acc[m][1] = acc[m][2] = acc[m][3] = 0.0f;
+    for (int k0 = ks0; k0 < ks1; k0 += S_KA) {
+        const int kend = (ks1 - k0) < S_KA ? (ks1 - k0) : S_KA;
+        for (int i = threadIdx.x; i < MR * S_KA; i += 256) {
             const int m = i / S_KA, k = i % S_KA;
-            As[m][k] = (m0 + m < M && k0 + k < K) ? a[(long long)(m0 + m) * a_sm + k0 + k] : 0.0f;
+            As[m][k] = (m0 + m < M && k < kend) ? a[(long long)(m0 + m) * a_sm + k0 + k] : 0.0f;
         }
         __syncthreads();
-        const int kend = (K - k0) < S_KA ? (K - k0) : S_KA;
-        for (int k = warp; k < kend; k += 8) {
-            const float* brow = b + (long long)(k0 + k) * b_sk;
-            const float b0 = c_ok0 ? brow[c0] : 0.0f, b1 = c_ok1 ? brow[c0 + 1] : 0.0f;
+        for (int k = warp; k < kend; k += 32) {
+            // four rows of B in flight per lane
+            float4 bv[4];
 #pragma unroll
-            for (int m = 0; m < S_MR; m++) {
-                const float av = As[m][k];
-                acc[m][0] = fmaf(av, b0, acc[m][0]);
-                acc[m][1] = fmaf(av, b1, acc[m][1]);
+            for (int u = 0; u < 4; u++) {
+                const int kr = k + u * 8;
+                bv[u] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                if (kr < kend) {
+                    const float* brow = b + (long long)(k0 + kr) * b_sk + c0;
+                    if (vec) { if (c0 < N) bv[u] = __ldg(reinterpret_cast<const float4*>(brow)); }
+                    else {
+                        if (c0 < N) bv[u].x = brow[0];
+                        if (c0 + 1 < N) bv[u].y = brow[1];
+                        if (c0 + 2 < N) bv[u].z = brow[2];
+                        if (c0 + 3 < N) bv[u].w = brow[3];
+                    }
+                }
+            }
+#pragma unroll
+            for (int u = 0; u < 4; u++) {
+                const int kr = k + u * 8;
+                if (kr >= kend) break;
+#pragma unroll
+                for (int m = 0; m < MR; m++) {
+                    const float av = As[m][kr];
+                    acc[m][0] = fmaf(av, bv[u].x, acc[m][0]); acc[m][1] = fmaf(av, bv[u].y, acc[m][1]);
+                    acc[m][2] = fmaf(av, bv[u].z, acc[m][2]); acc[m][3] = fmaf(av, bv[u].w, acc[m][3]);
+                }
             }
         }
         __syncthreads();
     }
 #pragma unroll
-    for (int m = 0; m < S_MR; m++) { part[warp][m][lane * 2] = acc[m][0]; part[warp][m][lane * 2 + 1] = acc[m][1]; }
+    for (int m = 0; m < MR; m++) *reinterpret_cast<float4*>(&part[warp][m][lane * 4]) = make_float4(acc[m][0], acc[m][1], acc[m][2], acc[m][3]);
     __syncthreads();
-    for (int i = threadIdx.x; i < S_MR * 64; i += 256) {
-        const int m = i / 64, c = i % 64;
+    for (int i = threadIdx.x; i < MR * 128; i += 256) {
+        const int m = i >> 7, c = i & 127;
         float v = 0.0f;
 #pragma unroll
         for (int w = 0; w < 8; w++) v += part[w][m][c];
-        if (m0 + m < M && n0 + c < N) d[(long long)(m0 + m) * ldd + n0 + c] = v;
+        mine[m][c] = v;
     }
+    cluster.sync();
+    if (rank == 0) {
+        for (int i = threadIdx.x; i < MR * 128; i += 256) {
+            const int m = i >> 7, c = i & 127;
+            float v = 0.0f;
+#pragma unroll
+            for (int r = 0; r < S_KSPLIT; r++) v += cluster.map_shared_rank(&mine[0][0], r)[m * 128 + c];
+            if (m0 + m < M && n0 + c < N) d[(long long)(m0 + m) * ldd + n0 + c] = v;
+        }
+    }
+    cluster.sync();               // the other CTAs' shared memory stays until the first has read it
 }
 
 // D[m, n] = sum_k A[k, m] * B[k, n] with few terms (a weight gradient at a small batch): every thread
@@ -320,19 +419,57 @@ static F32Route f32_route(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t
     if (M > 2 * S_MR && tiles >= 16 && K >= 64 && tiles < (1ll << 31)) return F32_TILED;
     return F32_NONE;
 }
+// f32 contractions of more than a few rows are worth the tensor cores in 3 x TF32 form (gemm.cu):
+// below 33 rows the few-row kernels above read the other operand once and are bound by that; from
+// there on even a mostly empty 256-row tile beats the FP32 pipes.  Operands must be contiguous along
+// k or along their row index.
+bool gemm_tf32_shape_ok(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk) {
+    if (M <= 2 * S_MR || N < 128 || K < 64) return false;
+    if (K <= 64 && a_sm == 1 && b_sn == 1) return false;       // the few-terms kernel: bound by writing the output
+    if ((double)M * (double)N * (double)K < 6.4e7) return false;
+    if (M >= (1ll << 31) || N >= (1ll << 31) || K >= (1ll << 31)) return false;
+    return (a_sk == 1 || a_sm == 1) && (b_sk == 1 || b_sn == 1);
+}
 bool gemm_f32_worth(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk) {
-    return f32_route(M, N, K, a_sm, a_sk, b_sn, b_sk) != F32_NONE;
+    return f32_route(M, N, K, a_sm, a_sk, b_sn, b_sk) != F32_NONE || gemm_tf32_shape_ok(M, N, K, a_sm, a_sk, b_sn, b_sk);
 }
 
 int launch_gemm_f32(anl_device* dev, const float* a, const float* b, float* d, int64_t M, int64_t N, int64_t K,
                     int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk, cudaStream_t stream) {
     const F32Route route = f32_route(M, N, K, a_sm, a_sk, b_sn, b_sk);
     if (route == F32_FEW_ROWS_DOT || route == F32_FEW_ROWS_AXPY || route == F32_FEW_TERMS) {
-        const int groups = (int)((M + S_MR - 1) / S_MR);
-        if (route == F32_FEW_ROWS_DOT)
-            gemm_f32_few_rows_dot<<<dim3((unsigned)((N + 7) / 8), groups), 256, 0, stream>>>(a, b, d, (int)M, (int)N, (int)K, a_sm, b_sn, (int)N);
-        else if (route == F32_FEW_ROWS_AXPY)
-            gemm_f32_few_rows_axpy<<<dim3((unsigned)((N + 63) / 64), groups), 256, 0, stream>>>(a, b, d, (int)M, (int)N, (int)K, a_sm, b_sk, (int)N);
+        auto pick = [](int64_t rows, int most) { int r = 1; while (r < rows && r < most) r *= 2; return r; };
+        auto al16 = [](const void* p) { return ((uintptr_t)p & 15) == 0; };
+        if (route == F32_FEW_ROWS_DOT) {
+            const int mr = pick(M, S_MR), groups = (int)((M + mr - 1) / mr);
+            const int vec = al16(b) && b_sn % 4 == 0 && K % 4 == 0;
+            const int cw = mr >= 8 ? 4 : (mr == 4 ? 2 : 1);
+            const int colblocks = (int)((N + 8 * cw - 1) / (8 * cw));
+            // enough CTAs for two per SM, by splitting k across a cluster while a slice stays 256 long
+            int splits = 1;
+            while (splits < 8 && (int64_t)colblocks * groups * splits < 2 * dev->prop.multiProcessorCount && K / (splits * 2) >= 256) splits *= 2;
+            cudaLaunchConfig_t cfg{};
+            cfg.gridDim = dim3((unsigned)(colblocks * splits), (unsigned)groups, 1);
+            cfg.blockDim = dim3(256, 1, 1);
+            cfg.stream = stream;
+            cudaLaunchAttribute at[1];
+            at[0].id = cudaLaunchAttributeClusterDimension;
+            at[0].val.clusterDim.x = (unsigned)splits; at[0].val.clusterDim.y = 1; at[0].val.clusterDim.z = 1;
+            cfg.attrs = at; cfg.numAttrs = 1;
+            const int Mi = (int)M, Ni = (int)N, Ki = (int)K, ldd = (int)N;
+            cudaError_t le = cudaSuccess;
+#define ANL_DOT(R, C) le = cudaLaunchKernelEx(&cfg, gemm_f32_few_rows_dot<R, C>, a, b, d, Mi, Ni, Ki, (long long)a_sm, (long long)b_sn, ldd, vec, splits)
+            switch (mr) { case 1: ANL_DOT(1, 1); break; case 2: ANL_DOT(2, 1); break; case 4: ANL_DOT(4, 2); break; case 8: ANL_DOT(8, 4); break; default: ANL_DOT(16, 4); }
+#undef ANL_DOT
+            if (le != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm f32: launch: ") + cudaGetErrorString(le));
+        } else if (route == F32_FEW_ROWS_AXPY) {
+            const int mr = pick(M, S_MR_AXPY), groups = (int)((M + mr - 1) / mr);
+            const int vec = al16(b) && b_sk % 4 == 0 && N % 4 == 0;
+            const dim3 grid((unsigned)(S_KSPLIT * ((N + 127) / 128)), groups);
+#define ANL_AXPY(R) gemm_f32_few_rows_axpy<R><<<grid, 256, 0, stream>>>(a, b, d, (int)M, (int)N, (int)K, a_sm, b_sk, (int)N, vec)
+            switch (mr) { case 1: ANL_AXPY(1); break; case 2: ANL_AXPY(2); break; case 4: ANL_AXPY(4); break; default: ANL_AXPY(8); }
+#undef ANL_AXPY
+        }
         else {
             const int vec4 = (N % 4 == 0) && (b_sk % 4 == 0) && (((uintptr_t)b & 15) == 0) && (((uintptr_t)d & 15) == 0);
             const long long threads = M * ((N + 3) / 4);

@@ -36,6 +36,9 @@
 // the number of additions, so K is taken in chunks of chunk_kb k-blocks: the two accumulators
 // alternate between chunks instead of between tiles, and the epilogue adds each chunk's result to the
 // output in f32 round-to-nearest (the tile stays in L2 meanwhile) under the next chunk's main loop.
+// Where the tiles are too few to occupy the pairs and K is long, the host also splits K between
+// draws of the same tile: each writes its own copy of the output and the host adds the copies in a
+// fixed order.
 //
 // The host prepends the configuration:
 //   CFG_A_MN, CFG_B_MN   1 when the operand's m / n index is the contiguous one (else k is)
@@ -64,6 +67,9 @@ struct PairGemmArgs {
                             // of BNT/2 columns, so that the last, partly filled wave of tiles costs half a tile
     int chunk_kb;           // f32 form: k-blocks accumulated in tensor memory before the partial result is added, in f32
                             // round-to-nearest, to what the output holds (0: all of K in one go)
+    int k_splits;           // f32 form: with few tiles and a long K, every tile is drawn k_splits times, each draw taking
+    int kb_per_split;       // kb_per_split k-blocks and writing its sum to its own copy of the output, split_stride
+    long long split_stride; // elements after the one before; the host adds the copies in order afterwards (<= 1: off)
     int* status;
     int* tile_counter;      // [0] next tile number, [1] pairs that have signed off; both zero between launches
 };
@@ -239,6 +245,19 @@ __device__ __forceinline__ void warp_column_sums(float (&x)[32], int lane) {
     }
 }
 
+// drawn number -> tile number and the k-blocks it covers (all of them unless the f32 form splits K)
+__device__ __forceinline__ void split_of(const PairGemmArgs& g, int t, int tile_numbers, int kblocks, int& tile, int& sp, int& kb_first, int& nkb_all) {
+#if CFG_TF32
+    if (g.k_splits > 1) {
+        sp = t / tile_numbers; tile = t - sp * tile_numbers;
+        kb_first = sp * g.kb_per_split;
+        nkb_all = (kblocks - kb_first) < g.kb_per_split ? (kblocks - kb_first) : g.kb_per_split;
+        return;
+    }
+#endif
+    tile = t; sp = 0; kb_first = 0; nkb_all = kblocks;
+}
+
 extern "C" __global__ void __launch_bounds__(192, 1)
 gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b, const __grid_constant__ TensorMap map_b_half,
                       const __grid_constant__ TensorMap map_a_lo, const __grid_constant__ TensorMap map_b_lo, const PairGemmArgs g) {
@@ -256,10 +275,10 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
     const unsigned rank = cluster_ctarank();            // 0 leads
     const int tiles_m = g.tiles_m;
     const int whole_tiles = tiles_m * g.tiles_n;
-    const int num_tiles = whole_tiles + (whole_tiles - g.full_tiles);     // every tile past full_tiles counts twice
+    const int tile_numbers = whole_tiles + (whole_tiles - g.full_tiles);  // every tile past full_tiles counts twice
+    const int num_tiles = tile_numbers * ((CFG_TF32 && g.k_splits > 1) ? g.k_splits : 1);
     const int kblocks = (g.K + BK - 1) / BK;
-    const int chunk_kb = (CFG_TF32 && g.chunk_kb > 0 && g.chunk_kb < kblocks) ? g.chunk_kb : kblocks;
-    const int chunks = kblocks > 0 ? (kblocks + chunk_kb - 1) / chunk_kb : 1;
+    const int chunk_kb = (CFG_TF32 && g.chunk_kb > 0 && g.chunk_kb < kblocks) ? g.chunk_kb : (kblocks > 0 ? kblocks : 1);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
@@ -304,15 +323,18 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 }
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
                 if (t < 0) { if (rank == 0) retire_tile_counter(g.tile_counter, (int)gridDim.x / 2); break; }
+                int tt, sp, kb_first, nkb_all;
+                split_of(g, t, tile_numbers, kblocks, tt, sp, kb_first, nkb_all);
+                const int chunks = (nkb_all + chunk_kb - 1) / chunk_kb;
                 int tm, col0, width;
-                tile_of(t, tiles_m, g.tiles_n, g.full_tiles, tm, col0, width);
+                tile_of(tt, tiles_m, g.tiles_n, g.full_tiles, tm, col0, width);
                 const bool narrow = width != BNT;
                 const int m0 = tm * (2 * BM) + (int)rank * BM;           // this CTA's rows of A
                 const int n0 = col0 + (int)rank * (width / 2);           // this CTA's half of B
                 const unsigned stage_bytes = A_TILE_BYTES + (narrow ? BHALF_BYTES / 2 : BHALF_BYTES);
                 const TensorMap* const mb = narrow ? &map_b_half : &map_b;
                 for (int ch = 0; ch < chunks && ok; ch++) {
-                    const int kb0 = ch * chunk_kb, nkb = (kblocks - kb0) < chunk_kb ? (kblocks - kb0) : chunk_kb;
+                    const int kb0 = kb_first + ch * chunk_kb, nkb = (nkb_all - ch * chunk_kb) < chunk_kb ? (nkb_all - ch * chunk_kb) : chunk_kb;
                     for (int it = 0; it < PASSES * nkb && ok; it++) {
                         const int pass = it / nkb, kb = kb0 + it - pass * nkb;
                         // 3 x TF32: pass 0 = A_lo · B_hi, pass 1 = A_hi · B_lo, pass 2 = A_hi · B_hi
@@ -350,9 +372,12 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 mbar_arrive(smem_u32(&tq_empty[qs]));
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
                 if (t < 0) break;
-                const unsigned idesc = idesc_base | ((unsigned)((t < g.full_tiles ? BNT : BNT / 2) >> 3) << 17);
+                int tt, sp, kb_first, nkb_all;
+                split_of(g, t, tile_numbers, kblocks, tt, sp, kb_first, nkb_all);
+                const int chunks = (nkb_all + chunk_kb - 1) / chunk_kb;
+                const unsigned idesc = idesc_base | ((unsigned)((tt < g.full_tiles ? BNT : BNT / 2) >> 3) << 17);
                 for (int ch = 0; ch < chunks && ok; ch++) {
-                    const int nkb = (kblocks - ch * chunk_kb) < chunk_kb ? (kblocks - ch * chunk_kb) : chunk_kb;
+                    const int nkb = (nkb_all - ch * chunk_kb) < chunk_kb ? (nkb_all - ch * chunk_kb) : chunk_kb;
                     if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned tmem_d = tmem_base + acc * BNT;
@@ -401,11 +426,14 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
             if (lane == 0) mbar_arrive_cluster(map_to_cta(smem_u32(&tq_empty[qs]), 0));
             if (++qs == TQ) { qs = 0; qphase ^= 1; }
             if (t < 0) break;
+            int tt, sp, kb_first, nkb_all;
+            split_of(g, t, tile_numbers, kblocks, tt, sp, kb_first, nkb_all);
+            const int chunks = (nkb_all + chunk_kb - 1) / chunk_kb;
             int tm, n0, width;
-            tile_of(t, tiles_m, g.tiles_n, g.full_tiles, tm, n0, width);
+            tile_of(tt, tiles_m, g.tiles_n, g.full_tiles, tm, n0, width);
             const int m0 = tm * (2 * BM) + (int)rank * BM;
             const int row = m0 + quad * 32 + lane;
-            const size_t row_off = (size_t)row * g.ldd;
+            const size_t row_off = (size_t)row * g.ldd + (CFG_TF32 ? (size_t)sp * (size_t)g.split_stride : 0);
             const bool row_ok = row < g.M;
             const bool vec_ok = (g.ldd % 8 == 0); (void)vec_ok;
             for (int ch = 0; ch < chunks; ch++) {

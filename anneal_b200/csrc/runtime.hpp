@@ -191,6 +191,7 @@ double gemm_flops(const Plan& plan, int64_t sym_value);
 // true when this launch (with the symbolic extent bound to sym_value) goes to the contraction kernel
 bool gemm_taken(const Plan& plan, int64_t sym_value);
 bool gemm_f32_worth(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk);
+bool gemm_tf32_shape_ok(int64_t M, int64_t N, int64_t K, int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk);
 int launch_gemm_f32(anl_device* dev, const float* a, const float* b, float* d, int64_t M, int64_t N, int64_t K,
                     int64_t a_sm, int64_t a_sk, int64_t b_sn, int64_t b_sk, cudaStream_t stream);
 
