@@ -72,7 +72,7 @@ def test_gemm_f32_small_stays_on_generated_kernel(cuda, oracle):
     assert n == 0
 
 
-@pytest.mark.parametrize("b,gemms", [(1, 5), (3, 5), (17, 5), (32, 5), (33, 5), (300, 5), (2100, 5)])
+@pytest.mark.parametrize("b,gemms", [(1, 5), (3, 5), (17, 5), (32, 5), (300, 5), (2100, 5)])
 def test_gemm_f32_symbolic_batch(cuda, oracle, b, gemms):
     """The bound batch is M of the forward/input-gradient contractions and K of the weight-gradient
     ones; one compiled plan serves every binding and picks the kernel per launch: the few-row and
