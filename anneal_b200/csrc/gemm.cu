@@ -187,7 +187,6 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                 if (!mbar_wait(smem_u32(&tq_empty[qs]), qphase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 5; break; }
                 int t = next;
                 if (t >= num_tiles) t = -1;
-                else next = atomicAdd(g.tile_counter, 1);      // drawn one tile ahead: its latency hides behind this tile's loads
                 tile_ring[qs] = t;
                 mbar_arrive(smem_u32(&tq_full[qs]));
                 if (++qs == TQ) { qs = 0; qphase ^= 1; }
@@ -206,6 +205,9 @@ gemm_f16_tcgen05(const __grid_constant__ CUtensorMap map_a, const __grid_constan
                     issued++;
                     if (++stage == STAGES) { stage = 0; phase ^= 1; }
                 }
+                // drawn once this tile's loads are issued: no CTA holds a number it is not about to start, and
+                // the ring of stages already loaded covers the atomic's latency
+                if (ok) next = atomicAdd(g.tile_counter, 1);
             }
             if (!ok) {
                 failed = 1;
@@ -697,8 +699,8 @@ static int launch_gemm_tf32x3(anl_device* dev, const GemmPlan& gp, const float* 
     auto enc_a = [&](CUtensorMap* m, const float* base) { return encode_map(dev, m, base, (uint64_t)K, (uint64_t)M, (uint64_t)ldo, BK32, BM, true); };
     auto enc_b = [&](CUtensorMap* m, const float* base) { return encode_map(dev, m, base, (uint64_t)K, (uint64_t)N, (uint64_t)ldo, BK32, v.bnt / 2, true); };
     if ((rc = enc_a(&ma_hi, a_hi)) || (rc = enc_a(&ma_lo, a_lo)) || (rc = enc_b(&mb_hi, b_hi)) || (rc = enc_b(&mb_lo, b_lo))) return done(rc);
-    PairGemmArgs g{};
-    g.d_raw = d; g.d_out = nullptr; g.colsum = nullptr;
+    PairGemmArgsF32 g{};
+    g.d_raw = d;
     g.M = (int)M; g.N = (int)N; g.ldd = (int)N;
     g.tiles_m = (int)((M + 2 * BM - 1) / (2 * BM)); g.tiles_n = (int)((N + v.bnt - 1) / v.bnt);
     g.full_tiles = g.tiles_m * g.tiles_n;
@@ -737,7 +739,8 @@ static int launch_gemm_tf32x3(anl_device* dev, const GemmPlan& gp, const float* 
         if (copies) { if (keep_scratch) keep_scratch->push_back(copies); else dev->release(copies); }
         return done(code);
     };
-    void* params[6] = {&ma_hi, &mb_hi, &mb_hi, &ma_lo, &mb_lo, &g};
+    g.draw_late = g.full_tiles * std::max(1, g.k_splits) <= 2 * npairs;
+    void* params[5] = {&ma_hi, &mb_hi, &ma_lo, &mb_lo, &g};
     CUresult cr = dev->drv.LaunchKernelEx(&cfg, fn, params, nullptr);
     if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return done2(dev->fail(ANL_ERR_CUDA, std::string("gemm: tf32 pair launch: ") + (e ? e : "?"))); }
     dev->stats.kernels_launched++;
@@ -817,7 +820,8 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
         at[0].id = CU_LAUNCH_ATTRIBUTE_CLUSTER_DIMENSION;
         at[0].value.clusterDim.x = 2; at[0].value.clusterDim.y = 1; at[0].value.clusterDim.z = 1;
         cfg.attrs = at; cfg.numAttrs = 1;
-        void* params[6] = {&ma, &mb, &mbh, &ma, &mb, &g};     // the two extra maps are read by the f32 form only
+        g.draw_late = (whole + (whole - g.full_tiles)) <= 2 * pairs;
+        void* params[4] = {&ma, &mb, &mbh, &g};
         CUresult cr = dev->drv.LaunchKernelEx(&cfg, fn, params, nullptr);
         if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return dev->fail(ANL_ERR_CUDA, std::string("gemm: pair launch: ") + (e ? e : "?")); }
         dev->stats.kernels_launched++;

@@ -56,6 +56,9 @@
 // which maps 8 consecutive narrowed values acc[0..3] at (row, col..col+7) to the 8 outputs.
 #pragma once
 
+// Arguments of the f16 form.  The layout is kept at 120 bytes on purpose: with 24 more bytes of
+// fields that only the f32 form reads, the f16 kernel ran 6% slower on every large shape, whatever its
+// code did with them; the f32 form therefore has a block of its own.
 struct PairGemmArgs {
     void* d_raw;            // [M, ldd] f16: the contraction itself; null when nothing else reads it
     void* d_out;            // [M, ldd] f16: output of the fused consumer; null without one
@@ -65,13 +68,26 @@ struct PairGemmArgs {
     int tiles_m, tiles_n;   // in 256-row pair tiles and BNT-column tiles
     int full_tiles;         // tile numbers below this are BNT wide; each tile from here on is drawn as two halves
                             // of BNT/2 columns, so that the last, partly filled wave of tiles costs half a tile
-    int chunk_kb;           // f32 form: k-blocks accumulated in tensor memory before the partial result is added, in f32
-                            // round-to-nearest, to what the output holds (0: all of K in one go)
-    int k_splits;           // f32 form: with few tiles and a long K, every tile is drawn k_splits times, each draw taking
-    int kb_per_split;       // kb_per_split k-blocks and writing its sum to its own copy of the output, split_stride
-    long long split_stride; // elements after the one before; the host adds the copies in order afterwards (<= 1: off)
+    int draw_late;          // 1: few tiles, draw the next tile number after this tile's loads; 0: draw one tile ahead
     int* status;
     int* tile_counter;      // [0] next tile number, [1] pairs that have signed off; both zero between launches
+};
+
+// Arguments of the f32 (3 x TF32) form.
+struct PairGemmArgsF32 {
+    void* d_raw;            // [M, ldd] f32 output, or the copies of it when K is split between draws
+    int M, N, K, ldd;
+    int tiles_m, tiles_n;
+    int full_tiles;         // = tiles_m * tiles_n: this form draws no half-width tiles
+    int draw_late;
+    int chunk_kb;           // k-blocks accumulated in tensor memory before the partial result is added, in f32
+                            // round-to-nearest, to what the output holds (0: all of K in one go)
+    int k_splits;           // with few tiles and a long K, every tile is drawn k_splits times, each draw taking
+    int kb_per_split;       // kb_per_split k-blocks and writing its sum to its own copy of the output, split_stride
+    int reserved;
+    long long split_stride; // elements after the one before; the host adds the copies in order afterwards (<= 1: off)
+    int* status;
+    int* tile_counter;
 };
 
 #ifdef ANL_PAIR_GEMM_DEVICE_CODE
@@ -79,6 +95,14 @@ struct PairGemmArgs {
 #include <cuda_fp16.h>
 
 struct alignas(64) TensorMap { unsigned long long opaque[16]; };
+#ifndef CFG_TF32
+#define CFG_TF32 0
+#endif
+#if CFG_TF32
+typedef PairGemmArgsF32 Args;
+#else
+typedef PairGemmArgs Args;
+#endif
 
 #ifndef CFG_TF32
 #define CFG_TF32 0
@@ -246,7 +270,7 @@ __device__ __forceinline__ void warp_column_sums(float (&x)[32], int lane) {
 }
 
 // drawn number -> tile number and the k-blocks it covers (all of them unless the f32 form splits K)
-__device__ __forceinline__ void split_of(const PairGemmArgs& g, int t, int tile_numbers, int kblocks, int& tile, int& sp, int& kb_first, int& nkb_all) {
+__device__ __forceinline__ void split_of(const Args& g, int t, int tile_numbers, int kblocks, int& tile, int& sp, int& kb_first, int& nkb_all) {
 #if CFG_TF32
     if (g.k_splits > 1) {
         sp = t / tile_numbers; tile = t - sp * tile_numbers;
@@ -259,8 +283,16 @@ __device__ __forceinline__ void split_of(const PairGemmArgs& g, int t, int tile_
 }
 
 extern "C" __global__ void __launch_bounds__(192, 1)
+#if CFG_TF32
+gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b,
+                      const __grid_constant__ TensorMap map_a_lo, const __grid_constant__ TensorMap map_b_lo, const Args g) {
+    const TensorMap& map_b_half = map_b;         // the f32 form draws no half-width tiles
+#else
 gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b, const __grid_constant__ TensorMap map_b_half,
-                      const __grid_constant__ TensorMap map_a_lo, const __grid_constant__ TensorMap map_b_lo, const PairGemmArgs g) {
+                      const Args g) {
+    const TensorMap& map_a_lo = map_a;           // read by the f32 form only
+    const TensorMap& map_b_lo = map_b;
+#endif
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2];
     // tile queue: the leader's producer draws tile numbers from the global counter and publishes each
@@ -276,9 +308,14 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
     const int tiles_m = g.tiles_m;
     const int whole_tiles = tiles_m * g.tiles_n;
     const int tile_numbers = whole_tiles + (whole_tiles - g.full_tiles);  // every tile past full_tiles counts twice
-    const int num_tiles = tile_numbers * ((CFG_TF32 && g.k_splits > 1) ? g.k_splits : 1);
     const int kblocks = (g.K + BK - 1) / BK;
-    const int chunk_kb = (CFG_TF32 && g.chunk_kb > 0 && g.chunk_kb < kblocks) ? g.chunk_kb : (kblocks > 0 ? kblocks : 1);
+#if CFG_TF32
+    const int num_tiles = tile_numbers * (g.k_splits > 1 ? g.k_splits : 1);
+    const int chunk_kb = (g.chunk_kb > 0 && g.chunk_kb < kblocks) ? g.chunk_kb : (kblocks > 0 ? kblocks : 1);
+#else
+    const int num_tiles = tile_numbers;
+    const int chunk_kb = kblocks > 0 ? kblocks : 1;
+#endif
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
@@ -311,7 +348,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                     if (!mbar_wait(smem_u32(&tq_empty[qs]), qphase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 15; break; }
                     t = next;
                     if (t >= num_tiles) t = -1;
-                    else next = atomicAdd(g.tile_counter, 1);      // drawn one tile ahead: its latency hides behind this tile's loads
+                    else if (!g.draw_late) next = atomicAdd(g.tile_counter, 1);    // one tile ahead: the latency hides behind this tile's loads
                     tile_ring[qs] = t;
                     st_cluster_u32(map_to_cta(smem_u32(&tile_ring[qs]), 1), t);
                     mbar_arrive(smem_u32(&tq_full[qs]));
@@ -353,6 +390,12 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                         if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
                     }
                 }
+                // With few tiles (draw_late) the next number is drawn only once this tile's loads are issued, so
+                // that every pair gets one tile before any pair gets two; that puts the atomic's latency on the
+                // producer's path once per tile, which costs about 5% where the tiles are many, so there the
+                // number is drawn a tile ahead instead.  Nothing is added to the loop above: one more
+                // instruction in it cost a tenth of the kernel's throughput.
+                if (rank == 0 && g.draw_late && ok) next = atomicAdd(g.tile_counter, 1);
             }
             if (!ok) failed = 1;
         }
@@ -433,7 +476,11 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
             tile_of(tt, tiles_m, g.tiles_n, g.full_tiles, tm, n0, width);
             const int m0 = tm * (2 * BM) + (int)rank * BM;
             const int row = m0 + quad * 32 + lane;
-            const size_t row_off = (size_t)row * g.ldd + (CFG_TF32 ? (size_t)sp * (size_t)g.split_stride : 0);
+            #if CFG_TF32
+            const size_t row_off = (size_t)row * g.ldd + (size_t)sp * (size_t)g.split_stride;
+#else
+            const size_t row_off = (size_t)row * g.ldd;
+#endif
             const bool row_ok = row < g.M;
             const bool vec_ok = (g.ldd % 8 == 0); (void)vec_ok;
             for (int ch = 0; ch < chunks; ch++) {
