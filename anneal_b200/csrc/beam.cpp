@@ -55,6 +55,7 @@ int time_plan(anl_device* dev, const Plan& plan, const Item& it, std::vector<voi
     double best = 1e30;
     int rc = ANL_OK;
     for (int i = 0; i < 7 && rc == ANL_OK; i++) {
+        launch_hold_stream(dev->stream, 200000);       // the launch is queued before the GPU reaches e0
         cudaEventRecord(e0, dev->stream);
         rc = launch_plan(dev, plan, it, ptrs.data(), 0, dev->stream, nullptr);
         cudaEventRecord(e1, dev->stream);

@@ -490,15 +490,22 @@ std::string pair_source(const PairVariant& v, const std::string& epilogue) {
 }
 
 int get_pair_kernel(anl_device* dev, const PairVariant& v, const std::string& epilogue, CUfunction* fn) {
+    // looked up by the configuration, so that a launch does not assemble and hash 40 KB of source
+    char head[96];
+    std::snprintf(head, sizeof head, "%d,%d,%d,%d,%d,%d,%d|", v.bnt, v.stages, v.group_m, v.stream_stores, (int)v.a_mn, (int)v.b_mn, (int)v.tf32);
+    const std::string key = head + epilogue;
+    auto hit = dev->pair_kernels.find(key);
+    if (hit != dev->pair_kernels.end()) { *fn = (CUfunction)hit->second; return ANL_OK; }
     std::shared_ptr<Module> m;
     if (int rc = compile_source(dev, pair_source(v, epilogue), m)) return rc;
     auto f = m->fn.find("gemm_f16_tcgen05_pair");
-    if (f != m->fn.end()) { *fn = f->second; return ANL_OK; }
+    if (f != m->fn.end()) { *fn = f->second; dev->pair_kernels[key] = (void*)*fn; return ANL_OK; }
     CUresult cr = dev->drv.ModuleGetFunction(fn, m->mod, "gemm_f16_tcgen05_pair");
     if (cr != CUDA_SUCCESS) return dev->fail(ANL_ERR_CUDA, "gemm: pair kernel entry point missing");
     cr = dev->drv.FuncSetAttribute(*fn, CU_FUNC_ATTRIBUTE_MAX_DYNAMIC_SHARED_SIZE_BYTES, pair_smem_bytes(v.bnt, v.stages));
     if (cr != CUDA_SUCCESS) { const char* e = nullptr; dev->drv.GetErrorString(cr, &e); return dev->fail(ANL_ERR_CUDA, std::string("gemm: cuFuncSetAttribute: ") + (e ? e : "?")); }
     m->fn["gemm_f16_tcgen05_pair"] = *fn;
+    dev->pair_kernels[key] = (void*)*fn;
     return ANL_OK;
 }
 

@@ -121,6 +121,19 @@ __global__ void __launch_bounds__(256, 6) sgd_kernel(float* __restrict__ master,
     }
 }
 
+// Holds the stream for about `ns` nanoseconds (bounded: at most 4096 sleeps of 1 us), so that the launch
+// to be timed is already queued behind the first event when the GPU reaches it; without it the host's
+// time to prepare the launch is measured as part of the kernel.
+__global__ void hold_stream(unsigned long long ns) {
+    unsigned long long t0, t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t0));
+    for (int i = 0; i < 4096; i++) {
+        asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+        if (t - t0 >= ns) break;
+        __nanosleep(1000);
+    }
+}
+
 // Benchmark operands: finite values of magnitude 0.5 .. 1 with random signs and mantissas (f16 pairs or
 // f32 words), so that a timed contraction switches as many bits as one fed with real activations; a
 // zero-filled operand lets the tensor cores idle and flatters the clock.
@@ -173,6 +186,8 @@ void anl_device::trim() {
 }
 
 namespace anl {
+
+void launch_hold_stream(cudaStream_t stream, unsigned long long ns) { hold_stream<<<1, 1, 0, stream>>>(ns); }
 
 int ensure_driver(anl_device* dev) {
     if (dev->drv.loaded) return ANL_OK;
@@ -1157,6 +1172,7 @@ static int benchmark_impl(anl_device* dev, const uint8_t* blob, size_t blob_len,
     if (rc == ANL_OK) {
         cudaEvent_t e0, e1; cudaEventCreate(&e0); cudaEventCreate(&e1);
         for (int i = 0; i < warmup + iterations && rc == ANL_OK; i++) {
+            launch_hold_stream(dev->stream, 200000);
             cudaEventRecord(e0, dev->stream);
             rc = launch_plan(dev, *plan, it, ptrs.data(), 0, dev->stream, nullptr);
             cudaEventRecord(e1, dev->stream);

@@ -139,6 +139,7 @@ struct anl_device {
     int* gemm_status_host = nullptr;      // mapped, host-visible: code of a barrier wait that ran out
     int* gemm_status_dev = nullptr;
     bool gemm_attr_set = false;
+    std::unordered_map<std::string, void*> pair_kernels;   // configuration (tunables + fused consumer's text) -> loaded two-CTA kernel
     anl::GemmTuning gemm_defaults;        // device-wide tunables of the contraction kernels; a plan's own non-zero fields win
     void* nccl_comm = nullptr;
     int rank = 0, nranks = 1;
@@ -173,6 +174,7 @@ int plan_gemm(const Item& item, const GemmTuning& tune, Plan& plan);
 int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sym_value, cudaStream_t stream,
                 int64_t m_begin = 0, int64_t m_end = -1, const GemmFusion* fusion = nullptr, std::vector<void*>* keep_scratch = nullptr);
 // true when the plan runs on the two-CTA kernel, the one that can carry a fused consumer
+void launch_hold_stream(cudaStream_t stream, unsigned long long ns);
 bool gemm_pair_eligible(const Plan& plan);
 bool gemm_tf32_eligible(const Plan& plan);
 int gemm_tf32_source(const Plan& plan, std::string& out, std::string& note);
