@@ -1648,6 +1648,7 @@ struct Gen {
         bool saw_acc = false;
         cur_top = &prelude;
         int vi = 0;
+        std::ostringstream loads;
         for (int i = 0; i < n; i++) {
             if (N(i).op != OP_INDEX || i == dst || !is_live(i)) continue;
             const int p = (int)N(N(i).src[0]).arg;
@@ -1664,9 +1665,12 @@ struct Gen {
             if (vec_load.count(i)) continue;
             const int p = (int)N(N(i).src[0]).arg;
             Lin f = flat_index(i);
-            const std::string arr = "v" + std::to_string(vi++);
-            stmt(-1, "__half2 " + arr + "_raw[4];");
-            stmt(-1, "ldv_<__half2, 4>(reinterpret_cast<const __half2*>(data" + std::to_string(p) + " + " + render(f, -1) + "), " + arr + "_raw);");
+            // the loads live in a function of their own (epi8_load_), so that the contraction kernel can
+            // issue them a chunk ahead of the arithmetic that needs them
+            const std::string arr = "v" + std::to_string(vi);
+            loads << "  ldv_<__half2, 4>(reinterpret_cast<const __half2*>(data" << p << " + " << render(f, -1) << "), raw[" << vi << "]);\n";
+            stmt(-1, "const __half2* " + arr + "_raw = raw[" + std::to_string(vi) + "];");
+            vi++;
             vec_load[i] = arr + "_raw";
         }
         cur_top = nullptr;
@@ -1675,17 +1679,23 @@ struct Gen {
         if (!err.empty()) return false;
         std::ostringstream k;
         k << "#define LANES 1\n#define TOUTS 1\n#define RC_LAYOUT 1\n" << preamble();
-        k << "__device__ __forceinline__ void epi8_(const int row, const int col, const __half2* __restrict__ acc, __half2* __restrict__ out, const void* const* ep) {\n";
-        k << "  const int r" << N(r0).aux << " = row; (void)r" << N(r0).aux << ";\n";
-        k << "  const int r" << N(r1).aux << " = col; (void)r" << N(r1).aux << ";\n";
+        std::ostringstream head;
+        head << "  const int r" << N(r0).aux << " = row; (void)r" << N(r0).aux << ";\n";
+        head << "  const int r" << N(r1).aux << " = col; (void)r" << N(r1).aux << ";\n";
         out.params.clear();
         for (int b = 1; b < (int)it.bufs.size(); b++) {
             if (b == acc_param) continue;
             if (it.bufs[b].dtype != DT_F16) return fail("epilogue: an operand is not f16");
-            k << "  const __half* __restrict__ data" << b << " = reinterpret_cast<const __half*>(ep[" << out.params.size() << "]);\n";
+            head << "  const __half* __restrict__ data" << b << " = reinterpret_cast<const __half*>(ep[" << out.params.size() << "]); (void)data" << b << ";\n";
             out.params.push_back(b);
         }
         if (out.params.size() > 6) return fail("epilogue: more than six operands");
+        // EPI_NRAW groups of 8 consecutive f16 are loaded per call; raw[k] holds group k as four pairs
+        k << "#define EPI_NRAW " << vi << "\n";
+        k << "__device__ __forceinline__ void epi8_load_(const int row, const int col, const void* const* ep, __half2 (*raw)[4]) {\n";
+        k << head.str() << loads.str() << "}\n";
+        k << "__device__ __forceinline__ void epi8_(const int row, const int col, const __half2* __restrict__ acc, __half2* __restrict__ out, const void* const* ep, const __half2 (*raw)[4]) {\n";
+        k << head.str();
         k << prelude.code;
         k << "  _Pragma(\"unroll\") for (int u = 0; u < 4; u++) {\n" << top.code << "    out[u] = " << v << ";\n  }\n}\n";
         out.source = k.str();

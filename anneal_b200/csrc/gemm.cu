@@ -44,6 +44,7 @@ constexpr int B_TILE_BYTES = BN * BK * 2;          // 32 KiB
 constexpr int STAGE_BYTES = A_TILE_BYTES + B_TILE_BYTES;
 constexpr int SMEM_BYTES = STAGES * STAGE_BYTES + 1024;   // + alignment slack
 constexpr int GEMM_THREADS = 192;
+constexpr int PAIR_THREADS = 320;        // two-CTA kernel: producer, MMA issuer and eight epilogue warps
 constexpr int TQ = 4;                               // depth of the per-CTA tile queue
 constexpr unsigned WAIT_LIMIT = 1u << 20;
 
@@ -717,7 +718,7 @@ static int launch_gemm_tf32x3(anl_device* dev, const GemmPlan& gp, const float* 
     const int pairs = std::min(g.full_tiles, npairs);
     CUlaunchConfig cfg{};
     cfg.gridDimX = 2 * pairs; cfg.gridDimY = 1; cfg.gridDimZ = 1;
-    cfg.blockDimX = GEMM_THREADS; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+    cfg.blockDimX = PAIR_THREADS; cfg.blockDimY = 1; cfg.blockDimZ = 1;
     cfg.sharedMemBytes = pair_smem_bytes(v.bnt, v.stages);
     cfg.hStream = (CUstream)stream;
     CUlaunchAttribute at[1];
@@ -820,7 +821,7 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
         const int pairs = std::min(whole + (whole - g.full_tiles), npairs);
         CUlaunchConfig cfg{};
         cfg.gridDimX = 2 * pairs; cfg.gridDimY = 1; cfg.gridDimZ = 1;
-        cfg.blockDimX = GEMM_THREADS; cfg.blockDimY = 1; cfg.blockDimZ = 1;
+        cfg.blockDimX = PAIR_THREADS; cfg.blockDimY = 1; cfg.blockDimZ = 1;
         cfg.sharedMemBytes = pair_smem_bytes(v.bnt, v.stages);
         cfg.hStream = (CUstream)stream;
         CUlaunchAttribute at[1];
@@ -859,18 +860,37 @@ int launch_gemm(anl_device* dev, const Plan& plan, void* const* bufs, int64_t sy
 }
 
 // Finishes a bias gradient whose per-32-row partial column sums a contraction's epilogue left in
-// `partials` [parts, N]: ascending sum in f32, one narrowing to f16 — the arithmetic of the REDUCE the
-// schedule holds for it (f32 accumulator, narrowed once), with the rows grouped by 32.
+// `partials` [parts, N]: summed in f32 in a fixed order, one narrowing to f16 — the arithmetic of the REDUCE
+// the schedule holds for it (f32 accumulator, narrowed once), with the rows grouped.
 __global__ void __launch_bounds__(256) colsum_finish(const float* __restrict__ partials, int parts, int n, __half* __restrict__ out) {
-    const int col = blockIdx.x * blockDim.x + threadIdx.x;
-    if (col >= n) return;
+    // a block owns 32 columns; its 8 warps take contiguous eighths of the parts (ascending inside each),
+    // and the eight sums are added in warp order: a fixed order, wide enough to keep loads in flight
+    __shared__ float part[8][32];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int col = blockIdx.x * 32 + lane;
+    const int per = (parts + 7) / 8, p0 = warp * per, p1 = (p0 + per) < parts ? (p0 + per) : parts;
     float acc = 0.0f;
-    for (int p = 0; p < parts; p++) acc = acc + partials[(size_t)p * n + col];
-    out[col] = __float2half_rn(acc);
+    if (col < n) {
+        int p = p0;
+        for (; p + 4 <= p1; p += 4) {
+            const float a = partials[(size_t)p * n + col], b = partials[(size_t)(p + 1) * n + col];
+            const float c = partials[(size_t)(p + 2) * n + col], d = partials[(size_t)(p + 3) * n + col];
+            acc = (((acc + a) + b) + c) + d;
+        }
+        for (; p < p1; p++) acc = acc + partials[(size_t)p * n + col];
+    }
+    part[warp][lane] = acc;
+    __syncthreads();
+    if (warp == 0 && col < n) {
+        float v = part[0][lane];
+#pragma unroll
+        for (int w = 1; w < 8; w++) v = v + part[w][lane];
+        out[col] = __float2half_rn(v);
+    }
 }
 
 int launch_colsum_finish(anl_device* dev, const float* partials, int64_t parts, int64_t n, void* out, cudaStream_t stream) {
-    colsum_finish<<<(unsigned)((n + 255) / 256), 256, 0, stream>>>(partials, (int)parts, (int)n, (__half*)out);
+    colsum_finish<<<(unsigned)((n + 31) / 32), 256, 0, stream>>>(partials, (int)parts, (int)n, (__half*)out);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return dev->fail(ANL_ERR_CUDA, std::string("gemm: column-sum finish: ") + cudaGetErrorString(e));
     dev->stats.kernels_launched++;

@@ -15,7 +15,8 @@
 // even CTA leads: it owns the "full" barriers (both CTAs' TMA loads complete on them) and issues the
 // MMAs; its commits release the stage and publish the accumulator in both CTAs.  No load is
 // multicast: every CTA issues its own.  Warp roles: 0 TMA producer, 1 MMA issuer (owns the tensor
-// memory allocation), 2-5 epilogue (one 32-lane quadrant of tensor memory each).  Two accumulators
+// memory allocation), 2-9 epilogue (two per 32-lane quadrant of tensor memory, half of the columns
+// each: with four, a fused consumer on a short K was bound by the epilogue).  Two accumulators
 // let the epilogue of tile i run under the main loop of tile i+1.  Tile numbers are drawn from a
 // global counter, so a pair that starts late (its SMs were busy with a collective) takes fewer.
 //
@@ -52,8 +53,12 @@
 //   CFG_STREAM_STORES    1: outputs are written with the streaming hint (they are not read again by
 //                        this kernel and should not push operand tiles out of L2)
 // and, when CFG_EPI is 1, the text of
-//   __device__ void epi8_(int row, int col, const __half2* acc, __half2* out, const void* const* ep)
-// which maps 8 consecutive narrowed values acc[0..3] at (row, col..col+7) to the 8 outputs.
+//   EPI_NRAW                                  how many groups of 8 consecutive f16 the consumer loads per call
+//   __device__ void epi8_load_(int row, int col, const void* const* ep, __half2 (*raw)[4])
+//   __device__ void epi8_(int row, int col, const __half2* acc, __half2* out, const void* const* ep, const __half2 (*raw)[4])
+// the second of which maps 8 consecutive narrowed values acc[0..3] at (row, col..col+7) to the 8 outputs
+// from the operand values the first one loaded (the kernel calls it a chunk of 32 columns ahead: the
+// loads' latency would otherwise be paid once per chunk by each of only four epilogue warps).
 #pragma once
 
 // Arguments of the f16 form.  The layout is kept at 120 bytes on purpose: with 24 more bytes of
@@ -119,6 +124,7 @@ constexpr int A_TILE_BYTES = BM * BK * ESZ;
 constexpr int BHALF_BYTES = (BNT / 2) * BK * ESZ;
 constexpr int STAGE_B = A_TILE_BYTES + BHALF_BYTES;
 constexpr int TQ = 4;
+constexpr int EPI_WARPS = 8;         // two per 32-lane quadrant of tensor memory, each taking half of the tile's columns
 constexpr unsigned WAIT_LIMIT = 1u << 20;
 
 __device__ __forceinline__ unsigned smem_u32(const void* p) { return (unsigned)__cvta_generic_to_shared(p); }
@@ -254,20 +260,12 @@ __device__ __forceinline__ void store16(void* p, uint4 v) {
 #endif
 }
 
-// Sum over the 32 lanes of a warp of x[j], for each j in [0, 32): on return lane j holds column j's
-// sum in x[0].  Recursive halving: 31 shuffles instead of 160, and a fixed order of additions.
-__device__ __forceinline__ void warp_column_sums(float (&x)[32], int lane) {
-#pragma unroll
-    for (int off = 16; off >= 1; off >>= 1) {
-        const bool upper = (lane & off) != 0;
-#pragma unroll
-        for (int i = 0; i < off; i++) {
-            const float send = upper ? x[i] : x[i + off];
-            const float keep = upper ? x[i + off] : x[i];
-            x[i] = keep + __shfl_xor_sync(0xffffffffu, send, off);
-        }
-    }
+__device__ __forceinline__ uint4 shfl_xor_u4(uint4 v, int mask) {
+    v.x = __shfl_xor_sync(0xffffffffu, v.x, mask); v.y = __shfl_xor_sync(0xffffffffu, v.y, mask);
+    v.z = __shfl_xor_sync(0xffffffffu, v.z, mask); v.w = __shfl_xor_sync(0xffffffffu, v.w, mask);
+    return v;
 }
+__device__ __forceinline__ uint4 sel_u4(bool c, uint4 a, uint4 b) { return c ? a : b; }
 
 // drawn number -> tile number and the k-blocks it covers (all of them unless the f32 form splits K)
 __device__ __forceinline__ void split_of(const Args& g, int t, int tile_numbers, int kblocks, int& tile, int& sp, int& kb_first, int& nkb_all) {
@@ -282,7 +280,7 @@ __device__ __forceinline__ void split_of(const Args& g, int t, int tile_numbers,
     tile = t; sp = 0; kb_first = 0; nkb_all = kblocks;
 }
 
-extern "C" __global__ void __launch_bounds__(192, 1)
+extern "C" __global__ void __launch_bounds__(64 + 32 * EPI_WARPS, 1)
 #if CFG_TF32
 gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_constant__ TensorMap map_b,
                       const __grid_constant__ TensorMap map_a_lo, const __grid_constant__ TensorMap map_b_lo, const Args g) {
@@ -296,7 +294,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) unsigned long long full_bar[NSTAGE], empty_bar[NSTAGE], acc_full[2], acc_empty[2];
     // tile queue: the leader's producer draws tile numbers from the global counter and publishes each
-    // one in both CTAs; a slot is recycled once all ten consumers of the pair have read it
+    // one in both CTAs; a slot is recycled once all consumers of the pair have read it
     __shared__ __align__(8) unsigned long long tq_full[TQ], tq_empty[TQ];
     __shared__ int tile_ring[TQ];
     __shared__ unsigned tmem_base_slot;
@@ -319,8 +317,8 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < NSTAGE; s++) { mbar_init(smem_u32(&full_bar[s]), 1); mbar_init(smem_u32(&empty_bar[s]), 1); }
-        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 8); }
-        for (int q = 0; q < TQ; q++) { mbar_init(smem_u32(&tq_full[q]), 1); mbar_init(smem_u32(&tq_empty[q]), 10); }
+        for (int a = 0; a < 2; a++) { mbar_init(smem_u32(&acc_full[a]), 1); mbar_init(smem_u32(&acc_empty[a]), 2 * EPI_WARPS); }
+        for (int q = 0; q < TQ; q++) { mbar_init(smem_u32(&tq_full[q]), 1); mbar_init(smem_u32(&tq_empty[q]), 2 + 2 * EPI_WARPS); }
         failed = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -453,14 +451,18 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
             if (!ok) failed = 1;
         }
     } else {
-        // ── epilogue: warps 2..5, tensor-memory lane quadrant = warp % 4 ──
-        const int quad = warp & 3;
+        // ── epilogue: warps 2..9, tensor-memory lane quadrant = warp % 4, column half = (warp - 2) / 4 ──
+        const int quad = warp & 3, col_half = (warp - 2) >> 2;
         unsigned acc = 0, acc_phase = 0;
         bool ok = true;
         unsigned qs = 0, qphase = 0;
         __half* const d_raw = (__half*)g.d_raw; (void)d_raw;
 #if CFG_EPI
         __half* const d_out = (__half*)g.d_out;
+        // the fused consumer's operands, loaded one 32-column chunk ahead of the arithmetic that needs
+        // them: [group of 8 columns][operand][pair]
+        constexpr int EPI_NR = EPI_NRAW > 0 ? EPI_NRAW : 1;
+        __half2 raw_next[4][EPI_NR][4];
 #endif
         while (ok) {
             if (!mbar_wait_cluster(smem_u32(&tq_full[qs]), qphase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 18; failed = 1; } break; }
@@ -483,13 +485,39 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
 #endif
             const bool row_ok = row < g.M;
             const bool vec_ok = (g.ldd % 8 == 0); (void)vec_ok;
+            const int c_begin = col_half * (width / 64), c_end = c_begin + width / 64;      // this warp's 32-column chunks
+            // After the narrowing, groups of four lanes exchange their rows' 8-column pieces, so that lane 4g+i
+            // holds piece i (8 columns from ucol) of the rows urow0 .. urow0+3: a store or load instruction then
+            // touches 8 rows x 64 contiguous bytes instead of 32 rows x 16.
+            const int urow0 = m0 + quad * 32 + (lane & ~3), ucol = 8 * (lane & 3);
+            (void)urow0; (void)ucol;
+#if CFG_EPI
+            // the first chunk's operands are asked for before the accumulator is even complete
+#pragma unroll
+            for (int q = 0; q < 4; q++)
+                if (urow0 + q < g.M && n0 + c_begin * 32 + ucol < g.N) epi8_load_(urow0 + q, n0 + c_begin * 32 + ucol, g.ep, raw_next[q]);
+#endif
             for (int ch = 0; ch < chunks; ch++) {
             if (!mbar_wait(smem_u32(&acc_full[acc]), acc_phase, &failed)) { ok = false; if (lane == 0) { *(volatile int*)g.status = 14; failed = 1; } break; }
             asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
 #pragma unroll 1
-            for (int c = 0; c < width / 32; c++) {
+            for (int c = c_begin; c < c_end; c++) {
                 unsigned v[32];
                 tmem_ld32(tmem_base + ((unsigned)(quad * 32) << 16) + acc * BNT + c * 32, v);
+#if CFG_EPI
+                __half2 raw[4][EPI_NR][4];
+#pragma unroll
+                for (int q = 0; q < 4; q++)
+#pragma unroll
+                    for (int k = 0; k < EPI_NR; k++)
+#pragma unroll
+                        for (int u = 0; u < 4; u++) raw[q][k][u] = raw_next[q][k][u];
+                if (c + 1 < c_end) {
+#pragma unroll
+                    for (int q = 0; q < 4; q++)
+                        if (urow0 + q < g.M && n0 + (c + 1) * 32 + ucol < g.N) epi8_load_(urow0 + q, n0 + (c + 1) * 32 + ucol, g.ep, raw_next[q]);
+                }
+#endif
                 asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                 const int col = n0 + c * 32;
                 if (col >= g.N) continue;                  // warp-uniform
@@ -516,39 +544,56 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
 #pragma unroll
                 for (int j = 0; j < 16; j++) h[j] = __floats2half2_rn(__uint_as_float(v[2 * j]), __uint_as_float(v[2 * j + 1]));
                 if (vec_ok) {
-#if CFG_EPI
-                    __half2 o[16];
-#endif
+                    // 4 x 4 transpose of 16-byte pieces inside each group of four lanes: two exchange rounds
+                    const bool b0 = (lane & 1) != 0, b1 = (lane & 2) != 0;
+                    const uint4* const Q = reinterpret_cast<const uint4*>(h);
+                    uint4 A[2][2], T[4];
+#pragma unroll
+                    for (int k = 0; k < 2; k++) {
+                        const uint4 got = shfl_xor_u4(sel_u4(b0, Q[2 * k], Q[2 * k + 1]), 1), keep = sel_u4(b0, Q[2 * k + 1], Q[2 * k]);
+                        A[k][0] = sel_u4(b0, got, keep);          // piece 2k + (lane & 1) of the even lane's row
+                        A[k][1] = sel_u4(b0, keep, got);          // ... of the odd lane's row
+                    }
+#pragma unroll
+                    for (int j = 0; j < 2; j++) {
+                        const uint4 got = shfl_xor_u4(sel_u4(b1, A[0][j], A[1][j]), 2), keep = sel_u4(b1, A[1][j], A[0][j]);
+                        T[j] = sel_u4(b1, got, keep);             // rows urow0 + 0, 1
+                        T[2 + j] = sel_u4(b1, keep, got);         // rows urow0 + 2, 3
+                    }
+                    const int ucolc = col + ucol;
+                    float x[8];
+#pragma unroll
+                    for (int j = 0; j < 8; j++) x[j] = 0.0f;
 #pragma unroll
                     for (int q = 0; q < 4; q++) {
-                        const bool on = row_ok && col + q * 8 < g.N;     // N is a multiple of 8 here: a group of 8 is all in or all out
-                        if (on && d_raw) store16(d_raw + row_off + col + q * 8, *reinterpret_cast<const uint4*>(&h[q * 4]));
+                        const bool on = urow0 + q < g.M && ucolc < g.N;      // N is a multiple of 8 here: a piece is all in or all out
+                        const size_t off = (size_t)(urow0 + q) * g.ldd + ucolc;
+                        if (on && d_raw) store16(d_raw + off, T[q]);
 #if CFG_EPI
+                        uint4 O = make_uint4(0u, 0u, 0u, 0u);
                         if (on) {
-                            epi8_(row, col + q * 8, &h[q * 4], &o[q * 4], g.ep);
-                            store16(d_out + row_off + col + q * 8, *reinterpret_cast<const uint4*>(&o[q * 4]));
-                        } else {
-                            o[q * 4] = o[q * 4 + 1] = o[q * 4 + 2] = o[q * 4 + 3] = __float2half2_rn(0.0f);
+                            epi8_(urow0 + q, ucolc, reinterpret_cast<const __half2*>(&T[q]), reinterpret_cast<__half2*>(&O), g.ep, raw[q]);
+                            store16(d_out + off, O);
                         }
 #else
-                        if (!on) h[q * 4] = h[q * 4 + 1] = h[q * 4 + 2] = h[q * 4 + 3] = __float2half2_rn(0.0f);
+                        const uint4 O = on ? T[q] : make_uint4(0u, 0u, 0u, 0u);
 #endif
+                        const __half2* const oh = reinterpret_cast<const __half2*>(&O);
+#pragma unroll
+                        for (int j = 0; j < 4; j++) { const float2 f = __half22float2(oh[j]); x[2 * j] += f.x; x[2 * j + 1] += f.y; }
                     }
                     if (g.colsum && m0 + quad * 32 < g.M) {      // warp-uniform: groups of 32 rows that start inside the matrix
-                        // partial column sums over this warp's 32 rows of what was stored (rows and columns
-                        // outside the matrix contribute zero); lane j ends up with column col + j
-                        float x[32];
+                        // partial column sums over this warp's 32 rows of what was stored (rows and columns outside
+                        // the matrix contribute zero): the four rows of a lane first, then across the eight groups
 #pragma unroll
-                        for (int j = 0; j < 16; j++) {
-#if CFG_EPI
-                            const float2 f = __half22float2(o[j]);
-#else
-                            const float2 f = __half22float2(h[j]);
-#endif
-                            x[2 * j] = f.x; x[2 * j + 1] = f.y;
+                        for (int off = 4; off <= 16; off <<= 1)
+#pragma unroll
+                            for (int j = 0; j < 8; j++) x[j] += __shfl_xor_sync(0xffffffffu, x[j], off);
+                        if (lane < 4 && ucolc < g.N) {
+                            float* const cs = g.colsum + (size_t)((m0 + quad * 32) >> 5) * g.N + ucolc;
+#pragma unroll
+                            for (int j = 0; j < 8; j++) cs[j] = x[j];
                         }
-                        warp_column_sums(x, lane);
-                        if (col + lane < g.N) g.colsum[(size_t)((m0 + quad * 32) >> 5) * g.N + col + lane] = x[0];
                     }
                 } else if (row_ok) {
                     // row stride not a multiple of 16 bytes (no fused consumer on this route): scalar stores
