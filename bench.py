@@ -32,7 +32,7 @@ CFG = dict(batch=8192, width=4096, classes=1000, depth=4)
 
 #: DRAM bytes (read + write) of one launch of the dominant kernel from a separate ncu capture; a
 #: constant of that capture, not a measurement of this run
-PAIR_GEMM_TRAFFIC = {"bytes": 351.7e6, "of": "one 4096x4096x8192 weight-gradient launch under ncu, 160 MB algorithmic (operands 128 MB, output 32 MB)"}
+PAIR_GEMM_TRAFFIC = {"bytes": 376.5e6, "of": "one 4096x4096x8192 weight-gradient launch under ncu (346.3 MB read + 30.2 MB written), 160 MB algorithmic (operands 128 MB, output 32 MB); a forward launch with its fused bias + GELU: 148.3 + 106.5 MB against 96 MB operands + 128 MB of outputs"}
 ROW_CHAIN_TRAFFIC = {"bytes": 775.7e6, "of": "one row_chain launch over 8192x8192 under ncu, 805.3 MB algorithmic"}
 
 
