@@ -115,8 +115,8 @@ int anl_get_stats(anl_device* dev, anl_stats* out);
 #define ANL_OPEN_NO_ROW_CHAIN 8u    /* launch every item on its own instead of fusing per-row kernel chains */
 #define ANL_OPEN_BEAM 4u           /* apply / search autotuned transforms (the reference's ANNEAL_BEAM=1) */
 #define ANL_OPEN_NO_EPILOGUE_FUSION 32u /* launch a contraction, its elementwise consumer and a bias gradient separately */
-#define ANL_OPEN_NO_TF32X3 64u          /* keep large f32 contractions on the FP32 pipes (fused multiply-add in ascending k) instead of
-                                         the tensor cores' 3 x TF32 form */
+#define ANL_OPEN_NO_TF32X3 64u          /* keep f32 contractions of more than 32 rows off the tensor cores' 3 x TF32 form: fused
+                                         multiply-add in ascending k on the FP32 pipes instead */
 #define ANL_OPEN_TAIL_SPLIT 16u    /* split the last all-reduced contraction into two row windows even on one rank
                                       (done by itself when ranks > 1; the flag exists to test the path on one GPU) */
 
