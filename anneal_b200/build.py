@@ -40,8 +40,11 @@ def build(force: bool = False, verbose: bool = False) -> str:
     for src in SOURCES:
         obj = os.path.join(LIBDIR, src.rsplit(".", 1)[0] + ".o")
         path = os.path.join(CSRC, src)
-        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(
-                os.path.getmtime(os.path.join(CSRC, f)) for f in os.listdir(CSRC) if f.endswith((".hpp", ".h", ".cuh")) or f == src):
+        # every object depends on its source, on every header beside it and on the public header (struct
+        # layouts such as anl_stats are part of anl_device, which all of them see)
+        deps = [os.path.join(CSRC, f) for f in os.listdir(CSRC) if f.endswith((".hpp", ".h", ".cuh")) or f == src]
+        deps.append(os.path.join(HERE, "..", "include", "anneal_cuda.h"))
+        if force or not os.path.exists(obj) or os.path.getmtime(obj) < max(os.path.getmtime(d) for d in deps):
             cmd = [NVCC, *FLAGS, "-c", path, "-o", obj]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")

@@ -694,6 +694,21 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
         }
         return ANL_OK;
     };
+    // A small kernel whose output nothing later in the schedule reads (the scalar loss, a bias gradient)
+    // need not hold up the contractions behind it: inside a captured graph it goes to the side stream,
+    // behind what has been queued so far, and joins at the end like the updates.  Only where that is
+    // plainly safe: scratch stays with the graph (keep_scratch), and no later kernel writes memory this
+    // one reads or writes (slots share allocations, so memory is compared, not buffer ids).
+    auto side_ok = [&](size_t i, const std::vector<void*>& ptrs) -> bool {
+        if (!keep_scratch || dev->profiling || !dev->comm_stream || (dev->flags & ANL_OPEN_BEAM)) return false;
+        for (size_t r = i + 1; r < items.size(); r++) {
+            for (size_t b = 1; b < items[r].bufs.size(); b++)
+                if (items[r].bufs[b].id == items[i].bufs[0].id || t.bufs[items[r].bufs[b].id].ptr == ptrs[0]) return false;
+            void* w = t.bufs[items[r].bufs[0].id].ptr;
+            for (void* q : ptrs) if (q == w) return false;
+        }
+        return true;
+    };
     for (size_t i = 0; i < items.size(); i++) {
         const Item& it = items[i];
         if (chains_on && !absorbed.count(i)) {
@@ -733,7 +748,9 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             auto ab = absorbed.find(i);
             if (ab != absorbed.end()) {
                 // a bias gradient whose partial column sums an earlier contraction's epilogue produced
-                if (int rc = launch_colsum_finish(dev, (const float*)ab->second.partials, ab->second.parts, ab->second.cols, ptrs[0], stream)) return rc;
+                cudaStream_t on = stream;
+                if (side_ok(i, ptrs)) { comm_fork(dev, stream); on = dev->comm_stream; dev->stats.side_launches++; }
+                if (int rc = launch_colsum_finish(dev, (const float*)ab->second.partials, ab->second.parts, ab->second.cols, ptrs[0], on)) return rc;
                 if (keep_scratch) t.owned.push_back(ab->second.partials); else dev->release(ab->second.partials);
                 dev->stats.colsums_fused++;
                 if (ra != t.after.end() && ra->second.allreduce)
@@ -825,7 +842,9 @@ int run_items(anl_device* dev, const std::vector<Item>& items, const Bindings& b
             allow_shard = true;
             continue;
         }
-        if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), stream, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
+        cudaStream_t on = stream;
+        if (!gemm_taken(*plan, item_sym(it, binds)) && side_ok(i, ptrs)) { comm_fork(dev, stream); on = dev->comm_stream; dev->stats.side_launches++; }
+        if (int rc = launch_plan(dev, *plan, it, ptrs.data(), item_sym(it, binds), on, keep_scratch ? &t.owned : nullptr)) { dev->err = "kernel " + std::to_string(i) + ": " + dev->err; return rc; }
         // side stream: [all-reduce this gradient] behind the producing kernel ...
         if (ra != t.after.end() && ra->second.allreduce)
             if (int rc = reduce_part(ra->second, 0, ra->second.resident->elems)) return rc;

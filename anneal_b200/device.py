@@ -47,7 +47,7 @@ class _Bench(C.Structure):
 class _Stats(C.Structure):
     _fields_ = [(n, C.c_uint64) for n in ("kernels_launched", "gemm_launched", "nvrtc_compiles", "nvrtc_cache_hits",
                                           "lower_cache_hits", "h2d_bytes", "d2h_bytes", "graph_replays",
-                                          "graph_captures", "device_allocs", "epilogues_fused", "colsums_fused")]
+                                          "graph_captures", "device_allocs", "epilogues_fused", "colsums_fused", "side_launches")]
 
 
 class _Prof(C.Structure):

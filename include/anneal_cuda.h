@@ -101,6 +101,7 @@ typedef struct {
     uint64_t h2d_bytes, d2h_bytes, graph_replays, graph_captures, device_allocs;
     uint64_t epilogues_fused;   /* elementwise kernels run inside the epilogue of the contraction before them */
     uint64_t colsums_fused;     /* row-sum kernels finished from partial sums a contraction's epilogue left */
+    uint64_t side_launches;     /* small kernels with no later reader that a captured graph runs beside the main stream */
 } anl_stats;
 
 /* ── lifecycle: webgpu.Open / Device.Close / AdapterName / HasShaderF16 (backend/webgpu/open.go:89-175) ── */

@@ -119,3 +119,31 @@ def test_device_stats_hook_reports_what_a_realize_launched(cuda):
     assert st["gemm_launched"] == 8 and st["epilogues_fused"] == 5 and st["colsums_fused"] == 2
     assert st["kernels_launched"] > st["gemm_launched"] and st["h2d_bytes"] > 0 and st["d2h_bytes"] > 0
     assert np.isfinite(g.loss.data).all()
+
+
+def test_captured_step_runs_leaf_kernels_beside_the_contractions():
+    """Inside a captured graph the scalar loss and the bias-gradient finishes — small kernels whose
+    output no later kernel reads — go to the side stream; launched one by one they stay in order on
+    the main stream. Both give the same losses and parameters, bit for bit, step by step."""
+    from anneal_b200.train import ResidentTrainer
+    res = []
+    for use_graph in (True, False):
+        dev = Device(0)
+        try:
+            R.reset()
+            m = W.WideMLP(batch=512, width=512, classes=136, depth=3)
+            x, y = m.make_inputs()
+            tr = ResidentTrainer(dev, m, 0.05, use_graph=use_graph, resident_inputs=True)
+            tr.load_batch(x, y)
+            losses = []
+            for _ in range(5):
+                tr.step()
+                losses.append(tr.loss())
+            res.append((losses, tr.parameters(), dev.stats()["side_launches"]))
+        finally:
+            dev.close()
+    (lg, pg, ng), (le, pe, ne) = res
+    assert ng >= 3 and ne == 0, (ng, ne)
+    assert lg == le
+    for a, b in zip(pg, pe):
+        assert np.array_equal(a, b)
