@@ -22,7 +22,8 @@
 // kernels.  The two-CTA kernel that the large contractions run on is gemm_pair_kernel.cuh: it is
 // compiled at run time, once per configuration (operand major-ness, tile width, ring depth, raster,
 // fused elementwise consumer), so that the consumer's generated code can sit in its epilogue and the
-// tunables are compile-time constants a search can vary.
+// tunables are compile-time constants a search can vary.  The same text serves f32 contractions in
+// 3 x TF32 form; its host side (operand split pre-pass, K slices, their sum) is further down.
 #include <cuda_fp16.h>
 
 #include <cstdlib>

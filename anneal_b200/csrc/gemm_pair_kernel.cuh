@@ -58,7 +58,7 @@
 //   __device__ void epi8_(int row, int col, const __half2* acc, __half2* out, const void* const* ep, const __half2 (*raw)[4])
 // the second of which maps 8 consecutive narrowed values acc[0..3] at (row, col..col+7) to the 8 outputs
 // from the operand values the first one loaded (the kernel calls it a chunk of 32 columns ahead: the
-// loads' latency would otherwise be paid once per chunk by each of only four epilogue warps).
+// loads' latency would otherwise be paid once per chunk by each of a handful of epilogue warps).
 #pragma once
 
 // Arguments of the f16 form.  The layout is kept at 120 bytes on purpose: with 24 more bytes of
