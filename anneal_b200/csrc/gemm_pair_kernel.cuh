@@ -29,7 +29,8 @@
 //
 // f32 operands (CFG_TF32 = 1) take the same kernel in "3 x TF32" form: each operand arrives as two
 // k-contiguous f32 arrays, hi = the value rounded to TF32's 11 significant bits and lo = value - hi (exact), and
-// the tile is accumulated from three passes over K — lo·hi, hi·lo, hi·hi, smallest first — with
+// every k-block is loaded once as four parts (A_hi, A_lo, B_hi, B_lo: 64 KB a stage, three stages) and
+// accumulated as three products — lo·hi, hi·lo, hi·hi — with
 // tcgen05.mma.kind::tf32, whose products of 11-bit factors are exact in the f32 accumulator.  What is
 // dropped is lo·lo (2^-22 of the product) and the bits of lo beyond TF32's reach (2^-22 of the
 // operand); the sum carries f32 accumulation like the reference's loop, in another order.  The
@@ -118,11 +119,12 @@ constexpr int BM = 128, BK = 128 / ESZ;
 constexpr int MNBOX = 64;                   // f16 elements of m (or n) in one row of an MN-major box
 constexpr int KSTEP_BYTES_MN = 16 * 128;    // one MMA's k-rows in an MN-major tile
 static_assert(!(CFG_TF32 && (CFG_A_MN || CFG_B_MN)), "the f32 form takes k-contiguous operands only: the host's split pre-pass rewrites the others");
-constexpr int PASSES = CFG_TF32 ? 3 : 1;
 constexpr int BNT = CFG_BNT, NSTAGE = CFG_STAGES;
 constexpr int A_TILE_BYTES = BM * BK * ESZ;
 constexpr int BHALF_BYTES = (BNT / 2) * BK * ESZ;
-constexpr int STAGE_B = A_TILE_BYTES + BHALF_BYTES;
+// a stage holds this CTA's A rows and its half of B; in the f32 form both as hi and lo parts, so that one
+// set of loads serves the three passes (A_hi, A_lo, B_hi, B_lo: 64 KB)
+constexpr int STAGE_B = (CFG_TF32 ? 2 : 1) * (A_TILE_BYTES + BHALF_BYTES);
 constexpr int TQ = 4;
 constexpr int EPI_WARPS = 8;         // two per 32-lane quadrant of tensor memory, each taking half of the tile's columns
 constexpr unsigned WAIT_LIMIT = 1u << 20;
@@ -370,21 +372,29 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                 const TensorMap* const mb = narrow ? &map_b_half : &map_b;
                 for (int ch = 0; ch < chunks && ok; ch++) {
                     const int kb0 = kb_first + ch * chunk_kb, nkb = (nkb_all - ch * chunk_kb) < chunk_kb ? (nkb_all - ch * chunk_kb) : chunk_kb;
-                    for (int it = 0; it < PASSES * nkb && ok; it++) {
-                        const int pass = it / nkb, kb = kb0 + it - pass * nkb;
-                        // 3 x TF32: pass 0 = A_lo · B_hi, pass 1 = A_hi · B_lo, pass 2 = A_hi · B_hi
-                        const TensorMap* const ma = (CFG_TF32 && pass == 0) ? &map_a_lo : &map_a;
-                        const TensorMap* const mbp = (CFG_TF32 && pass == 1) ? &map_b_lo : mb;
+                    for (int it = 0; it < nkb && ok; it++) {
+                        const int kb = kb0 + it;
                         if (!mbar_wait(smem_u32(&empty_bar[stage]), phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 11; break; }
                         const unsigned own_fb = smem_u32(&full_bar[stage]);
                         const unsigned fb = map_to_cta(own_fb, 0);
+                        const int k0 = kb * BK;
+#if CFG_TF32
+                        // hi and lo parts of both operands: A_hi, A_lo, B_hi, B_lo
+                        const unsigned sa = smem_base + stage * STAGE_B, sb = sa + 2 * A_TILE_BYTES;
+                        if (rank == 0) mbar_expect_tx(own_fb, 2 * STAGE_B);
+                        tma_load_2d_pair(sa, &map_a, k0, m0, fb);
+                        tma_load_2d_pair(sa + A_TILE_BYTES, &map_a_lo, k0, m0, fb);
+                        tma_load_2d_pair(sb, &map_b, k0, n0, fb);
+                        tma_load_2d_pair(sb + BHALF_BYTES, &map_b_lo, k0, n0, fb);
+                        (void)stage_bytes; (void)mb;
+#else
                         const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
                         if (rank == 0) mbar_expect_tx(own_fb, 2 * stage_bytes);
-                        const int k0 = kb * BK;
-                        if (CFG_A_MN) { for (int j = 0; j < BM / MNBOX; j++) tma_load_2d_pair(sa + j * (BK * 128), ma, m0 + MNBOX * j, k0, fb); }
-                        else tma_load_2d_pair(sa, ma, k0, m0, fb);
-                        if (CFG_B_MN) { for (int j = 0; j < (width / 2) / MNBOX; j++) tma_load_2d_pair(sb + j * (BK * 128), mbp, n0 + MNBOX * j, k0, fb); }
-                        else tma_load_2d_pair(sb, mbp, k0, n0, fb);
+                        if (CFG_A_MN) { for (int j = 0; j < BM / MNBOX; j++) tma_load_2d_pair(sa + j * (BK * 128), &map_a, m0 + MNBOX * j, k0, fb); }
+                        else tma_load_2d_pair(sa, &map_a, k0, m0, fb);
+                        if (CFG_B_MN) { for (int j = 0; j < (width / 2) / MNBOX; j++) tma_load_2d_pair(sb + j * (BK * 128), mb, n0 + MNBOX * j, k0, fb); }
+                        else tma_load_2d_pair(sb, mb, k0, n0, fb);
+#endif
                         if (++stage == NSTAGE) { stage = 0; phase ^= 1; }
                     }
                 }
@@ -422,13 +432,24 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                     if (!mbar_wait(smem_u32(&acc_empty[acc]), acc_phase ^ 1, &failed)) { ok = false; *(volatile int*)g.status = 12; break; }
                     asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
                     const unsigned tmem_d = tmem_base + acc * BNT;
-                    for (int kb = 0; kb < PASSES * nkb; kb++) {
+                    for (int kb = 0; kb < nkb; kb++) {
                         if (!mbar_wait(smem_u32(&full_bar[stage]), phase, &failed)) { ok = false; *(volatile int*)g.status = 13; break; }
                         asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory");
+#if CFG_TF32
+                        // 3 x TF32 on one set of loads: A_lo · B_hi, A_hi · B_lo, A_hi · B_hi (k-contiguous operands)
+                        const unsigned sa = smem_base + stage * STAGE_B, sb = sa + 2 * A_TILE_BYTES;
+#pragma unroll
+                        for (int pass = 0; pass < 3; pass++) {
+                            const unsigned pa = pass == 0 ? sa + A_TILE_BYTES : sa, pb = pass == 1 ? sb + BHALF_BYTES : sb;
+#pragma unroll
+                            for (int k = 0; k < 4; k++)
+                                umma_f16_pair(tmem_d, make_desc(pa + k * 32, 16, 1024), make_desc(pb + k * 32, 16, 1024), idesc, (kb | pass | k) != 0);
+                        }
+#else
                         const unsigned sa = smem_base + stage * STAGE_B, sb = sa + A_TILE_BYTES;
 #pragma unroll
                         for (int k = 0; k < 4; k++) {
-                            // One MMA covers 32 bytes of k (16 f16 or 8 tf32 elements): four per k-block.
+                            // One MMA covers 32 bytes of k (16 f16 elements): four per k-block.
                             // K-major: 32 bytes inside the 128-byte row, 8-row groups 1 KiB apart.
                             // MN-major: the MMA's k-rows are whole 128-byte rows (KSTEP_BYTES_MN of them per
                             // step), m/n groups of one swizzle row's width one box (BK*128 B) apart.
@@ -436,6 +457,7 @@ gemm_f16_tcgen05_pair(const __grid_constant__ TensorMap map_a, const __grid_cons
                             const unsigned long long bd = CFG_B_MN ? make_desc(sb + k * KSTEP_BYTES_MN, BK * 128, 1024) : make_desc(sb + k * 32, 16, 1024);
                             umma_f16_pair(tmem_d, ad, bd, idesc, (kb | k) != 0);
                         }
+#endif
                         const unsigned eb = smem_u32(&empty_bar[stage]);
                         umma_commit_pair(map_to_cta(eb, 0));       // frees the stage here ...
                         umma_commit_pair(map_to_cta(eb, 1));       // ... and in the partner CTA
