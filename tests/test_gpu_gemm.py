@@ -110,7 +110,7 @@ def test_gemm_f32_symbolic_batch(cuda, oracle, b, gemms):
 
 
 # ── large f32 contractions: the tensor-core kernel in 3 x TF32 form ──────────────────────────────
-@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (2100, 1000, 1031), (515, 1000, 20001)])
+@pytest.mark.parametrize("M,N,K", [(2048, 1024, 1024), (2100, 1000, 1031), (515, 1000, 20001), (64, 2048, 1024), (100, 1000, 700)])
 @pytest.mark.parametrize("layout", ["KK", "KM", "MM", "MK"])
 def test_gemm_f32_on_tensor_cores(cuda, M, N, K, layout):
     """Against float64 on a sample of rows: the split into TF32 halves plus chunked f32 accumulation
