@@ -120,11 +120,15 @@ class ClockSampler(threading.Thread):
                 "reasons": sorted(self.reasons), "samples": len(self.sm), "source": self.source}
 
 
+NUMA_NOTE = None      # why the binding below did or did not happen; carried in the e2e record
+
+
 def bind_to_gpu_numa_node(index: int):
     """Restrict this process to the CPUs NVML lists as local to GPU `index`, before any pinned memory is
     allocated, so that the staged batches sit on the GPU's own NUMA node (with one process per GPU all
     ranks otherwise tend to allocate on one socket and share its memory controllers and PCIe root).
-    Changes only this process's scheduling mask; returns the CPU list or None."""
+    Changes only this process's scheduling mask; returns the CPU list or None (NUMA_NOTE says why)."""
+    global NUMA_NOTE
     try:
         import pynvml as nv
         nv.nvmlInit()
@@ -132,19 +136,27 @@ def bind_to_gpu_numa_node(index: int):
         if vis:
             ids = [v.strip() for v in vis.split(",") if v.strip()]
             if index < len(ids) and ids[index].isdigit():
-                index = int(ids[index])
-        h = nv.nvmlDeviceGetHandleByIndex(index)
+                h = nv.nvmlDeviceGetHandleByIndex(int(ids[index]))
+            elif index < len(ids):
+                h = nv.nvmlDeviceGetHandleByUUID(ids[index].encode() if isinstance(ids[index], str) else ids[index])
+            else:
+                h = nv.nvmlDeviceGetHandleByIndex(index)
+        else:
+            h = nv.nvmlDeviceGetHandleByIndex(index)
         words = (os.cpu_count() + 63) // 64
         mask = nv.nvmlDeviceGetCpuAffinity(h, words)
-        cpus = [w * 64 + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1]
+        local = [w * 64 + b for w, m in enumerate(mask) for b in range(64) if (m >> b) & 1]
         allowed = os.sched_getaffinity(0)
-        cpus = [c for c in cpus if c in allowed]
+        cpus = [c for c in local if c in allowed]
         nv.nvmlShutdown()
         if cpus and len(cpus) < len(allowed):
             os.sched_setaffinity(0, cpus)
+            NUMA_NOTE = f"bound to {len(cpus)} of the {len(allowed)} CPUs this process may use ({len(local)} are local to the GPU)"
             return cpus
-    except Exception:
-        pass
+        NUMA_NOTE = (f"not bound: {len(local)} CPUs are local to the GPU, this process may use {len(allowed)}, "
+                     f"{len(cpus)} of them local" + (" (already all local)" if cpus and len(cpus) == len(allowed) else ""))
+    except Exception as e:
+        NUMA_NOTE = f"not bound: {type(e).__name__}: {e}"
     return None
 
 
@@ -361,7 +373,7 @@ def run_ours(args):
     e2e = {"value": CFG["batch"] * world * args.steps / (ms2 / 1e3), "unit": UNIT,
            "h2d_bytes_per_step": int((x.size + y.size) * np.dtype(hdt).itemsize), "host_batch_dtype": np.dtype(hdt).name, "d2h_bytes_per_step": 4, "ms_per_step": ms2 / args.steps,
            "how": "batch i+1 copied from pinned host memory on a copy stream while step i runs; every step's loss is copied to the host behind the step and read there while the next step runs",
-           "host_cpus_bound": len(numa_cpus) if numa_cpus else None,
+           "host_cpus_bound": len(numa_cpus) if numa_cpus else None, "host_cpus_note": NUMA_NOTE,
            "loss": e2e_loss}
 
     # the same step looped for seconds: what the clocks settle at under the power limit, and the
