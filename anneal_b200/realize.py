@@ -79,7 +79,7 @@ def build_schedule(tensors: Sequence[Tensor]):
 #: kernels and bias gradients that ran inside a contraction's epilogue, graph replays, compiles, bytes
 #: moved each way.  Same threading rule as the schedule hook.
 DEVICE_STATS_HOOK = None
-_DEVICE_COUNTERS = ("kernels_launched", "gemm_launched", "epilogues_fused", "colsums_fused", "graph_replays", "graph_captures",
+_DEVICE_COUNTERS = ("kernels_launched", "gemm_launched", "epilogues_fused", "colsums_fused", "side_launches", "graph_replays", "graph_captures",
                     "nvrtc_compiles", "h2d_bytes", "d2h_bytes")
 
 
