@@ -238,6 +238,8 @@ def test_contraction_kernel_sources_compile_with_and_without_a_fused_consumer(li
             continue
         fused += 1
         assert "void epi8_(" in f["source"] and "#define CFG_EPI 1" in f["source"]
+        # the consumer's operand loads live in a function of their own, so that the kernel can issue them ahead
+        assert "void epi8_load_(" in f["source"] and re.search(r"#define EPI_NRAW [12]\b", f["source"])
         device.compile_check(f["source"])
     assert plain == 7 and fused == 5, (plain, fused)
     assert layouts == {"gemm tcgen05 A:K B:K", "gemm tcgen05 A:K B:MN", "gemm tcgen05 A:MN B:MN"}
