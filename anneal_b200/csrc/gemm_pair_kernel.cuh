@@ -123,7 +123,7 @@ constexpr int BNT = CFG_BNT, NSTAGE = CFG_STAGES;
 constexpr int A_TILE_BYTES = BM * BK * ESZ;
 constexpr int BHALF_BYTES = (BNT / 2) * BK * ESZ;
 // a stage holds this CTA's A rows and its half of B; in the f32 form both as hi and lo parts, so that one
-// set of loads serves the three passes (A_hi, A_lo, B_hi, B_lo: 64 KB)
+// set of loads serves the three products (A_hi, A_lo, B_hi, B_lo: 64 KB)
 constexpr int STAGE_B = (CFG_TF32 ? 2 : 1) * (A_TILE_BYTES + BHALF_BYTES);
 constexpr int TQ = 4;
 constexpr int EPI_WARPS = 8;         // two per 32-lane quadrant of tensor memory, each taking half of the tile's columns
